@@ -1,0 +1,93 @@
+// Shared helpers for every kernel file: element types, error reporting, small device utilities.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <cstring>
+
+namespace ms {
+
+// Last error message of this thread; every shared library exports it under its own name
+// (MS_DEFINE_LAST_ERROR) so Python can turn a non-zero return code into an exception.
+inline char* error_buffer() {
+  static thread_local char buf[1024];
+  return buf;
+}
+
+inline int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+
+#define MS_CHECK_ARG(cond, ...)                         \
+  do {                                                  \
+    if (!(cond)) return ::ms::fail(__VA_ARGS__);        \
+  } while (0)
+
+#define MS_CHECK_CUDA(expr)                                                                  \
+  do {                                                                                       \
+    cudaError_t err__ = (expr);                                                              \
+    if (err__ != cudaSuccess)                                                                \
+      return ::ms::fail("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, \
+                        __LINE__);                                                           \
+  } while (0)
+
+#define MS_CHECK_LAUNCH() MS_CHECK_CUDA(cudaGetLastError())
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a whole block in a fixed order (lane tree, then warps in index order), so the
+// result depends only on the values and the block size.
+template <int MAX_WARPS = 32>
+__device__ __forceinline__ float block_sum(float v, float* scratch /* MAX_WARPS floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarps; ++w) total += scratch[w];
+  return total;
+}
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace ms
+
+#include <cstdarg>
+inline int ms::fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(ms::error_buffer(), 1024, fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+// dtype codes shared with Python
+enum MsDtype : int { MS_F32 = 0, MS_BF16 = 1 };
+
+#define MS_EXPORT extern "C" __attribute__((visibility("default")))
+#define MS_DEFINE_LAST_ERROR(name) \
+  MS_EXPORT const char* name() { return ::ms::error_buffer(); }

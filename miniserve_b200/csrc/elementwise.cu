@@ -1,0 +1,165 @@
+// Embedding gather, RMSNorm (with the residual add and an optional row gather fused in),
+// and SiLU-and-multiply. One templated kernel each for float32 and bfloat16 activations;
+// the residual stream is float32 in both modes and every statistic is computed in float32.
+//
+// Formulas follow miniserve/model/qwen3.py:78-82 (RMSNorm: x * rsqrt(mean(x^2) + eps), then
+// times the weight), :211 (embedding), :128-131 (SiLU(gate) * up) and the fused operator list
+// of miniserve/model/fused.py:160-211 (residual add + norm in one pass).
+#include "common.cuh"
+
+namespace ms {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_gather_kernel(float* __restrict__ residual, const T* __restrict__ table,
+                                    const int* __restrict__ ids, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; stay in bounds anyway
+  const T* src = table + (size_t)id * hidden;
+  float* dst = residual + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Elem<T>::load(src + i);
+}
+
+// ---------------------------------------------------------------- (add +) RMSNorm (+ gather)
+// For output row i: r = rows ? rows[i] : i.
+//   h = residual[r] (+ delta[r] if delta)            float32
+//   if (write_residual) residual[r] = h              (only without a gather)
+//   out[i] = h / sqrt(mean(h^2) + eps) * w           rounded once to T
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta,
+                   const T* __restrict__ w, const int* __restrict__ rows, float eps, int hidden,
+                   int write_residual) {
+  extern __shared__ float row_buf[];  // hidden floats
+  __shared__ float red[32];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const T* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    float h = res[c];
+    if (dl) h += Elem<T>::load(dl + c);
+    row_buf[c] = h;
+    ss += h * h;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    const float h = row_buf[c];
+    if (write_residual && dl) res[c] = h;
+    Elem<T>::store(o + c, (h * inv) * Elem<T>::load(w + c));
+  }
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int c = (int)(idx - t * inter);
+  const float g = Elem<T>::load(gate_up + t * 2 * inter + c);
+  const float u = Elem<T>::load(gate_up + t * 2 * inter + inter + c);
+  const float s = g / (1.0f + expf(-g));
+  Elem<T>::store(out + idx, s * u);
+}
+
+// bfloat16, 8 elements per thread (inter % 8 == 0)
+__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                       int inter8, size_t total8) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const size_t t = idx / inter8;
+  const int c = (int)(idx - t * inter8);
+  const uint4 gv = reinterpret_cast<const uint4*>(gate_up)[t * 2 * inter8 + c];
+  const uint4 uv = reinterpret_cast<const uint4*>(gate_up)[t * 2 * inter8 + inter8 + c];
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 ov;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 g = __bfloat1622float2(g2[k]);
+    const float2 u = __bfloat1622float2(u2[k]);
+    float2 r;
+    r.x = g.x / (1.0f + expf(-g.x)) * u.x;
+    r.y = g.y / (1.0f + expf(-g.y)) * u.y;
+    o2[k] = __float22bfloat162_rn(r);
+  }
+  reinterpret_cast<uint4*>(out)[idx] = ov;
+}
+
+// ---------------------------------------------------------------- float32 <- T copy (logits of a bf16 GEMM)
+template <typename T>
+__global__ void to_float_kernel(float* __restrict__ out, const T* __restrict__ in, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = Elem<T>::load(in + i);
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* ids, int tokens, int hidden,
+                              int vocab, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_CHECK_ARG(tokens > 0 && hidden > 0 && vocab > 0, "embed_gather: bad sizes T=%d H=%d V=%d", tokens, hidden, vocab);
+  const int threads = hidden >= 256 ? 256 : 64;
+  if (dtype == MS_F32)
+    embed_gather_kernel<float><<<tokens, threads, 0, stream>>>((float*)residual_f32, (const float*)table, ids, hidden, vocab);
+  else
+    embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((float*)residual_f32, (const __nv_bfloat16*)table, ids, hidden, vocab);
+  MS_CHECK_LAUNCH();
+  return 0;
+}
+
+MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, const void* weight, const int* rows,
+                             float eps, int num_out_rows, int hidden, int write_residual, int dtype,
+                             cudaStream_t stream) {
+  if (num_out_rows == 0) return 0;
+  MS_CHECK_ARG(num_out_rows > 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d H=%d", num_out_rows, hidden);
+  MS_CHECK_ARG(!(rows && write_residual), "add_rmsnorm: a gathered norm cannot write the residual back");
+  const size_t smem = (size_t)hidden * sizeof(float);
+  MS_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", hidden, smem);
+  constexpr int THREADS = 256;
+  if (dtype == MS_F32) {
+    auto k = add_rmsnorm_kernel<float, THREADS>;
+    if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<num_out_rows, THREADS, smem, stream>>>((float*)out, (float*)residual_f32, (const float*)delta, (const float*)weight, rows, eps, hidden, write_residual);
+  } else {
+    auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
+    if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<num_out_rows, THREADS, smem, stream>>>((__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+  }
+  MS_CHECK_LAUNCH();
+  return 0;
+}
+
+MS_EXPORT int ms_silu_mul(void* out, const void* gate_up, int tokens, int inter, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_CHECK_ARG(tokens > 0 && inter > 0, "silu_mul: bad sizes T=%d I=%d", tokens, inter);
+  const size_t total = (size_t)tokens * inter;
+  if (dtype == MS_F32) {
+    silu_mul_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+  } else if (inter % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)gate_up % 16 == 0)) {
+    const size_t total8 = total / 8;
+    silu_mul_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter / 8, total8);
+  } else {
+    silu_mul_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, total);
+  }
+  MS_CHECK_LAUNCH();
+  return 0;
+}
+
+MS_EXPORT int ms_to_float(void* out_f32, const void* in, long long n, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (dtype == MS_F32)
+    to_float_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((float*)out_f32, (const float*)in, (size_t)n);
+  else
+    to_float_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((float*)out_f32, (const __nv_bfloat16*)in, (size_t)n);
+  MS_CHECK_LAUNCH();
+  return 0;
+}

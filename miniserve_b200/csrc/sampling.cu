@@ -1,0 +1,217 @@
+// Token selection on the device from float32 logits [rows, vocab]: greedy argmax (first maximal
+// index wins), temperature sampling by the Gumbel-max trick with hashed noise, and nucleus
+// (top-p) masking.
+//
+// Restates miniserve/engine/sampler.py: :91 (argmax), :95 (z = logits / T in float32), :29-46 (noise:
+// u = ((mix32((key + v*0x9E3779B9) mod 2^32) >> 8) + 0.5) / 2^24, key = mix32(seed ^ mix32(counter)),
+// mix32 = two rounds of x = ((x >> 16) ^ x) * 0x45D9F3B, then (x >> 16) ^ x), :98-99
+// (g = -log(-log u), argmax(z + g)), :102-112 (keep the most likely tokens while the probability
+// mass before them is below top_p; ties keep index order). The noise is a pure function of
+// (seed, counter, vocabulary index), so a row samples the same token wherever it sits in a batch.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace ms {
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x = ((x >> 16) ^ x) * 0x45D9F3Bu;
+  x = ((x >> 16) ^ x) * 0x45D9F3Bu;
+  return (x >> 16) ^ x;
+}
+
+__device__ __forceinline__ float gumbel(uint32_t key, uint32_t v) {
+  const uint32_t h = mix32(key + v * 0x9E3779B9u);
+  const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -logf(-logf(u));
+}
+
+struct Best {
+  float val;
+  int idx;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // larger value wins; on equal values the lower index wins
+  if (b.val > a.val || (b.val == a.val && b.idx < a.idx)) return b;
+  return a;
+}
+__device__ __forceinline__ Best block_best(Best b, Best* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.val = __shfl_xor_sync(0xffffffffu, b.val, o);
+    other.idx = __shfl_xor_sync(0xffffffffu, b.idx, o);
+    b = better(b, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = b;
+  __syncthreads();
+  Best r = scratch[0];
+  for (int w = 1; w < nwarps; ++w) r = better(r, scratch[w]);
+  return r;
+}
+
+// Per row nucleus description written by nucleus_kernel and read by sample_kernel.
+struct Nucleus {
+  float zmax;     // max of z = logit / T
+  float sum;      // sum of exp(z - zmax)
+  float cut;      // smallest probability that is kept
+  int ties_kept;  // how many tokens with probability == cut are kept, in index order
+};
+
+__device__ __forceinline__ float prob_of(float logit, float inv_t, const Nucleus& n) {
+  return expf(logit * inv_t - n.zmax) / n.sum;
+}
+
+// One block per row. 31-step search over the bit pattern of the cut probability.
+__global__ void __launch_bounds__(1024)
+nucleus_kernel(Nucleus* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ temperature,
+               const float* __restrict__ top_p, int vocab) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float t = temperature[r], tp = top_p[r];
+  Nucleus n;
+  n.zmax = 0.f; n.sum = 1.f; n.cut = 0.f; n.ties_kept = 0x7fffffff;
+  if (!(t > 0.f) || tp >= 1.f) {  // greedy row or whole distribution: nothing to mask
+    if (threadIdx.x == 0) out[r] = n;
+    return;
+  }
+  const float inv_t = 1.0f / t;
+  const float* lg = logits + (size_t)r * vocab;
+  float mx = -INFINITY;
+  for (int v = threadIdx.x; v < vocab; v += blockDim.x) mx = fmaxf(mx, lg[v] * inv_t);
+  mx = warp_max(mx);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+  float s = 0.f;
+  for (int v = threadIdx.x; v < vocab; v += blockDim.x) s += expf(lg[v] * inv_t - mx);
+  n.zmax = mx;
+  n.sum = block_sum(s, red);
+  // smallest x (as float bits) with f(x) = sum of probabilities greater than x  <  top_p
+  uint32_t lo = 0u, hi = 0x3f800000u;  // f(1.0) = 0 < top_p always holds at hi
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    const float x = __uint_as_float(mid);
+    float f = 0.f;
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+      const float p = prob_of(lg[v], inv_t, n);
+      if (p > x) f += p;
+    }
+    f = block_sum(f, red);
+    if (f < tp) hi = mid; else lo = mid + 1;
+  }
+  n.cut = __uint_as_float(lo);
+  float f = 0.f;
+  for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+    const float p = prob_of(lg[v], inv_t, n);
+    if (p > n.cut) f += p;
+  }
+  f = block_sum(f, red);
+  // the k-th tie (k = 0, 1, ...) is kept while f + k*cut < top_p
+  int k = 1;
+  if (n.cut > 0.f) {
+    const float room = (tp - f) / n.cut;
+    k = room >= 2147483000.f ? 0x7fffffff : max(1, (int)ceilf(room));
+  } else {
+    k = 0x7fffffff;
+  }
+  n.ties_kept = k;
+  if (threadIdx.x == 0) out[r] = n;
+}
+
+// One block per row: tokens[r] = argmax(logits) if temperature == 0, else argmax(z + gumbel) over
+// the tokens the nucleus keeps.
+__global__ void __launch_bounds__(1024)
+sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, const float* __restrict__ temperature,
+              const long long* __restrict__ seed, const long long* __restrict__ counter,
+              const Nucleus* __restrict__ nucleus, int vocab) {
+  __shared__ Best scratch[32];
+  __shared__ int tie_base[33];
+  const int r = blockIdx.x;
+  const float* lg = logits + (size_t)r * vocab;
+  const float t = temperature ? temperature[r] : 0.f;
+  Best b;
+  b.val = -INFINITY;
+  b.idx = 0x7fffffff;
+  if (!(t > 0.f)) {
+    for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+      const float x = lg[v];
+      if (x > b.val) { b.val = x; b.idx = v; }
+    }
+  } else {
+    const float inv_t = 1.0f / t;
+    const uint32_t key = mix32((uint32_t)seed[r] ^ mix32((uint32_t)counter[r]));
+    const bool masked = nucleus != nullptr && nucleus[r].ties_kept != 0x7fffffff;
+    if (!masked) {
+      for (int v = threadIdx.x; v < vocab; v += blockDim.x) {
+        const float x = lg[v] / t + gumbel(key, (uint32_t)v);
+        if (x > b.val) { b.val = x; b.idx = v; }
+      }
+    } else {
+      // Each warp owns a contiguous stretch of the vocabulary so that ties at the cut can be
+      // ranked in index order.
+      const Nucleus n = nucleus[r];
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+      const int per_warp = ((vocab + nwarps - 1) / nwarps + 31) / 32 * 32;
+      const int begin = min(warp * per_warp, vocab), end = min(begin + per_warp, vocab);
+      int ties = 0;
+      for (int v0 = begin; v0 < end; v0 += 32) {
+        const int v = v0 + lane;
+        const bool tie = v < end && prob_of(lg[v], inv_t, n) == n.cut;
+        ties += __popc(__ballot_sync(0xffffffffu, tie));
+      }
+      if (lane == 0) tie_base[warp + 1] = ties;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        tie_base[0] = 0;
+        for (int w = 0; w < nwarps; ++w) tie_base[w + 1] += tie_base[w];
+      }
+      __syncthreads();
+      int rank0 = tie_base[warp];
+      for (int v0 = begin; v0 < end; v0 += 32) {
+        const int v = v0 + lane;
+        float p = -1.f;
+        if (v < end) p = prob_of(lg[v], inv_t, n);
+        const bool tie = v < end && p == n.cut;
+        const unsigned ballot = __ballot_sync(0xffffffffu, tie);
+        const int rank = rank0 + __popc(ballot & ((1u << lane) - 1u));
+        rank0 += __popc(ballot);
+        const bool keep = v < end && (p > n.cut || (tie && rank < n.ties_kept));
+        if (keep) {
+          const float x = lg[v] / t + gumbel(key, (uint32_t)v);
+          if (x > b.val || (x == b.val && v < b.idx)) { b.val = x; b.idx = v; }
+        }
+      }
+    }
+  }
+  b = block_best(b, scratch);
+  if (threadIdx.x == 0) tokens[r] = b.idx == 0x7fffffff ? 0 : b.idx;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+MS_EXPORT int ms_nucleus_bytes() { return (int)sizeof(Nucleus); }
+
+MS_EXPORT int ms_sample(int* tokens, const float* logits, const float* temperature, const float* top_p,
+                        const long long* seed, const long long* counter, void* nucleus_scratch, int rows, int vocab,
+                        cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_CHECK_ARG(rows > 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+  MS_CHECK_ARG(temperature == nullptr || (seed != nullptr && counter != nullptr), "sample: temperature rows need seeds and counters");
+  const int threads = vocab >= 8192 ? 1024 : 256;
+  if (top_p != nullptr) {
+    MS_CHECK_ARG(nucleus_scratch != nullptr && temperature != nullptr, "sample: top_p needs scratch and temperatures");
+    nucleus_kernel<<<rows, threads, 0, stream>>>((Nucleus*)nucleus_scratch, logits, temperature, top_p, vocab);
+    MS_CHECK_LAUNCH();
+  }
+  sample_kernel<<<rows, threads, 0, stream>>>(tokens, logits, temperature, seed, counter,
+                                              top_p ? (const Nucleus*)nucleus_scratch : nullptr, vocab);
+  MS_CHECK_LAUNCH();
+  return 0;
+}

@@ -1,0 +1,42 @@
+"""What the parts see of one step: the flat batch on the device, and its geometry on the host."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class StepContext:
+    """One step's batch. All device tensors are int32 views into one arena filled by the C++
+    packer and copied in a single transfer.
+
+    Rows are requests; row r brings ``q_len[r]`` new tokens at absolute positions
+    ``q_start[r] .. q_start[r] + q_len[r] - 1``; tokens of all rows are flattened in row order.
+    """
+
+    num_tokens: int  # including padding rows' tokens
+    num_rows: int  # including padding rows
+    num_logit_rows: int
+    stream: int  # CUDA stream handle every kernel of the step is launched on
+    # device, int32
+    token_ids: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T]
+    row_of_token: torch.Tensor  # [T]
+    cu_q: torch.Tensor  # [R + 1] first flat token of each row
+    q_start: torch.Tensor  # [R] tokens of the row already in the cache
+    kv_len: torch.Tensor  # [R] tokens in the cache after this step
+    state_slot: torch.Tensor  # [R] slot of the row's fixed-size state (-1: none)
+    logit_rows: torch.Tensor  # [W] flat token indices whose logits are wanted
+    page_indptr: list[torch.Tensor]  # per cache group: [R + 1]
+    page_indices: list[torch.Tensor]  # per cache group: page ids, -1 where a window gave one back
+    status: torch.Tensor  # [1] int32, raised by a kernel that finds inconsistent input
+    # host copies of the geometry, for launch configuration and for parts written in PyTorch
+    host_q_start: list[int] = field(default_factory=list)
+    host_q_len: list[int] = field(default_factory=list)
+    max_q_len: int = 1
+    max_kv_len: int = 1
+    decode_only: bool = False
+    sm_count: int = 148
+    scratch: dict = field(default_factory=dict)  # per-step or persistent scratch buffers of kernels

@@ -1,0 +1,204 @@
+"""Python faces of the CUDA kernels: each function takes torch tensors, checks what the
+kernel cannot check itself, and launches on the given stream. Tensors are only containers
+here; every operation below runs this package's own kernels, except the bfloat16 matrix
+product, which may go to the vendor library where the reference's engine does the same
+(miniserve/model/qwen3.py:115-131 uses F.linear, i.e. cuBLAS).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import native
+from .native import NativeError, OutOfBlocks
+
+__all__ = [
+    "NativeError", "OutOfBlocks", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
+    "qk_norm_rope_kv", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
+]
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"the kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(stream) -> int:
+    return torch.cuda.current_stream().cuda_stream if stream is None else stream
+
+
+def _check_dev(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("kernel operands must be contiguous CUDA tensors")
+
+
+def require_cuda_kernels():
+    """Load (building first if needed) the kernel library; raises if that is impossible."""
+    return native.kernels()
+
+
+def embed_gather(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, stream=None) -> None:
+    """residual[t] = float32(table[ids[t]]); residual [T, H] float32, ids int32."""
+    _check_dev(residual, table, ids)
+    assert residual.dtype == torch.float32 and ids.dtype == torch.int32
+    t, h = residual.shape
+    assert table.shape[1] == h and ids.numel() >= t
+    k = native.kernels()
+    native.kernel_check(k.ms_embed_gather(_ptr(residual), _ptr(table), _ptr(ids), t, h, table.shape[0],
+                                          dtype_code(table.dtype), _stream(stream)))
+
+
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                eps: float, rows: torch.Tensor | None = None, num_rows: int | None = None,
+                write_residual: bool = True, stream=None) -> None:
+    """out[i] = rmsnorm(residual[r] + delta[r]) * weight with r = rows[i] (or i); the sum is
+    written back to ``residual`` when there is no gather. Statistics in float32."""
+    _check_dev(out, residual, delta, weight, rows)
+    assert residual.dtype == torch.float32 and out.dtype == weight.dtype
+    assert delta is None or delta.dtype == out.dtype
+    hidden = residual.shape[-1]
+    n = out.shape[0] if num_rows is None else num_rows
+    assert weight.numel() == hidden and out.shape[-1] == hidden and out.shape[0] >= n
+    if rows is None:
+        assert residual.shape[0] >= n
+    k = native.kernels()
+    native.kernel_check(k.ms_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(rows),
+                                         float(eps), n, hidden, int(write_residual and rows is None),
+                                         dtype_code(out.dtype), _stream(stream)))
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, stream=None) -> None:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c], computed in float32."""
+    _check_dev(out, gate_up)
+    t, inter = out.shape
+    assert gate_up.shape == (t, 2 * inter) and gate_up.dtype == out.dtype
+    k = native.kernels()
+    native.kernel_check(k.ms_silu_mul(_ptr(out), _ptr(gate_up), t, inter, dtype_code(out.dtype), _stream(stream)))
+
+
+def to_float(out: torch.Tensor, x: torch.Tensor, stream=None) -> None:
+    _check_dev(out, x)
+    assert out.dtype == torch.float32 and out.numel() == x.numel()
+    k = native.kernels()
+    native.kernel_check(k.ms_to_float(_ptr(out), _ptr(x), x.numel(), dtype_code(x.dtype), _stream(stream)))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """x [M, K] times weight[N, K]^T -> [M, N].
+
+    float32: this package's FFMA kernel (true 32-bit, fixed summation order per element).
+    bfloat16: the vendor library's matrix product with float32 accumulation; ``out`` may be
+    float32 (logits) or bfloat16.
+    """
+    _check_dev(x, weight, out)
+    m, kdim = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == kdim, f"linear: x is [{m}, {kdim}], weight is {tuple(weight.shape)}"
+    if x.dtype == torch.float32:
+        assert weight.dtype == torch.float32
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        assert out.dtype == torch.float32 and out.shape == (m, n)
+        k = native.kernels()
+        native.kernel_check(k.ms_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, kdim, kdim, n, _stream(stream)))
+        return out
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    if out.dtype == torch.float32:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    else:
+        torch.mm(x, weight.t(), out=out)
+    return out
+
+
+def qk_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None,
+                    qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None,
+                    inv_freq: torch.Tensor | None, rotary_dim: int, eps: float, positions: torch.Tensor,
+                    row_of_token: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor,
+                    page_size: int, status: torch.Tensor, stream=None) -> None:
+    """Per-head norm of q and k, rotation by position, q written to ``q_out`` [T, nq, d] and the
+    new k, v written into their pages. ``k_pool``/``v_pool``: [pages, nkv, page_size, d], or None
+    when this entry only reads another entry's cache (then ``qkv`` holds q alone)."""
+    _check_dev(q_out, k_pool, v_pool, qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, page_indptr,
+               page_indices, status)
+    t, nq, d = q_out.shape
+    if k_pool is not None:
+        nkv = k_pool.shape[1]
+        assert k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
+        assert k_pool.dtype == qkv.dtype
+        assert qkv.shape == (t, (nq + 2 * nkv) * d)
+    else:
+        nkv = 1
+        assert qkv.shape == (t, nq * d)
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2)
+    k = native.kernels()
+    native.kernel_check(k.ms_qk_norm_rope_kv(
+        _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+        _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, d,
+        rotary_dim if inv_freq is not None else 0, float(eps), page_size, _ptr(status), dtype_code(qkv.dtype),
+        _stream(stream)))
+
+
+def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                      positions: torch.Tensor, row_of_token: torch.Tensor, page_indptr: torch.Tensor,
+                      page_indices: torch.Tensor, scale: float, window: int | None, status: torch.Tensor,
+                      stream=None) -> None:
+    """Causal attention of every new token over its request's pages; one warp per (token, head),
+    float32 arithmetic in a fixed order (bit-identical however the tokens were batched)."""
+    _check_dev(out, q, k_pool, v_pool, positions, row_of_token, page_indptr, page_indices, status)
+    t, nq, d = q.shape
+    nkv, page_size = k_pool.shape[1], k_pool.shape[2]
+    assert out.shape == q.shape and k_pool.shape[3] == d and k_pool.dtype == q.dtype
+    k = native.kernels()
+    native.kernel_check(k.ms_attention_rowwise(
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
+        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), page_size, _ptr(status),
+        dtype_code(q.dtype), _stream(stream)))
+
+
+def nucleus_bytes() -> int:
+    return native.kernels().ms_nucleus_bytes()
+
+
+def sample(tokens: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor | None = None,
+           top_p: torch.Tensor | None = None, seed: torch.Tensor | None = None,
+           counter: torch.Tensor | None = None, scratch: torch.Tensor | None = None, stream=None) -> None:
+    """tokens[r] (int32) from float32 logits [rows, vocab]: argmax where temperature is 0 (or
+    no temperatures are given), Gumbel-max sampling otherwise, inside the nucleus if ``top_p``."""
+    _check_dev(tokens, logits, temperature, top_p, seed, counter, scratch)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and tokens.dtype == torch.int32 and tokens.numel() >= rows
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and seed.dtype == torch.int64 and counter.dtype == torch.int64
+    if top_p is not None:
+        assert top_p.dtype == torch.float32 and scratch is not None and scratch.numel() * scratch.element_size() >= rows * nucleus_bytes()
+    k = native.kernels()
+    native.kernel_check(k.ms_sample(_ptr(tokens), _ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed),
+                                    _ptr(counter), _ptr(scratch), rows, vocab, _stream(stream)))
+
+
+def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+              scale: float, window: int | None) -> None:
+    """Causal attention of the step's new tokens over the paged cache of cache group ``group``.
+
+    float32 runs the row-wise kernel (bit-identical however the step was cut). bfloat16 runs the
+    tensor-core kernels when they take this head size, else the row-wise kernel too."""
+    from . import attention_bf16
+
+    if q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2]):
+        attention_bf16.run(out, q, k_pool, v_pool, ctx, group, scale, window)
+        return
+    attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
+                      ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream)

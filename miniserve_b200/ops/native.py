@@ -1,0 +1,103 @@
+"""ctypes bindings of the native libraries (built on demand by ``build.py``).
+
+There is no Python or library fallback behind these: if a library cannot be built or
+loaded, the import of the function that needs it raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_longlong, c_void_p
+from functools import lru_cache
+
+from . import build
+
+_p = c_void_p
+_i = c_int
+_ll = c_longlong
+_f = c_float
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class OutOfBlocks(RuntimeError):
+    """The pool has fewer free pages than a call needs; nothing was changed."""
+
+
+def _declare(lib, name, argtypes, restype=c_int):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+@lru_cache(maxsize=None)
+def host():
+    lib = ctypes.CDLL(str(build.ensure_built(build.HOST)))
+    _declare(lib, "ms_host_last_error", [], c_char_p)
+    _declare(lib, "ms_alloc_create", [_i, _i], _p)
+    _declare(lib, "ms_alloc_destroy", [_p], None)
+    _declare(lib, "ms_alloc_num_free", [_p])
+    _declare(lib, "ms_alloc_num_blocks", [_p])
+    _declare(lib, "ms_alloc_block_size", [_p])
+    _declare(lib, "ms_alloc_refcount", [_p, _i, POINTER(c_int)])
+    _declare(lib, "ms_alloc_allocate", [_p, _i, POINTER(c_int32)])
+    _declare(lib, "ms_alloc_incref", [_p, POINTER(c_int32), _i])
+    _declare(lib, "ms_alloc_free", [_p, POINTER(c_int32), _i])
+    _declare(lib, "ms_alloc_check", [_p])
+    _declare(lib, "ms_table_create", [_p], _p)
+    _declare(lib, "ms_table_destroy", [_p], None)
+    _declare(lib, "ms_table_num_tokens", [_p], _ll)
+    _declare(lib, "ms_table_num_entries", [_p])
+    _declare(lib, "ms_table_num_held", [_p])
+    _declare(lib, "ms_table_blocks_needed", [_p, _ll, POINTER(c_int)])
+    _declare(lib, "ms_table_append_tokens", [_p, _ll])
+    _declare(lib, "ms_table_slot", [_p, _ll, POINTER(_ll)])
+    _declare(lib, "ms_table_rewind", [_p, _ll])
+    _declare(lib, "ms_table_release", [_p])
+    _declare(lib, "ms_table_release_below", [_p, _ll, POINTER(c_int)])
+    _declare(lib, "ms_table_copy_blocks", [_p, POINTER(c_int32), _i])
+    _declare(lib, "ms_pack_step",
+             [_p, _ll, POINTER(_ll), _i, _i, _p, _p, _p, _p, _p, _i, _i, POINTER(c_void_p), _p], _ll)
+    return lib
+
+
+def host_check(rc: int) -> None:
+    """Turn a host-core return code into the exception the reference's allocator raises
+    (miniserve/cache/block_allocator.py: OutOfBlocks, ValueError, IndexError)."""
+    if rc == 0:
+        return
+    msg = host().ms_host_last_error().decode()
+    if rc == 2:
+        raise OutOfBlocks(msg)
+    if rc == 3:
+        raise IndexError(msg)
+    raise ValueError(msg)
+
+
+@lru_cache(maxsize=None)
+def kernels():
+    lib = ctypes.CDLL(str(build.ensure_built(build.KERNELS)))
+    _declare(lib, "ms_kernels_last_error", [], c_char_p)
+    _declare(lib, "ms_device_sm_count", [_i, POINTER(c_int)])
+    _declare(lib, "ms_device_arch", [_i, POINTER(c_int), POINTER(c_int)])
+    _declare(lib, "ms_embed_gather", [_p, _p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
+    _declare(lib, "ms_qk_norm_rope_kv",
+             [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p, _i, _p])
+    _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_attention_rowwise",
+             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_nucleus_bytes", [])
+    _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
+    return lib
+
+
+def kernel_check(rc: int, lib=None, errfn: str = "ms_kernels_last_error") -> None:
+    if rc != 0:
+        lib = lib or kernels()
+        raise NativeError(getattr(lib, errfn)().decode())

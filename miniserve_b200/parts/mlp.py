@@ -1,0 +1,37 @@
+"""Dense gated feed-forward."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, WeightDecl, param, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(Part):
+    """down(silu(gate(x)) * up(x)), no biases (miniserve/model/qwen3.py:128-131). The gate and
+    up matrices are stacked at load so that one product makes both
+    (miniserve/model/fused.py:41-95 does the same). Parameters: ``hidden``, ``intermediate``."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = param(spec, "hidden", int)
+        self.inter = param(spec, "intermediate", int)
+
+    def weights(self):
+        return {
+            "gate_proj.weight": WeightDecl((self.inter, self.hidden)),
+            "up_proj.weight": WeightDecl((self.inter, self.hidden)),
+            "down_proj.weight": WeightDecl((self.hidden, self.inter)),
+        }
+
+    def bind(self, tensors):
+        self.w_gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream)
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        ops.silu_mul(act, gate_up, stream=ctx.stream)
+        return ops.linear(act, self.w_down, stream=ctx.stream)
