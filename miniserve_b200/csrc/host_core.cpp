@@ -226,14 +226,18 @@ MS_EXPORT int ms_table_copy_blocks(void* h, int* out, int cap) {
 //   token_ids[T'] positions[T'] row_of_token[T'] cu_q[R'+1] q_start[R'] kv_len[R'] state_slot[R']
 //   logit_rows[W] then for each cache group g: page_indptr_g[R'+1] page_indices_g[P_g]
 // with R' = rows + pad_rows and T' = tokens + pad_rows. A padding row is one token 0 at
-// position 0 whose single page is `pad_page` (a page outside the allocator).
+// position 0 whose single page is `pad_page` (a page outside the allocator); with want_pad_rows its
+// logits are wanted too, so that the layout depends on R' alone. indices_cap > 0 gives every
+// group's page_indices exactly that many entries (a layout that does not move with the number of
+// pages, as a captured CUDA graph needs); 0 packs them tightly.
 // offsets_out receives the start of each field: 8 + 2*groups entries, then the total.
 static long long align4(long long x) { return (x + 3) & ~3LL; }
 
 MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long* offsets_out, int rows, int pad_rows,
                                  const int* q_start, const int* q_len, const int* token_ids,
                                  const int* state_slot, const int* logit_rows, int num_logit_rows, int groups,
-                                 void* const* tables /* [groups][rows] */, const int* pad_page /* [groups] */) {
+                                 void* const* tables /* [groups][rows] */, const int* pad_page /* [groups] */,
+                                 long long indices_cap, int want_pad_rows) {
   if (rows < 0 || pad_rows < 0 || groups < 0) return -err(VALUE_ERROR, "pack_step: negative count");
   long long T = 0;
   for (int r = 0; r < rows; ++r) {
@@ -250,7 +254,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
     return at;
   };
   const long long o_ids = field(Tp), o_pos = field(Tp), o_row = field(Tp), o_cu = field(Rp + 1), o_qs = field(Rp),
-                  o_kv = field(Rp), o_ss = field(Rp), o_lr = field(num_logit_rows);
+                  o_kv = field(Rp), o_ss = field(Rp), o_lr = field(num_logit_rows + (want_pad_rows ? pad_rows : 0));
   std::vector<long long> o_indptr(groups), o_indices(groups);
   for (int g = 0; g < groups; ++g) {
     long long pages = pad_rows;
@@ -261,8 +265,10 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
                     t->num_tokens, q_start[r] + q_len[r]);
       pages += (long long)t->blocks.size();
     }
+    if (indices_cap > 0 && pages > indices_cap)
+      return -err(VALUE_ERROR, "pack_step: group %d needs %lld page entries, the fixed layout has %lld", g, pages, indices_cap);
     o_indptr[g] = field(Rp + 1);
-    o_indices[g] = field(pages);
+    o_indices[g] = field(indices_cap > 0 ? indices_cap : pages);
   }
   offsets_out[f] = off;
   if (off > arena_cap) return -err(VALUE_ERROR, "pack_step: arena of %lld entries, step needs %lld", arena_cap, off);
@@ -286,6 +292,8 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
     if (logit_rows[i] < 0 || logit_rows[i] >= T) return -err(INDEX_ERROR, "pack_step: logit row %d outside [0, %lld)", logit_rows[i], T);
     arena[o_lr + i] = logit_rows[i];
   }
+  if (want_pad_rows)
+    for (int i = 0; i < pad_rows; ++i) arena[o_lr + num_logit_rows + i] = (int32_t)(T + i);
   for (int g = 0; g < groups; ++g) {
     long long p = 0;
     arena[o_indptr[g]] = 0;

@@ -40,3 +40,4 @@ class StepContext:
     decode_only: bool = False
     sm_count: int = 148
     scratch: dict = field(default_factory=dict)  # per-step or persistent scratch buffers of kernels
+    graph_bucket: int = 0  # > 0 while a CUDA graph for this padded batch size is captured or replayed

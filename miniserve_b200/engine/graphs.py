@@ -1,0 +1,125 @@
+"""CUDA graphs for decode-only steps.
+
+A decode step of a small model is launch-bound: a few hundred short kernels. The reference
+captures one graph per batch-size bucket and pads a step up to its bucket with rows that write
+a page outside the allocator (miniserve/engine/cuda_graph.py:49-274). The same is done here:
+buckets are the powers of two up to the largest batch, and that batch itself; a graph holds the
+whole forward pass and the sampling kernel; the step's metadata is packed on the host and
+copied into a fixed device arena before the replay, so nothing inside the graph moves.
+Graphs are captured on first use of their bucket.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .step import StepFunction, StepRow
+
+
+def graph_buckets(max_bs: int) -> list[int]:
+    out, b = [], 1
+    while b < max_bs:
+        out.append(b)
+        b *= 2
+    out.append(max_bs)
+    return out
+
+
+class _Captured:
+    __slots__ = ("graph", "tokens", "logits", "f32", "i64")
+
+    def __init__(self, graph, tokens, logits, f32, i64):
+        self.graph, self.tokens, self.logits, self.f32, self.i64 = graph, tokens, logits, f32, i64
+
+
+class DecodeGraphs:
+    def __init__(self, step_fn: StepFunction, sampler, max_bs: int):
+        self.step_fn = step_fn
+        self.sampler = sampler
+        self.buckets = graph_buckets(max_bs)
+        self.max_batch = self.buckets[-1]
+        cache = step_fn.cache
+        self.indices_cap = cache.num_pages + self.max_batch + 4
+        step_fn.reserve_arena(16 * (self.max_batch + 8) + cache.num_groups * (self.indices_cap + self.max_batch + 16) + 256)
+        self._generation = step_fn.arena_generation
+        self._graphs: dict[tuple[int, str], _Captured] = {}
+        self._pool = None
+        self.capture_stream = torch.cuda.Stream(device=step_fn.device)
+
+    def takes(self, num_rows: int) -> bool:
+        return num_rows <= self.max_batch
+
+    def _bucket(self, n: int) -> int:
+        return next(b for b in self.buckets if b >= n)
+
+    def run(self, rows: Sequence[StepRow], sampling: dict | None) -> torch.Tensor:
+        """One decode step (every row brings one token and wants its logits). Returns the
+        sampled tokens of the real rows, int32 on the device."""
+        sf = self.step_fn
+        if sf.arena_generation != self._generation:
+            self._graphs.clear()
+            self._generation = sf.arena_generation
+        n = len(rows)
+        bucket = self._bucket(n)
+        pad = bucket - n
+        mode = "greedy"
+        if sampling is not None:
+            mode = "top_p" if any(p < 1 for p in sampling["top_ps"]) else "temperature"
+        ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True)
+        if sf.arena_generation != self._generation:  # the arena moved while preparing
+            self._graphs.clear()
+            self._generation = sf.arena_generation
+        cap = self._graphs.get((bucket, mode))
+        if cap is None:
+            cap = self._capture(ctx, bucket, mode)
+            self._graphs[(bucket, mode)] = cap
+        if sampling is not None:
+            f32 = torch.ones((2, bucket), dtype=torch.float32)
+            i64 = torch.zeros((2, bucket), dtype=torch.int64)
+            f32[0, :n] = torch.tensor(sampling["temperatures"], dtype=torch.float32)
+            f32[0, n:] = 0.0
+            f32[1, :n] = torch.tensor(sampling["top_ps"], dtype=torch.float32)
+            i64[0, :n] = torch.tensor(sampling["seeds"], dtype=torch.int64)
+            i64[1, :n] = torch.tensor(sampling["counters"], dtype=torch.int64)
+            cap.f32.copy_(f32.pin_memory(), non_blocking=True)
+            cap.i64.copy_(i64.pin_memory(), non_blocking=True)
+        cap.graph.replay()
+        for r in rows:
+            sf.cache.trim(r.cache)
+        return cap.tokens[:n]
+
+    def _forward(self, ctx, bucket: int, mode: str, f32, i64):
+        sf = self.step_fn
+        ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream
+        ctx.graph_bucket = bucket
+        logits = sf.model.forward(ctx, sf.cache.entry_views)
+        tokens = torch.empty(bucket, dtype=torch.int32, device=sf.device)
+        from .. import ops
+
+        if mode == "greedy":
+            ops.sample(tokens, logits, stream=ctx.stream)
+        else:
+            ops.sample(tokens, logits, temperature=f32[0], top_p=f32[1] if mode == "top_p" else None, seed=i64[0],
+                       counter=i64[1], scratch=self.sampler._scratch if mode == "top_p" else None,
+                       stream=ctx.stream)
+        return logits, tokens
+
+    def _capture(self, ctx, bucket: int, mode: str) -> _Captured:
+        sf = self.step_fn
+        f32 = torch.zeros((2, bucket), dtype=torch.float32, device=sf.device)
+        f32[1] = 1.0
+        i64 = torch.zeros((2, bucket), dtype=torch.int64, device=sf.device)
+        self.sampler._ensure(bucket)
+        torch.cuda.current_stream(sf.device).synchronize()
+        s = self.capture_stream
+        with torch.cuda.stream(s):
+            self._forward(ctx, bucket, mode, f32, i64)  # warm-up outside the capture
+        s.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._pool, stream=s):
+            logits, tokens = self._forward(ctx, bucket, mode, f32, i64)
+        if self._pool is None:
+            self._pool = graph.pool()
+        return _Captured(graph, tokens, logits, f32, i64)

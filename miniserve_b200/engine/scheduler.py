@@ -1,0 +1,214 @@
+"""The scheduler: which requests run in the next step, and with how many tokens each.
+
+Decisions, following miniserve/engine/scheduler.py:
+
+* With a chunk budget (``chunked_prefill_size`` tokens per step, the default): decode first.
+  Every decoding request gets its one token; what is left of the budget goes to portions of
+  prompts, first of requests already part-way through theirs (in admission order), then of newly
+  admitted ones in arrival order (:227-279).
+* Without (``chunked_prefill_size=0``): prefill first. Waiting requests are admitted whole under
+  ``max_prefill_tokens`` (the first always); a step holds either whole prompts or decode tokens
+  (:156-201).
+* Admission needs the pages of the whole prompt plus one token, on top of what every running
+  request may still allocate; it stops at the first request that does not fit: no skipping ahead
+  (:249-257, 294-303). A request that could never fit in the pool is rejected when it is added
+  (:143-154).
+* When pages run out: requests are preempted, newest admitted first and never the oldest running
+  one, until what the rest may still allocate fits. A preempted request gives back everything it
+  holds, keeps its output, and goes to the front of the waiting queue to be run again from its
+  first token (:281-323). So the oldest request always progresses and nothing deadlocks.
+
+Budgets are per cache group (a tuple of page counts) and include the slot for per-request state.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache.manager import CacheManager
+from .request import Request, RequestState
+
+
+@dataclass
+class PlanRow:
+    request: Request
+    start: int  # tokens of the request already in the cache
+    count: int  # new tokens this step
+
+    @property
+    def completes(self) -> bool:
+        """The row reaches the end of its sequence, so a token is sampled from its last position."""
+        return self.start + self.count == self.request.seq_len
+
+
+@dataclass
+class Plan:
+    rows: list[PlanRow]
+    num_decode: int  # rows[:num_decode] are single decode tokens
+    preempted: list[Request] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(r.count for r in self.rows)
+
+    @property
+    def phase(self) -> str:
+        if self.num_decode == len(self.rows):
+            return "decode"
+        return "prefill" if self.num_decode == 0 else "mixed"
+
+
+def _add(a: tuple[int, ...], b: tuple[int, ...]) -> tuple[int, ...]:
+    return tuple(x + y for x, y in zip(a, b))
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_running: int = 64, max_prefill_tokens: int = 8192,
+                 chunked_prefill_size: int = 2048):
+        if max_running < 1 or max_prefill_tokens < 1:
+            raise ValueError("max_running and max_prefill_tokens must be positive")
+        if chunked_prefill_size < 0:
+            raise ValueError(f"chunked_prefill_size must be >= 0, got {chunked_prefill_size}")
+        if max_running > cache.max_requests:
+            raise ValueError(f"max_running={max_running} exceeds the cache's {cache.max_requests} request slots")
+        self.cache = cache
+        self.max_running = max_running
+        self.max_prefill_tokens = max_prefill_tokens
+        self.chunked_prefill_size = chunked_prefill_size
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []  # admission order
+        self.num_preemptions = 0
+        self.stats = dict(first_tokens=0, re_tokens=0)
+
+    # ------------------------------------------------------------------ queues
+    def add(self, req: Request) -> None:
+        if req.state is not RequestState.WAITING:
+            raise ValueError(f"request {req.rid} is {req.state.name}, expected WAITING")
+        need = self.cache.pages_for(req.max_len)
+        if any(n > self.cache.num_pages for n in need):
+            raise ValueError(f"request {req.rid} needs up to {req.max_len} tokens of cache, "
+                             f"the pool holds {self.cache.num_pages * self.cache.page_size}")
+        self.waiting.append(req)
+
+    def retire(self, req: Request) -> None:
+        if not req.is_done:
+            raise ValueError(f"request {req.rid} is {req.state.name}, not done")
+        if req in self.running:
+            self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+
+    @property
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ budget arithmetic
+    @staticmethod
+    def _decodes(r: Request) -> bool:
+        return r.state is RequestState.DECODE and not r.reached_max_tokens
+
+    def _zero(self) -> tuple[int, ...]:
+        return (0,) * self.cache.num_groups
+
+    def _outstanding(self, reqs) -> tuple[int, ...]:
+        """Pages per group that ``reqs`` may still allocate before any of them finishes: one
+        token for each decoding request; the rest of the prompt plus one token for each
+        request still in its prefill."""
+        need = self._zero()
+        for r in reqs:
+            if self._decodes(r):
+                need = _add(need, self.cache.pages_needed(r.cache, 1))
+            elif r.state is RequestState.PREFILL:
+                whole = self.cache.pages_for(r.seq_len + 1)
+                held = self.cache.pages_held(r.cache)
+                need = _add(need, tuple(max(0, w - h) for w, h in zip(whole, held)))
+        return need
+
+    def _admission_need(self, req: Request) -> tuple[int, ...]:
+        return self.cache.pages_for(req.seq_len + 1)
+
+    # ------------------------------------------------------------------ preemption
+    def _preempt(self, req: Request) -> None:
+        req.transition(RequestState.WAITING)
+        self.cache.release(req.cache)
+        req.cache = None
+        self.running.remove(req)
+        self.waiting.appendleft(req)  # victims are taken newest first, so arrival order is kept
+        req.num_preemptions += 1
+        self.num_preemptions += 1
+
+    def _make_room(self, pool: list[Request]) -> list[Request]:
+        """Preempt until what ``pool`` may still allocate fits into the free pages."""
+        preempted: list[Request] = []
+        while not self.cache.fits(self._outstanding(pool)):
+            candidates = [r for r in pool if r is not self.running[0]]
+            if not candidates:
+                raise RuntimeError("a lone request does not fit in the pool")  # add() rejects those
+            victim = candidates[-1]
+            if pool is not self.running:
+                pool.remove(victim)
+            self._preempt(victim)
+            preempted.append(victim)
+        return preempted
+
+    # ------------------------------------------------------------------ step assembly
+    def schedule(self) -> Plan | None:
+        """The next step, or None if nothing can run. Moves admitted requests to PREFILL and
+        preempted ones back to WAITING."""
+        if self.chunked_prefill_size:
+            return self._schedule_chunked()
+        return self._schedule_whole()
+
+    def _admit(self, req: Request) -> None:
+        req.cache = self.cache.new_request()
+        self.waiting.remove(req)
+        req.transition(RequestState.PREFILL)
+        self.running.append(req)
+        self.stats["first_tokens" if req.num_preemptions == 0 else "re_tokens"] += req.seq_len
+
+    def _schedule_chunked(self) -> Plan | None:
+        preempted = self._make_room(self.running)
+        budget = self.chunked_prefill_size
+        rows = [PlanRow(r, r.seq_len - 1, 1) for r in self.running if self._decodes(r)]
+        num_decode = len(rows)
+        budget -= num_decode
+        for r in self.running:
+            if r.state is RequestState.PREFILL and budget > 0:
+                start = r.num_cached
+                n = min(r.seq_len - start, budget)
+                rows.append(PlanRow(r, start, n))
+                budget -= n
+        for req in list(self.waiting):
+            if budget <= 0 or len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
+                break
+            if not self.cache.fits(self._admission_need(req), margin=self._outstanding(self.running)):
+                break
+            self._admit(req)
+            n = min(req.seq_len, budget)
+            rows.append(PlanRow(req, 0, n))
+            budget -= n
+        if not rows:
+            return None
+        return Plan(rows, num_decode, preempted)
+
+    def _schedule_whole(self) -> Plan | None:
+        admitted: list[Request] = []
+        budget = self.max_prefill_tokens
+        for req in list(self.waiting):
+            if len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
+                break
+            if admitted and req.seq_len > budget:  # the first is admitted even over the budget
+                break
+            if not self.cache.fits(self._admission_need(req), margin=self._outstanding(self.running)):
+                break
+            self._admit(req)
+            admitted.append(req)
+            budget -= req.seq_len
+        if admitted:
+            return Plan([PlanRow(r, 0, r.seq_len) for r in admitted], 0)
+        decoding = [r for r in self.running if self._decodes(r)]
+        preempted = self._make_room(decoding)
+        if not decoding:
+            return None
+        return Plan([PlanRow(r, r.seq_len - 1, 1) for r in decoding], len(decoding), preempted)

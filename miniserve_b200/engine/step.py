@@ -55,6 +55,7 @@ class StepFunction:
         self._events: list[torch.cuda.Event | None] = []
         self._dev_arena: torch.Tensor | None = None
         self._turn = 0
+        self.arena_generation = 0  # bumped when the device arena moves (captured graphs become stale)
         self._grow(arena_ints)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         props = torch.cuda.get_device_properties(self.device)
@@ -68,14 +69,22 @@ class StepFunction:
         self._pinned = [torch.empty(ints, dtype=torch.int32, pin_memory=True) for _ in range(_NUM_BUFFERS)]
         self._events = [None] * _NUM_BUFFERS
         self._dev_arena = torch.empty(ints, dtype=torch.int32, device=self.device)
+        self.arena_generation += 1
 
-    def _arena_need(self, rows: Sequence[StepRow], pad_rows: int) -> int:
+    def reserve_arena(self, ints: int) -> None:
+        """Make the arena at least this large now, so that it does not move later."""
+        if ints > self._arena_ints:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._grow(ints)
+
+    def _arena_need(self, rows: Sequence[StepRow], pad_rows: int, indices_cap: int = 0) -> int:
         t = sum(len(r.tokens) for r in rows) + pad_rows
         r = len(rows) + pad_rows
         w = sum(len(x.want) for x in rows)
         pages = sum(sum(tb.num_entries + tb.blocks_needed(len(x.tokens)) for tb in x.cache.tables) for x in rows)
         groups = self.cache.num_groups
-        return 3 * (t + 4) + 4 * (r + 5) + (w + 4) + groups * (r + 5 + pad_rows + 4) + pages + 64
+        return (3 * (t + 4) + 4 * (r + 5) + (w + pad_rows + 4) + groups * (r + 5 + pad_rows + 4 + indices_cap)
+                + pages + 64)
 
     # ------------------------------------------------------------------ the step
     def run(self, rows: Sequence[StepRow], pad_rows: int = 0) -> torch.Tensor:
@@ -88,7 +97,12 @@ class StepFunction:
             self.cache.trim(r.cache)
         return logits
 
-    def prepare(self, rows: Sequence[StepRow], pad_rows: int = 0) -> StepContext:
+    def prepare(self, rows: Sequence[StepRow], pad_rows: int = 0, indices_cap: int = 0,
+                want_pad_rows: bool = False) -> StepContext:
+        """Reserve pages, pack the step and start its copy to the device. ``pad_rows`` adds
+        padding rows (one token at position 0 on a page outside the allocator);
+        ``indices_cap`` / ``want_pad_rows`` ask for the layout that depends on the padded row
+        count alone (see ``csrc/host_core.cpp``), which captured graphs need."""
         if not rows:
             raise ValueError("a step needs at least one row")
         q_len = np.fromiter((len(r.tokens) for r in rows), dtype=np.int32, count=len(rows))
@@ -110,7 +124,7 @@ class StepFunction:
         want_arr = np.asarray(want, dtype=np.int32)
         slots = np.fromiter((r.cache.state_slot for r in rows), dtype=np.int32, count=len(rows))
 
-        need = self._arena_need(rows, pad_rows)
+        need = self._arena_need(rows, pad_rows, indices_cap)
         if need > self._arena_ints:
             torch.cuda.current_stream(self.device).synchronize()
             self._grow(2 * need)
@@ -133,7 +147,7 @@ class StepFunction:
         total = self._host_lib.ms_pack_step(
             pinned.data_ptr(), self._arena_ints, offsets, len(rows), pad_rows, q_start.ctypes.data,
             q_len.ctypes.data, ids.ctypes.data, slots.ctypes.data, want_arr.ctypes.data, len(want), groups, tables,
-            pad_page.ctypes.data)
+            pad_page.ctypes.data, indices_cap, int(want_pad_rows))
         if total < 0:
             # undo the reservation so that a failed step leaves the tables as they were
             for r, n in zip(rows, q_len):
@@ -161,10 +175,12 @@ class StepFunction:
             page_indices.append(view(o[9 + 2 * g], max(end - o[9 + 2 * g], 1)))
         kv_end = q_start + q_len
         return StepContext(
-            num_tokens=t_all, num_rows=r_all, num_logit_rows=len(want), stream=stream.cuda_stream,
+            num_tokens=t_all, num_rows=r_all, num_logit_rows=len(want) + (pad_rows if want_pad_rows else 0),
+            stream=stream.cuda_stream,
             token_ids=view(o[0], t_all), positions=view(o[1], t_all), row_of_token=view(o[2], t_all),
             cu_q=view(o[3], r_all + 1), q_start=view(o[4], r_all), kv_len=view(o[5], r_all),
-            state_slot=view(o[6], r_all), logit_rows=view(o[7], max(len(want), 1)),
+            state_slot=view(o[6], r_all),
+            logit_rows=view(o[7], max(len(want) + (pad_rows if want_pad_rows else 0), 1)),
             page_indptr=page_indptr, page_indices=page_indices, status=self.status,
             host_q_start=q_start.tolist(), host_q_len=q_len.tolist(),
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
