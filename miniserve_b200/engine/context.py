@@ -35,6 +35,7 @@ class StepContext:
     # host copies of the geometry, for launch configuration and for parts written in PyTorch
     host_q_start: list[int] = field(default_factory=list)
     host_q_len: list[int] = field(default_factory=list)
+    host_state_slot: list[int] = field(default_factory=list)
     max_q_len: int = 1
     max_kv_len: int = 1
     decode_only: bool = False

@@ -28,10 +28,11 @@ def graph_buckets(max_bs: int) -> list[int]:
 
 
 class _Captured:
-    __slots__ = ("graph", "tokens", "logits", "f32", "i64")
+    __slots__ = ("graph", "tokens", "logits", "f32", "i64", "launches")
 
-    def __init__(self, graph, tokens, logits, f32, i64):
+    def __init__(self, graph, tokens, logits, f32, i64, launches):
         self.graph, self.tokens, self.logits, self.f32, self.i64 = graph, tokens, logits, f32, i64
+        self.launches = launches  # launches of this package's kernels inside the graph
 
 
 class DecodeGraphs:
@@ -47,6 +48,7 @@ class DecodeGraphs:
         self._graphs: dict[tuple[int, str], _Captured] = {}
         self._pool = None
         self.capture_stream = torch.cuda.Stream(device=step_fn.device)
+        self.replayed_launches = 0  # kernels of this package launched through graph replays so far
 
     def takes(self, num_rows: int) -> bool:
         return num_rows <= self.max_batch
@@ -86,6 +88,7 @@ class DecodeGraphs:
             cap.f32.copy_(f32.pin_memory(), non_blocking=True)
             cap.i64.copy_(i64.pin_memory(), non_blocking=True)
         cap.graph.replay()
+        self.replayed_launches += cap.launches
         for r in rows:
             sf.cache.trim(r.cache)
         return cap.tokens[:n]
@@ -117,9 +120,14 @@ class DecodeGraphs:
         with torch.cuda.stream(s):
             self._forward(ctx, bucket, mode, f32, i64)  # warm-up outside the capture
         s.synchronize()
+        from ..ops import native
+
         graph = torch.cuda.CUDAGraph()
+        before = native.LAUNCHES[0]
         with torch.cuda.graph(graph, pool=self._pool, stream=s):
             logits, tokens = self._forward(ctx, bucket, mode, f32, i64)
+        launches = native.LAUNCHES[0] - before
+        native.LAUNCHES[0] = before  # a capture launches nothing
         if self._pool is None:
             self._pool = graph.pool()
-        return _Captured(graph, tokens, logits, f32, i64)
+        return _Captured(graph, tokens, logits, f32, i64, launches)

@@ -61,6 +61,7 @@ class StepFunction:
         props = torch.cuda.get_device_properties(self.device)
         self.sm_count = props.multi_processor_count
         self.persistent_scratch: dict = {}
+        self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
 
     # ------------------------------------------------------------------ arena
     def _grow(self, ints: int) -> None:
@@ -157,6 +158,7 @@ class StepFunction:
         stream = torch.cuda.current_stream(self.device)
         dev = self._dev_arena
         dev[:total].copy_(pinned[:total], non_blocking=True)
+        self.h2d_bytes += int(total) * 4
         ev = torch.cuda.Event()
         ev.record(stream)
         self._events[turn] = ev
@@ -182,7 +184,8 @@ class StepFunction:
             state_slot=view(o[6], r_all),
             logit_rows=view(o[7], max(len(want) + (pad_rows if want_pad_rows else 0), 1)),
             page_indptr=page_indptr, page_indices=page_indices, status=self.status,
-            host_q_start=q_start.tolist(), host_q_len=q_len.tolist(),
+            host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [1] * pad_rows,
+            host_state_slot=slots.tolist() + [-1] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
             decode_only=bool((q_len == 1).all()), sm_count=self.sm_count, scratch=self.persistent_scratch)
 

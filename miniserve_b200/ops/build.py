@@ -53,6 +53,11 @@ KERNELS = Module(
 )
 
 
+def all_modules() -> list[Module]:
+    """Every module of the package (what ``__graft_entry__.build`` compiles)."""
+    return [HOST, KERNELS]
+
+
 def log(msg: str) -> None:
     print(f"[miniserve_b200] {msg}", file=sys.stderr, flush=True)
 

@@ -97,7 +97,11 @@ def kernels():
     return lib
 
 
-def kernel_check(rc: int, lib=None, errfn: str = "ms_kernels_last_error") -> None:
+LAUNCHES = [0]  # launches of this package's own kernels since import (a launcher may launch more than one)
+
+
+def kernel_check(rc: int, lib=None, errfn: str = "ms_kernels_last_error", launches: int = 1) -> None:
+    LAUNCHES[0] += launches
     if rc != 0:
         lib = lib or kernels()
         raise NativeError(getattr(lib, errfn)().decode())

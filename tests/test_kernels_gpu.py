@@ -1,0 +1,311 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same operation, at sizes
+other than the engine's (odd widths, head sizes in steps of 16, vocabularies that are no power
+of two), and with inputs made so that a fault would show."""
+
+import math
+
+import pytest
+import torch
+
+from miniserve_b200 import ops
+from tests.kernel_util import PagedBatch, reference_attention
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, vocab, tokens", [(24, 77, 5), (1000, 333, 130)])
+def test_embed_gather(dtype, hidden, vocab, tokens):
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    ids = torch.randint(0, vocab, (tokens,), device=DEV, dtype=torch.int32)
+    ids[0], ids[-1] = vocab - 1, 0
+    out = torch.empty(tokens, hidden, device=DEV)
+    ops.embed_gather(out, table, ids)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, rows, eps", [(24, 3, 1e-5), (1000, 37, 1e-6), (4100, 2, 1e-3)])
+def test_add_rmsnorm(dtype, hidden, rows, eps):
+    res = torch.randn(rows, hidden, device=DEV) * 3
+    delta = (torch.randn(rows, hidden, device=DEV)).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype)
+    total = res + delta.float()
+    expect = total * torch.rsqrt((total * total).mean(-1, keepdim=True) + eps) * w.float()
+    got_res = res.clone()
+    out = torch.empty(rows, hidden, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(out, got_res, delta, w, eps)
+    assert torch.allclose(got_res, total, atol=1e-6)  # the sum is stored back
+    assert torch.allclose(out.float(), expect, **_tol(dtype))
+    # without an addend the residual is left alone
+    out2 = torch.empty_like(out)
+    keep = res.clone()
+    ops.add_rmsnorm(out2, keep, None, w, eps)
+    assert torch.equal(keep, res)
+    e2 = res * torch.rsqrt((res * res).mean(-1, keepdim=True) + eps) * w.float()
+    assert torch.allclose(out2.float(), e2, **_tol(dtype))
+    # gathered rows: only those rows, residual untouched
+    idx = torch.tensor([rows - 1, 0], device=DEV, dtype=torch.int32)
+    out3 = torch.full((2, hidden), float("nan"), device=DEV, dtype=dtype)
+    keep = res.clone()
+    ops.add_rmsnorm(out3, keep, delta, w, eps, rows=idx)
+    assert torch.equal(keep, res)
+    assert torch.allclose(out3.float(), expect[idx.long()], **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, inter", [(3, 7), (65, 224), (9, 3072)])
+def test_silu_mul(dtype, tokens, inter):
+    gu = (torch.randn(tokens, 2 * inter, device=DEV) * 3).to(dtype)
+    out = torch.empty(tokens, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(out, gu)
+    g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    assert torch.allclose(out.float(), g * torch.sigmoid(g) * u, **_tol(dtype))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 5, 3), (7, 503, 96), (130, 70, 129), (64, 64, 16)])
+def test_gemm_f32_is_true_32bit_and_row_independent(m, n, k):
+    a = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    out = ops.linear(a, w)
+    expect = (a.double() @ w.double().T)
+    assert (out.double() - expect).abs().max().item() < 1e-4 * math.sqrt(k)
+    # far tighter than a reduced-precision (tf32/bf16 input) product could be
+    assert (out.double() - expect).abs().max().item() < 0.05 * (a.bfloat16().double() @ w.bfloat16().double().T - expect).abs().max().item() + 1e-6
+    # a row's result does not depend on the rows beside it
+    alone = ops.linear(a[m // 2:m // 2 + 1].contiguous(), w)
+    assert torch.equal(alone[0], out[m // 2])
+
+
+def test_bf16_linear_accumulates_in_float32():
+    a = torch.randn(33, 520, device=DEV).bfloat16()
+    w = torch.randn(77, 520, device=DEV).bfloat16()
+    expect = a.float() @ w.float().T
+    out32 = torch.empty(33, 77, device=DEV)
+    ops.linear(a, w, out=out32)
+    assert torch.allclose(out32, expect, atol=1e-3, rtol=1e-3)
+    assert torch.allclose(ops.linear(a, w).float(), expect, atol=0.3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, d, page, theta, eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 1, 48, 8, 1e6, 1e-5),
+                                                        (3, 3, 80, 4, 5e5, 1e-6), (2, 1, 256, 32, 1e6, 1e-6)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, theta, eps):
+    rows = [(0, 9), (13, 1), (30, 6)]  # a fresh portion, a decode token, a portion across a page edge
+    pb = PagedBatch(rows, page, nkv, d, dtype, seed=3)
+    t = pb.num_tokens
+    qkv = torch.randn(t, (nq + 2 * nkv) * d, device=DEV).to(dtype)
+    qw = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype)
+    kw = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))).to(DEV)
+    q_out = torch.empty(t, nq, d, device=DEV, dtype=dtype)
+    ops.qk_norm_rope_kv(q_out, pb.k_pool, pb.v_pool, qkv, qw, kw, inv_freq, d, eps, pb.positions, pb.row_of_token,
+                        pb.page_indptr, pb.page_indices, page, pb.status)
+    assert pb.status.item() == 0
+    # plain float32 reference of the same operation
+    x = qkv.float().cpu()
+    q, k, v = x[:, :nq * d].view(t, nq, d), x[:, nq * d:(nq + nkv) * d].view(t, nkv, d), x[:, (nq + nkv) * d:].view(t, nkv, d)
+    cos, sin = plain.rope_cos_sin(pb.positions.cpu(), d, theta, torch.float32)
+    q_ref = plain.apply_rope(plain.rms_norm(q, qw.float().cpu(), eps), cos, sin)
+    k_ref = plain.apply_rope(plain.rms_norm(k, kw.float().cpu(), eps), cos, sin)
+    tol = dict(atol=5e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(q_out.float().cpu(), q_ref, **tol)
+    at = 0
+    written = torch.zeros(pb.num_pages, page, dtype=torch.bool)
+    for r, (s, n) in enumerate(rows):
+        for i in range(n):
+            p = s + i
+            pg = pb.tables[r][p // page]
+            written[pg, p % page] = True
+            assert torch.allclose(pb.k_pool[pg, :, p % page].float().cpu(), k_ref[at], **tol)
+            assert torch.equal(pb.v_pool[pg, :, p % page].float().cpu(), v[at])
+            at += 1
+    # nothing but the new tokens' slots was written (the pool was NaN before)
+    assert torch.equal(~torch.isnan(pb.k_pool[:, 0, :, 0]).cpu(), written)
+
+
+def test_rope_angles_at_far_positions_are_32bit():
+    d, theta, page = 32, 1e6, 16
+    pb = PagedBatch([(40000, 3)], page, 1, d, torch.float32)
+    qkv = torch.randn(3, 3 * d, device=DEV)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))).to(DEV)
+    q_out = torch.empty(3, 1, d, device=DEV)
+    ops.qk_norm_rope_kv(q_out, pb.k_pool, pb.v_pool, qkv, None, None, inv_freq, d, 0.0, pb.positions, pb.row_of_token,
+                        pb.page_indptr, pb.page_indices, page, pb.status)
+    cos, sin = plain.rope_cos_sin(pb.positions.cpu(), d, theta, torch.float32)
+    ref = plain.apply_rope(qkv[:, :d].view(3, 1, d).cpu(), cos, sin)
+    assert torch.allclose(q_out.cpu(), ref, atol=2e-5)
+
+
+def _attention_case(dtype, rows, nq, nkv, d, page, window=None, needle=None, seed=0):
+    torch.manual_seed(seed)
+    pb = PagedBatch(rows, page, nkv, d, dtype, seed=seed)
+    qs, refs = [], []
+    scale = d ** -0.5
+    for r, (s, n) in enumerate(rows):
+        k = torch.randn(s + n, nkv, d, device=DEV).to(dtype)
+        v = torch.randn(s + n, nkv, d, device=DEV).to(dtype)
+        q = torch.randn(n, nq, d, device=DEV).to(dtype)
+        if needle is not None and s + n > needle:
+            # one far key that the last query must find: its score stands out, and its value is unlike the rest
+            q[-1] = (k[needle, 0] * 4).to(dtype)
+            v[needle] = 50.0
+        pb.fill(r, k, v)
+        qs.append(q)
+        refs.append(reference_attention(q, k, v, list(range(s, s + n)), scale, window))
+    q_all = torch.cat(qs).contiguous()
+    return pb, q_all, torch.cat(refs), scale
+
+
+ATT_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 8, 48, 4), (16, 8, 128, 16), (5, 5, 80, 32), (2, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, d, page", ATT_SHAPES)
+def test_attention_rowwise_mixed_batch(dtype, nq, nkv, d, page):
+    rows = [(0, 37), (52, 1), (15, 18), (0, 1), (63, 2)]
+    pb, q, ref, scale = _attention_case(dtype, rows, nq, nkv, d, page)
+    out = torch.empty_like(q)
+    ops.attention_rowwise(out, q, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
+                          pb.page_indices, scale, None, pb.status)
+    assert pb.status.item() == 0
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(out.float(), ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_rowwise_finds_a_far_key_among_hundreds(dtype):
+    rows = [(700, 1), (0, 650)]
+    pb, q, ref, scale = _attention_case(dtype, rows, 4, 2, 64, 16, needle=3)
+    out = torch.empty_like(q)
+    ops.attention_rowwise(out, q, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
+                          pb.page_indices, scale, None, pb.status)
+    assert ref[0, 0].mean().item() > 40  # the needle dominates the decode row's head 0
+    tol = dict(atol=2e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.3, rtol=2e-2)
+    assert torch.allclose(out.float(), ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 16, 33])
+def test_attention_rowwise_window_edge(dtype, window):
+    rows = [(0, 50), (49, 1)]
+    pb, q, ref, scale = _attention_case(dtype, rows, 4, 2, 32, 8, window=window)
+    out = torch.empty_like(q)
+    ops.attention_rowwise(out, q, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
+                          pb.page_indices, scale, window, pb.status)
+    tol = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(out.float(), ref, **tol)
+
+
+def test_attention_rowwise_is_bit_identical_across_batching():
+    nq, nkv, d, page = 6, 2, 48, 8
+    torch.manual_seed(4)
+    n = 77
+    k = torch.randn(n, nkv, d, device=DEV)
+    v = torch.randn(n, nkv, d, device=DEV)
+    q = torch.randn(n, nq, d, device=DEV)
+
+    def run(rows_spec, seed):
+        pb = PagedBatch(rows_spec, page, nkv, d, torch.float32, seed=seed)
+        qs = []
+        for r, (s, cnt) in enumerate(rows_spec):
+            pb.fill(r, k[:s + cnt], v[:s + cnt])
+            qs.append(q[s:s + cnt])
+        qq = torch.cat(qs).contiguous()
+        out = torch.empty_like(qq)
+        ops.attention_rowwise(out, qq, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
+                              pb.page_indices, d ** -0.5, None, pb.status)
+        return out
+
+    whole = run([(0, n)], 0)
+    parts = run([(60, 17), (0, 5), (5, 55)], 9)  # other pages, other neighbours, other order
+    assert torch.equal(parts[:17], whole[60:]) and torch.equal(parts[17:22], whole[:5]) and torch.equal(parts[22:], whole[5:60])
+
+
+def test_attention_reports_a_page_that_was_given_back():
+    pb, q, _, scale = _attention_case(torch.float32, [(0, 20)], 2, 1, 16, 8)
+    pb.page_indices[0] = -1
+    out = torch.empty_like(q)
+    ops.attention_rowwise(out, q, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
+                          pb.page_indices, scale, None, pb.status)
+    assert pb.status.item() != 0
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("vocab", [5, 503, 151936])
+def test_argmax_first_index_wins(vocab):
+    logits = torch.randn(7, vocab, device=DEV)
+    logits[2, 3] = logits[2, vocab - 1] = 99.0  # a tie: the lower index wins
+    logits[4, :] = 1.0
+    tokens = torch.empty(7, dtype=torch.int32, device=DEV)
+    ops.sample(tokens, logits)
+    expect = torch.argmax(logits, -1)
+    assert tokens.tolist() == expect.tolist() and tokens[2].item() == 3 and tokens[4].item() == 0
+
+
+def _sample(logits, temps, top_ps, seeds, counters):
+    rows = logits.shape[0]
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * ops.nucleus_bytes(), dtype=torch.uint8, device=DEV)
+    use_p = top_ps is not None
+    ops.sample(tokens, logits, temperature=torch.tensor(temps, device=DEV),
+               top_p=torch.tensor(top_ps, device=DEV) if use_p else None,
+               seed=torch.tensor(seeds, dtype=torch.int64, device=DEV),
+               counter=torch.tensor(counters, dtype=torch.int64, device=DEV), scratch=scratch if use_p else None)
+    return tokens.tolist()
+
+
+def test_temperature_sampling_matches_the_plain_sampler_and_ignores_neighbours():
+    vocab = 503
+    logits = torch.randn(6, vocab, device=DEV) * 2
+    temps = [0.7, 0.0, 1.3, 0.7, 1.0, 0.0]
+    seeds = [1, 2, 4000000000, 1, 77, 5]
+    counters = [10, 11, 12, 10, 300, 1]
+    got = _sample(logits, temps, None, seeds, counters)
+    for r in range(6):
+        assert got[r] == plain.sample_token(logits[r].cpu(), temps[r], seeds[r], counters[r])
+    # the same (seed, counter, logits) samples the same token anywhere in any batch
+    alone = _sample(logits[3:4].contiguous(), [0.7], None, [1], [10])
+    assert alone[0] == got[3]
+    assert _sample(logits, temps, None, seeds, [c + 1 for c in counters]) != got
+
+
+def test_top_p_matches_the_plain_sampler():
+    vocab = 300
+    torch.manual_seed(1)
+    logits = torch.randn(40, vocab, device=DEV) * 3
+    logits[5, :] = 0.0           # all ties: the nucleus keeps the first tokens in index order
+    logits[6, 10:20] = 7.0       # a tied group at the cut
+    temps = [1.0] * 40
+    tops = [0.05 + 0.9 * (i % 10) / 10 for i in range(40)]
+    tops[7] = 1.0
+    seeds = list(range(100, 140))
+    counters = list(range(40))
+    got = _sample(logits, temps, tops, seeds, counters)
+    same = sum(got[r] == plain.sample_token(logits[r].cpu(), temps[r], seeds[r], counters[r], tops[r]) for r in range(40))
+    assert same >= 39  # a cut that falls within rounding of top_p may go either way
+    # every sampled token lies inside its row's nucleus
+    for r in range(40):
+        p = torch.softmax(logits[r].cpu().float(), -1)
+        sp, order = torch.sort(p, descending=True, stable=True)
+        keep = (torch.cumsum(sp, 0) - sp) < tops[r] + 1e-6
+        assert got[r] in set(order[keep].tolist())
+    assert got[5] < max(1, int(0.55 * vocab) + 2)
+
+
+def test_top_p_distribution():
+    vocab = 8
+    probs = torch.tensor([0.4, 0.25, 0.15, 0.1, 0.05, 0.03, 0.01, 0.01])
+    rows = 20000
+    logits = probs.log().repeat(rows, 1).to(DEV).contiguous()
+    got = torch.tensor(_sample(logits, [1.0] * rows, [0.7] * rows, list(range(rows)), [3] * rows))
+    freq = torch.bincount(got, minlength=vocab).float() / rows
+    expect = torch.tensor([0.4, 0.25, 0.15, 0, 0, 0, 0, 0]) / 0.8
+    assert (freq - expect).abs().max().item() < 0.015

@@ -1,0 +1,215 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with
+state of its own that is registered, built and stepped without touching the package."""
+
+import pytest
+import torch
+
+from miniserve_b200.cache import CacheManager
+from miniserve_b200.cache.manager import KVEntryView
+from miniserve_b200.config import (Architecture, LayerSpec, ModelSpec, PartSpec, RunEntry, register_architecture,
+                                   resolve, unregister_architecture)
+from miniserve_b200.engine.context import StepContext
+from miniserve_b200.engine.step import StepFunction, StepRow
+from miniserve_b200.parts import (BuildEnv, DecoderModel, FixedState, Part, ResidualStream, WeightDecl, build_part,
+                                  register_part, unregister_part)
+from miniserve_b200.parts.block import build_block
+from miniserve_b200.weights import random_tensors
+from tests.kernel_util import PagedBatch
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda")
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _ctx(pb: PagedBatch, logit_rows=None) -> StepContext:
+    lr = torch.tensor(logit_rows if logit_rows is not None else [0], dtype=torch.int32, device=DEV)
+    return StepContext(
+        num_tokens=pb.num_tokens, num_rows=len(pb.rows), num_logit_rows=len(logit_rows or []),
+        stream=torch.cuda.current_stream().cuda_stream, token_ids=None, positions=pb.positions,
+        row_of_token=pb.row_of_token, cu_q=pb.cu_q, q_start=pb.q_start, kv_len=pb.kv_len,
+        state_slot=torch.full((len(pb.rows),), -1, dtype=torch.int32, device=DEV), logit_rows=lr,
+        page_indptr=[pb.page_indptr], page_indices=[pb.page_indices], status=pb.status,
+        host_q_start=[s for s, _ in pb.rows], host_q_len=[n for _, n in pb.rows],
+        max_q_len=max(n for _, n in pb.rows), max_kv_len=max(s + n for s, n in pb.rows),
+        decode_only=all(n == 1 for _, n in pb.rows))
+
+
+def _tol(dtype, scale=1.0):
+    return dict(atol=1e-5 * scale, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2 * scale, rtol=3e-2)
+
+
+def _bind_random(part, dtype, seed=0, std=0.2):
+    tensors = random_tensors(part.all_weights(), seed, dtype=dtype, std=std, device=DEV)
+    part.bind_all(tensors)
+    return {k: v.float().cpu() for k, v in tensors.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part(dtype):
+    env = BuildEnv(dtype, DEV)
+    norm = build_part("norm", PartSpec("rmsnorm", dict(size=72, eps=1e-5)), env)
+    w = _bind_random(norm, dtype)
+    res = torch.randn(11, 72, device=DEV)
+    pb = PagedBatch([(0, 11)], 16, 1, 16, dtype)
+    out = norm.forward(res, None, _ctx(pb))
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(res.cpu(), w["weight"], 1e-5), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_part(dtype):
+    env = BuildEnv(dtype, DEV)
+    ffn = build_part("feed_forward", PartSpec("swiglu", dict(hidden=40, intermediate=72)), env)
+    w = _bind_random(ffn, dtype)
+    x = torch.randn(9, 40, device=DEV).to(dtype)
+    pb = PagedBatch([(0, 9)], 16, 1, 16, dtype)
+    out = ffn.forward(x, _ctx(pb))
+    ref = plain.mlp_block({"model.layers.0.mlp." + k: v for k, v in w.items()}, 0, x.float().cpu())
+    assert torch.allclose(out.float().cpu(), ref, **_tol(dtype, 3.0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, d, page", [(4, 2, 16, 8), (6, 1, 48, 16)])
+def test_attention_part_whole_and_in_portions(dtype, heads, kv_heads, d, page):
+    hidden, eps, theta, n = 56, 1e-5, 1e4, 29
+    env = BuildEnv(dtype, DEV)
+    spec = PartSpec("gqa_attention", dict(hidden=hidden, heads=heads, kv_heads=kv_heads, head_dim=d, qk_norm=True,
+                                          qk_norm_eps=eps, position=PartSpec("rope_neox", dict(head_dim=d, theta=theta))))
+    att = build_part("mixer", spec, env)
+    w = _bind_random(att, dtype)
+    x = torch.randn(n, hidden, device=DEV).to(dtype)
+    cfg = dict(heads=heads, kv_heads=kv_heads, head_dim=d, eps=eps, theta=theta)
+    ref = plain.attention_block(cfg, {"model.layers.0.self_attn." + k: v for k, v in w.items()}, 0, x.float().cpu(),
+                                torch.arange(n))
+    # whole
+    pb = PagedBatch([(0, n)], page, kv_heads, d, dtype, seed=1)
+    out = att.forward(x, _ctx(pb), KVEntryView(0, pb.k_pool, pb.v_pool, page))
+    assert pb.status.item() == 0
+    assert torch.allclose(out.float().cpu(), ref, **_tol(dtype, 2.0))
+    # in two portions over the same pages: the second reads what the first wrote
+    full = PagedBatch([(0, n)], page, kv_heads, d, dtype, seed=2)
+    view = KVEntryView(0, full.k_pool, full.v_pool, page)
+    pb1 = PagedBatch([(0, 18)], page, kv_heads, d, dtype, share=full)
+    o1 = att.forward(x[:18].contiguous(), _ctx(pb1), view)
+    pb2 = PagedBatch([(18, n - 18)], page, kv_heads, d, dtype, share=full)
+    o2 = att.forward(x[18:].contiguous(), _ctx(pb2), view)
+    assert torch.allclose(torch.cat((o1, o2)).float().cpu(), ref, **_tol(dtype, 2.0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prenorm_block_embedding_and_head(dtype):
+    raw = plain.tiny_config_b()
+    _, _, spec = resolve(raw)
+    env = BuildEnv(dtype, DEV)
+    block = build_block(spec.layers[0], env)
+    w = _bind_random(block, dtype, std=0.1)
+    n, page = 13, 8
+    h0 = torch.randn(n, raw["hidden_size"], device=DEV)
+    pb = PagedBatch([(0, n)], page, raw["num_key_value_heads"], raw["head_dim"], dtype)
+    stream = block.forward(ResidualStream(h0.clone()), _ctx(pb), KVEntryView(0, pb.k_pool, pb.v_pool, page))
+    cfg = dict(heads=6, kv_heads=1, head_dim=32, eps=raw["rms_norm_eps"], theta=raw["rope_theta"])
+    ref = plain.decoder_layer(cfg, {"model.layers.0." + k: v for k, v in w.items()}, 0, h0.cpu(), torch.arange(n))
+    got = stream.total + stream.pending.float()
+    assert torch.allclose(got.cpu(), ref, **_tol(dtype, 3.0))
+
+    emb = build_part("embedding", spec.embedding, env)
+    head = build_part("head", spec.head, env)
+    we, wh = _bind_random(emb, dtype), _bind_random(head, dtype, seed=1)
+    ctx = _ctx(pb)
+    ctx.token_ids = torch.randint(0, raw["vocab_size"], (n,), dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ctx).cpu(), we["model.embed_tokens.weight"][ctx.token_ids.long().cpu()])
+    x = torch.randn(4, raw["hidden_size"], device=DEV).to(dtype)
+    logits = head.forward(x, ctx)
+    assert logits.dtype == torch.float32
+    assert torch.allclose(logits.cpu(), x.float().cpu() @ wh["lm_head.weight"].T, **_tol(dtype, 2.0))
+
+
+# ------------------------------------------------------------------ a toy mixer with state of its own
+class RunningMeanMixer(Part):
+    """y_t = W * mean(x_0 .. x_t): needs the sum so far and the count, per request."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = spec["hidden"]
+
+    def weights(self):
+        return {"mix.weight": WeightDecl((self.hidden, self.hidden))}
+
+    def bind(self, tensors):
+        self.w = tensors["mix.weight"].float()
+
+    def cache_need(self):
+        return FixedState((self.hidden + 1,), torch.float32)
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        at = 0
+        for start, n, slot in zip(ctx.host_q_start, ctx.host_q_len, ctx.host_state_slot):
+            state = cache.state[slot]
+            if start == 0:
+                state.zero_()  # a fresh request (or one that is run again) starts from nothing
+            assert int(state[-1].item()) == start, "the state does not belong to this request's past"
+            sums = state[:-1] + torch.cumsum(x[at:at + n].float(), 0)
+            counts = start + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+            out[at:at + n] = ((sums / counts[:, None]) @ self.w.T).to(x.dtype)
+            state[:-1] = sums[-1]
+            state[-1] = start + n
+            at += n
+        return out
+
+
+def _toy_spec(raw):
+    hidden = raw["hidden_size"]
+    norm = PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"]))
+    block = PartSpec("prenorm", dict(names=dict(mixer="mixer.", feed_forward="ffn.", norm1="ln1.", norm2="ln2.")))
+    ffn = PartSpec("swiglu", dict(hidden=hidden, intermediate=raw["inter"]))
+    att = PartSpec("gqa_attention", dict(hidden=hidden, heads=4, kv_heads=2, head_dim=16, qk_norm=False,
+                                         position=PartSpec("rope_neox", dict(head_dim=16, theta=100.0))))
+    toy = PartSpec("running_mean", dict(hidden=hidden))
+    layers = tuple(LayerSpec(f"layers.{i}.", block, m, ffn, dict(norm1=norm, norm2=norm))
+                   for i, m in enumerate([toy, att]))
+    # run order: toy, attention, then the toy layer once more (same weights, state of its own)
+    return ModelSpec("ToyStateLM", hidden, raw["vocab"],
+                     PartSpec("token_embedding", dict(vocab=raw["vocab"], hidden=hidden, name="embed.weight")),
+                     layers, (RunEntry(0), RunEntry(1), RunEntry(0)),
+                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"], name="final.")),
+                     PartSpec("linear_head", dict(vocab=raw["vocab"], hidden=hidden, tied=True, name="head.weight",
+                                                  tied_to="embed.weight")))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    register_part("mixer", "running_mean")(RunningMeanMixer)
+    register_architecture(Architecture("ToyStateLM", lambda raw: raw, _toy_spec))
+    try:
+        raw = dict(architectures=["ToyStateLM"], hidden_size=32, inter=48, vocab=61, eps=1e-5)
+        _, _, spec = resolve(raw)
+        model = DecoderModel(spec, dtype, DEV)
+        assert [type(ec.need).__name__ for ec in model.entry_caches] == ["FixedState", "PagedKV", "FixedState"]
+        model.bind(random_tensors(model.weight_decls(), 3, dtype=dtype, std=0.3, device=DEV))
+        cache = CacheManager(model.entry_caches, 12, 8, max_requests=2, dtype=dtype, device=DEV)
+        assert cache.num_groups == 1 and cache.entry_views[0].state is not cache.entry_views[2].state
+        step = StepFunction(model, cache)
+        ids = torch.randint(0, 61, (30,)).tolist()
+        a = cache.new_request()
+        whole = step.run([StepRow(a, ids, range(30))])
+        cache.release(a)
+        # the same tokens in portions, beside another request, in the slot the first one gave back
+        b, c = cache.new_request(), cache.new_request()
+        outs, i = [], 0
+        for n in (7, 2, 1, 12, 8):
+            rows = [StepRow(b, ids[i:i + n], range(n))]
+            if i < 20:
+                rows.append(StepRow(c, ids[::-1][i:i + n], []))
+            outs.append(step.run(rows)[:n])
+            i += n
+        step.check_status()
+        got = torch.cat(outs)
+        tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=5e-2, rtol=5e-2)
+        assert torch.allclose(got, whole, **tol)
+        cache.release(b)
+        cache.release(c)
+        assert cache.is_idle()
+    finally:
+        unregister_part("mixer", "running_mean")
+        unregister_architecture("ToyStateLM")
