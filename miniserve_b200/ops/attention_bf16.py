@@ -1,11 +1,93 @@
-"""bfloat16 tensor-core attention kernels (compiled per head size on first use)."""
+"""bfloat16 tensor-core attention (``csrc/attention_bf16.cu``), compiled per head size on first
+use: a model only pays for the head size it has."""
 
 from __future__ import annotations
 
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_void_p
+from functools import lru_cache
+
+import torch
+
+from . import build, native
+
+_p, _i, _f = c_void_p, c_int, c_float
+
 
 def supports(head_dim: int, page_size: int) -> bool:
-    return False
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size & (page_size - 1) == 0
 
 
-def run(out, q, k_pool, v_pool, ctx, group, scale, window) -> None:
-    raise NotImplementedError
+def module_for(head_dim: int) -> build.Module:
+    return build.Module(f"attn_bf16_d{head_dim}", ("attention_bf16.cu",), defines=(f"MS_HEAD_DIM={head_dim}",))
+
+
+@lru_cache(maxsize=None)
+def _lib(head_dim: int):
+    if not supports(head_dim, 16):
+        raise ValueError(f"the bfloat16 attention kernels take head sizes that are multiples of 16 up to 256, not {head_dim}")
+    lib = ctypes.CDLL(str(build.ensure_built(module_for(head_dim))))
+    pre = f"ms_attn_bf16_d{head_dim}_"
+    fns = {}
+    for name, args, res in (
+        ("last_error", [], c_char_p),
+        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _p], c_int),
+        ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
+    ):
+        fn = getattr(lib, pre + name)
+        fn.argtypes, fn.restype = args, res
+        fns[name] = fn
+    fns["lib"] = lib
+    return fns
+
+
+def _check(fns, rc: int, launches: int = 1) -> None:
+    native.LAUNCHES[0] += launches
+    if rc != 0:
+        raise native.NativeError(fns["last_error"]().decode())
+
+
+def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count: int) -> int:
+    """How many ways the keys of each (request, kv head) are split across CTAs: enough for about
+    four waves of two CTAs per SM, but at least 64 keys per split."""
+    want = -(-8 * sm_count // max(rows * head_chunks, 1))
+    by_len = 64 if max_kv_len is None else max(1, -(-max_kv_len // 64))
+    return max(1, min(want, by_len, 128))
+
+
+def _scratch(ctx, rows: int, nq: int, splits: int, d: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    need = rows * nq * splits
+    if ctx.graph_bucket:
+        # inside a CUDA graph capture: memory of the graph's own pool, alive as long as the graph
+        return (torch.empty(need * d, dtype=torch.float32, device=device),
+                torch.empty(need * 2, dtype=torch.float32, device=device))
+    buf = ctx.scratch.get("attn_decode")
+    if buf is None or buf[0].numel() < need * d:
+        buf = (torch.empty(need * d, dtype=torch.float32, device=device),
+               torch.empty(need * 2, dtype=torch.float32, device=device))
+        ctx.scratch["attn_decode"] = buf
+    return buf
+
+
+def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+        scale: float, window: int | None) -> None:
+    t, nq, d = q.shape
+    nkv, page_size = k_pool.shape[1], k_pool.shape[2]
+    fns = _lib(d)
+    indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
+    if ctx.decode_only:
+        chunks = nkv * -(-(nq // nkv) // 16)
+        splits = choose_splits(ctx.num_rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o, part_ml = _scratch(ctx, ctx.num_rows, nq, splits, d, q.device)
+        _check(fns, fns["decode"](
+            out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+            indices.data_ptr(), ctx.num_rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
+            launches=2 if splits > 1 else 1)
+        return
+    _check(fns, fns["prefill"](
+        out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr(), ctx.q_start.data_ptr(),
+        indptr.data_ptr(), indices.data_ptr(), ctx.num_rows, ctx.max_q_len, nq, nkv, float(scale), int(window or 0),
+        page_size, ctx.stream))

@@ -53,9 +53,16 @@ KERNELS = Module(
 )
 
 
+# head sizes whose attention kernels __graft_entry__.build() compiles ahead of time (the tests'
+# and the benchmark's); any other multiple of 16 up to 256 is compiled when a model first needs it
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 128, 256)
+
+
 def all_modules() -> list[Module]:
     """Every module of the package (what ``__graft_entry__.build`` compiles)."""
-    return [HOST, KERNELS]
+    from .attention_bf16 import module_for
+
+    return [HOST, KERNELS] + [module_for(d) for d in PREBUILT_HEAD_DIMS]
 
 
 def log(msg: str) -> None:

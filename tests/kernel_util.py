@@ -85,3 +85,21 @@ def reference_attention(q, k, v, q_positions, scale, window=None):
             s = s.masked_fill(~ok, float("-inf"))
             out[i, h] = torch.softmax(s, 0) @ v[:, h // group].float()
     return out
+
+
+def make_context(pb: PagedBatch, logit_rows=None, device="cuda"):
+    """A StepContext built by hand from a PagedBatch (independently of the product's packer)."""
+    from miniserve_b200.engine.context import StepContext
+
+    lr = torch.tensor(logit_rows if logit_rows is not None else [0], dtype=torch.int32, device=device)
+    props = torch.cuda.get_device_properties(0)
+    return StepContext(
+        num_tokens=pb.num_tokens, num_rows=len(pb.rows), num_logit_rows=len(logit_rows or []),
+        stream=torch.cuda.current_stream().cuda_stream, token_ids=None, positions=pb.positions,
+        row_of_token=pb.row_of_token, cu_q=pb.cu_q, q_start=pb.q_start, kv_len=pb.kv_len,
+        state_slot=torch.full((len(pb.rows),), -1, dtype=torch.int32, device=device), logit_rows=lr,
+        page_indptr=[pb.page_indptr], page_indices=[pb.page_indices], status=pb.status,
+        host_q_start=[s for s, _ in pb.rows], host_q_len=[n for _, n in pb.rows],
+        host_state_slot=[-1] * len(pb.rows),
+        max_q_len=max(n for _, n in pb.rows), max_kv_len=max(s + n for s, n in pb.rows),
+        decode_only=all(n == 1 for _, n in pb.rows), sm_count=props.multi_processor_count)

@@ -8,7 +8,8 @@ import pytest
 import torch
 
 from miniserve_b200 import ops
-from tests.kernel_util import PagedBatch, reference_attention
+from miniserve_b200.ops import attention_bf16
+from tests.kernel_util import PagedBatch, make_context, reference_attention
 from tests.plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -154,8 +155,10 @@ def _attention_case(dtype, rows, nq, nkv, d, page, window=None, needle=None, see
         v = torch.randn(s + n, nkv, d, device=DEV).to(dtype)
         q = torch.randn(n, nq, d, device=DEV).to(dtype)
         if needle is not None and s + n > needle:
-            # one far key that the last query must find: its score stands out, and its value is unlike the rest
-            q[-1] = (k[needle, 0] * 4).to(dtype)
+            # one far key that the last query must find: its score (16 * sqrt(d)) stands out from the
+            # others (about +-4 * 3.5), and its value is unlike the rest
+            q[-1] = 4.0
+            k[needle] = 4.0
             v[needle] = 50.0
         pb.fill(r, k, v)
         qs.append(q)
@@ -236,6 +239,59 @@ def test_attention_reports_a_page_that_was_given_back():
     ops.attention_rowwise(out, q, pb.k_pool, pb.v_pool, pb.positions, pb.row_of_token, pb.page_indptr,
                           pb.page_indices, scale, None, pb.status)
     assert pb.status.item() != 0
+
+
+# ------------------------------------------------------------------ bfloat16 tensor-core attention
+BF16_TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nq, nkv, d, page", ATT_SHAPES + [(8, 2, 64, 64), (32, 1, 16, 16)])
+def test_attention_bf16_prompts_and_mixed_steps(nq, nkv, d, page):
+    rows = [(0, 37), (52, 1), (15, 18), (0, 1), (63, 2), (0, 150), (100, 70), (64, 64)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, nq, nkv, d, page)
+    out = torch.full_like(q, float("nan"))
+    attention_bf16.run(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, None)
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 7, 64, 65, 100])
+def test_attention_bf16_prompt_window_edge(window):
+    rows = [(0, 200), (130, 3), (199, 1)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 32, 8, window=window)
+    out = torch.full_like(q, float("nan"))
+    attention_bf16.run(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, window)
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+@pytest.mark.parametrize("nq, nkv, d, page", ATT_SHAPES + [(8, 2, 64, 64), (40, 1, 32, 16)])
+@pytest.mark.parametrize("splits", [None, 1, 7])
+def test_attention_bf16_decode(nq, nkv, d, page, splits, monkeypatch):
+    rows = [(700, 1), (0, 1), (15, 1), (16, 1), (63, 1), (64, 1), (333, 1)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, nq, nkv, d, page, needle=3)
+    if splits is not None:
+        monkeypatch.setattr(attention_bf16, "choose_splits", lambda *a, **k: splits)
+    out = torch.full_like(q, float("nan"))
+    ctx = make_context(pb)
+    assert ctx.decode_only
+    attention_bf16.run(out, q, pb.k_pool, pb.v_pool, ctx, 0, scale, None)
+    assert ref[0, 0].mean().item() > 40  # the far key dominates row 0
+    assert torch.allclose(out.float(), ref, atol=0.3, rtol=2e-2)
+    assert torch.allclose(out.float()[1:3], ref[1:3], **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 16, 17, 100])
+def test_attention_bf16_decode_window_edge(window):
+    rows = [(200, 1), (5, 1), (99, 1), (100, 1)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 6, 2, 48, 8, window=window)
+    out = torch.full_like(q, float("nan"))
+    attention_bf16.run(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, window)
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+def test_attention_bf16_refuses_other_head_sizes():
+    assert not attention_bf16.supports(40, 16) and not attention_bf16.supports(272, 16)
+    with pytest.raises(ValueError):
+        attention_bf16._lib(40)
 
 
 # ------------------------------------------------------------------ sampling

@@ -14,7 +14,7 @@ from miniserve_b200.parts import (BuildEnv, DecoderModel, FixedState, Part, Resi
                                   register_part, unregister_part)
 from miniserve_b200.parts.block import build_block
 from miniserve_b200.weights import random_tensors
-from tests.kernel_util import PagedBatch
+from tests.kernel_util import PagedBatch, make_context
 from tests.plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -22,17 +22,7 @@ DEV = torch.device("cuda")
 DTYPES = [torch.float32, torch.bfloat16]
 
 
-def _ctx(pb: PagedBatch, logit_rows=None) -> StepContext:
-    lr = torch.tensor(logit_rows if logit_rows is not None else [0], dtype=torch.int32, device=DEV)
-    return StepContext(
-        num_tokens=pb.num_tokens, num_rows=len(pb.rows), num_logit_rows=len(logit_rows or []),
-        stream=torch.cuda.current_stream().cuda_stream, token_ids=None, positions=pb.positions,
-        row_of_token=pb.row_of_token, cu_q=pb.cu_q, q_start=pb.q_start, kv_len=pb.kv_len,
-        state_slot=torch.full((len(pb.rows),), -1, dtype=torch.int32, device=DEV), logit_rows=lr,
-        page_indptr=[pb.page_indptr], page_indices=[pb.page_indices], status=pb.status,
-        host_q_start=[s for s, _ in pb.rows], host_q_len=[n for _, n in pb.rows],
-        max_q_len=max(n for _, n in pb.rows), max_kv_len=max(s + n for s, n in pb.rows),
-        decode_only=all(n == 1 for _, n in pb.rows))
+_ctx = make_context
 
 
 def _tol(dtype, scale=1.0):

@@ -89,13 +89,26 @@ def plain_logits(model_dir, sequences: dict[str, list[int]]) -> dict[str, torch.
     return {k: plain.all_logits(cfg, w, ids) for k, ids in sequences.items()}
 
 
-def bfloat16_noise(model_dir, sequences: dict[str, list[int]], expect: dict[str, torch.Tensor]) -> float:
-    """How far the plain implementation itself moves when it is run in bfloat16 instead of
-    float32 on these sequences (the largest logit difference). This is what rounding to
-    bfloat16 costs on this model and these inputs; the engine's bfloat16 path has to stay
-    within it."""
+def bfloat16_noise(model_dir, sequences: dict[str, list[int]], expect: dict[str, torch.Tensor]) -> tuple[float, float]:
+    """How far the plain implementation itself moves when it runs in bfloat16 instead of float32
+    on these sequences: (largest, mean over positions) of the per-position largest logit
+    difference. This is what rounding to bfloat16 costs on this model and these inputs."""
     cfg, w = plain.read_config(model_dir), plain.read_weights(model_dir, torch.bfloat16)
-    return max((plain.all_logits(cfg, w, ids).float() - expect[k]).abs().max().item() for k, ids in sequences.items())
+    errs = torch.cat([(plain.all_logits(cfg, w, ids).float() - expect[k]).abs().max(dim=1).values
+                      for k, ids in sequences.items()])
+    return errs.max().item(), errs.mean().item()
+
+
+def check_bfloat16(errors: torch.Tensor, noise: tuple[float, float], what: str = "") -> None:
+    """``errors``: per position, the engine's largest logit difference from the float32 truth.
+    The engine keeps more in float32 than a plain bfloat16 run does, so on average it must be
+    at least as near to the truth; a single position may be up to twice the plain run's worst
+    (both are the largest of many random rounding errors). A dropped, stale or misplaced key
+    moves logits by the size of the logits themselves, far beyond either bound."""
+    worst, mean = noise
+    assert errors.mean().item() <= mean, f"{what}: mean error {errors.mean().item():.3e} above bfloat16 noise {mean:.3e}"
+    assert errors.max().item() <= 2 * worst, (
+        f"{what}: position {int(errors.argmax())} is off by {errors.max().item():.3e}, bfloat16 noise peaks at {worst:.3e}")
 
 
 def sharpen_attention(model_dir, factor: float = 2.5) -> None:
