@@ -253,6 +253,10 @@ def run_ours(args) -> dict:
     weight_bytes = model.weight_bytes()
     kv_bytes_per_token = eng.cache.bytes_per_token()
 
+    if args.only == "prefill":
+        pre_ms = time_prefill(eng, PREFILL_TOKENS, repeats=max(1, min(args.steps, 5)))
+        return {"impl": "ours", "only": "prefill", "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1),
+                                                                "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4)}}
     sampler = ClockSampler()
     sampler.start()
     ms, launches, mean_ctx = time_decode(eng, args.batch, CONTEXT, args.steps, args.warmup)
@@ -261,6 +265,10 @@ def run_ours(args) -> dict:
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_bytes_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
+    if args.only == "decode":
+        return {"impl": "ours", "only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4),
+                "batch": args.batch, "gpu_launches": int(round(launches * args.steps)), "clocks": clocks,
+                "roofline_frac": round(achieved / peaks["hbm_gbs"], 4)}
     points = {}
     for b in (1, 64):
         pms, _, _ = time_decode(eng, b, CONTEXT, min(args.steps, 128), args.warmup)
@@ -365,6 +373,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:

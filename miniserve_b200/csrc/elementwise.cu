@@ -23,12 +23,13 @@ __global__ void embed_gather_kernel(float* __restrict__ residual, const T* __res
 
 // ---------------------------------------------------------------- (add +) RMSNorm (+ gather)
 // For output row i: r = rows ? rows[i] : i.
-//   h = residual[r] (+ delta[r] if delta)            float32
+//   h = residual[r] (+ delta[r] if delta) (+ parts[0][r] + parts[1][r] + ... in that order)   float32
 //   if (write_residual) residual[r] = h              (only without a gather)
 //   out[i] = h / sqrt(mean(h^2) + eps) * w           rounded once to T
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta,
+                   const float* __restrict__ parts, int num_parts, size_t part_stride,
                    const T* __restrict__ w, const int* __restrict__ rows, float eps, int hidden,
                    int write_residual) {
   extern __shared__ float row_buf[];  // hidden floats
@@ -41,6 +42,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* _
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     float h = res[c];
     if (dl) h += Elem<T>::load(dl + c);
+    for (int p = 0; p < num_parts; ++p) h += parts[p * part_stride + (size_t)r * hidden + c];
     row_buf[c] = h;
     ss += h * h;
   }
@@ -49,7 +51,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* _
   T* o = out + (size_t)i * hidden;
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     const float h = row_buf[c];
-    if (write_residual && dl) res[c] = h;
+    if (write_residual && (dl || num_parts)) res[c] = h;
     Elem<T>::store(o + c, (h * inv) * Elem<T>::load(w + c));
   }
 }
@@ -116,7 +118,11 @@ MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* 
   return 0;
 }
 
-MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, const void* weight, const int* rows,
+// delta: an addend in the activation dtype, or null. parts: float32 partial sums
+// [num_parts][..][hidden] that are `part_stride` floats apart (the split-K output of the skinny
+// matrix product), or null. Both are added to the residual before the norm.
+MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, const float* parts, int num_parts,
+                             long long part_stride, const void* weight, const int* rows,
                              float eps, int num_out_rows, int hidden, int write_residual, int dtype,
                              cudaStream_t stream) {
   if (num_out_rows == 0) return 0;
@@ -128,11 +134,11 @@ MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, c
   if (dtype == MS_F32) {
     auto k = add_rmsnorm_kernel<float, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<num_out_rows, THREADS, smem, stream>>>((float*)out, (float*)residual_f32, (const float*)delta, (const float*)weight, rows, eps, hidden, write_residual);
+    k<<<num_out_rows, THREADS, smem, stream>>>((float*)out, (float*)residual_f32, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
   } else {
     auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<num_out_rows, THREADS, smem, stream>>>((__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    k<<<num_out_rows, THREADS, smem, stream>>>((__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
   }
   MS_CHECK_LAUNCH();
   return 0;

@@ -1,0 +1,176 @@
+// Weight-streaming matrix product for a handful of tokens (decode steps):
+// C[M, N] = X[M, K] * W[N, K]^T with M <= 16, bfloat16 operands, float32 accumulation.
+//
+// At these sizes the product is bound by reading W once from HBM (about M flops per byte), so the
+// kernel is built around the weight stream: a CTA owns 16 rows of W and a slice of K; each of its
+// eight warps streams its part of that slice straight from global memory into tensor-core
+// fragments with 16-byte loads (eight in flight per lane), multiplies it with the matching
+// activations from shared memory, and the warps' partial sums are added in shared memory in a
+// fixed order. With `splits` > 1 the K dimension is also cut across CTAs and each split writes
+// float32 partial sums [splits, M, N]; the consumer (the fused residual-add + RMSNorm kernel) adds
+// them, so narrow outputs (N = hidden) still fill the machine without atomics.
+// Stands where the reference's decode step calls F.linear (miniserve/model/qwen3.py:115-131,186).
+#include "common.cuh"
+
+namespace ms {
+
+constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32, SK_ROWS = 16, SK_UNROLL = 4;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: float32 partials [splits, M, N]
+template <int MT, int MODE>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
+                   int M, int N, int K, int k_per_split) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * SK_ROWS;
+  const int k_begin = blockIdx.y * k_per_split, k_end = min(K, k_begin + k_per_split);
+  const int k_len = k_end - k_begin;
+  const int xs_stride = k_per_split + 32;  // bf16 elements: rows 64 bytes apart modulo 128, so 16-byte reads of two rows do not collide
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+  // this warp's part of the slice, in chunks of 32 k (8 per lane of a quad)
+  const int per_warp = ((k_len + SK_WARPS * 32 - 1) / (SK_WARPS * 32)) * 32;
+  const int wk_begin = warp * per_warp, wk_end = min(k_len, wk_begin + per_warp);
+  const bool row_a = n0 + g < N, row_b = n0 + g + 8 < N;
+  const __nv_bfloat16* wa_ptr = W + (size_t)(n0 + (row_a ? g : 0)) * K + k_begin + 8 * t;
+  const __nv_bfloat16* wb_ptr = W + (size_t)(n0 + (row_b ? g + 8 : 0)) * K + k_begin + 8 * t;
+
+  uint4 wa[SK_UNROLL], wb[SK_UNROLL];
+  auto fetch = [&](int k) {
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int kk = k + 32 * u;
+      const bool in = kk + 8 * t < wk_end;
+      wa[u] = (in && row_a) ? ldg_stream(wa_ptr + kk) : make_uint4(0u, 0u, 0u, 0u);
+      wb[u] = (in && row_b) ? ldg_stream(wb_ptr + kk) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  // the weights do not depend on anything this step computed: start their stream first
+  fetch(wk_begin);
+
+  // activations of this K slice: [MT * 8][k_len], rows past M are zero
+  const int chunks = k_len >> 3;
+  for (int idx = tid; idx < MT * 8 * chunks; idx += SK_THREADS) {
+    const int row = idx / chunks, c = idx - row * chunks;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < M) v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + k_begin + c * 8);
+    *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
+  }
+  __syncthreads();
+
+  float acc[MT][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+  for (int k = wk_begin; k < wk_end; k += 32 * SK_UNROLL) {
+    uint4 ca[SK_UNROLL], cb[SK_UNROLL];
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      ca[u] = wa[u];
+      cb[u] = wb[u];
+    }
+    if (k + 32 * SK_UNROLL < wk_end) fetch(k + 32 * SK_UNROLL);  // next group in flight while this one is used
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int kk = k + 32 * u;
+      if (kk >= wk_end) break;
+      const bool in = kk + 8 * t < wk_end;
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        if (in) xb = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * xs_stride + kk + 8 * t);
+        mma_bf16_16816(acc[j], ca[u].x, cb[u].x, ca[u].y, cb[u].y, xb.x, xb.y);
+        mma_bf16_16816(acc[j], ca[u].z, cb[u].z, ca[u].w, cb[u].w, xb.z, xb.w);
+      }
+    }
+  }
+
+  // add the warps' partial sums in warp order
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(smem_raw);  // [warps][16 rows][MT * 8 tokens]
+  constexpr int TOK = MT * 8;
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    float* base = red + (size_t)warp * SK_ROWS * TOK;
+    base[g * TOK + 8 * j + 2 * t] = acc[j][0];
+    base[g * TOK + 8 * j + 2 * t + 1] = acc[j][1];
+    base[(g + 8) * TOK + 8 * j + 2 * t] = acc[j][2];
+    base[(g + 8) * TOK + 8 * j + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < SK_ROWS * TOK; idx += SK_THREADS) {
+    const int tok = idx / SK_ROWS, row = idx - tok * SK_ROWS;  // consecutive threads: consecutive n
+    if (tok >= M || n0 + row >= N) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < SK_WARPS; ++w) s += red[(size_t)w * SK_ROWS * TOK + row * TOK + tok];
+    const size_t o = (size_t)tok * N + n0 + row;
+    if (MODE == 0) {
+      reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(s);
+    } else if (MODE == 1) {
+      reinterpret_cast<float*>(out)[o] = s;
+    } else {
+      reinterpret_cast<float*>(out)[(size_t)blockIdx.y * M * N + o] = s;
+    }
+  }
+}
+
+template <int MT, int MODE>
+static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, int splits, cudaStream_t stream) {
+  // whole multiples of 8 warps x 32 k per split keep every warp's range aligned
+  int k_per_split = ceil_div(ceil_div(K, splits), 32) * 32;
+  const int used_splits = ceil_div(K, k_per_split);
+  MS_CHECK_ARG(used_splits == splits, "gemm_skinny: %d splits leave some without work (K=%d)", splits, K);
+  const size_t smem_x = (size_t)MT * 8 * (k_per_split + 32) * 2;
+  const size_t smem_red = (size_t)SK_WARPS * SK_ROWS * MT * 8 * 4;
+  const size_t smem = smem_x > smem_red ? smem_x : smem_red;
+  MS_CHECK_ARG(smem <= 200 * 1024, "gemm_skinny: K slice of %d needs %zu bytes of shared memory", k_per_split, smem);
+  auto kernel = gemm_skinny_kernel<MT, MODE>;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(ceil_div(N, SK_ROWS), splits);
+  kernel<<<grid, SK_THREADS, smem, stream>>>(out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split);
+  MS_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+// out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
+MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,
+                                  cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  MS_CHECK_ARG(M > 0 && M <= 16, "gemm_skinny: M=%d is outside 1..16", M);
+  MS_CHECK_ARG(K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a multiple of 8", K);
+  MS_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: operands must be 16-byte aligned");
+  MS_CHECK_ARG(splits >= 1 && (splits == 1 || out_mode == 2), "gemm_skinny: only partial sums can be split over K");
+  MS_CHECK_ARG(out_mode >= 0 && out_mode <= 2, "gemm_skinny: bad output mode %d", out_mode);
+  MS_CHECK_ARG(ceil_div(N, SK_ROWS) <= 2147483647 && splits <= 65535, "gemm_skinny: grid too large");
+  const bool wide = M > 8;
+#define MS_SK(MT, MODE) return launch_skinny<MT, MODE>(out, X, W, M, N, K, splits, stream)
+  if (out_mode == 0) { if (wide) MS_SK(2, 0); else MS_SK(1, 0); }
+  if (out_mode == 1) { if (wide) MS_SK(2, 1); else MS_SK(1, 1); }
+  if (wide) MS_SK(2, 2); else MS_SK(1, 2);
+#undef MS_SK
+}

@@ -192,15 +192,64 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, const 
   if (threadIdx.x == 0) tokens[r] = b.idx == 0x7fffffff ? 0 : b.idx;
 }
 
+// Two-stage selection for rows without a nucleus: stage one takes the best of a stretch of the
+// vocabulary per block (so a few rows still use the whole machine), stage two the best of those.
+__global__ void __launch_bounds__(256)
+sample_partial_kernel(Best* __restrict__ partial, const float* __restrict__ logits,
+                      const float* __restrict__ temperature, const long long* __restrict__ seed,
+                      const long long* __restrict__ counter, int vocab, int per_block) {
+  __shared__ Best scratch[32];
+  const int r = blockIdx.y;
+  const float* lg = logits + (size_t)r * vocab;
+  const float t = temperature ? temperature[r] : 0.f;
+  const int begin = blockIdx.x * per_block, end = min(vocab, begin + per_block);
+  Best b;
+  b.val = -INFINITY;
+  b.idx = 0x7fffffff;
+  if (!(t > 0.f)) {
+    for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+      const float x = lg[v];
+      if (x > b.val) { b.val = x; b.idx = v; }
+    }
+  } else {
+    const uint32_t key = mix32((uint32_t)seed[r] ^ mix32((uint32_t)counter[r]));
+    for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+      const float x = lg[v] / t + gumbel(key, (uint32_t)v);
+      if (x > b.val) { b.val = x; b.idx = v; }
+    }
+  }
+  b = block_best(b, scratch);
+  if (threadIdx.x == 0) partial[(size_t)r * gridDim.x + blockIdx.x] = b;
+}
+
+__global__ void __launch_bounds__(256)
+sample_final_kernel(int* __restrict__ tokens, const Best* __restrict__ partial, int num_partials) {
+  __shared__ Best scratch[32];
+  const int r = blockIdx.x;
+  Best b;
+  b.val = -INFINITY;
+  b.idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < num_partials; i += blockDim.x) b = better(b, partial[(size_t)r * num_partials + i]);
+  b = block_best(b, scratch);
+  if (threadIdx.x == 0) tokens[r] = b.idx == 0x7fffffff ? 0 : b.idx;
+}
+
 }  // namespace ms
 
 using namespace ms;
 
+// Bytes of scratch the two-stage path needs for `rows` rows of `vocab` logits (0: one stage).
+static int partial_blocks(int vocab) { return vocab >= 16384 ? ceil_div(vocab, 4096) : 0; }
+MS_EXPORT long long ms_sample_scratch_bytes(int rows, int vocab) {
+  return (long long)rows * partial_blocks(vocab) * (long long)sizeof(Best);
+}
+
 MS_EXPORT int ms_nucleus_bytes() { return (int)sizeof(Nucleus); }
 
+// partial_scratch: ms_sample_scratch_bytes(rows, vocab) bytes, or null to select in one stage.
 MS_EXPORT int ms_sample(int* tokens, const float* logits, const float* temperature, const float* top_p,
-                        const long long* seed, const long long* counter, void* nucleus_scratch, int rows, int vocab,
-                        cudaStream_t stream) {
+                        const long long* seed, const long long* counter, void* nucleus_scratch, void* partial_scratch,
+                        int rows, int vocab, cudaStream_t stream) {
   if (rows == 0) return 0;
   MS_CHECK_ARG(rows > 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   MS_CHECK_ARG(temperature == nullptr || (seed != nullptr && counter != nullptr), "sample: temperature rows need seeds and counters");
@@ -209,6 +258,15 @@ MS_EXPORT int ms_sample(int* tokens, const float* logits, const float* temperatu
     MS_CHECK_ARG(nucleus_scratch != nullptr && temperature != nullptr, "sample: top_p needs scratch and temperatures");
     nucleus_kernel<<<rows, threads, 0, stream>>>((Nucleus*)nucleus_scratch, logits, temperature, top_p, vocab);
     MS_CHECK_LAUNCH();
+  } else if (partial_scratch != nullptr && partial_blocks(vocab) > 0) {
+    const int nblk = partial_blocks(vocab);
+    MS_CHECK_ARG(rows <= 65535, "sample: too many rows (%d) for one launch", rows);
+    sample_partial_kernel<<<dim3(nblk, rows), 256, 0, stream>>>((Best*)partial_scratch, logits, temperature, seed, counter,
+                                                               vocab, ceil_div(vocab, nblk));
+    MS_CHECK_LAUNCH();
+    sample_final_kernel<<<rows, 256, 0, stream>>>(tokens, (const Best*)partial_scratch, nblk);
+    MS_CHECK_LAUNCH();
+    return 0;
   }
   sample_kernel<<<rows, threads, 0, stream>>>(tokens, logits, temperature, seed, counter,
                                               top_p ? (const Nucleus*)nucleus_scratch : nullptr, vocab);

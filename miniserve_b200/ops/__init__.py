@@ -15,7 +15,7 @@ from . import native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
-    "NativeError", "OutOfBlocks", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
+    "NativeError", "OutOfBlocks", "PartialSums", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
     "qk_norm_rope_kv", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
@@ -59,12 +59,37 @@ def embed_gather(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
                                           dtype_code(table.dtype), _stream(stream)))
 
 
-def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
-                eps: float, rows: torch.Tensor | None = None, num_rows: int | None = None,
+class PartialSums:
+    """The output of a matrix product whose K dimension was cut across CTAs: float32 partial
+    sums ``parts`` [splits, M, N] that the consumer adds up (the fused add + RMSNorm kernel takes
+    them as they are)."""
+
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+        self.parts = parts
+        self.dtype = dtype  # the activation dtype the sum stands for
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    def float(self) -> torch.Tensor:
+        return self.parts.sum(dim=0)
+
+    def materialize(self) -> torch.Tensor:
+        return self.parts.sum(dim=0).to(self.dtype)
+
+
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: "torch.Tensor | PartialSums | None",
+                weight: torch.Tensor, eps: float, rows: torch.Tensor | None = None, num_rows: int | None = None,
                 write_residual: bool = True, stream=None) -> None:
     """out[i] = rmsnorm(residual[r] + delta[r]) * weight with r = rows[i] (or i); the sum is
-    written back to ``residual`` when there is no gather. Statistics in float32."""
-    _check_dev(out, residual, delta, weight, rows)
+    written back to ``residual`` when there is no gather. Statistics in float32. ``delta`` may be
+    a tensor in the activation dtype or the float32 partial sums of a split matrix product."""
+    parts = None
+    if isinstance(delta, PartialSums):
+        parts, delta = delta.parts, None
+        assert parts.dtype == torch.float32 and parts.is_contiguous() and parts.shape[-1] == residual.shape[-1]
+    _check_dev(out, residual, delta, weight, rows, parts)
     assert residual.dtype == torch.float32 and out.dtype == weight.dtype
     assert delta is None or delta.dtype == out.dtype
     hidden = residual.shape[-1]
@@ -73,7 +98,10 @@ def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor |
     if rows is None:
         assert residual.shape[0] >= n
     k = native.kernels()
-    native.kernel_check(k.ms_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(rows),
+    native.kernel_check(k.ms_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(parts),
+                                         0 if parts is None else parts.shape[0],
+                                         0 if parts is None else parts.shape[1] * parts.shape[2],
+                                         _ptr(weight), _ptr(rows),
                                          float(eps), n, hidden, int(write_residual and rows is None),
                                          dtype_code(out.dtype), _stream(stream)))
 
@@ -94,12 +122,45 @@ def to_float(out: torch.Tensor, x: torch.Tensor, stream=None) -> None:
     native.kernel_check(k.ms_to_float(_ptr(out), _ptr(x), x.numel(), dtype_code(x.dtype), _stream(stream)))
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+SKINNY_MAX_M = 16
+_SM_COUNT: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    m, k = x.shape
+    return (0 < m <= SKINNY_MAX_M and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and 16 * (k + 32) * 2 <= 200 * 1024)
+
+
+def skinny_splits(n: int, k: int, sm_count: int) -> int:
+    """K splits for a narrow output: enough CTAs (16 rows of W each) for two per SM, every split
+    at least 256 wide and all of them non-empty."""
+    tiles = -(-n // 16)
+    want = max(1, min(-(-2 * sm_count // tiles), k // 256))
+    while want > 1:
+        per = -(-(-(-k // want)) // 32) * 32
+        if -(-k // per) == want:
+            break
+        want -= 1
+    return want
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None,
+           partials: bool = False) -> "torch.Tensor | PartialSums":
     """x [M, K] times weight[N, K]^T -> [M, N].
 
     float32: this package's FFMA kernel (true 32-bit, fixed summation order per element).
-    bfloat16: the vendor library's matrix product with float32 accumulation; ``out`` may be
-    float32 (logits) or bfloat16.
+    bfloat16 with at most 16 rows (decode steps): this package's weight-streaming kernel; with
+    ``partials`` the result may come back as float32 ``PartialSums`` for a fused consumer.
+    bfloat16 otherwise: the vendor library's matrix product with float32 accumulation. ``out``
+    may be float32 (logits) or bfloat16.
     """
     _check_dev(x, weight, out)
     m, kdim = x.shape
@@ -114,6 +175,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         native.kernel_check(k.ms_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, kdim, kdim, n, _stream(stream)))
         return out
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    if _skinny_ok(x, weight):
+        k = native.kernels()
+        if partials and out is None:
+            splits = skinny_splits(n, kdim, _sm_count(x.device))
+            if splits > 1:
+                parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+                native.kernel_check(k.ms_gemm_skinny_bf16(_ptr(parts), _ptr(x), _ptr(weight), m, n, kdim, splits, 2,
+                                                          _stream(stream)))
+                return PartialSums(parts, torch.bfloat16)
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        assert out.shape == (m, n)
+        native.kernel_check(k.ms_gemm_skinny_bf16(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, 1,
+                                                  1 if out.dtype == torch.float32 else 0, _stream(stream)))
+        return out
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
     if out.dtype == torch.float32:
@@ -185,8 +261,14 @@ def sample(tokens: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor
     if top_p is not None:
         assert top_p.dtype == torch.float32 and scratch is not None and scratch.numel() * scratch.element_size() >= rows * nucleus_bytes()
     k = native.kernels()
+    partial = None
+    if top_p is None:
+        need = k.ms_sample_scratch_bytes(rows, vocab)
+        if need:
+            partial = torch.empty(need, dtype=torch.uint8, device=logits.device)
     native.kernel_check(k.ms_sample(_ptr(tokens), _ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(seed),
-                                    _ptr(counter), _ptr(scratch), rows, vocab, _stream(stream)))
+                                    _ptr(counter), _ptr(scratch), _ptr(partial), rows, vocab, _stream(stream)),
+                        launches=2)
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,

@@ -48,9 +48,11 @@ def _check(fns, rc: int, launches: int = 1) -> None:
 
 
 def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count: int) -> int:
-    """How many ways the keys of each (request, kv head) are split across CTAs: enough for about
-    four waves of two CTAs per SM, but at least 64 keys per split."""
-    want = -(-8 * sm_count // max(rows * head_chunks, 1))
+    """How many ways the keys of each (request, kv head) are split across CTAs: as many as give
+    one wave of two CTAs per SM (measured best on B200: more splits only add partial results to
+    merge, fewer leave SMs idle), but at least 64 keys per split. ``max_kv_len`` None (inside a
+    CUDA graph, where the launch cannot follow the context length): assume a few thousand keys."""
+    want = (2 * sm_count) // max(rows * head_chunks, 1)
     by_len = 64 if max_kv_len is None else max(1, -(-max_kv_len // 64))
     return max(1, min(want, by_len, 128))
 

@@ -73,7 +73,9 @@ class GQAttention(Part):
         self.w_q_norm = tensors["q_norm.weight"].contiguous() if self.qk_norm else None
         self.w_k_norm = tensors["k_norm.weight"].contiguous() if self.qk_norm and self.owns_cache else None
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, cache):
+        """Returns the mixer's addend to the residual stream: a tensor [T, hidden], or float32
+        partial sums of it that the next norm adds up (``ops.PartialSums``)."""
         t = x.shape[0]
         qkv = ops.linear(x, self.w_qkv, stream=ctx.stream)
         q = torch.empty((t, self.heads, self.head_dim), dtype=x.dtype, device=x.device)
@@ -85,4 +87,4 @@ class GQAttention(Part):
             ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream)
         out = torch.empty_like(q)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
-        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream)
+        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=True)

@@ -34,4 +34,4 @@ class SwiGLU(Part):
         gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         ops.silu_mul(act, gate_up, stream=ctx.stream)
-        return ops.linear(act, self.w_down, stream=ctx.stream)
+        return ops.linear(act, self.w_down, stream=ctx.stream, partials=True)

@@ -95,6 +95,47 @@ def test_bf16_linear_accumulates_in_float32():
     assert torch.allclose(ops.linear(a, w).float(), expect, atol=0.3, rtol=2e-2)
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n, k", [(16, 32), (503, 96), (1000, 1024), (72, 3080), (151936, 64)])
+def test_skinny_gemm_bf16(m, n, k):
+    torch.manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = torch.randn(n, k, device=DEV).bfloat16()
+    expect = x.float() @ w.float().T
+    tol = dict(atol=2e-3 * (k ** 0.5), rtol=2e-3)
+    out32 = torch.full((m, n), float("nan"), device=DEV)
+    ops.linear(x, w, out=out32)
+    assert torch.allclose(out32, expect, **tol)
+    out16 = ops.linear(x, w)
+    assert out16.dtype == torch.bfloat16 and torch.allclose(out16.float(), expect, atol=0.05 * (k ** 0.5), rtol=2e-2)
+    parts = ops.linear(x, w, partials=True)
+    if isinstance(parts, ops.PartialSums):
+        assert parts.parts.shape[0] > 1 and parts.parts.shape[1:] == (m, n)
+        assert torch.allclose(parts.float(), expect, **tol)
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, n, device=DEV)
+    ops.linear(x[m - 1:m].contiguous(), w, out=alone)
+    assert torch.equal(alone[0], out32[m - 1])
+
+
+def test_add_rmsnorm_takes_partial_sums():
+    hidden, rows, eps = 1000, 5, 1e-6
+    res = torch.randn(rows, hidden, device=DEV)
+    parts = torch.randn(3, rows, hidden, device=DEV)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).bfloat16()
+    total = res + parts[0] + parts[1] + parts[2]
+    expect = total * torch.rsqrt((total * total).mean(-1, keepdim=True) + eps) * w.float()
+    out = torch.empty(rows, hidden, device=DEV, dtype=torch.bfloat16)
+    got = res.clone()
+    ops.add_rmsnorm(out, got, ops.PartialSums(parts, torch.bfloat16), w, eps)
+    assert torch.allclose(got, total, atol=1e-6) and torch.allclose(out.float(), expect, atol=2e-2, rtol=2e-2)
+    idx = torch.tensor([4, 1], device=DEV, dtype=torch.int32)
+    out2 = torch.empty(2, hidden, device=DEV, dtype=torch.bfloat16)
+    keep = res.clone()
+    ops.add_rmsnorm(out2, keep, ops.PartialSums(parts, torch.bfloat16), w, eps, rows=idx)
+    assert torch.equal(keep, res) and torch.allclose(out2.float(), expect[idx.long()], atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq, nkv, d, page, theta, eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 1, 48, 8, 1e6, 1e-5),
                                                         (3, 3, 80, 4, 5e5, 1e-6), (2, 1, 256, 32, 1e6, 1e-6)])
