@@ -311,7 +311,22 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   auto issue = [&](int i) {
     if (i < my_count) {
       __nv_bfloat16* st = pipe + (i % DC_STAGES) * DecodeSmem::stage_elems;
-      load_kv_tile<DC_SLICE, 32>(st, st + DC_SLICE * DPAD, kv, (my_first + i * DC_WARPS) * DC_SLICE, lo, kv_len, lane);
+      const int key0 = (my_first + i * DC_WARPS) * DC_SLICE;
+      if (page_shift >= 4) {
+        // pages of at least 16 tokens: the whole slice lies in one page, one lookup per slice
+        const int page = kv.pages[key0 >> page_shift];
+        const size_t base = ((((size_t)max(page, 0) * nkv + kvh) << page_shift) + (key0 & ((1 << page_shift) - 1))) * D;
+#pragma unroll
+        for (int it = 0; it < DC_SLICE * CHUNKS / 32; ++it) {
+          const int idx = it * 32 + lane, row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+          const bool valid = key0 + row >= lo && key0 + row < kv_len;
+          const size_t off = valid ? base + row * D + chunk * 8 : 0;
+          cp_async16(st + row * DPAD + chunk * 8, kv.k + off, valid);
+          cp_async16(st + (DC_SLICE + row) * DPAD + chunk * 8, kv.v + off, valid);
+        }
+      } else {
+        load_kv_tile<DC_SLICE, 32>(st, st + DC_SLICE * DPAD, kv, key0, lo, kv_len, lane);
+      }
     }
     cp_async_commit();
   };
@@ -370,12 +385,17 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     a[1] = pack_bf16(s[0][2], s[0][3]);
     a[2] = pack_bf16(s[1][0], s[1][1]);
     a[3] = pack_bf16(s[1][2], s[1][3]);
+    // the running maximum rarely moves after the first slices: rescale only when it did
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+      for (int dt = 0; dt < DTILES; ++dt) {
+        o[dt][0] *= alpha[0]; o[dt][1] *= alpha[0]; o[dt][2] *= alpha[1]; o[dt][3] *= alpha[1];
+      }
+    }
 #pragma unroll
     for (int dp = 0; dp < DTILES / 2; ++dp) {
       uint32_t b[4];
       ldmatrix_x4_trans(b, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * DPAD + dp * 16 + (lane >> 4) * 8);
-      o[2 * dp][0] *= alpha[0]; o[2 * dp][1] *= alpha[0]; o[2 * dp][2] *= alpha[1]; o[2 * dp][3] *= alpha[1];
-      o[2 * dp + 1][0] *= alpha[0]; o[2 * dp + 1][1] *= alpha[0]; o[2 * dp + 1][2] *= alpha[1]; o[2 * dp + 1][3] *= alpha[1];
       mma_bf16(o[2 * dp], a, b[0], b[1]);
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
