@@ -103,6 +103,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                     const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
                     int page_shift) {
+  pdl_prologue();
   const int r = blockIdx.y, head = blockIdx.z;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
   const int m0 = blockIdx.x * PF_BM;
@@ -266,6 +267,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
                    float scale_log2, int window, int page_shift, int num_splits) {
+  pdl_prologue();
   const int split = blockIdx.x, r = blockIdx.y;
   const int group = nq / nkv, chunks_per_group = (group + 15) / 16;
   const int kvh = blockIdx.z / chunks_per_group, head0 = kvh * group + (blockIdx.z % chunks_per_group) * 16;
@@ -451,6 +453,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, int num_splits) {
+  pdl_prologue();
   const size_t item = blockIdx.x;  // r * nq + head
   const float* ml = part_ml + item * num_splits * 2;
   float m = -INFINITY;
@@ -476,6 +479,7 @@ using namespace ms;
 #define MS_ATTN_FN(name) MS_CAT(MS_CAT(MS_CAT(ms_attn_bf16_d, MS_HEAD_DIM), _), name)
 
 MS_DEFINE_LAST_ERROR(MS_ATTN_FN(last_error))
+MS_DEFINE_PDL_SWITCH(MS_ATTN_FN(set_pdl))
 
 MS_EXPORT int MS_ATTN_FN(head_dim)() { return D; }
 
@@ -500,7 +504,7 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
     configured = true;
   }
   dim3 grid(ceil_div(max_q_len, PF_BM), num_rows, nq);
-  attn_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
+  MS_LAUNCH(attn_prefill_kernel, grid, PF_THREADS, smem, stream,
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
       q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, shift_of(page_size));
   MS_CHECK_LAUNCH();
@@ -525,15 +529,13 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
     configured = true;
   }
   dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
-  attn_decode_kernel<<<grid, DC_THREADS, DecodeSmem::bytes, stream>>>(
+  MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
       (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
       (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
       shift_of(page_size), num_splits);
-  MS_CHECK_LAUNCH();
   if (num_splits > 1) {
-    attn_decode_merge_kernel<<<num_rows * nq, D >= 128 ? 128 : 64, 0, stream>>>((__nv_bfloat16*)out, (const float*)part_o,
-                                                                               (const float*)part_ml, num_splits);
-    MS_CHECK_LAUNCH();
+    MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
+              (const float*)part_o, (const float*)part_ml, num_splits);
   }
   return 0;
 }

@@ -31,6 +31,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          int num_tokens, int nq, int nkv, int d, float scale, int window, int page_shift,
                          int* __restrict__ status) {
   extern __shared__ float q_smem[];  // [warps][d]
+  pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
   if (item >= (long long)num_tokens * nq) return;
@@ -116,14 +117,13 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   if (dtype == MS_F32)
-    attention_rowwise_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+    MS_LAUNCH(attention_rowwise_kernel<float>, blocks, warps * 32, smem, stream,
         (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, row_of_token, page_indptr,
         page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift, status);
   else
-    attention_rowwise_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+    MS_LAUNCH(attention_rowwise_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream,
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift,
         status);
-  MS_CHECK_LAUNCH();
   return 0;
 }

@@ -74,6 +74,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* MAX_WARPS 
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// ---- programmatic dependent launch
+// Every kernel of this package starts with pdl_prologue(): it lets the next kernel in the stream
+// begin launching (its CTAs become resident and may fetch what does not depend on earlier
+// kernels, i.e. weights), then waits until everything launched before it has completed and is
+// visible. Because every kernel waits before it touches activations or the cache, completion
+// order stays the launch order and no kernel reads or overwrites data too early. Launched
+// without the attribute (or when the switch below is off) both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+inline int& pdl_switch() {
+  static int on = 1;
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_switch() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace ms
 
 #include <cstdarg>
@@ -91,3 +126,8 @@ enum MsDtype : int { MS_F32 = 0, MS_BF16 = 1 };
 #define MS_EXPORT extern "C" __attribute__((visibility("default")))
 #define MS_DEFINE_LAST_ERROR(name) \
   MS_EXPORT const char* name() { return ::ms::error_buffer(); }
+// The per-library switch for programmatic dependent launch (1: on, the default).
+#define MS_DEFINE_PDL_SWITCH(name) \
+  MS_EXPORT void name(int on) { ::ms::pdl_switch() = on; }
+#define MS_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  MS_CHECK_CUDA(::ms::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__))

@@ -13,6 +13,7 @@ namespace ms {
 template <typename T>
 __global__ void embed_gather_kernel(float* __restrict__ residual, const T* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab) {
+  pdl_prologue();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; stay in bounds anyway
@@ -34,6 +35,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* _
                    int write_residual) {
   extern __shared__ float row_buf[];  // hidden floats
   __shared__ float red[32];
+  pdl_prologue();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* res = residual + (size_t)r * hidden;
@@ -59,6 +61,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* _
 // ---------------------------------------------------------------- SiLU(gate) * up
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  pdl_prologue();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / inter;
@@ -72,6 +75,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
 // bfloat16, 8 elements per thread (inter % 8 == 0)
 __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
                                        int inter8, size_t total8) {
+  pdl_prologue();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const size_t t = idx / inter8;
@@ -97,6 +101,7 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
 // ---------------------------------------------------------------- float32 <- T copy (logits of a bf16 GEMM)
 template <typename T>
 __global__ void to_float_kernel(float* __restrict__ out, const T* __restrict__ in, size_t n) {
+  pdl_prologue();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = Elem<T>::load(in + i);
 }
@@ -111,10 +116,9 @@ MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* 
   MS_CHECK_ARG(tokens > 0 && hidden > 0 && vocab > 0, "embed_gather: bad sizes T=%d H=%d V=%d", tokens, hidden, vocab);
   const int threads = hidden >= 256 ? 256 : 64;
   if (dtype == MS_F32)
-    embed_gather_kernel<float><<<tokens, threads, 0, stream>>>((float*)residual_f32, (const float*)table, ids, hidden, vocab);
+    MS_LAUNCH(embed_gather_kernel<float>, tokens, threads, 0, stream, (float*)residual_f32, (const float*)table, ids, hidden, vocab);
   else
-    embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((float*)residual_f32, (const __nv_bfloat16*)table, ids, hidden, vocab);
-  MS_CHECK_LAUNCH();
+    MS_LAUNCH(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (float*)residual_f32, (const __nv_bfloat16*)table, ids, hidden, vocab);
   return 0;
 }
 
@@ -134,13 +138,12 @@ MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, c
   if (dtype == MS_F32) {
     auto k = add_rmsnorm_kernel<float, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<num_out_rows, THREADS, smem, stream>>>((float*)out, (float*)residual_f32, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
   } else {
     auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<num_out_rows, THREADS, smem, stream>>>((__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
   }
-  MS_CHECK_LAUNCH();
   return 0;
 }
 
@@ -149,23 +152,21 @@ MS_EXPORT int ms_silu_mul(void* out, const void* gate_up, int tokens, int inter,
   MS_CHECK_ARG(tokens > 0 && inter > 0, "silu_mul: bad sizes T=%d I=%d", tokens, inter);
   const size_t total = (size_t)tokens * inter;
   if (dtype == MS_F32) {
-    silu_mul_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+    MS_LAUNCH(silu_mul_kernel<float>, (unsigned)((total + 255) / 256), 256, 0, stream, (float*)out, (const float*)gate_up, inter, total);
   } else if (inter % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)gate_up % 16 == 0)) {
     const size_t total8 = total / 8;
-    silu_mul_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter / 8, total8);
+    MS_LAUNCH(silu_mul_bf16x8_kernel, (unsigned)((total8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter / 8, total8);
   } else {
-    silu_mul_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, total);
+    MS_LAUNCH(silu_mul_kernel<__nv_bfloat16>, (unsigned)((total + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, total);
   }
-  MS_CHECK_LAUNCH();
   return 0;
 }
 
 MS_EXPORT int ms_to_float(void* out_f32, const void* in, long long n, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (dtype == MS_F32)
-    to_float_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((float*)out_f32, (const float*)in, (size_t)n);
+    MS_LAUNCH(to_float_kernel<float>, (unsigned)((n + 255) / 256), 256, 0, stream, (float*)out_f32, (const float*)in, (size_t)n);
   else
-    to_float_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((float*)out_f32, (const __nv_bfloat16*)in, (size_t)n);
-  MS_CHECK_LAUNCH();
+    MS_LAUNCH(to_float_kernel<__nv_bfloat16>, (unsigned)((n + 255) / 256), 256, 0, stream, (float*)out_f32, (const __nv_bfloat16*)in, (size_t)n);
   return 0;
 }

@@ -14,6 +14,7 @@ gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float*
                 int lda, int ldw, int ldc) {
   __shared__ float As[GBK][GBM + 4];
   __shared__ float Ws[GBK][GBN + 4];
+  pdl_prologue();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each 4 x 4 outputs
@@ -72,7 +73,6 @@ MS_EXPORT int ms_gemm_f32(float* C, const float* A, const float* W, int M, int N
   MS_CHECK_ARG(lda >= K && ldw >= K && ldc >= N, "gemm_f32: leading dimensions too small");
   dim3 grid(ceil_div(N, GBN), ceil_div(M, GBM));
   MS_CHECK_ARG(grid.y <= 65535, "gemm_f32: M=%d too large for one launch", M);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(C, A, W, M, N, K, lda, ldw, ldc);
-  MS_CHECK_LAUNCH();
+  MS_LAUNCH(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
   return 0;
 }

@@ -61,8 +61,11 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
       wb[u] = (in && row_b) ? ldg_stream(wb_ptr + kk) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  // the weights do not depend on anything this step computed: start their stream first
+  // the weights do not depend on anything this step computed: their stream starts before the
+  // wait for the kernels launched earlier (which produce X)
+  pdl_launch_dependents();
   fetch(wk_begin);
+  pdl_wait();
 
   // activations of this K slice: [MT * 8][k_len], rows past M are zero
   const int chunks = k_len >> 3;
@@ -148,8 +151,7 @@ static int launch_skinny(void* out, const void* X, const void* W, int M, int N, 
     configured = smem;
   }
   dim3 grid(ceil_div(N, SK_ROWS), splits);
-  kernel<<<grid, SK_THREADS, smem, stream>>>(out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split);
-  MS_CHECK_LAUNCH();
+  MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split);
   return 0;
 }
 

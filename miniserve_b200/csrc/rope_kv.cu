@@ -26,6 +26,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const int* __restrict__ positions, const int* __restrict__ row_of_token,
     const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
     int num_tokens, int nq, int nkv, int d, int rot, float eps, int page_shift, int* __restrict__ status) {
+  pdl_prologue();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = nq + (k_pool ? 2 * nkv : 0);
@@ -121,15 +122,14 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   if (dtype == MS_F32)
-    qk_norm_rope_kv_kernel<float><<<blocks, warps * 32, 0, stream>>>(
+    MS_LAUNCH(qk_norm_rope_kv_kernel<float>, blocks, warps * 32, 0, stream,
         (float*)q_out, (float*)k_pool, (float*)v_pool, (const float*)qkv, (const float*)q_norm_w, (const float*)k_norm_w,
         inv_freq, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps,
         page_shift, status);
   else
-    qk_norm_rope_kv_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
+    MS_LAUNCH(qk_norm_rope_kv_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv,
         (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, inv_freq, positions, row_of_token, page_indptr,
         page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps, page_shift, status);
-  MS_CHECK_LAUNCH();
   return 0;
 }

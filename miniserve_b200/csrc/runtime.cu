@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 MS_DEFINE_LAST_ERROR(ms_kernels_last_error)
+MS_DEFINE_PDL_SWITCH(ms_kernels_set_pdl)
 
 MS_EXPORT int ms_device_sm_count(int device, int* out) {
   MS_CHECK_CUDA(cudaDeviceGetAttribute(out, cudaDevAttrMultiProcessorCount, device));

@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(1024)
 nucleus_kernel(Nucleus* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ temperature,
                const float* __restrict__ top_p, int vocab) {
   __shared__ float red[32];
+  pdl_prologue();
   const int r = blockIdx.x;
   const float t = temperature[r], tp = top_p[r];
   Nucleus n;
@@ -131,6 +132,7 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, const 
               const Nucleus* __restrict__ nucleus, int vocab) {
   __shared__ Best scratch[32];
   __shared__ int tie_base[33];
+  pdl_prologue();
   const int r = blockIdx.x;
   const float* lg = logits + (size_t)r * vocab;
   const float t = temperature ? temperature[r] : 0.f;
@@ -199,6 +201,7 @@ sample_partial_kernel(Best* __restrict__ partial, const float* __restrict__ logi
                       const float* __restrict__ temperature, const long long* __restrict__ seed,
                       const long long* __restrict__ counter, int vocab, int per_block) {
   __shared__ Best scratch[32];
+  pdl_prologue();
   const int r = blockIdx.y;
   const float* lg = logits + (size_t)r * vocab;
   const float t = temperature ? temperature[r] : 0.f;
@@ -225,6 +228,7 @@ sample_partial_kernel(Best* __restrict__ partial, const float* __restrict__ logi
 __global__ void __launch_bounds__(256)
 sample_final_kernel(int* __restrict__ tokens, const Best* __restrict__ partial, int num_partials) {
   __shared__ Best scratch[32];
+  pdl_prologue();
   const int r = blockIdx.x;
   Best b;
   b.val = -INFINITY;
@@ -256,20 +260,16 @@ MS_EXPORT int ms_sample(int* tokens, const float* logits, const float* temperatu
   const int threads = vocab >= 8192 ? 1024 : 256;
   if (top_p != nullptr) {
     MS_CHECK_ARG(nucleus_scratch != nullptr && temperature != nullptr, "sample: top_p needs scratch and temperatures");
-    nucleus_kernel<<<rows, threads, 0, stream>>>((Nucleus*)nucleus_scratch, logits, temperature, top_p, vocab);
-    MS_CHECK_LAUNCH();
+    MS_LAUNCH(nucleus_kernel, rows, threads, 0, stream, (Nucleus*)nucleus_scratch, logits, temperature, top_p, vocab);
   } else if (partial_scratch != nullptr && partial_blocks(vocab) > 0) {
     const int nblk = partial_blocks(vocab);
     MS_CHECK_ARG(rows <= 65535, "sample: too many rows (%d) for one launch", rows);
-    sample_partial_kernel<<<dim3(nblk, rows), 256, 0, stream>>>((Best*)partial_scratch, logits, temperature, seed, counter,
-                                                               vocab, ceil_div(vocab, nblk));
-    MS_CHECK_LAUNCH();
-    sample_final_kernel<<<rows, 256, 0, stream>>>(tokens, (const Best*)partial_scratch, nblk);
-    MS_CHECK_LAUNCH();
+    MS_LAUNCH(sample_partial_kernel, dim3(nblk, rows), 256, 0, stream, (Best*)partial_scratch, logits, temperature, seed,
+              counter, vocab, ceil_div(vocab, nblk));
+    MS_LAUNCH(sample_final_kernel, rows, 256, 0, stream, tokens, (const Best*)partial_scratch, nblk);
     return 0;
   }
-  sample_kernel<<<rows, threads, 0, stream>>>(tokens, logits, temperature, seed, counter,
-                                              top_p ? (const Nucleus*)nucleus_scratch : nullptr, vocab);
-  MS_CHECK_LAUNCH();
+  MS_LAUNCH(sample_kernel, rows, threads, 0, stream, tokens, logits, temperature, seed, counter,
+            top_p ? (const Nucleus*)nucleus_scratch : (const Nucleus*)nullptr, vocab);
   return 0;
 }

@@ -37,6 +37,9 @@ def _lib(head_dim: int):
         fn = getattr(lib, pre + name)
         fn.argtypes, fn.restype = args, res
         fns[name] = fn
+    set_pdl = getattr(lib, pre + "set_pdl")
+    set_pdl.argtypes, set_pdl.restype = [c_int], None
+    set_pdl(int(native.pdl_enabled()))
     fns["lib"] = lib
     return fns
 

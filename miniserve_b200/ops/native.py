@@ -18,6 +18,14 @@ _ll = c_longlong
 _f = c_float
 
 
+def pdl_enabled() -> bool:
+    """Programmatic dependent launch (a kernel's CTAs become resident while the kernel before it
+    drains) is on unless MINISERVE_PDL=0."""
+    import os
+
+    return os.environ.get("MINISERVE_PDL", "1") != "0"
+
+
 class NativeError(RuntimeError):
     pass
 
@@ -81,6 +89,8 @@ def host_check(rc: int) -> None:
 def kernels():
     lib = ctypes.CDLL(str(build.ensure_built(build.KERNELS)))
     _declare(lib, "ms_kernels_last_error", [], c_char_p)
+    _declare(lib, "ms_kernels_set_pdl", [_i], None)
+    lib.ms_kernels_set_pdl(int(pdl_enabled()))
     _declare(lib, "ms_device_sm_count", [_i, POINTER(c_int)])
     _declare(lib, "ms_device_arch", [_i, POINTER(c_int), POINTER(c_int)])
     _declare(lib, "ms_embed_gather", [_p, _p, _p, _i, _i, _i, _i, _p])
