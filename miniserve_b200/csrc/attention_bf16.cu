@@ -539,3 +539,54 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
   }
   return 0;
 }
+
+// ------------------------------------------------------------------ decode without allocation
+// See attention_noalloc.h: the same computation as the decode entry point above, with the
+// split-K scratch in a file-scope device array instead of caller-provided memory.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[MS_ATTN_NOALLOC_SCRATCH_FLOATS];
+
+// Device address of g_noalloc_scratch per device. In host code the array's name is only a
+// stand-in for the symbol, not a device pointer, so the address is looked up once per device
+// (with that device current) and passed to the kernels as an ordinary argument.
+static int noalloc_scratch_address(float** out) {
+  constexpr int MAX_DEVICES = 64;
+  static float* address[MAX_DEVICES] = {};
+  int device = 0;
+  MS_CHECK_CUDA(cudaGetDevice(&device));
+  MS_CHECK_ARG(device >= 0 && device < MAX_DEVICES, "decode_noalloc: device index %d is not supported", device);
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    MS_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    MS_CHECK_ARG(ptr != nullptr, "decode_noalloc: the scratch array has no device address");
+    address[device] = static_cast<float*>(ptr);
+  }
+  *out = address[device];
+  return 0;
+}
+
+MS_EXPORT int MS_ATTN_FN(decode_noalloc)(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                         const int* kv_len, const int* page_indptr, const int* page_indices,
+                                         int num_rows, int nq, int nkv, float scale, int window, int page_size,
+                                         int num_splits, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  MS_CHECK_ARG(num_rows > 0 && nq > 0 && num_splits >= 1, "decode_noalloc: bad sizes rows=%d heads=%d splits=%d", num_rows, nq,
+               num_splits);
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  if (num_splits > 1) {
+    const long long items = (long long)num_rows * nq * num_splits;
+    const long long need = items * (D + 2);
+    MS_CHECK_ARG(need <= (long long)MS_ATTN_NOALLOC_SCRATCH_FLOATS,
+                 "decode_noalloc: rows * heads * splits * (D + 2) = %lld floats of scratch, the built-in array holds %d; "
+                 "use fewer splits or rows, or the allocating entry point",
+                 need, MS_ATTN_NOALLOC_SCRATCH_FLOATS);
+    float* base = nullptr;
+    if (int rc = noalloc_scratch_address(&base)) return rc;
+    part_o = base;               // [rows, heads, splits, D]
+    part_ml = base + items * D;  // [rows, heads, splits, 2]
+  }
+  return MS_ATTN_FN(decode)(out, part_o, part_ml, q, k_pool, v_pool, kv_len, page_indptr, page_indices, num_rows, nq, nkv,
+                            scale, window, page_size, num_splits, stream);
+}
