@@ -23,6 +23,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const T* __restrict__ q_norm_w,   // [d] or null (no q/k norm)
     const T* __restrict__ k_norm_w,
     const float* __restrict__ inv_freq,  // [rot/2] or null (no rotation)
+    const float* __restrict__ cos_sin,   // [T, rot]: cos then sin of every (token, pair), or null (computed here)
     const int* __restrict__ positions, const int* __restrict__ row_of_token,
     const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
     int num_tokens, int nq, int nkv, int d, int rot, float eps, int page_shift, int* __restrict__ status) {
@@ -82,9 +83,13 @@ __global__ void qk_norm_rope_kv_kernel(
       hi = (hi * inv) * Elem<T>::load(nw + j + half);
     }
     if (rotate) {
-      const float ang = (float)pos * inv_freq[j];
       float sn, cs;
-      sincosf(ang, &sn, &cs);
+      if (cos_sin) {
+        cs = cos_sin[(size_t)t * rot + j];
+        sn = cos_sin[(size_t)t * rot + half + j];
+      } else {
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+      }
       const float olo = lo * cs - hi * sn;
       const float ohi = hi * cs + lo * sn;
       lo = olo;
@@ -101,12 +106,37 @@ __global__ void qk_norm_rope_kv_kernel(
   }
 }
 
+// cos and sin of every (token, rotation pair) of a step: table[t, j] = cos(pos_t * inv_freq_j),
+// table[t, rot/2 + j] = sin(...). Made once per step and read by every layer's q/k kernel.
+__global__ void rope_table_kernel(float* __restrict__ table, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int num_tokens, int rot) {
+  pdl_prologue();
+  const int half = rot >> 1;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)num_tokens * half) return;
+  const int t = (int)(idx / half), j = (int)(idx - (long long)t * half);
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+  table[(size_t)t * rot + j] = cs;
+  table[(size_t)t * rot + half + j] = sn;
+}
+
 }  // namespace ms
 
 using namespace ms;
 
+MS_EXPORT int ms_rope_table(float* table, const int* positions, const float* inv_freq, int num_tokens, int rotary_dim,
+                            cudaStream_t stream) {
+  if (num_tokens == 0 || rotary_dim == 0) return 0;
+  MS_CHECK_ARG(rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table: rotary_dim=%d must be even", rotary_dim);
+  const long long items = (long long)num_tokens * (rotary_dim / 2);
+  MS_LAUNCH(rope_table_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, table, positions, inv_freq, num_tokens,
+            rotary_dim);
+  return 0;
+}
+
 MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const void* qkv, const void* q_norm_w,
-                                 const void* k_norm_w, const float* inv_freq, const int* positions,
+                                 const void* k_norm_w, const float* inv_freq, const float* cos_sin, const int* positions,
                                  const int* row_of_token, const int* page_indptr, const int* page_indices,
                                  int num_tokens, int nq, int nkv, int head_dim, int rotary_dim, float eps,
                                  int page_size, int* status, int dtype, cudaStream_t stream) {
@@ -124,12 +154,12 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
   if (dtype == MS_F32)
     MS_LAUNCH(qk_norm_rope_kv_kernel<float>, blocks, warps * 32, 0, stream,
         (float*)q_out, (float*)k_pool, (float*)v_pool, (const float*)qkv, (const float*)q_norm_w, (const float*)k_norm_w,
-        inv_freq, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps,
+        inv_freq, cos_sin, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps,
         page_shift, status);
   else
     MS_LAUNCH(qk_norm_rope_kv_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv,
-        (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, inv_freq, positions, row_of_token, page_indptr,
+        (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, inv_freq, cos_sin, positions, row_of_token, page_indptr,
         page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps, page_shift, status);
   return 0;
 }

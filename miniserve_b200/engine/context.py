@@ -41,4 +41,5 @@ class StepContext:
     decode_only: bool = False
     sm_count: int = 148
     scratch: dict = field(default_factory=dict)  # per-step or persistent scratch buffers of kernels
+    step_cache: dict = field(default_factory=dict)  # what parts compute once per step and share (e.g. the rotation table)
     graph_bucket: int = 0  # > 0 while a CUDA graph for this padded batch size is captured or replayed

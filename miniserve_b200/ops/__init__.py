@@ -16,7 +16,7 @@ from .native import NativeError, OutOfBlocks
 
 __all__ = [
     "NativeError", "OutOfBlocks", "PartialSums", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
-    "qk_norm_rope_kv", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
+    "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -203,7 +203,7 @@ def qk_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: to
                     qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None,
                     inv_freq: torch.Tensor | None, rotary_dim: int, eps: float, positions: torch.Tensor,
                     row_of_token: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor,
-                    page_size: int, status: torch.Tensor, stream=None) -> None:
+                    page_size: int, status: torch.Tensor, stream=None, cos_sin: torch.Tensor | None = None) -> None:
     """Per-head norm of q and k, rotation by position, q written to ``q_out`` [T, nq, d] and the
     new k, v written into their pages. ``k_pool``/``v_pool``: [pages, nkv, page_size, d], or None
     when this entry only reads another entry's cache (then ``qkv`` holds q alone)."""
@@ -219,12 +219,22 @@ def qk_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: to
         nkv = 1
         assert qkv.shape == (t, nq * d)
     assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2)
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (t, rotary_dim) and cos_sin.is_contiguous())
     k = native.kernels()
     native.kernel_check(k.ms_qk_norm_rope_kv(
         _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
-        _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, d,
+        _ptr(cos_sin if inv_freq is not None else None), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, d,
         rotary_dim if inv_freq is not None else 0, float(eps), page_size, _ptr(status), dtype_code(qkv.dtype),
         _stream(stream)))
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, num_tokens: int, rotary_dim: int, stream=None) -> torch.Tensor:
+    """float32 [T, rotary_dim]: cos then sin of position * inv_freq for every token of a step."""
+    table = torch.empty((num_tokens, rotary_dim), dtype=torch.float32, device=inv_freq.device)
+    k = native.kernels()
+    native.kernel_check(k.ms_rope_table(_ptr(table), _ptr(positions), _ptr(inv_freq), num_tokens, rotary_dim,
+                                        _stream(stream)))
+    return table
 
 
 def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -84,7 +84,8 @@ class GQAttention(Part):
         ops.qk_norm_rope_kv(
             q, cache.k if self.owns_cache else None, cache.v if self.owns_cache else None, qkv,
             self.w_q_norm, self.w_k_norm, inv_freq, rotary_dim, self.qk_norm_eps, ctx.positions,
-            ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream)
+            ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream,
+            cos_sin=self.position.step_table(ctx))
         out = torch.empty_like(q)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
         return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=True)

@@ -9,7 +9,7 @@ checkpoint tensors it wants by name relative to its own prefix, receives them in
 Categories and what each must provide:
 
 ``norm``          ``forward(residual, delta, ctx, rows=None, write_residual=True) -> Tensor``
-``position``      ``kernel_table() -> (inv_freq | None, rotary_dim)``
+``position``      ``kernel_table() -> (inv_freq | None, rotary_dim)``, ``step_table(ctx) -> cos/sin table | None``
 ``mixer``         ``cache_need() -> CacheNeed | None`` and ``forward(x, ctx, cache) -> Tensor``
 ``feed_forward``  ``forward(x, ctx) -> Tensor``
 ``block``         ``forward(stream, ctx, cache) -> ResidualStream`` (arranges the four above)

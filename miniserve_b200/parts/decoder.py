@@ -106,6 +106,7 @@ class DecoderModel:
         of run entry i. Returns float32 logits at ``ctx.logit_rows``: [wanted, vocab]."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet (bind() was not called)")
+        ctx.step_cache.clear()  # what parts share within one pass is made anew by every pass
         stream = ResidualStream(self.embedding.forward(ctx))
         for i, entry in enumerate(self.spec.run_order):
             stream = self.layers[entry.layer].forward(stream, ctx, caches[i])

@@ -27,6 +27,19 @@ class RotaryNeox(Part):
     def kernel_table(self) -> tuple[torch.Tensor | None, int]:
         return self.inv_freq, self.rotary_dim
 
+    def step_table(self, ctx) -> torch.Tensor | None:
+        """cos/sin of every token of this step, made once per step and shared by all layers
+        whose encoding has the same frequencies (the reference's fused path keeps the same
+        float32 table, miniserve/model/fused.py:183-184)."""
+        from .. import ops
+
+        key = ("rope_table", self.theta, self.rotary_dim)
+        table = ctx.step_cache.get(key)
+        if table is None:
+            table = ops.rope_table(ctx.positions, self.inv_freq, ctx.num_tokens, self.rotary_dim, stream=ctx.stream)
+            ctx.step_cache[key] = table
+        return table
+
 
 @register_part("position", "none")
 class NoPosition(Part):
@@ -34,3 +47,6 @@ class NoPosition(Part):
 
     def kernel_table(self):
         return None, 0
+
+    def step_table(self, ctx):
+        return None
