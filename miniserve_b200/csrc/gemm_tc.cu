@@ -1,0 +1,347 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+// C[M, N] = A[M, K] * W[N, K]^T (both operands K-major), float32 accumulation in tensor memory.
+//
+// One CTA computes a 128 x BN tile of C. Roles by warp:
+//   warp 0   one elected lane streams A and W tiles (128 x 64 and BN x 64 bf16, 128-byte swizzle)
+//            into a ring of shared-memory stages with TMA (cp.async.bulk.tensor) and mbarriers;
+//   warp 1   allocates tensor memory; one elected lane issues tcgen05.mma (M=128, N=BN, K=16, four
+//            per stage) on shared-memory descriptors and releases each stage with tcgen05.commit;
+//   warps 2-5 read the accumulator back with tcgen05.ld (each warp its own 32 lanes), apply the
+//            epilogue and store: plain (bf16 or float32 out), or SiLU(gate) * up for the stacked
+//            gate|up projection, which then never writes the 2 x intermediate tensor.
+// Every wait on an mbarrier is bounded: after a limit the kernel raises a status word, stops
+// waiting, frees its tensor memory and returns.
+//
+// Stands where the reference calls F.linear on cuBLAS (miniserve/model/qwen3.py:115-131) and, for
+// the fused epilogue, flashinfer.silu_and_mul after the gate_up product (miniserve/model/fused.py:195).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace ms {
+
+constexpr int TC_BM = 128, TC_BK = 64;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;  // polls of an mbarrier before giving up (far beyond any real wait)
+
+enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_SILU_MUL = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity. Returns false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) wide, laid
+// out by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset),
+// the leading byte offset is unused for swizzled K-major tiles (set to 1), version 1, layout 2.
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+  const uint32_t addr = smem_u32(tile);
+  uint64_t desc = 0;
+  desc |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+  desc |= (uint64_t)1 << 16;                  // leading byte offset (ignored)
+  desc |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
+  desc |= (uint64_t)1 << 46;                  // descriptor version for this architecture
+  desc |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+  return desc;
+}
+
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+template <int BN>
+struct TcSmem {
+  static constexpr int a_bytes = TC_BM * TC_BK * 2;
+  static constexpr int b_bytes = BN * TC_BK * 2;
+  static constexpr int stage_bytes = a_bytes + b_bytes;
+};
+
+// grid: (ceil(N_out / (BN or BN/2 for SiLU)), ceil(M / 128)). For TC_SILU_MUL, W is [2 * inter, K]
+// (gate rows, then up rows), BN is 256 and a CTA computes 128 gate and the matching 128 up columns.
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+               int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+  extern __shared__ unsigned char smem_dyn[];
+  // 128-byte swizzled tiles want 1024-byte alignment
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int gave_up;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;  // output columns per CTA
+  const int n0 = blockIdx.x * COLS, m0 = blockIdx.y * TC_BM;
+  const int k_iters = (K + TC_BK - 1) / TC_BK;
+  constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  // everything above touches nothing an earlier kernel wrote; A does
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int it = 0; it < k_iters; ++it) {
+        const int s = it % STAGES;
+        if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
+          atomicExch(status, 11);
+          gave_up = 1;
+          break;
+        }
+        unsigned char* a_tile = smem + (size_t)s * TcSmem<BN>::stage_bytes;
+        unsigned char* b_tile = a_tile + TcSmem<BN>::a_bytes;
+        mbar_expect_tx(&full_bar[s], TcSmem<BN>::stage_bytes);
+        tma_load_2d(a_tile, &map_a, &full_bar[s], it * TC_BK, m0);
+        if (EPI == TC_SILU_MUL) {
+          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
+          tma_load_2d(b_tile + TcSmem<BN>::b_bytes / 2, &map_w, &full_bar[s], it * TC_BK, up_row_offset + n0);
+        } else {
+          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+          atomicExch(status, 12);
+          gave_up = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned char* a_tile = smem + (size_t)s * TcSmem<BN>::stage_bytes;
+        const unsigned char* b_tile = a_tile + TcSmem<BN>::a_bytes;
+        const uint64_t da = make_smem_desc(a_tile), db = make_smem_desc(b_tile);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          // 16 bf16 = 32 bytes further along K inside the swizzle atom: 2 units of 16 bytes
+          umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0);
+        }
+        umma_commit(&empty_bar[s]);  // arrives when the MMAs that read this stage are done
+      }
+      umma_commit(&accum_bar);  // arrives when every MMA issued so far is done
+    }
+  } else {
+    // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quad = warp & 3;
+    const int row = m0 + quad * 32 + lane;
+    bool ok = mbar_wait(&accum_bar, 0);
+    if (!ok) {
+      atomicExch(status, 13);
+      gave_up = 1;
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (ok) {
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < COLS; c += 32) {
+        uint32_t acc[32];
+        tmem_ld32(lane_addr + (uint32_t)c, acc);
+        uint32_t up[32];
+        if (EPI == TC_SILU_MUL) tmem_ld32(lane_addr + (uint32_t)(COLS + c), up);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (row < M) {
+          const int col0 = n0 + c;
+          if (EPI == TC_OUT_F32) {
+            float* dst = reinterpret_cast<float*>(out) + (size_t)row * N_out + col0;
+            if (col0 + 32 <= N_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __uint_as_float(acc[j]);
+            }
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __uint_as_float(acc[j]);
+              if (EPI == TC_SILU_MUL) x = x / (1.0f + expf(-x)) * __uint_as_float(up[j]);
+              v[j] = x;
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N_out + col0;
+            if (col0 + 32 <= N_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + j) = pk;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encode(EncodeFn* out) {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MS_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres));
+    MS_CHECK_ARG(ptr != nullptr && qres == cudaDriverEntryPointSuccess, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
+    fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  *out = fn;
+  return 0;
+}
+
+// A 2-D bfloat16 tensor [rows, cols] (cols contiguous), boxes of box_rows x 64 columns, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeFn encode;
+  if (int rc = get_encode(&encode)) return rc;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult res = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MS_CHECK_ARG(res == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld)", (int)res, rows, cols);
+  return 0;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_tc(void* out, const void* A, const void* W, int M, int N_out, int w_rows, int K, int up_row_offset,
+                     int* status, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(&map_a, A, M, K, TC_BM)) return rc;
+  if (int rc = make_map(&map_w, W, w_rows, K, EPI == TC_SILU_MUL ? BN / 2 : BN)) return rc;
+  constexpr size_t smem = (size_t)STAGES * TcSmem<BN>::stage_bytes + 1024;
+  auto kernel = gemm_tc_kernel<BN, STAGES, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;
+  dim3 grid(ceil_div(N_out, COLS), ceil_div(M, TC_BM));
+  MS_LAUNCH(kernel, grid, TC_THREADS, smem, stream, map_a, map_w, out, M, N_out, K, up_row_offset, status);
+  return 0;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+MS_DEFINE_LAST_ERROR(ms_gemm_tc_last_error)
+MS_DEFINE_PDL_SWITCH(ms_gemm_tc_set_pdl)
+
+// epilogue 0: out bf16 [M, N]; 1: out float32 [M, N]; 2: W is [2 * N, K] (gate rows then up rows),
+// out bf16 [M, N] = silu(A gate^T) * (A up^T). status: a device int the kernel raises if a wait ran out.
+MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,
+                              cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  MS_CHECK_ARG(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  MS_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+  MS_CHECK_ARG(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  MS_CHECK_ARG(status != nullptr, "gemm_tc: needs a status word");
+  MS_CHECK_ARG(ceil_div(M, TC_BM) <= 65535, "gemm_tc: M=%d too large for one launch", M);
+  switch (epilogue) {
+    case TC_OUT_BF16: return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+    case TC_OUT_F32: return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+    case TC_SILU_MUL: return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+    default: return fail("gemm_tc: unknown epilogue %d", epilogue);
+  }
+}

@@ -57,7 +57,9 @@ class StepFunction:
         self._turn = 0
         self.arena_generation = 0  # bumped when the device arena moves (captured graphs become stale)
         self._grow(arena_ints)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from .. import ops
+
+        self.status = ops.device_status(self.device)  # shared by every kernel launched on this device
         props = torch.cuda.get_device_properties(self.device)
         self.sm_count = props.multi_processor_count
         self.persistent_scratch: dict = {}
@@ -195,4 +197,5 @@ class StepFunction:
         code = int(self.status.item())
         if code:
             self.status.zero_()
-            raise StepError(f"a kernel reported inconsistent cache metadata (code {code})")
+            raise StepError(f"a kernel reported a fault it caught itself (code {code}: 2-3 inconsistent cache "
+                            f"metadata, 11-13 a bounded wait in the tensor-core pipeline ran out)")

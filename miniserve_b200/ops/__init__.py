@@ -16,7 +16,7 @@ from .native import NativeError, OutOfBlocks
 
 __all__ = [
     "NativeError", "OutOfBlocks", "PartialSums", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
-    "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
+    "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -122,6 +122,49 @@ def to_float(out: torch.Tensor, x: torch.Tensor, stream=None) -> None:
     native.kernel_check(k.ms_to_float(_ptr(out), _ptr(x), x.numel(), dtype_code(x.dtype), _stream(stream)))
 
 
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def device_status(device: torch.device | str = "cuda") -> torch.Tensor:
+    """The per-device status word (int32 [1]) that kernels raise instead of faulting or hanging:
+    inconsistent cache metadata, or a bounded wait in a TMA / tensor-core pipeline that ran out."""
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _STATUS:
+        _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _STATUS[idx]
+
+
+def tc_gemm_enabled() -> bool:
+    import os
+
+    return os.environ.get("MINISERVE_TC_GEMM", "1") != "0"
+
+
+TC_EPILOGUE = {"bf16": 0, "f32": 1, "silu_mul": 2}
+
+
+def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16", stream=None) -> torch.Tensor:
+    """x [M, K] times weight^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+    ``epilogue``: ``bf16`` / ``f32`` write x W^T [M, N]; ``silu_mul`` takes weight [2I, K] (gate rows
+    then up rows) and writes silu(x Wg^T) * (x Wu^T) [M, I] without materialising the 2I-wide tensor."""
+    _check_dev(x, weight, out)
+    m, kdim = x.shape
+    n = out.shape[1]
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] == kdim
+    assert weight.shape[0] == (2 * n if epilogue == "silu_mul" else n) and out.shape[0] == m
+    assert out.dtype == (torch.float32 if epilogue == "f32" else torch.bfloat16)
+    lib = native.gemm_tc()
+    native.kernel_check(lib.ms_gemm_tc_bf16(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, TC_EPILOGUE[epilogue],
+                                            _ptr(device_status(x.device)), _stream(stream)),
+                        lib=lib, errfn="ms_gemm_tc_last_error")
+    return out
+
+
+def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (tc_gemm_enabled() and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
 SKINNY_MAX_M = 16
 _SM_COUNT: dict[int, int] = {}
 
@@ -192,6 +235,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         return out
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    if tc_gemm_ok(x, weight):
+        return linear_tc(x, weight, out, "f32" if out.dtype == torch.float32 else "bf16", stream=stream)
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
     else:

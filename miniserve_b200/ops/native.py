@@ -110,6 +110,16 @@ def kernels():
     return lib
 
 
+@lru_cache(maxsize=None)
+def gemm_tc():
+    lib = ctypes.CDLL(str(build.ensure_built(build.GEMM_TC)))
+    _declare(lib, "ms_gemm_tc_last_error", [], c_char_p)
+    _declare(lib, "ms_gemm_tc_set_pdl", [_i], None)
+    _declare(lib, "ms_gemm_tc_bf16", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
+    lib.ms_gemm_tc_set_pdl(int(pdl_enabled()))
+    return lib
+
+
 LAUNCHES = [0]  # launches of this package's own kernels since import (a launcher may launch more than one)
 
 
