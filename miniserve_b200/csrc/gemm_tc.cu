@@ -119,7 +119,7 @@ struct TcSmem {
 // grid: (ceil(N_out / (BN or BN/2 for SiLU)), ceil(M / 128)). For TC_SILU_MUL, W is [2 * inter, K]
 // (gate rows, then up rows), BN is 256 and a CTA computes 128 gate and the matching 128 up columns.
 template <int BN, int STAGES, int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, (STAGES * (TC_BM + BN) * TC_BK * 2 + 2048 <= 110 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
   extern __shared__ unsigned char smem_dyn[];
@@ -330,6 +330,10 @@ MS_DEFINE_PDL_SWITCH(ms_gemm_tc_set_pdl)
 
 // epilogue 0: out bf16 [M, N]; 1: out float32 [M, N]; 2: W is [2 * N, K] (gate rows then up rows),
 // out bf16 [M, N] = silu(A gate^T) * (A up^T). status: a device int the kernel raises if a wait ran out.
+static int g_tc_config = 0;
+// Tile configuration for experiments: 0 = default.
+MS_EXPORT void ms_gemm_tc_set_config(int config) { g_tc_config = config; }
+
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,
                               cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
@@ -339,7 +343,12 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
   MS_CHECK_ARG(status != nullptr, "gemm_tc: needs a status word");
   MS_CHECK_ARG(ceil_div(M, TC_BM) <= 65535, "gemm_tc: M=%d too large for one launch", M);
   switch (epilogue) {
-    case TC_OUT_BF16: return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+    case TC_OUT_BF16:
+      if (g_tc_config == 1) return launch_tc<128, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 2) return launch_tc<256, 2, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 3) return launch_tc<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 4) return launch_tc<64, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_OUT_F32: return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_SILU_MUL: return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);

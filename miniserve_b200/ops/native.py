@@ -116,6 +116,7 @@ def gemm_tc():
     _declare(lib, "ms_gemm_tc_last_error", [], c_char_p)
     _declare(lib, "ms_gemm_tc_set_pdl", [_i], None)
     _declare(lib, "ms_gemm_tc_bf16", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
+    _declare(lib, "ms_gemm_tc_set_config", [_i], None)
     lib.ms_gemm_tc_set_pdl(int(pdl_enabled()))
     return lib
 
