@@ -334,8 +334,32 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
+    if q.dtype == torch.bfloat16 and not ctx.decode_only and attention_tc_ok(q, k_pool):
+        attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window)
+        return
     if q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2]):
         attention_bf16.run(out, q, k_pool, v_pool, ctx, group, scale, window)
         return
     attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
                       ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream)
+
+
+def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
+    """Whether the tcgen05 prefill attention takes this shape (head size 128, pages of 8..128)."""
+    import os
+
+    if os.environ.get("MINISERVE_TC_ATTENTION", "1") == "0" or q.shape[2] != 128:
+        return False
+    return bool(native.attn_tc().ms_attn_tc_supports(q.shape[2], k_pool.shape[2], q.shape[1], k_pool.shape[1]))
+
+
+def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+                         scale: float, window: int | None) -> None:
+    """Causal attention of prompts and mixed steps on the tcgen05 tensor cores (``csrc/attention_tc.cu``)."""
+    _check_dev(out, q, k_pool, v_pool)
+    t, nq, d = q.shape
+    lib = native.attn_tc()
+    native.kernel_check(lib.ms_attn_tc_prefill(
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.page_indptr[group]),
+        _ptr(ctx.page_indices[group]), ctx.num_rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
+        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), ctx.stream), lib=lib, errfn="ms_attn_tc_last_error")

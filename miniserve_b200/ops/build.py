@@ -60,13 +60,14 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 128, 256)
 
 
 GEMM_TC = Module("gemm_tc", ("gemm_tc.cu",))
+ATTN_TC = Module("attn_tc", ("attention_tc.cu",))
 
 
 def all_modules() -> list[Module]:
     """Every module of the package (what ``__graft_entry__.build`` compiles)."""
     from .attention_bf16 import module_for
 
-    return [HOST, KERNELS, GEMM_TC] + [module_for(d) for d in PREBUILT_HEAD_DIMS]
+    return [HOST, KERNELS, GEMM_TC, ATTN_TC] + [module_for(d) for d in PREBUILT_HEAD_DIMS]
 
 
 def log(msg: str) -> None:

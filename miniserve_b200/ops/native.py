@@ -121,6 +121,17 @@ def gemm_tc():
     return lib
 
 
+@lru_cache(maxsize=None)
+def attn_tc():
+    lib = ctypes.CDLL(str(build.ensure_built(build.ATTN_TC)))
+    _declare(lib, "ms_attn_tc_last_error", [], c_char_p)
+    _declare(lib, "ms_attn_tc_set_pdl", [_i], None)
+    _declare(lib, "ms_attn_tc_supports", [_i, _i, _i, _i])
+    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _p, _p])
+    lib.ms_attn_tc_set_pdl(int(pdl_enabled()))
+    return lib
+
+
 LAUNCHES = [0]  # launches of this package's own kernels since import (a launcher may launch more than one)
 
 

@@ -329,6 +329,63 @@ def test_attention_bf16_decode_window_edge(window):
     assert torch.allclose(out.float(), ref, **BF16_TOL)
 
 
+TC_SHAPES = [(16, 8, 128, 16), (8, 8, 128, 8), (32, 8, 128, 32), (8, 1, 128, 16), (4, 2, 128, 128), (6, 2, 128, 64)]
+
+
+@pytest.mark.parametrize("nq, nkv, d, page", TC_SHAPES)
+def test_attention_tcgen05_prompts_and_mixed_steps(nq, nkv, d, page):
+    rows = [(0, 37), (52, 1), (15, 18), (0, 1), (63, 2), (0, 150), (100, 70), (64, 64), (0, 300), (250, 130)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, nq, nkv, d, page)
+    assert ops.attention_tc_ok(q, pb.k_pool)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_tc_prefill(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, None)
+    torch.cuda.synchronize()
+    assert ops.device_status("cuda").item() == 0
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 7, 128, 129, 200])
+def test_attention_tcgen05_window_edge(window):
+    rows = [(0, 400), (130, 3), (399, 1), (256, 128)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 128, 16, window=window)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_tc_prefill(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, window)
+    torch.cuda.synchronize()
+    assert ops.device_status("cuda").item() == 0
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+def test_attention_tcgen05_finds_a_far_key_and_survives_poisoned_pages():
+    rows = [(0, 700), (900, 5)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 128, 16, needle=3)
+    out = torch.full_like(q, float("nan"))  # pages past each request's end are NaN (PagedBatch poisons them)
+    ops.attention_tc_prefill(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, scale, None)
+    torch.cuda.synchronize()
+    assert ops.device_status("cuda").item() == 0
+    assert ref[699, 0].mean().item() > 40 and ref[-1, 0].mean().item() > 40
+    assert torch.allclose(out.float(), ref, atol=0.3, rtol=2e-2)
+
+
+def test_attention_tcgen05_large_scores_keep_the_lazy_rescale_exact():
+    """Scores that keep growing along the keys force the running maximum up tile after tile."""
+    torch.manual_seed(3)
+    nq, nkv, d, page, n = 2, 1, 128, 16, 600
+    pb = PagedBatch([(0, n)], page, nkv, d, torch.bfloat16, seed=1)
+    k = torch.randn(n, nkv, d, device=DEV)
+    k[:, 0, 0] = torch.linspace(0, 40, n, device=DEV)  # a component that grows with the position
+    v = torch.randn(n, nkv, d, device=DEV)
+    q = torch.randn(n, nq, d, device=DEV) * 0.1
+    q[:, :, 0] = 11.0
+    k, v, q = k.bfloat16(), v.bfloat16(), q.bfloat16()
+    pb.fill(0, k, v)
+    ref = reference_attention(q, k, v, list(range(n)), d ** -0.5)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_tc_prefill(out, q, pb.k_pool, pb.v_pool, make_context(pb), 0, d ** -0.5, None)
+    torch.cuda.synchronize()
+    assert ops.device_status("cuda").item() == 0
+    assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
 def test_attention_bf16_refuses_other_head_sizes():
     assert not attention_bf16.supports(40, 16) and not attention_bf16.supports(272, 16)
     with pytest.raises(ValueError):
