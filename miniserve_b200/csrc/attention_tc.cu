@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <cfloat>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -116,6 +117,11 @@ __device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const float (&r)[32
         "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
       : "memory");
 }
+__device__ __forceinline__ float at_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 #define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory")
 #define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
 
@@ -129,8 +135,8 @@ struct AtSmem {
   static constexpr int q = 0;                         // 2 blocks
   static constexpr int kv = 2 * AT_BLOCK;             // 2 stages x (K: 2 blocks, V: 2 blocks)
   static constexpr int stage = 4 * AT_BLOCK;
-  static constexpr int p = kv + 2 * stage;            // 2 blocks
-  static constexpr int total = p + 2 * AT_BLOCK;      // 12 blocks = 192 KB
+  static constexpr int p = kv + 2 * stage;            // 2 buffers x 2 blocks
+  static constexpr int total = p + 4 * AT_BLOCK;      // 14 blocks = 224 KB
 };
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
@@ -138,17 +144,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                       int page_shift, int G, int* __restrict__ status) {
+                       int page_shift, int G, int* __restrict__ status, int dbg) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done[2];
   __shared__ uint32_t tmem_slot;
 
   pdl_prologue();
   const int r = blockIdx.y;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
   const int tpc = AT_ROWS / G;  // tokens per CTA
-  const int m0 = blockIdx.x * tpc;
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * tpc;  // later tiles see more keys: start them first
   if (m0 >= q_len) return;  // uniform for the CTA, before any barrier or allocation
   const int start = q_start[r], kv_len = start + q_len;
   const int head0 = blockIdx.z * G, kvh = head0 / (nq / nkv);
@@ -157,6 +163,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int q_first = start + m0, q_last = start + min(m0 + tpc, q_len) - 1;
   const int hi = min(kv_len, q_last + 1);
   const int lo = window > 0 ? max(0, q_first - window + 1) : 0;
+  const int lo_max = window > 0 ? max(0, q_last - window + 1) : 0;  // the highest lower bound among the rows
   const int tile_begin = lo / AT_KEYS, tile_end = (hi + AT_KEYS - 1) / AT_KEYS;
   const int n_tiles = tile_end - tile_begin;
 
@@ -169,7 +176,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       at_mbar_init(&s_empty[i], 128);
     }
     at_mbar_init(&p_full, 128);
-    at_mbar_init(&pv_done, 1);
+    at_mbar_init(&pv_done[0], 1);
+    at_mbar_init(&pv_done[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 5) {
@@ -185,33 +193,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
-    if (at_elect()) {
+    // Lane 0 issues every copy; all lanes fetch the tile's page ids together (one coalesced load
+    // instead of a chain of dependent ones).
+    if (lane == 0) {
       at_expect_tx(&q_full, 2 * AT_BLOCK);
       at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
       at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
-      const int* pages = page_indices + page_indptr[r];
-      const int page_size = 1 << page_shift;
-      const int box_rows = min(page_size, AT_KEYS);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !at_wait(&kv_empty[s], ((j >> 1) - 1) & 1)) {
-          atomicExch(status, 21);
+    }
+    const int* pages = page_indices + page_indptr[r];
+    const int page_size = 1 << page_shift;
+    const int box_rows = min(page_size, AT_KEYS);
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const int key0 = (tile_begin + j) * AT_KEYS;
+      const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;  // pages that exist
+      int my_row = 0;
+      if (lane < boxes) {
+        const int key = key0 + lane * box_rows;
+        const int page = pages[key >> page_shift];
+        my_row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
+      }
+      if (j >= 2) {
+        if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) atomicExch(status, 21);
           break;
         }
-        const int key0 = (tile_begin + j) * AT_KEYS;
-        const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;  // pages that exist
-        unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
-        unsigned char* vt = kt + 2 * AT_BLOCK;
-        at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
-        for (int b = 0; b < boxes; ++b) {
-          const int key = key0 + b * box_rows;
-          const int page = pages[key >> page_shift];
-          const int row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
-          const int off = b * box_rows * 128;
-          at_tma_2d(kt + off, &map_k, &kv_full[s], 0, row);
-          at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, row);
-          at_tma_2d(vt + off, &map_v, &kv_full[s], 0, row);
-          at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, row);
+      }
+      unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
+      unsigned char* vt = kt + 2 * AT_BLOCK;
+      if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * ((dbg & 8) ? 2 : 4));
+      __syncwarp();  // the expected byte count is posted before any copy can complete
+      if (lane < boxes) {  // every lane issues the four copies of its own page
+        const int off = lane * box_rows * 128;
+        at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
+        at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
+        if (!(dbg & 8)) {
+          at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
+          at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
         }
       }
     }
@@ -251,12 +272,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
           // A = P [rows][keys], K-major: 16 keys = 32 bytes along the row; B = V [keys][d], MN-major:
           // the two 64-wide halves of d are one block apart, 8-key groups 1024 bytes apart
-          const uint64_t da = at_desc(smem + AtSmem::p + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+          const uint64_t da = at_desc(smem + AtSmem::p + (s * 2 + (kk >> 2)) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
           const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
           at_mma(tmem_o, da, db, idesc_o, (j | kk) != 0);
         }
         at_commit(&kv_empty[s]);
-        at_commit(&pv_done);
+        at_commit(&pv_done[s]);
       }
       if (!ok) atomicExch(status, 23);
     }
@@ -273,53 +294,73 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!at_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
       AT_FENCE_AFTER();
       float sv[4][32];
+      if (!(dbg & 4)) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) at_tmem_ld32(tmem_s[b] + lane_base + (uint32_t)(c * 32), sv[c]);
+      } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[c][i] = (float)(i + c);
+      }
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
       AT_FENCE_BEFORE();
       at_arrive(&s_empty[b]);
       const int key0 = (tile_begin + j) * AT_KEYS;
+      // Only tiles that touch the diagonal, the window's edge or the end of the request need the
+      // mask; the maximum is tracked on the raw scores (the scale is positive).
+      const bool interior = key0 + AT_KEYS - 1 <= q_first && key0 >= lo_max;
       float m_tile = -INFINITY;
+      if (dbg & 2) {
+        m_tile = sv[0][0];
+      } else if (interior) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c * 32 + i;
-          const bool valid = key <= qpos && key >= lo && (window <= 0 || key > qpos - window);
-          sv[c][i] = valid ? sv[c][i] * scale_log2 : -INFINITY;
-          m_tile = fmaxf(m_tile, sv[c][i]);
-        }
+          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, sv[c][i]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            const bool valid = key <= qpos && key >= lo && (window <= 0 || key > qpos - window);
+            sv[c][i] = valid ? sv[c][i] : -INFINITY;
+            m_tile = fmaxf(m_tile, sv[c][i]);
+          }
+      }
       const float m_new = fmaxf(m_used, m_tile);
       float alpha = 1.f;
       bool rescale = false;
       if (m_used == -INFINITY) {
         m_used = m_new;  // nothing accumulated yet for this row
-      } else if (m_new - m_used > 8.f) {
-        alpha = exp2f(m_used - m_new);
+      } else if ((m_new - m_used) * scale_log2 > 8.f) {
+        alpha = at_ex2((m_used - m_new) * scale_log2);
         m_used = m_new;
         rescale = true;
       }
-      if (j > 0) {
-        // PV of the previous tile must be complete before O is touched or P is overwritten
-        if (!at_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
+      if (__any_sync(0xffffffffu, rescale)) {
+        // O may only be touched once the PV product of the previous tile has completed
+        if (!at_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
         AT_FENCE_AFTER();
-        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            float ov[32];
-            at_tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        for (int c = 0; c < 4; ++c) {
+          float ov[32];
+          at_tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-            at_tmem_st32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-          l_sum *= alpha;
+          for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+          at_tmem_st32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        l_sum *= alpha;
       }
-      const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-      float row_sum = 0.f;
-      unsigned char* p_row = smem + AtSmem::p + row * 128;
+      // this tile's P buffer was last read by the PV product two tiles ago
+      if (j >= 2 && !at_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
+      const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned char* p_row = smem + AtSmem::p + b * 2 * AT_BLOCK + row * 128;
+      if (!(dbg & 1))
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -327,8 +368,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           float e[8];
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
-            e[x] = exp2f(sv[c][i + x] - m_sub);
-            row_sum += e[x];
+            e[x] = at_ex2(fmaf(sv[c][i + x], scale_log2, -m_sub));  // ex2(-inf) = 0 for masked keys
+            part[x & 3] += e[x];
           }
           uint4 pk;
           __nv_bfloat162 p0 = __floats2bfloat162_rn(e[0], e[1]), p1 = __floats2bfloat162_rn(e[2], e[3]);
@@ -340,6 +381,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int chunk = c * 4 + (i >> 3);  // 16 chunks of 8 keys
           *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * AT_BLOCK + (((chunk & 7) ^ (row & 7)) << 4)) = pk;
         }
+      const float row_sum = (part[0] + part[1]) + (part[2] + part[3]);
       l_sum += row_sum;
       // keys past the end of the request in this tile: their V rows may hold anything (even NaN);
       // P is zero there, but 0 * NaN is NaN, so zero those rows of V
@@ -355,7 +397,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       AT_FENCE_BEFORE();
       at_arrive(&p_full);
     }
-    if (ok && n_tiles > 0) ok = at_wait(&pv_done, (n_tiles - 1) & 1);
+    if (ok && n_tiles > 0) ok = at_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
     if (!ok) atomicExch(status, 24);
     AT_FENCE_AFTER();
     if (ok) {
@@ -465,8 +507,9 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   }
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
+  static const int dbg = getenv("MINISERVE_ATTN_TC_DEBUG") ? atoi(getenv("MINISERVE_ATTN_TC_DEBUG")) : 0;  // timing experiments only
   dim3 grid(ceil_div(max_q_len, tpc), num_rows, nq / G);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, q_start,
-            page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status);
+            page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, dbg);
   return 0;
 }

@@ -45,7 +45,7 @@ def _paged(rows, page, nkv, d, seed, device):
         q_start=torch.tensor([s for s, _ in rows], **i32), kv_len=torch.tensor([s + n for s, n in rows], **i32),
         page_indptr=[torch.tensor(indptr, **i32)], page_indices=[torch.tensor([p for t in tables for p in t], **i32)],
         max_q_len=max(n for _, n in rows), max_kv_len=max(s + n for s, n in rows),
-        decode_only=all(n == 1 for _, n in rows), graph_bucket=0, scratch={},
+        decode_only=all(n == 1 for _, n in rows), graph_bucket=0, scratch={}, step_cache={},
         sm_count=torch.cuda.get_device_properties(0).multi_processor_count, stream=0)
     return k, v, ctx
 
@@ -95,6 +95,7 @@ def main(argv=None) -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--legacy", action="store_true", help="attention: force the mma.sync kernels")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -124,7 +125,10 @@ def main(argv=None) -> int:
         def calls(i, stream):
             k, v, ctx = sets[i]
             ctx.stream = stream
-            attention_bf16.run(o, q, k, v, ctx, 0, d ** -0.5, None)
+            if args.legacy:
+                attention_bf16.run(o, q, k, v, ctx, 0, d ** -0.5, None)
+            else:
+                ops.attention(o, q, k, v, ctx, 0, d ** -0.5, None)
     elif args.kernel == "skinny":
         byts = args.n * args.k * 2
         work = dict(bytes=byts)

@@ -85,6 +85,28 @@ def test_gemm_f32_is_true_32bit_and_row_independent(m, n, k):
     assert torch.equal(alone[0], out[m // 2])
 
 
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (17, 200, 72), (333, 1000, 1000), (2048, 1024, 2048), (130, 503, 96)])
+@pytest.mark.parametrize("epilogue", ["bf16", "f32", "silu_mul"])
+def test_tcgen05_gemm(m, n, k, epilogue):
+    torch.manual_seed(m + n)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    if epilogue == "silu_mul":
+        w = (torch.randn(2 * n, k, device=DEV) / 8).bfloat16()
+        g, u = x.float() @ w[:n].float().T, x.float() @ w[n:].float().T
+        expect = g * torch.sigmoid(g) * u
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    else:
+        w = torch.randn(n, k, device=DEV).bfloat16()
+        expect = x.float() @ w.float().T
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.float32 if epilogue == "f32" else torch.bfloat16)
+    ops.linear_tc(x, w, out, epilogue)
+    torch.cuda.synchronize()
+    assert ops.device_status(DEV).item() == 0
+    scale = expect.abs().max().item()
+    tol = 1e-4 * scale if epilogue == "f32" else 8e-3 * scale
+    assert (out.float() - expect).abs().max().item() <= tol
+
+
 def test_bf16_linear_accumulates_in_float32():
     a = torch.randn(33, 520, device=DEV).bfloat16()
     w = torch.randn(77, 520, device=DEV).bfloat16()
