@@ -196,7 +196,8 @@ def time_e2e(llm, batch: int, context: int, steps: int, warmup: int):
     rng = random.Random(1)
     vocab = llm.model.spec.vocab_size
     prompts = [[rng.randrange(vocab) for _ in range(context)] for _ in range(batch)]
-    reqs = [eng.add_request(p, SamplingParams(max_new_tokens=steps + warmup + 1)) for p in prompts]
+    # room to spare: a request that finished inside the timed region would shrink the batch
+    reqs = [eng.add_request(p, SamplingParams(max_new_tokens=steps + warmup + 64)) for p in prompts]
     while any(r.state.name in ("WAITING", "PREFILL") for r in reqs):
         eng.step()
     for _ in range(warmup):
@@ -335,7 +336,7 @@ def run_reference(args) -> dict:
                      radix=False, chunked_prefill_size=2048)
         rng = random.Random(1)
         prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(CONTEXT)] for _ in range(args.batch)]
-        reqs = [eng.add_request(p, SamplingParams(max_new_tokens=args.steps + args.warmup + 2)) for p in prompts]
+        reqs = [eng.add_request(p, SamplingParams(max_new_tokens=args.steps + args.warmup + 64)) for p in prompts]
         while any(r.state.name in ("WAITING", "PREFILL") for r in reqs):
             eng.step()
         for _ in range(max(args.warmup, 3)):
