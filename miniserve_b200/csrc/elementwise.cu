@@ -29,7 +29,7 @@ __global__ void embed_gather_kernel(float* __restrict__ residual, const T* __res
 //   out[i] = h / sqrt(mean(h^2) + eps) * w           rounded once to T
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta,
+add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __restrict__ residual_out, const T* __restrict__ delta,
                    const float* __restrict__ parts, int num_parts, size_t part_stride,
                    const T* __restrict__ w, const int* __restrict__ rows, float eps, int hidden,
                    int write_residual) {
@@ -53,7 +53,8 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* _
   T* o = out + (size_t)i * hidden;
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     const float h = row_buf[c];
-    if (write_residual && (dl || num_parts)) res[c] = h;
+    if (residual_out) residual_out[(size_t)r * hidden + c] = h;
+    else if (write_residual && (dl || num_parts)) res[c] = h;
     Elem<T>::store(o + c, (h * inv) * Elem<T>::load(w + c));
   }
 }
@@ -125,24 +126,25 @@ MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* 
 // delta: an addend in the activation dtype, or null. parts: float32 partial sums
 // [num_parts][..][hidden] that are `part_stride` floats apart (the split-K output of the skinny
 // matrix product), or null. Both are added to the residual before the norm.
-MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, const float* parts, int num_parts,
+// residual_out: if given, the sum goes there and `residual_f32` is left as it was.
+MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, void* residual_out, const void* delta, const float* parts, int num_parts,
                              long long part_stride, const void* weight, const int* rows,
                              float eps, int num_out_rows, int hidden, int write_residual, int dtype,
                              cudaStream_t stream) {
   if (num_out_rows == 0) return 0;
   MS_CHECK_ARG(num_out_rows > 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d H=%d", num_out_rows, hidden);
-  MS_CHECK_ARG(!(rows && write_residual), "add_rmsnorm: a gathered norm cannot write the residual back");
+  MS_CHECK_ARG(!(rows && (write_residual || residual_out)), "add_rmsnorm: a gathered norm cannot write the residual back");
   const size_t smem = (size_t)hidden * sizeof(float);
   MS_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", hidden, smem);
   constexpr int THREADS = 256;
   if (dtype == MS_F32) {
     auto k = add_rmsnorm_kernel<float, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (float*)residual_out, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
   } else {
     auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
   }
   return 0;
 }

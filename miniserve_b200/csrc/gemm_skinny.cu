@@ -31,11 +31,45 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
+// What the kernel does while it stages its activations (the weights are already in flight):
+//   PRO_PLAIN  X is bf16 [M, K], copied as it is;
+//   PRO_NORM   X = rmsnorm(res_in + delta) * norm_w, the fused residual-add + RMSNorm
+//              (miniserve/model/fused.py:170,192: fused_add_rmsnorm): every CTA recomputes the M rows
+//              (a few KB), the first CTA also stores the sum to res_out (a buffer other than res_in,
+//              since other CTAs still read res_in);
+//   PRO_SILU   X = silu(gate) * up of a stacked [M, 2K] gate|up tensor (miniserve/model/qwen3.py:128-131).
+enum SkinnyPrologue : int { PRO_PLAIN = 0, PRO_NORM = 1, PRO_SILU = 2 };
+
+struct SkinnyFused {
+  const float* res_in;           // PRO_NORM: [M, K] float32
+  const __nv_bfloat16* delta;    // PRO_NORM: [M, K] addend or null
+  float* res_out;                // PRO_NORM: [M, K] receives res_in + delta (may be null: not stored)
+  const __nv_bfloat16* norm_w;   // PRO_NORM: [K]
+  float eps;
+};
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 float_to_bf16x8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
 // MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: float32 partials [splits, M, N]
-template <int MT, int MODE>
+template <int MT, int MODE, int PRO>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
-                   int M, int N, int K, int k_per_split) {
+                   int M, int N, int K, int k_per_split, SkinnyFused fused) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * SK_ROWS;
@@ -69,11 +103,68 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
 
   // activations of this K slice: [MT * 8][k_len], rows past M are zero
   const int chunks = k_len >> 3;
-  for (int idx = tid; idx < MT * 8 * chunks; idx += SK_THREADS) {
-    const int row = idx / chunks, c = idx - row * chunks;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < M) v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + k_begin + c * 8);
-    *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
+  if (PRO == PRO_NORM) {
+    // one warp per row (rows warp, warp + 8); K is whole here (no split)
+    for (int row = warp; row < MT * 8; row += SK_WARPS) {
+      if (row >= M) {
+        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
+      const float* rin = fused.res_in + (size_t)row * K;
+      const __nv_bfloat16* dl = fused.delta ? fused.delta + (size_t)row * K : nullptr;
+      float ss = 0.f;
+      for (int c = lane; c < chunks; c += 32) {
+        float h[8], d[8];
+        *reinterpret_cast<float4*>(h) = *reinterpret_cast<const float4*>(rin + c * 8);
+        *reinterpret_cast<float4*>(h + 4) = *reinterpret_cast<const float4*>(rin + c * 8 + 4);
+        if (dl) {
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + c * 8), d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[i] += d[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += h[i] * h[i];
+        if (blockIdx.x == 0 && fused.res_out) {
+          *reinterpret_cast<float4*>(fused.res_out + (size_t)row * K + c * 8) = *reinterpret_cast<float4*>(h);
+          *reinterpret_cast<float4*>(fused.res_out + (size_t)row * K + c * 8 + 4) = *reinterpret_cast<float4*>(h + 4);
+        }
+      }
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)K + fused.eps);
+      for (int c = lane; c < chunks; c += 32) {
+        float h[8], d[8], wv[8];
+        *reinterpret_cast<float4*>(h) = *reinterpret_cast<const float4*>(rin + c * 8);
+        *reinterpret_cast<float4*>(h + 4) = *reinterpret_cast<const float4*>(rin + c * 8 + 4);
+        if (dl) {
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + c * 8), d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[i] += d[i];
+        }
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(fused.norm_w + c * 8), wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = (h[i] * inv) * wv[i];
+        *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = float_to_bf16x8(h);
+      }
+    }
+  } else {
+    for (int idx = tid; idx < MT * 8 * chunks; idx += SK_THREADS) {
+      const int row = idx / chunks, c = idx - row * chunks;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < M) {
+        if (PRO == PRO_SILU) {
+          // X is the stacked gate|up tensor [M, 2K]: silu(gate) * up in float32, rounded once
+          float gt[8], up[8];
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(X + (size_t)row * 2 * K + k_begin + c * 8), gt);
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(X + (size_t)row * 2 * K + K + k_begin + c * 8), up);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gt[i] = gt[i] / (1.0f + expf(-gt[i])) * up[i];
+          v = float_to_bf16x8(gt);
+        } else {
+          v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + k_begin + c * 8);
+        }
+      }
+      *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
+    }
   }
   __syncthreads();
 
@@ -134,8 +225,9 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
   }
 }
 
-template <int MT, int MODE>
-static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, int splits, cudaStream_t stream) {
+template <int MT, int MODE, int PRO>
+static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, int splits, const SkinnyFused& fused,
+                         cudaStream_t stream) {
   // whole multiples of 8 warps x 32 k per split keep every warp's range aligned
   int k_per_split = ceil_div(ceil_div(K, splits), 32) * 32;
   const int used_splits = ceil_div(K, k_per_split);
@@ -144,14 +236,14 @@ static int launch_skinny(void* out, const void* X, const void* W, int M, int N, 
   const size_t smem_red = (size_t)SK_WARPS * SK_ROWS * MT * 8 * 4;
   const size_t smem = smem_x > smem_red ? smem_x : smem_red;
   MS_CHECK_ARG(smem <= 200 * 1024, "gemm_skinny: K slice of %d needs %zu bytes of shared memory", k_per_split, smem);
-  auto kernel = gemm_skinny_kernel<MT, MODE>;
+  auto kernel = gemm_skinny_kernel<MT, MODE, PRO>;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid(ceil_div(N, SK_ROWS), splits);
-  MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split);
+  MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split, fused);
   return 0;
 }
 
@@ -159,20 +251,60 @@ static int launch_skinny(void* out, const void* X, const void* W, int M, int N, 
 
 using namespace ms;
 
+static int check_skinny(const void* W, int M, int N, int K, int splits, int out_mode) {
+  MS_CHECK_ARG(M > 0 && M <= 16, "gemm_skinny: M=%d is outside 1..16", M);
+  MS_CHECK_ARG(K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a multiple of 8", K);
+  MS_CHECK_ARG((uintptr_t)W % 16 == 0, "gemm_skinny: the weight must be 16-byte aligned");
+  MS_CHECK_ARG(splits >= 1 && (splits == 1 || out_mode == 2), "gemm_skinny: only partial sums can be split over K");
+  MS_CHECK_ARG(out_mode >= 0 && out_mode <= 2, "gemm_skinny: bad output mode %d", out_mode);
+  MS_CHECK_ARG(ceil_div(N, SK_ROWS) <= 2147483647 && splits <= 65535, "gemm_skinny: grid too large");
+  return 0;
+}
+
+#define MS_SK_DISPATCH(PRO)                                                                                   \
+  do {                                                                                                        \
+    const bool wide = M > 8;                                                                                  \
+    if (out_mode == 0) return wide ? launch_skinny<2, 0, PRO>(out, X, W, M, N, K, splits, fused, stream)      \
+                                   : launch_skinny<1, 0, PRO>(out, X, W, M, N, K, splits, fused, stream);     \
+    if (out_mode == 1) return wide ? launch_skinny<2, 1, PRO>(out, X, W, M, N, K, splits, fused, stream)      \
+                                   : launch_skinny<1, 1, PRO>(out, X, W, M, N, K, splits, fused, stream);     \
+    return wide ? launch_skinny<2, 2, PRO>(out, X, W, M, N, K, splits, fused, stream)                         \
+                : launch_skinny<1, 2, PRO>(out, X, W, M, N, K, splits, fused, stream);                        \
+  } while (0)
+
 // out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
 MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,
                                   cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  MS_CHECK_ARG(M > 0 && M <= 16, "gemm_skinny: M=%d is outside 1..16", M);
-  MS_CHECK_ARG(K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a multiple of 8", K);
-  MS_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: operands must be 16-byte aligned");
-  MS_CHECK_ARG(splits >= 1 && (splits == 1 || out_mode == 2), "gemm_skinny: only partial sums can be split over K");
-  MS_CHECK_ARG(out_mode >= 0 && out_mode <= 2, "gemm_skinny: bad output mode %d", out_mode);
-  MS_CHECK_ARG(ceil_div(N, SK_ROWS) <= 2147483647 && splits <= 65535, "gemm_skinny: grid too large");
-  const bool wide = M > 8;
-#define MS_SK(MT, MODE) return launch_skinny<MT, MODE>(out, X, W, M, N, K, splits, stream)
-  if (out_mode == 0) { if (wide) MS_SK(2, 0); else MS_SK(1, 0); }
-  if (out_mode == 1) { if (wide) MS_SK(2, 1); else MS_SK(1, 1); }
-  if (wide) MS_SK(2, 2); else MS_SK(1, 2);
-#undef MS_SK
+  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
+  MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
+  const SkinnyFused fused = {};
+  MS_SK_DISPATCH(PRO_PLAIN);
+}
+
+// out = rmsnorm(res_in + delta) * norm_w times W^T; res_out (a buffer other than res_in, or null)
+// receives res_in + delta. delta may be null.
+MS_EXPORT int ms_gemm_skinny_norm_bf16(void* out, const float* res_in, const void* delta, float* res_out, const void* norm_w,
+                                       float eps, const void* W, int M, int N, int K, int out_mode, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  const int splits = 1;
+  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
+  MS_CHECK_ARG(out_mode != 2, "gemm_skinny: the fused norm needs the whole K in one CTA (no partial sums)");
+  MS_CHECK_ARG(res_in != nullptr && norm_w != nullptr && res_out != res_in, "gemm_skinny: the fused norm needs res_in, norm_w and a separate res_out");
+  MS_CHECK_ARG(((uintptr_t)res_in % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)res_out % 16 == 0) && ((uintptr_t)norm_w % 16 == 0),
+               "gemm_skinny: fused-norm operands must be 16-byte aligned");
+  const void* X = nullptr;
+  const SkinnyFused fused = {res_in, (const __nv_bfloat16*)delta, res_out, (const __nv_bfloat16*)norm_w, eps};
+  MS_SK_DISPATCH(PRO_NORM);
+}
+
+// out = (silu(gate_up[:, :K]) * gate_up[:, K:]) times W^T for gate_up [M, 2K].
+MS_EXPORT int ms_gemm_skinny_silu_bf16(void* out, const void* gate_up, const void* W, int M, int N, int K, int splits,
+                                       int out_mode, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
+  MS_CHECK_ARG((uintptr_t)gate_up % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
+  const void* X = gate_up;
+  const SkinnyFused fused = {};
+  MS_SK_DISPATCH(PRO_SILU);
 }

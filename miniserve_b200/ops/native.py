@@ -94,7 +94,9 @@ def kernels():
     _declare(lib, "ms_device_sm_count", [_i, POINTER(c_int)])
     _declare(lib, "ms_device_arch", [_i, POINTER(c_int), POINTER(c_int)])
     _declare(lib, "ms_embed_gather", [_p, _p, _p, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _i, _ll, _p, _p, _f, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _i, _ll, _p, _p, _f, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_skinny_norm_bf16", [_p, _p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_skinny_silu_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])

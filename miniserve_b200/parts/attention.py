@@ -41,6 +41,8 @@ class GQAttention(Part):
         pos_spec = spec.get("position") or PartSpec("none")
         self.position = build_part("position", pos_spec, env)
 
+    takes_lazy_input = True  # forward() starts with ops.linear, which can fuse the norm before it
+
     @property
     def owns_cache(self) -> bool:
         return self.kv_source == "own"
@@ -88,4 +90,5 @@ class GQAttention(Part):
             cos_sin=self.position.step_table(ctx))
         out = torch.empty_like(q)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
-        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=True)
+        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream,
+                          partials=ops.SPLIT_K_PARTIALS)

@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+from .. import ops
 from ..config.spec import LayerSpec
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part
 
@@ -29,10 +30,17 @@ class PreNormBlock(Part):
                 self.names["norm1"]: self.norm1, self.names["norm2"]: self.norm2}
 
     def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
-        x = self.norm1.forward(stream.total, stream.pending, ctx)
+        # A mixer or feed-forward that sets ``takes_lazy_input`` starts with ops.linear, which can
+        # run the norm inside its own prologue (decode steps); the sum then lands in a new buffer.
+        total = stream.total
+        x = self.norm1.forward(total, stream.pending, ctx, lazy=getattr(self.mixer, "takes_lazy_input", False))
+        if isinstance(x, ops.LazyNorm):
+            total = x.residual_out
         a = self.mixer.forward(x, ctx, cache)
-        x = self.norm2.forward(stream.total, a, ctx)
-        return ResidualStream(stream.total, self.feed_forward.forward(x, ctx))
+        x = self.norm2.forward(total, a, ctx, lazy=getattr(self.feed_forward, "takes_lazy_input", False))
+        if isinstance(x, ops.LazyNorm):
+            total = x.residual_out
+        return ResidualStream(total, self.feed_forward.forward(x, ctx))
 
 
 def build_block(layer: LayerSpec, env: BuildEnv) -> Part:

@@ -30,8 +30,14 @@ class SwiGLU(Part):
         self.w_gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    takes_lazy_input = True  # forward() starts with ops.linear, which can fuse the norm before it
+
+    def forward(self, x, ctx) -> torch.Tensor:
         gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream)
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        if ops.FUSE_SILU and ops.fusable_rows(gate_up.shape[0], self.inter, gate_up.dtype):
+            # decode steps: SiLU(gate) * up runs while the down projection stages its input
+            return ops.linear(ops.LazyAct(gate_up, stream=ctx.stream), self.w_down, stream=ctx.stream,
+                              partials=ops.SPLIT_K_PARTIALS)
+        act = torch.empty((gate_up.shape[0], self.inter), dtype=gate_up.dtype, device=gate_up.device)
         ops.silu_mul(act, gate_up, stream=ctx.stream)
-        return ops.linear(act, self.w_down, stream=ctx.stream, partials=True)
+        return ops.linear(act, self.w_down, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS)

@@ -22,9 +22,14 @@ class RMSNorm(Part):
         return {"weight": WeightDecl((self.size,), init="ones_normal")}
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
-                num_rows: int | None = None, write_residual: bool = True) -> torch.Tensor:
+                num_rows: int | None = None, write_residual: bool = True, lazy: bool = False):
         """Normalise ``residual (+ delta)``; without ``rows`` the sum is stored back into
-        ``residual``. With ``rows`` (int32 indices) only those rows are produced."""
+        ``residual``. With ``rows`` (int32 indices) only those rows are produced. ``lazy``: the
+        caller's consumer takes an ``ops.LazyNorm`` (decode steps: the norm then runs inside the
+        product that consumes it, and the sum goes to ``LazyNorm.residual_out``)."""
+        if (lazy and ops.FUSE_NORM and rows is None and write_residual and (delta is None or isinstance(delta, torch.Tensor))
+                and ops.fusable_rows(residual.shape[0], self.size, self.env.dtype)):
+            return ops.LazyNorm(residual, delta, self.w_weight, self.eps, stream=ctx.stream)
         n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = torch.empty((n, self.size), dtype=self.env.dtype, device=residual.device)
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,

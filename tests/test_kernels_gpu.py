@@ -140,6 +140,49 @@ def test_skinny_gemm_bf16(m, n, k):
     assert torch.equal(alone[0], out32[m - 1])
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("n, k", [(72, 96), (4096, 1024), (503, 1000)])
+def test_skinny_gemm_with_the_norm_in_its_prologue(m, n, k):
+    torch.manual_seed(m + n)
+    res = torch.randn(m, k, device=DEV) * 2
+    delta = torch.randn(m, k, device=DEV).bfloat16()
+    nw = (1 + 0.1 * torch.randn(k, device=DEV)).bfloat16()
+    w = (torch.randn(n, k, device=DEV) / 4).bfloat16()
+    eps = 1e-6
+    total = res + delta.float()
+    xn = (total * torch.rsqrt((total * total).mean(-1, keepdim=True) + eps) * nw.float()).bfloat16()
+    expect = xn.float() @ w.float().T
+    for d in (delta, None):
+        lazy = ops.LazyNorm(res.clone(), d, nw, eps)
+        keep = lazy.residual_in.clone()
+        out = ops.linear(lazy, w)
+        tot = total if d is not None else res
+        xr = (tot * torch.rsqrt((tot * tot).mean(-1, keepdim=True) + eps) * nw.float()).bfloat16()
+        exp = xr.float() @ w.float().T
+        assert torch.allclose(out.float(), exp, atol=0.05 * (k ** 0.5), rtol=2e-2)
+        assert torch.allclose(lazy.residual_out, tot, atol=1e-6)       # the sum went to the new buffer
+        assert torch.equal(lazy.residual_in, keep)                      # and the old one is untouched
+        # the stand-alone norm gives the same activations
+        assert torch.allclose(ops.LazyNorm(res.clone(), d, nw, eps).materialize().float(), xr.float(), atol=2e-2, rtol=2e-2)
+    assert expect.shape == (m, n)
+
+
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("n, inter", [(1024, 3072), (96, 224), (503, 72)])
+def test_skinny_gemm_with_silu_mul_in_its_prologue(m, n, inter):
+    torch.manual_seed(m + n)
+    gu = (torch.randn(m, 2 * inter, device=DEV) * 2).bfloat16()
+    w = (torch.randn(n, inter, device=DEV) / 4).bfloat16()
+    g, u = gu[:, :inter].float(), gu[:, inter:].float()
+    act = (g * torch.sigmoid(g) * u).bfloat16()
+    expect = act.float() @ w.float().T
+    out = ops.linear(ops.LazyAct(gu), w)
+    assert torch.allclose(out.float(), expect, atol=0.05 * (inter ** 0.5), rtol=2e-2)
+    parts = ops.linear(ops.LazyAct(gu), w, partials=True)
+    assert torch.allclose(ops.materialize(parts).float(), expect, atol=0.05 * (inter ** 0.5), rtol=2e-2)
+    assert torch.allclose(ops.LazyAct(gu).materialize().float(), act.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_add_rmsnorm_takes_partial_sums():
     hidden, rows, eps = 1000, 5, 1e-6
     res = torch.randn(rows, hidden, device=DEV)
