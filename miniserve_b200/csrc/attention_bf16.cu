@@ -266,8 +266,11 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
-                   float scale_log2, int window, int page_shift, int num_splits) {
-  pdl_prologue();
+                   float scale_log2, int window, int page_shift, int num_splits, int* __restrict__ counters) {
+  // Until pdl_wait() below, only data written before this step is touched: the step's metadata and
+  // the keys and values of older tokens. So the CTA may start streaming them while the kernels
+  // before it (the q/k/v projection, the rotation and cache write) are still running.
+  pdl_launch_dependents();
   const int split = blockIdx.x, r = blockIdx.y;
   const int group = nq / nkv, chunks_per_group = (group + 15) / 16;
   const int kvh = blockIdx.z / chunks_per_group, head0 = kvh * group + (blockIdx.z % chunks_per_group) * 16;
@@ -286,22 +289,6 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 
   PagedKV kv{k_pool, v_pool, page_indices + page_indptr[r], kvh, nkv, page_shift};
 
-  for (int idx = tid; idx < 16 * CHUNKS; idx += DC_THREADS) {
-    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
-    const bool valid = row < heads_here;
-    const __nv_bfloat16* src = q + ((size_t)r * nq + head0 + (valid ? row : 0)) * D + chunk * 8;
-    cp_async16(qs + row * DPAD + chunk * 8, src, valid);
-  }
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-
-  uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
-  if (Q_IN_REGS) {
-#pragma unroll
-    for (int kk = 0; kk < (Q_IN_REGS ? KSTEPS : 1); ++kk)
-      ldmatrix_x4(qf[kk], qs + (lane & 15) * DPAD + kk * 16 + (lane >> 4) * 8);
-  }
   float o[DTILES][4];
 #pragma unroll
   for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -332,8 +319,29 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     }
     cp_async_commit();
   };
+  // Fill the pipeline with slices of older tokens; the slice that holds this step's own token
+  // (written by the kernel before this one) and the queries come after the wait.
+  const int newest_slice = (kv_len - 1) / DC_SLICE;
+  int issued = 0;
+  for (; issued < DC_STAGES - 1; ++issued) {
+    if (issued < my_count && my_first + issued * DC_WARPS >= newest_slice) break;
+    issue(issued);
+  }
+  pdl_wait();
+  for (int idx = tid; idx < 16 * CHUNKS; idx += DC_THREADS) {
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < heads_here) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + head0 + row) * D + chunk * 8);
+    *reinterpret_cast<uint4*>(qs + row * DPAD + chunk * 8) = v;
+  }
+  for (; issued < DC_STAGES - 1; ++issued) issue(issued);
+  __syncthreads();
+  uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+  if (Q_IN_REGS) {
 #pragma unroll
-  for (int i = 0; i < DC_STAGES - 1; ++i) issue(i);
+    for (int kk = 0; kk < (Q_IN_REGS ? KSTEPS : 1); ++kk)
+      ldmatrix_x4(qf[kk], qs + (lane & 15) * DPAD + kk * 16 + (lane >> 4) * 8);
+  }
 
   for (int i = 0; i < my_count; ++i) {
     issue(i + DC_STAGES - 1);
@@ -448,6 +456,36 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       }
     }
   }
+  if (num_splits == 1 || counters == nullptr) return;
+  // The split that finishes last merges them all (a ticket per (request, head chunk); no waiting):
+  // out = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m).
+  __shared__ int last_one;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* ticket = counters + (size_t)r * gridDim.z + blockIdx.z;
+    const int prev = atomicAdd(ticket, 1);
+    last_one = prev == num_splits - 1;
+    if (last_one) *ticket = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!last_one) return;
+  __threadfence();
+  for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
+    const int row = idx / D, c = idx - row * D;
+    const size_t item = (size_t)r * nq + head0 + row;
+    const float* ml = part_ml + item * num_splits * 2;
+    float m = -INFINITY;
+    for (int sp = 0; sp < num_splits; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
+    float acc = 0.f, l = 0.f;
+    for (int sp = 0; sp < num_splits; ++sp) {
+      const float ms_ = __ldcg(ml + 2 * sp);
+      const float wgt = ms_ == -INFINITY ? 0.f : exp2f(ms_ - m);
+      acc += wgt * __ldcg(part_o + (item * num_splits + sp) * D + c);
+      l += wgt * __ldcg(ml + 2 * sp + 1);
+    }
+    out[item * D + c] = __float2bfloat16_rn(acc / l);
+  }
 }
 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
@@ -511,11 +549,27 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
   return 0;
 }
 
+MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
+                                       const void* k_pool, const void* v_pool, const int* kv_len,
+                                       const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
+                                       float scale, int window, int page_size, int num_splits, cudaStream_t stream);
+
 // Scratch for num_splits > 1: part_o [rows, nq, splits, D] floats and part_ml [rows, nq, splits, 2] floats.
 MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const void* q, const void* k_pool,
                                  const void* v_pool, const int* kv_len, const int* page_indptr,
                                  const int* page_indices, int num_rows, int nq, int nkv, float scale, int window,
                                  int page_size, int num_splits, cudaStream_t stream) {
+  return MS_ATTN_FN(decode_fused)(out, part_o, part_ml, nullptr, q, k_pool, v_pool, kv_len, page_indptr, page_indices,
+                                  num_rows, nq, nkv, scale, window, page_size, num_splits, stream);
+}
+
+// As above; with `counters` (num_rows * kv_heads * ceil(group / 16) ints, zero before the first
+// launch, left zero by every launch) the split that finishes last merges the partial results
+// inside the same kernel and no second kernel is launched.
+MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
+                                       const void* k_pool, const void* v_pool, const int* kv_len,
+                                       const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
+                                       float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
@@ -532,8 +586,8 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
   MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
       (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
       (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
-      shift_of(page_size), num_splits);
-  if (num_splits > 1) {
+      shift_of(page_size), num_splits, counters);
+  if (num_splits > 1 && counters == nullptr) {
     MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
               (const float*)part_o, (const float*)part_ml, num_splits);
   }

@@ -33,6 +33,7 @@ def _lib(head_dim: int):
         ("last_error", [], c_char_p),
         ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _p], c_int),
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
     ):
         fn = getattr(lib, pre + name)
         fn.argtypes, fn.restype = args, res
@@ -83,14 +84,19 @@ def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     if ctx.decode_only:
         chunks = nkv * -(-(nq // nkv) // 16)
         splits = choose_splits(ctx.num_rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
-        part_o = part_ml = None
+        part_o = part_ml = counters = None
         if splits > 1:
             part_o, part_ml = _scratch(ctx, ctx.num_rows, nq, splits, d, q.device)
-        _check(fns, fns["decode"](
+            counters = ctx.scratch.get("attn_counters")
+            if counters is None or counters.numel() < ctx.num_rows * chunks:
+                # tickets of the fused merge: zero before the first launch, left zero by every launch
+                counters = torch.zeros(max(4096, ctx.num_rows * chunks), dtype=torch.int32, device=q.device)
+                ctx.scratch["attn_counters"] = counters
+        _check(fns, fns["decode_fused"](
             out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
-            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+            None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
             indices.data_ptr(), ctx.num_rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
-            launches=2 if splits > 1 else 1)
+            launches=1)
         return
     _check(fns, fns["prefill"](
         out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr(), ctx.q_start.data_ptr(),
