@@ -106,6 +106,102 @@ __global__ void qk_norm_rope_kv_kernel(
   }
 }
 
+// bfloat16 fast path for head sizes that are multiples of 64 with the whole head rotated: one
+// block per token, every warp takes a share of the heads, two adjacent elements per lane. What
+// depends on the token alone (position, page, cos/sin, norm weights) is fetched once per warp.
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_bf16_token_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_norm_w,
+    const __nv_bfloat16* __restrict__ k_norm_w, const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
+    const int* __restrict__ positions, const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
+    const int* __restrict__ page_indices, int nq, int nkv, int d, float eps, int page_shift, int* __restrict__ status) {
+  pdl_prologue();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int half = d >> 1, per_lane = half >> 6;  // iterations of 64 pairs (2 per lane)
+  const int pos = positions[t];
+  const bool has_kv = k_pool != nullptr;
+  const int heads_total = nq + (has_kv ? 2 * nkv : 0);
+  const __nv_bfloat16* row_in = qkv + (size_t)t * heads_total * d;
+  size_t slot_base = 0;
+  if (has_kv) {
+    const int page = page_indices[page_indptr[row_of_token[t]] + (pos >> page_shift)];
+    if (page < 0) {
+      if (threadIdx.x == 0) atomicExch(status, 2);
+      return;
+    }
+    const int page_size = 1 << page_shift;
+    slot_base = ((size_t)page * nkv * page_size + (pos & (page_size - 1))) * d;  // + kvh * page_size * d
+  }
+  // per-lane constants: cos/sin of its two pairs per iteration (at most 2 iterations: d <= 256)
+  float cs[2][2], sn[2][2];
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    if (it >= per_lane) break;
+    const int j = it * 64 + 2 * lane;
+    if (inv_freq == nullptr) {
+      cs[it][0] = cs[it][1] = 1.f;
+      sn[it][0] = sn[it][1] = 0.f;
+    } else if (cos_sin) {
+      const float2 c = *reinterpret_cast<const float2*>(cos_sin + (size_t)t * d + j);
+      const float2 s2 = *reinterpret_cast<const float2*>(cos_sin + (size_t)t * d + half + j);
+      cs[it][0] = c.x; cs[it][1] = c.y; sn[it][0] = s2.x; sn[it][1] = s2.y;
+    } else {
+      sincosf((float)pos * inv_freq[j], &sn[it][0], &cs[it][0]);
+      sincosf((float)pos * inv_freq[j + 1], &sn[it][1], &cs[it][1]);
+    }
+  }
+  for (int h = warp; h < heads_total; h += nwarps) {
+    const __nv_bfloat16* src = row_in + (size_t)h * d;
+    if (h >= nq + nkv) {  // a value head: copied as it is
+      const int kvh = h - nq - nkv;
+      __nv_bfloat16* dst = v_pool + slot_base + ((size_t)kvh << page_shift) * d;
+      for (int c = lane; c < (d >> 2); c += 32) reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
+      continue;
+    }
+    const bool is_q = h < nq;
+    __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * nq + h) * d : k_pool + slot_base + ((size_t)(h - nq) << page_shift) * d;
+    const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
+    float lo[2][2], hi[2][2];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      if (it >= per_lane) break;
+      const int j = it * 64 + 2 * lane;
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + j));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + half + j));
+      lo[it][0] = a.x; lo[it][1] = a.y; hi[it][0] = b.x; hi[it][1] = b.y;
+      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+    }
+    float inv = 1.f;
+    if (nw) {
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      if (it >= per_lane) break;
+      const int j = it * 64 + 2 * lane;
+      float wl[2] = {1.f, 1.f}, wh[2] = {1.f, 1.f};
+      if (nw) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + j));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + half + j));
+        wl[0] = a.x; wl[1] = a.y; wh[0] = b.x; wh[1] = b.y;
+      }
+      float ol[2], oh[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float l = nw ? (lo[it][e] * inv) * wl[e] : lo[it][e];
+        const float hgh = nw ? (hi[it][e] * inv) * wh[e] : hi[it][e];
+        ol[e] = l * cs[it][e] - hgh * sn[it][e];
+        oh[e] = hgh * cs[it][e] + l * sn[it][e];
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(ol[0], ol[1]);
+      *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = __floats2bfloat162_rn(oh[0], oh[1]);
+    }
+  }
+}
+
 // cos and sin of every (token, rotation pair) of a step: table[t, j] = cos(pos_t * inv_freq_j),
 // table[t, rot/2 + j] = sin(...). Made once per step and read by every layer's q/k kernel.
 __global__ void rope_table_kernel(float* __restrict__ table, const int* __restrict__ positions,
@@ -151,6 +247,16 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
   const long long items = (long long)num_tokens * (nq + (k_pool ? 2 * nkv : 0));
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (dtype == MS_BF16 && head_dim % 128 == 0 && head_dim <= 256 && (rotary_dim == head_dim || inv_freq == nullptr) &&
+      (k_pool == nullptr || (q_norm_w != nullptr) == (k_norm_w != nullptr)) && ((uintptr_t)qkv % 8 == 0) &&
+      ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)k_pool % 8 == 0) && ((uintptr_t)v_pool % 8 == 0) &&
+      (cos_sin == nullptr || (uintptr_t)cos_sin % 8 == 0)) {
+    MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+              (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
+              inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
+              head_dim, eps, page_shift, status);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(qk_norm_rope_kv_kernel<float>, blocks, warps * 32, 0, stream,
         (float*)q_out, (float*)k_pool, (float*)v_pool, (const float*)qkv, (const float*)q_norm_w, (const float*)k_norm_w,

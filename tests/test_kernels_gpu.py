@@ -203,7 +203,8 @@ def test_add_rmsnorm_takes_partial_sums():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq, nkv, d, page, theta, eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 1, 48, 8, 1e6, 1e-5),
-                                                        (3, 3, 80, 4, 5e5, 1e-6), (2, 1, 256, 32, 1e6, 1e-6)])
+                                                        (3, 3, 80, 4, 5e5, 1e-6), (2, 1, 256, 32, 1e6, 1e-6),
+                                                        (16, 8, 128, 16, 1e6, 1e-6), (5, 5, 128, 8, 1e4, 1e-5)])
 def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, theta, eps):
     rows = [(0, 9), (13, 1), (30, 6)]  # a fresh portion, a decode token, a portion across a page edge
     pb = PagedBatch(rows, page, nkv, d, dtype, seed=3)
