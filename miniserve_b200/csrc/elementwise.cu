@@ -107,9 +107,24 @@ __global__ void to_float_kernel(float* __restrict__ out, const T* __restrict__ i
   if (i < n) out[i] = Elem<T>::load(in + i);
 }
 
+// token_ids[dst[i]] = tokens[src[i]]: input ids that were sampled by the step before and have not
+// been read back to the host (miniserve/engine/model_runner.py:263-277 does this with index_copy).
+__global__ void fill_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ dst, const int* __restrict__ tokens,
+                                   const int* __restrict__ src, int n) {
+  pdl_prologue();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) token_ids[dst[i]] = tokens[src[i]];
+}
+
 }  // namespace ms
 
 using namespace ms;
+
+MS_EXPORT int ms_fill_tokens(int* token_ids, const int* dst, const int* tokens, const int* src, int n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  MS_LAUNCH(fill_tokens_kernel, (n + 127) / 128, 128, 0, stream, token_ids, dst, tokens, src, n);
+  return 0;
+}
 
 MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* ids, int tokens, int hidden,
                               int vocab, int dtype, cudaStream_t stream) {

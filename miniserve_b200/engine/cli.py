@@ -34,7 +34,8 @@ def add_engine_args(parser: argparse.ArgumentParser) -> None:
     g.add_argument("--schedule-policy", choices=["fcfs"], default="fcfs", help="admission order (only fcfs here)")
     g.add_argument("--block-backend", choices=["cpp"], default="cpp", help="block bookkeeping (C++ here)")
     g.add_argument("--disable-radix", action="store_true", help="no prefix cache (this engine has none)")
-    g.add_argument("--disable-overlap", action="store_true", help="no CPU-GPU overlap (this engine reads each step back)")
+    g.add_argument("--disable-overlap", action="store_true",
+                   help="read back each step's tokens before scheduling the next (no CPU-GPU overlap)")
     g.add_argument("--fused-ops", action="store_true", help="fused operators (this engine always uses its fused kernels)")
 
 
@@ -48,6 +49,7 @@ def engine_kwargs(args: argparse.Namespace) -> dict:
         chunked_prefill_size=args.chunked_prefill_size,
         cuda_graph=not args.disable_cuda_graph,
         cuda_graph_max_bs=args.cuda_graph_max_bs,
+        overlap=not args.disable_overlap,
     )
 
 

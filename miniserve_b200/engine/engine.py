@@ -1,8 +1,19 @@
-"""The engine loop: step() = schedule -> step function -> sample -> read back -> finish.
+"""The engine loop: step() = schedule -> launch (step function + sampling, nothing waits for the
+device) -> read back the PREVIOUS step's tokens and finish what ended.
 
-The same loop as miniserve/engine/engine.py:137-204 without its one-step-lag overlap: each step
-reads its sampled tokens back before the next is scheduled. Sampling stays on the device; the
-host reads the tokens (and the kernels' status word) once per step.
+The same loop as miniserve/engine/engine.py:137-204. With overlap scheduling (the default) a step
+is launched before the previous one is read back, so the host schedules and packs step t+1 while
+the GPU still runs step t:
+
+* a request that sampled a token in step t gets a placeholder output token, and its input id in
+  step t+1 is taken from step t's sampled tokens on the device;
+* a request that has sampled its last allowed token is not scheduled again;
+* a request that turns out to have sampled a stop token in step t was already given a row in
+  step t+1; that token is dropped when step t+1 is read back.
+
+Giving back the pages of a request that ended in step t while step t+1 still uses them is safe:
+they can be handed out again only when step t+2 is formed, and that runs after t+1 on the same
+stream.
 """
 
 from __future__ import annotations
@@ -16,18 +27,30 @@ import torch
 from ..cache.manager import CacheManager
 from ..parts.decoder import DecoderModel
 from ..sampling.sampler import Sampler
-from .request import Request, RequestState, SamplingParams
+from .request import PLACEHOLDER, Request, RequestState, SamplingParams
 from .scheduler import Plan, Scheduler
 from .step import StepError, StepFunction, StepRow
 
 DEFAULT_CHUNKED_PREFILL = 2048
 
 
+class _Launched:
+    """A launched step: its plan, the sampled tokens on the device (one per sampling row, then the
+    kernels' status word), their host copy once ``done``, each request's row among the sampled
+    tokens, and each sampling row's request and output slot."""
+
+    __slots__ = ("plan", "tokens", "host", "done", "row_of", "slots")
+
+    def __init__(self, plan, tokens, host, done, row_of, slots):
+        self.plan, self.tokens, self.host, self.done, self.row_of, self.slots = plan, tokens, host, done, row_of, slots
+
+
 class Engine:
     def __init__(self, model: DecoderModel, kv_pool_tokens: int | None = None, page_size: int = 16,
                  max_running: int = 64, max_prefill_tokens: int = 8192, chunked_prefill_size: int | None = None,
                  seed: int = 0, cuda_graph: bool = True, cuda_graph_max_bs: int | None = None,
-                 kv_mem_fraction: float = 0.9, cache: CacheManager | None = None, step_fn=None, sampler=None):
+                 kv_mem_fraction: float = 0.9, overlap: bool = True, cache: CacheManager | None = None, step_fn=None,
+                 sampler=None):
         """``kv_pool_tokens``: exact size of the cache pool in tokens, rounded down to whole pages
         (default: ``kv_mem_fraction`` of the memory the device has free after the weights, less a
         reserve for activations). ``chunked_prefill_size``: tokens per step, decode tokens included,
@@ -35,6 +58,7 @@ class Engine:
         prefill-only steps; default 2048. ``seed`` seeds the sampling of requests that bring no
         seed of their own, in submission order. ``cuda_graph``: replay captured CUDA graphs for
         decode-only steps of up to ``cuda_graph_max_bs`` requests (default ``max_running``).
+        ``overlap``: launch each step before reading back the previous one.
         Names and meanings follow miniserve/engine/engine.py:42-77. ``cache``, ``step_fn`` and
         ``sampler`` replace the ones the engine would build (a test can run the whole loop on the
         host against a stand-in step function this way)."""
@@ -60,7 +84,11 @@ class Engine:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.step_fn, self.sampler, cuda_graph_max_bs or max_running)
+        self.overlap = overlap
         self.num_steps = 0
+        self.launched: Plan | None = None  # the plan the last step() launched
+        self._inflight: _Launched | None = None
+        self._pinned: list[torch.Tensor] = []
 
     @staticmethod
     def _pool_pages(model, kv_pool_tokens, page_size, fraction, step_tokens, max_running) -> int:
@@ -102,9 +130,10 @@ class Engine:
 
     @property
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished
+        return self.scheduler.has_unfinished or self._inflight is not None
 
     def _retire(self, req: Request) -> None:
+        req.drop_pending()
         if req.cache is not None:
             self.cache.release(req.cache)
             req.cache = None
@@ -113,9 +142,19 @@ class Engine:
 
     # ------------------------------------------------------------------ the loop
     def step(self) -> Plan | None:
+        """Run one step. Returns the plan launched by this call (None if nothing could run). With
+        overlap the tokens it samples are read back by the NEXT call."""
         plan = self.scheduler.schedule()
-        if plan is None:
-            return None
+        prev = self._inflight
+        self.launched = plan
+        self._inflight = self._launch(plan, prev) if plan is not None else None
+        if not self.overlap:
+            prev, self._inflight = self._inflight, None
+        if prev is not None:
+            self._process(prev)
+        return plan
+
+    def _launch(self, plan: Plan, prev: _Launched | None) -> _Launched:
         self.num_steps += 1
         sampling = [r for r in plan.rows if r.completes]
         reqs = [r.request for r in sampling]
@@ -123,28 +162,69 @@ class Engine:
         args = None if greedy else dict(
             temperatures=[r.params.temperature for r in reqs], top_ps=[r.params.top_p for r in reqs],
             seeds=[r.seed for r in reqs], counters=[r.seq_len for r in reqs])
-        rows = [StepRow(r.request.cache, r.request.token_slice(r.start, r.count),
-                        (r.count - 1,) if r.completes else ()) for r in plan.rows]
+        rows = []
+        prev_tokens = None
+        for r in plan.rows:
+            req = r.request
+            tokens = req.token_slice(r.start, r.count)
+            fill_from = None
+            if tokens and tokens[-1] == PLACEHOLDER:
+                # only a decode row's single input can be a token that is not read back yet
+                if r.count != 1 or prev is None or req.rid not in prev.row_of:
+                    raise RuntimeError("a placeholder token outside a decode row, or without the step that sampled it")
+                fill_from, prev_tokens, tokens = prev.row_of[req.rid], prev.tokens, [0]
+            rows.append(StepRow(req.cache, tokens, (r.count - 1,) if r.completes else (), fill_from))
         if self.graphs is not None and self.logits_hook is None and plan.phase == "decode" and self.graphs.takes(len(rows)):
-            tokens = self.graphs.run(rows, args)
+            tokens = self.graphs.run(rows, args, prev_tokens=prev_tokens)
         else:
-            logits = self.step_fn.run(rows)
+            logits = self.step_fn.run(rows, prev_tokens=prev_tokens) if prev_tokens is not None else self.step_fn.run(rows)
             if self.logits_hook is not None:
                 self.logits_hook(plan, logits)
             tokens = self.sampler.sample(logits, **(args or {}))
-        host = torch.cat((tokens[:len(reqs)], self.step_fn.status)).tolist()
-        if host[-1]:
-            self.step_fn.status.zero_()
-            raise StepError(f"a kernel reported inconsistent cache metadata (code {host[-1]})")
-        host.pop()
-        for req, tok in zip(reqs, host):
-            req.output_ids.append(tok)
+        n = len(reqs)
+        both = torch.cat((tokens[:n], self.step_fn.status))
+        host, done = both, None
+        if both.is_cuda:
+            host = self._pinned_buffer(n + 1)
+            host.copy_(both, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        slots = []
+        for req in reqs:
+            slots.append((req, len(req.output_ids)))
+            req.output_ids.append(PLACEHOLDER)
+            req.num_pending += 1
             if req.state is RequestState.PREFILL:
                 req.transition(RequestState.DECODE)
-            if req.should_stop():
+        return _Launched(plan, tokens, host, done, {req.rid: i for i, req in enumerate(reqs)}, slots)
+
+    def _pinned_buffer(self, n: int) -> torch.Tensor:
+        """Two pinned staging buffers in turn: the one a launch writes was read back a step ago."""
+        if len(self._pinned) < 2 or self._pinned[0].numel() < n:
+            size = max(n, 2 * (self._pinned[0].numel() if self._pinned else 64))
+            self._pinned = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._pinned.reverse()
+        return self._pinned[0][:n]
+
+    def _process(self, launched: _Launched) -> None:
+        """Wait for the launched step's tokens (the one device-to-host wait of a step), put them in
+        place of the placeholders, and retire the requests that ended."""
+        if launched.done is not None:
+            launched.done.synchronize()
+        values = launched.host.tolist()
+        status = values.pop()
+        if status:
+            self.step_fn.status.zero_()
+            raise StepError(f"a kernel reported a fault it caught itself (code {status})")
+        for (req, slot), tok in zip(launched.slots, values):
+            if req.is_done:  # ended before (this token lies past its end)
+                continue
+            req.output_ids[slot] = tok
+            req.num_pending -= 1
+            if slot + 1 >= req.params.max_new_tokens or tok in req.params.stop_token_ids:
+                req.drop_pending()
                 req.transition(RequestState.FINISHED)
                 self._retire(req)
-        return plan
 
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams]) -> list[list[int]]:
         """Submit all prompts (token ids) at once and run to completion; output token ids per prompt."""
@@ -152,6 +232,6 @@ class Engine:
             params = [params] * len(prompts)
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         while self.has_unfinished:
-            if self.step() is None:
+            if self.step() is None and self._inflight is None and self.scheduler.has_unfinished:
                 raise RuntimeError("the scheduler produced no step although requests are unfinished")
         return [r.output_ids for r in reqs]

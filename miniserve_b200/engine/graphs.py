@@ -56,7 +56,7 @@ class DecodeGraphs:
     def _bucket(self, n: int) -> int:
         return next(b for b in self.buckets if b >= n)
 
-    def run(self, rows: Sequence[StepRow], sampling: dict | None) -> torch.Tensor:
+    def run(self, rows: Sequence[StepRow], sampling: dict | None, prev_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """One decode step (every row brings one token and wants its logits). Returns the
         sampled tokens of the real rows, int32 on the device."""
         sf = self.step_fn
@@ -69,7 +69,7 @@ class DecodeGraphs:
         mode = "greedy"
         if sampling is not None:
             mode = "top_p" if any(p < 1 for p in sampling["top_ps"]) else "temperature"
-        ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True)
+        ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # the arena moved while preparing
             self._graphs.clear()
             self._generation = sf.arena_generation

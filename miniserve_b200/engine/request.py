@@ -29,12 +29,19 @@ class RequestState(enum.Enum):
 
 
 _EDGES = {
-    RequestState.WAITING: {RequestState.PREFILL, RequestState.ABORTED},
+    # WAITING -> FINISHED: with overlap scheduling, a request preempted before its last sampled
+    # token was read back, which then turns out to end it
+    RequestState.WAITING: {RequestState.PREFILL, RequestState.ABORTED, RequestState.FINISHED},
     RequestState.PREFILL: {RequestState.DECODE, RequestState.FINISHED, RequestState.ABORTED, RequestState.WAITING},
     RequestState.DECODE: {RequestState.FINISHED, RequestState.ABORTED, RequestState.WAITING},
     RequestState.FINISHED: set(),
     RequestState.ABORTED: set(),
 }
+
+
+# Output slot of a token that was sampled on the device and has not been read back yet
+# (overlap scheduling, miniserve/engine/request.py:47).
+PLACEHOLDER = -1
 
 
 class InvalidTransition(RuntimeError):
@@ -79,6 +86,7 @@ class Request:
     cache: RequestCache | None = None  # held between admission and release
     seed: int = 0
     num_preemptions: int = 0
+    num_pending: int = 0  # trailing PLACEHOLDER entries of output_ids
 
     def __post_init__(self):
         if not self.prompt_ids:
@@ -118,6 +126,17 @@ class Request:
         if start + n <= p:
             return self.prompt_ids[start:start + n]
         return self.prompt_ids[start:] + self.output_ids[:start + n - p]
+
+    @property
+    def ready_ids(self) -> list[int]:
+        """Output tokens read back so far."""
+        return self.output_ids[:len(self.output_ids) - self.num_pending]
+
+    def drop_pending(self) -> None:
+        """Forget tokens sampled after the request ended (launched before its end was known)."""
+        if self.num_pending:
+            del self.output_ids[-self.num_pending:]
+            self.num_pending = 0
 
     def should_stop(self) -> bool:
         return self.reached_max_tokens or (bool(self.output_ids) and self.output_ids[-1] in self.params.stop_token_ids)

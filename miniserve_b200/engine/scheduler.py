@@ -142,11 +142,17 @@ class Scheduler:
         """Preempt until what ``pool`` may still allocate fits into the free pages."""
         preempted: list[Request] = []
         while not self.cache.fits(self._outstanding(pool)):
-            candidates = [r for r in pool if r is not self.running[0]]
-            if not candidates:
-                raise RuntimeError("a lone request does not fit in the pool")  # add() rejects those
-            victim = candidates[-1]
-            if pool is not self.running:
+            # requests that have sampled their last token and only wait for it to be read back cost
+            # nothing to preempt (they will never run again): take those first
+            spent = [r for r in self.running if r.state is RequestState.DECODE and r.reached_max_tokens]
+            if spent:
+                victim = spent[-1]
+            else:
+                candidates = [r for r in pool if r is not self.running[0]]
+                if not candidates:
+                    raise RuntimeError("a lone request does not fit in the pool")  # add() rejects those
+                victim = candidates[-1]
+            if pool is not self.running and victim in pool:
                 pool.remove(victim)
             self._preempt(victim)
             preempted.append(victim)
@@ -182,6 +188,8 @@ class Scheduler:
         for req in list(self.waiting):
             if budget <= 0 or len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
                 break
+            if req.num_pending:  # its last token is not read back yet; its prefill needs it
+                break
             if not self.cache.fits(self._admission_need(req), margin=self._outstanding(self.running)):
                 break
             self._admit(req)
@@ -197,6 +205,8 @@ class Scheduler:
         budget = self.max_prefill_tokens
         for req in list(self.waiting):
             if len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
+                break
+            if req.num_pending:
                 break
             if admitted and req.seq_len > budget:  # the first is admitted even over the budget
                 break

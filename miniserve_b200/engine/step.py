@@ -30,6 +30,9 @@ class StepRow:
     cache: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # If set, the row brings one token that the host does not know yet: it is entry ``fill_from``
+    # of the previous step's sampled tokens, still on the device (``tokens`` then holds any valid id).
+    fill_from: int | None = None
 
 
 class StepError(RuntimeError):
@@ -90,18 +93,18 @@ class StepFunction:
                 + pages + 64)
 
     # ------------------------------------------------------------------ the step
-    def run(self, rows: Sequence[StepRow], pad_rows: int = 0) -> torch.Tensor:
+    def run(self, rows: Sequence[StepRow], pad_rows: int = 0, prev_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Run one step. Returns float32 logits ``[wanted, vocab]`` on the device, in the order
         of the rows and of each row's ``want``. Raises ``OutOfBlocks`` (nothing changed) if
         the pool cannot hold the step's new tokens."""
-        ctx = self.prepare(rows, pad_rows)
+        ctx = self.prepare(rows, pad_rows, prev_tokens=prev_tokens)
         logits = self.model.forward(ctx, self.cache.entry_views)
         for r in rows:
             self.cache.trim(r.cache)
         return logits
 
     def prepare(self, rows: Sequence[StepRow], pad_rows: int = 0, indices_cap: int = 0,
-                want_pad_rows: bool = False) -> StepContext:
+                want_pad_rows: bool = False, prev_tokens: torch.Tensor | None = None) -> StepContext:
         """Reserve pages, pack the step and start its copy to the device. ``pad_rows`` adds
         padding rows (one token at position 0 on a page outside the allocator);
         ``indices_cap`` / ``want_pad_rows`` ask for the layout that depends on the padded row
@@ -127,7 +130,11 @@ class StepFunction:
         want_arr = np.asarray(want, dtype=np.int32)
         slots = np.fromiter((r.cache.state_slot for r in rows), dtype=np.int32, count=len(rows))
 
-        need = self._arena_need(rows, pad_rows, indices_cap)
+        fills = [(i, r.fill_from) for i, r in enumerate(rows) if r.fill_from is not None]
+        if fills:
+            if prev_tokens is None or any(len(rows[i].tokens) != 1 for i, _ in fills):
+                raise ValueError("a row filled from the previous step brings exactly one token and needs that step's tokens")
+        need = self._arena_need(rows, pad_rows, indices_cap) + 2 * len(fills) + 8
         if need > self._arena_ints:
             torch.cuda.current_stream(self.device).synchronize()
             self._grow(2 * need)
@@ -159,8 +166,20 @@ class StepFunction:
             native.host_check(int(-total))
         stream = torch.cuda.current_stream(self.device)
         dev = self._dev_arena
+        packed = int(total)
+        if fills:
+            # (flat token index, entry of the previous step's tokens) pairs ride behind the packed step
+            starts = np.concatenate(([0], np.cumsum(q_len)[:-1]))
+            tail = np.asarray([starts[i] for i, _ in fills] + [src for _, src in fills], dtype=np.int32)
+            pinned[packed:packed + tail.size] = torch.from_numpy(tail)
+            total = packed + tail.size
         dev[:total].copy_(pinned[:total], non_blocking=True)
         self.h2d_bytes += int(total) * 4
+        if fills:
+            k = native.kernels()
+            native.kernel_check(k.ms_fill_tokens(dev[int(offsets[0]):].data_ptr(), dev[packed:].data_ptr(), prev_tokens.data_ptr(),
+                                                 dev[packed + len(fills):].data_ptr(), len(fills), stream.cuda_stream))
+            total = packed
         ev = torch.cuda.Event()
         ev.record(stream)
         self._events[turn] = ev

@@ -41,7 +41,12 @@ class ToyStep:
         g = torch.Generator().manual_seed(int.from_bytes(h[:8], "little") % (2 ** 63))
         return torch.randn(VOCAB, generator=g)
 
-    def run(self, rows):
+    def run(self, rows, prev_tokens=None):
+        rows = list(rows)
+        for r in rows:
+            if r.fill_from is not None:  # a token the host has not read back yet: it is on the "device"
+                assert len(r.tokens) == 1 and prev_tokens is not None
+                r.tokens = [int(prev_tokens[r.fill_from])]
         self.cache.reserve([(r.cache, len(r.tokens)) for r in rows])
         self.max_tokens_seen = max(self.max_tokens_seen, sum(len(r.tokens) for r in rows))
         out = []
@@ -70,10 +75,10 @@ class ToySampler:
                              for i in range(n)], dtype=torch.int32)
 
 
-def _engine(pages, page=4, chunk=8, max_running=64, **kw):
+def _engine(pages, page=4, chunk=8, max_running=64, overlap=False, **kw):
     cm = _cache(pages, page, max_running)
     eng = Engine(None, cache=cm, step_fn=ToyStep(cm), sampler=ToySampler(), max_running=max_running,
-                 chunked_prefill_size=chunk, cuda_graph=False, **kw)
+                 chunked_prefill_size=chunk, cuda_graph=False, overlap=overlap, **kw)
     return eng
 
 
@@ -224,6 +229,32 @@ def test_abort_gives_everything_back():
     eng.abort(12345)  # unknown ids are ignored
 
 
+def test_overlap_launches_before_it_reads_back():
+    eng = _engine(pages=32, chunk=8, overlap=True)
+    a = eng.add_request([4, 5, 6], SamplingParams(4))
+    eng.step()  # launches the prefill; nothing is read back yet
+    assert a.output_ids == [-1] and a.num_pending == 1 and a.state is RequestState.DECODE and a.ready_ids == []
+    plan = eng.step()  # launches the first decode step with a placeholder input, reads the prefill's token
+    assert plan.phase == "decode" and a.num_pending == 1 and len(a.ready_ids) == 1
+    while eng.has_unfinished:
+        eng.step()
+    assert a.output_ids == _alone([4, 5, 6], SamplingParams(4), a.seed) and a.num_pending == 0
+    assert eng.cache.is_idle()
+
+
+def test_overlap_drops_the_token_sampled_past_a_stop():
+    free_run = _alone([4, 5, 6], SamplingParams(8), 0)
+    stop = free_run[2]
+    eng = _engine(pages=32, chunk=8, overlap=True)
+    r = eng.add_request([4, 5, 6], SamplingParams(8, stop_token_ids=frozenset({stop})))
+    other = eng.add_request([9, 9], SamplingParams(8))
+    while eng.has_unfinished:
+        eng.step()
+    assert r.output_ids == free_run[:free_run.index(stop) + 1] and r.num_pending == 0
+    assert other.output_ids == _alone([9, 9], SamplingParams(8), other.seed)
+    assert eng.cache.is_idle()
+
+
 def test_stop_token_is_kept_and_ends_the_request():
     eng = _engine(pages=16, chunk=8)
     free_run = _alone([4, 5, 6], SamplingParams(6), 0)
@@ -236,12 +267,13 @@ def test_stop_token_is_kept_and_ends_the_request():
 
 
 # ------------------------------------------------------------------ randomised load
+@pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("pages, chunk", [(8, 3), (16, 3), (64, 3), (8, 2048), (16, 2048), (64, 2048), (8, 0), (64, 0)])
-def test_random_load_equals_each_request_alone(pages, chunk):
+def test_random_load_equals_each_request_alone(pages, chunk, overlap):
     preemptions = 0
     for seed in range(6):
         rng = random.Random(1000 * pages + seed)
-        eng = _engine(pages=pages, page=4, chunk=chunk, max_running=6, seed=seed, max_prefill_tokens=24)
+        eng = _engine(pages=pages, page=4, chunk=chunk, max_running=6, seed=seed, max_prefill_tokens=24, overlap=overlap)
         specs = []
         for i in range(12):
             prompt = [rng.randrange(VOCAB) for _ in range(rng.randint(1, 14))]
@@ -258,8 +290,8 @@ def test_random_load_equals_each_request_alone(pages, chunk):
                     reqs.append(eng.add_request(*pending.pop(0)))
             if eng.has_unfinished:
                 plan = eng.step()
-                assert plan is not None
-                if chunk:
+                assert plan is not None or eng.overlap
+                if chunk and plan is not None:
                     assert plan.num_tokens <= max(chunk, plan.num_decode)
                 eng.cache.check_invariants()
             steps += 1
