@@ -6,17 +6,13 @@
 // absolute position p sees keys 0..p of its request (or the last `window`), query head h reads kv
 // head h / (heads / kv_heads), softmax in float32 with scale head_dim^-0.5.
 //
-// One CTA owns 128 query rows: G query heads of one kv head x 128/G consecutive tokens, so that
-// the G heads share every K/V tile. Roles by warp:
-//   warps 0-3  softmax: thread r owns row r (tensor-memory lane r). Per key tile it reads its row
-//              of S with tcgen05.ld, masks, keeps a running maximum and sum, writes P (bf16) into
-//              shared memory in the tensor core's K-major swizzled layout, and rescales O in tensor
-//              memory only when the maximum has grown by more than 2^8 (the stale maximum is exact
-//              in the end because the same one scales the sum);
-//   warp 4     one lane issues all TMA loads: Q once, then K and V tiles (128 keys) page by page
-//              into a two-stage ring;
-//   warp 5     allocates tensor memory; one lane issues the MMAs: S(j+1) is issued before P(j) is
-//              ready so that the tensor cores work while the softmax of tile j runs.
+// One CTA owns 256 query rows in two groups of 128 (G query heads of one kv head x 128/G
+// consecutive tokens each), so that every K/V tile is fetched once for all of them. Thread r of a
+// softmax group owns row r (tensor-memory lane r): per key tile it reads its row of S with
+// tcgen05.ld, masks it if the tile touches the diagonal, a window's edge or the request's end,
+// keeps a running maximum and sum, stores P (bfloat16) back into tensor memory, and rescales O
+// only when the maximum has grown by more than 2^8 (the stale maximum is exact in the end because
+// the same one scales the sum).
 // Every mbarrier wait is bounded; on a timeout the kernel raises the status word and winds down.
 #include <cuda.h>
 
@@ -31,7 +27,6 @@
 namespace ms {
 
 constexpr int AT_D = 128, AT_ROWS = 128, AT_KEYS = 128;
-constexpr int AT_THREADS = 192;
 constexpr uint32_t AT_WAIT_LIMIT = 1u << 24;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 constexpr int AT_BLOCK = 128 * 64 * 2;  // one [128 rows][64 bf16] swizzled block: 16 KB
@@ -122,6 +117,23 @@ __device__ __forceinline__ float at_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA pipes (for x <= 8): round to the nearest integer with the 1.5 * 2^23 trick, a
+// cubic for 2^fraction on [-0.5, 0.5] (relative error 1e-4, far below the bfloat16 rounding of P),
+// and the integer part added to the exponent bits. Used for a share of the elements so that the
+// special-function unit (16 ex2 per clock per SM) would not limit the softmax. Measured on B200 it
+// is not the limit here (0, 2, 3 or 4 of every 8 emulated: 411, 427, 421, 431 us for 8,192 tokens).
+__device__ __forceinline__ float at_ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0558382829f, 0.2426394785f);
+  p = fmaf(p, f, 0.6931367339f);
+  p = fmaf(p, f, 0.9999245570f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+#ifndef AT_EMULATED_OF_8
+#define AT_EMULATED_OF_8 0  // of every 8 exponentials, this many go to the FMA pipes (measured: no gain, so none)
+#endif
 #define AT_FENCE_BEFORE() asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory")
 #define AT_FENCE_AFTER() asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory")
 
@@ -130,42 +142,77 @@ __host__ __device__ constexpr uint32_t at_idesc(bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// The kernel: 256 query rows per CTA as two groups of 128 that take turns on the tensor cores.
+// Both groups (A: tokens m0 .. m0+tpc-1, B: the next tpc tokens; G heads each) attend over the
+// same K/V tiles, so every tile is fetched once for twice the rows. While group A's softmax
+// warps work on tile j, the tensor cores run group B's products, and the other way round. P never
+// goes through shared memory: the softmax threads store it (bfloat16, two per 32-bit column) into
+// the tensor-memory columns its S tile occupied, and the second product takes its A operand from
+// there. Tensor memory: S/P of A [0,128), S/P of B [128,256), O of A [256,384), O of B [384,512).
+// Warps 0-3: softmax A, 4-7: softmax B, 8: TMA, 9: MMA.
+constexpr int AT_THREADS = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
+
 struct AtSmem {
-  // offsets from a 1024-byte aligned base
-  static constexpr int q = 0;                         // 2 blocks
-  static constexpr int kv = 2 * AT_BLOCK;             // 2 stages x (K: 2 blocks, V: 2 blocks)
+  static constexpr int q = 0;                     // group A: 2 blocks, group B: 2 blocks
+  static constexpr int kv = 4 * AT_BLOCK;         // 2 stages x (K: 2 blocks, V: 2 blocks)
   static constexpr int stage = 4 * AT_BLOCK;
-  static constexpr int p = kv + 2 * stage;            // 2 buffers x 2 blocks
-  static constexpr int total = p + 4 * AT_BLOCK;      // 14 blocks = 224 KB
+  static constexpr int total = kv + 2 * stage;    // 12 blocks = 192 KB
 };
+
+__device__ __forceinline__ void at_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void at_tmem_st16(uint32_t taddr, const uint32_t (&u)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
+        "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15])
+      : "memory");
+}
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
-                       const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
-                       const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                       int page_shift, int G, int* __restrict__ status, int dbg) {
+                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
+                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
+                        int page_shift, int G, int* __restrict__ status, long long* __restrict__ trace) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done[2];
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_final[2];
+  // timing experiments only: the first CTA stamps clock64() at its hand-off points
+  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#define AT_STAMP(slot) do { if (tracing) trace[(slot)] = clock64(); } while (0)
   __shared__ uint32_t tmem_slot;
 
   pdl_prologue();
   const int r = blockIdx.y;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
-  const int tpc = AT_ROWS / G;  // tokens per CTA
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * tpc;  // later tiles see more keys: start them first
-  if (m0 >= q_len) return;  // uniform for the CTA, before any barrier or allocation
+  const int tpc = AT_ROWS / G;                                  // tokens per group
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * 2 * tpc;       // later tiles see more keys: start them first
+  if (m0 >= q_len) return;
   const int start = q_start[r], kv_len = start + q_len;
   const int head0 = blockIdx.z * G, kvh = head0 / (nq / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int q_first = start + m0, q_last = start + min(m0 + tpc, q_len) - 1;
-  const int hi = min(kv_len, q_last + 1);
-  const int lo = window > 0 ? max(0, q_first - window + 1) : 0;
-  const int lo_max = window > 0 ? max(0, q_last - window + 1) : 0;  // the highest lower bound among the rows
-  const int tile_begin = lo / AT_KEYS, tile_end = (hi + AT_KEYS - 1) / AT_KEYS;
-  const int n_tiles = tile_end - tile_begin;
+  // per group: the key tiles it needs (B needs at least as many as A; B may have no rows at all)
+  const bool has_b = m0 + tpc < q_len;
+  int n_tiles[2], q_first[2], q_last[2], lo_g[2], lo_max[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    q_first[g] = start + m0 + g * tpc;
+    q_last[g] = start + min(m0 + (g + 1) * tpc, q_len) - 1;
+    lo_g[g] = window > 0 ? max(0, q_first[g] - window + 1) : 0;
+    lo_max[g] = window > 0 ? max(0, q_last[g] - window + 1) : 0;
+  }
+  const int tile_begin = lo_g[0] / AT_KEYS;
+  n_tiles[0] = (min(kv_len, q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin;
+  n_tiles[1] = has_b ? (min(kv_len, q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin : 0;
+  const int n_all = max(n_tiles[0], n_tiles[1]);
 
   if (threadIdx.x == 0) {
     at_mbar_init(&q_full, 1);
@@ -173,14 +220,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       at_mbar_init(&kv_full[i], 1);
       at_mbar_init(&kv_empty[i], 1);
       at_mbar_init(&s_full[i], 1);
-      at_mbar_init(&s_empty[i], 128);
+      at_mbar_init(&p_full[i], 128);
+      at_mbar_init(&o_final[i], 1);
     }
-    at_mbar_init(&p_full, 128);
-    at_mbar_init(&pv_done[0], 1);
-    at_mbar_init(&pv_done[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(at_smem(&tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -188,26 +233,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   AT_FENCE_AFTER();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tmem_s[2] = {tmem, tmem + 128u};
-  const uint32_t tmem_o = tmem + 256u;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
-    // Lane 0 issues every copy; all lanes fetch the tile's page ids together (one coalesced load
-    // instead of a chain of dependent ones).
     if (lane == 0) {
-      at_expect_tx(&q_full, 2 * AT_BLOCK);
+      at_expect_tx(&q_full, (has_b ? 4 : 2) * AT_BLOCK);
       at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
       at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
+      if (has_b) {
+        at_tma_3d(smem + AtSmem::q + 2 * AT_BLOCK, &map_q, &q_full, 0, head0, tok0 + m0 + tpc);
+        at_tma_3d(smem + AtSmem::q + 3 * AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0 + tpc);
+      }
     }
     const int* pages = page_indices + page_indptr[r];
     const int page_size = 1 << page_shift;
     const int box_rows = min(page_size, AT_KEYS);
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; j < n_all; ++j) {
       const int s = j & 1;
       const int key0 = (tile_begin + j) * AT_KEYS;
-      const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;  // pages that exist
+      const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
       int my_row = 0;
       if (lane < boxes) {
         const int key = key0 + lane * box_rows;
@@ -218,196 +263,185 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) {
-          if (lane == 0) atomicExch(status, 21);
+          if (lane == 0) atomicExch(status, 31);
           break;
         }
       }
       unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
       unsigned char* vt = kt + 2 * AT_BLOCK;
-      if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * ((dbg & 8) ? 2 : 4));
-      __syncwarp();  // the expected byte count is posted before any copy can complete
-      if (lane < boxes) {  // every lane issues the four copies of its own page
+      if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
+      __syncwarp();
+      if (lane < boxes) {
         const int off = lane * box_rows * 128;
         at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
         at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
-        if (!(dbg & 8)) {
-          at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
-          at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
-        }
+        at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
+        at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
     if (at_elect()) {
       constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
       bool ok = at_wait(&q_full, 0);
-      if (!ok) atomicExch(status, 22);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!at_wait(&kv_full[s], (j >> 1) & 1)) return false;
-        if (j >= 2 && !at_wait(&s_empty[s], ((j >> 1) - 1) & 1)) return false;
+      int kv_ready = -1;  // the last tile whose kv_full this thread has waited for
+      auto need_kv = [&](int j) -> bool {
+        if (j <= kv_ready) return true;
+        if (!at_wait(&kv_full[j & 1], (j >> 1) & 1)) return false;
+        kv_ready = j;
         AT_FENCE_AFTER();
-        const unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
-#pragma unroll
-        for (int kk = 0; kk < AT_D / 16; ++kk) {
-          const uint64_t da = at_desc(smem + AtSmem::q + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-          const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-          at_mma(tmem_s[s], da, db, idesc_s, kk != 0);
-        }
-        at_commit(&s_full[s]);
         return true;
       };
-      if (ok && n_tiles > 0) ok = issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);
-        if (!ok) break;
-        if (!at_wait(&p_full, j & 1)) {
-          ok = false;
-          break;
-        }
-        AT_FENCE_AFTER();
-        const int s = j & 1;
-        const unsigned char* vt = smem + AtSmem::kv + s * AtSmem::stage + 2 * AT_BLOCK;
+      auto issue_s = [&](int g, int j) -> bool {
+        if (!need_kv(j)) return false;
+        const unsigned char* kt = smem + AtSmem::kv + (j & 1) * AtSmem::stage;
+        const unsigned char* qt = smem + AtSmem::q + g * 2 * AT_BLOCK;
 #pragma unroll
-        for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
-          // A = P [rows][keys], K-major: 16 keys = 32 bytes along the row; B = V [keys][d], MN-major:
-          // the two 64-wide halves of d are one block apart, 8-key groups 1024 bytes apart
-          const uint64_t da = at_desc(smem + AtSmem::p + (s * 2 + (kk >> 2)) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-          const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
-          at_mma(tmem_o, da, db, idesc_o, (j | kk) != 0);
+        for (int kk = 0; kk < AT_D / 16; ++kk) {
+          const uint64_t da = at_desc(qt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+          const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+          at_mma(tmem + (uint32_t)(g * 128), da, db, idesc_s, kk != 0);
         }
-        at_commit(&kv_empty[s]);
-        at_commit(&pv_done[s]);
+        at_commit(&s_full[g]);
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok && n_tiles[1] > 0) ok = issue_s(1, 0);
+      for (int j = 0; j < n_all && ok; ++j) {
+        const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
+#pragma unroll 1
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (j >= n_tiles[g]) continue;
+          if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
+          AT_FENCE_AFTER();
+          if (j < 40) AT_STAMP(16 * j + 1 + 2 * g);
+#pragma unroll
+          for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
+            // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
+            // B = V [keys][d], MN-major
+            const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
+            at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
+          }
+          if (j < 40) AT_STAMP(16 * j + 2 + 2 * g);
+          if (j + 1 < n_tiles[g]) {
+            ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
+          } else {
+            at_commit(&o_final[g]);
+          }
+        }
+        if (ok) at_commit(&kv_empty[j & 1]);
       }
-      if (!ok) atomicExch(status, 23);
+      if (!ok) atomicExch(status, 33);
     }
   } else {
-    // ------------------------------------------------------------ softmax, thread = row
-    const int row = threadIdx.x;                    // 0..127, also the tensor-memory lane
-    const int tok = row / G, hd = row - tok * G;    // rows are ordered token-major, head-minor
-    const int qpos = start + m0 + tok;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // ------------------------------------------------------------ softmax, thread = row of its group
+    const int g = warp >> 2;
+    const int row = threadIdx.x & 127;                // row within the group = tensor-memory lane
+    const int tok = row / G, hd = row - tok * G;
+    const int tok_in_req = m0 + g * tpc + tok;
+    const int qpos = start + tok_in_req;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
+    const int n_mine = n_tiles[g];
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      if (!at_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
+    for (int j = 0; j < n_mine && ok; ++j) {
+      if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
       AT_FENCE_AFTER();
-      float sv[4][32];
-      if (!(dbg & 4)) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) at_tmem_ld32(tmem_s[b] + lane_base + (uint32_t)(c * 32), sv[c]);
-      } else {
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sv[c][i] = (float)(i + c);
-      }
-      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      AT_FENCE_BEFORE();
-      at_arrive(&s_empty[b]);
+      if (row == 0 && j < 40) AT_STAMP(16 * j + 8 + 3 * g);
       const int key0 = (tile_begin + j) * AT_KEYS;
-      // Only tiles that touch the diagonal, the window's edge or the end of the request need the
-      // mask; the maximum is tracked on the raw scores (the scale is positive).
-      const bool interior = key0 + AT_KEYS - 1 <= q_first && key0 >= lo_max;
-      float m_tile = -INFINITY;
-      if (dbg & 2) {
-        m_tile = sv[0][0];
-      } else if (interior) {
+      const bool interior = key0 + AT_KEYS - 1 <= q_first[g] && key0 >= lo_max[g];
+      // the whole row of scores in registers: four loads in flight, one wait
+      float sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (interior) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, sv[c][i]);
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
       } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
-            const bool valid = key <= qpos && key >= lo && (window <= 0 || key > qpos - window);
+            const bool valid = key <= qpos && key >= lo_g[g] && (window <= 0 || key > qpos - window);
             sv[c][i] = valid ? sv[c][i] : -INFINITY;
-            m_tile = fmaxf(m_tile, sv[c][i]);
+            mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
           }
       }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      if (row == 0 && j < 40) AT_STAMP(16 * j + 9 + 3 * g);
       const float m_new = fmaxf(m_used, m_tile);
       float alpha = 1.f;
       bool rescale = false;
       if (m_used == -INFINITY) {
-        m_used = m_new;  // nothing accumulated yet for this row
+        m_used = m_new;
       } else if ((m_new - m_used) * scale_log2 > 8.f) {
         alpha = at_ex2((m_used - m_new) * scale_log2);
         m_used = m_new;
         rescale = true;
       }
       if (__any_sync(0xffffffffu, rescale)) {
-        // O may only be touched once the PV product of the previous tile has completed
-        if (!at_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
-        AT_FENCE_AFTER();
+        // S(j) is complete, so the product P(j-1) V(j-1) issued before it is complete too: O is quiet
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float ov[32];
-          at_tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
           for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-          at_tmem_st32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+          at_tmem_st32(t_o + (uint32_t)(c * 32), ov);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
         l_sum *= alpha;
       }
-      // this tile's P buffer was last read by the PV product two tiles ago
-      if (j >= 2 && !at_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
+      // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
+      // (masked scores are -inf and give 0)
       const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
       float part[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned char* p_row = smem + AtSmem::p + b * 2 * AT_BLOCK + row * 128;
-      if (!(dbg & 1))
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          float e[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            e[x] = at_ex2(fmaf(sv[c][i + x], scale_log2, -m_sub));  // ex2(-inf) = 0 for masked keys
-            part[x & 3] += e[x];
-          }
-          uint4 pk;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(e[0], e[1]), p1 = __floats2bfloat162_rn(e[2], e[3]);
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(e[4], e[5]), p3 = __floats2bfloat162_rn(e[6], e[7]);
-          pk.x = *reinterpret_cast<uint32_t*>(&p0);
-          pk.y = *reinterpret_cast<uint32_t*>(&p1);
-          pk.z = *reinterpret_cast<uint32_t*>(&p2);
-          pk.w = *reinterpret_cast<uint32_t*>(&p3);
-          const int chunk = c * 4 + (i >> 3);  // 16 chunks of 8 keys
-          *reinterpret_cast<uint4*>(p_row + (chunk >> 3) * AT_BLOCK + (((chunk & 7) ^ (row & 7)) << 4)) = pk;
+        for (int i = 0; i < 32; i += 2) {
+          const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
+          const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
+          const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
+          part[(i >> 1) & 3] += e0 + e1;
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
         }
-      const float row_sum = (part[0] + part[1]) + (part[2] + part[3]);
-      l_sum += row_sum;
-      // keys past the end of the request in this tile: their V rows may hold anything (even NaN);
-      // P is zero there, but 0 * NaN is NaN, so zero those rows of V
+        at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
+      }
+      l_sum += (part[0] + part[1]) + (part[2] + part[3]);
       const int valid_keys = kv_len - key0;
       if (valid_keys < AT_KEYS && row >= valid_keys) {
-        unsigned char* vt = smem + AtSmem::kv + b * AtSmem::stage + 2 * AT_BLOCK;
+        unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(vt + h * AT_BLOCK + row * 128 + cc * 16) = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
       AT_FENCE_BEFORE();
-      at_arrive(&p_full);
+      at_arrive(&p_full[g]);
+      if (row == 0 && j < 40) AT_STAMP(16 * j + 10 + 3 * g);
     }
-    if (ok && n_tiles > 0) ok = at_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
-    if (!ok) atomicExch(status, 24);
+    if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
+    if (!ok) atomicExch(status, 34);
     AT_FENCE_AFTER();
-    if (ok) {
-      const bool store = m0 + tok < q_len;  // rows of the tile past the end of the request are dropped
+    if (ok && n_mine > 0) {
+      const bool store = tok_in_req < q_len;
       const float inv = 1.0f / l_sum;
-      __nv_bfloat16* dst = out + ((size_t)(tok0 + m0 + (store ? tok : 0)) * nq + head0 + hd) * AT_D;
+      __nv_bfloat16* dst = out + ((size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd) * AT_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float ov[32];
-        at_tmem_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);  // warp-wide: every lane takes part
+        at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         if (store) {
 #pragma unroll
@@ -427,7 +461,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   AT_FENCE_BEFORE();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
   }
 }
@@ -453,6 +487,11 @@ static int at_get_encode(AtEncodeFn* out) {
 }  // namespace ms
 
 using namespace ms;
+
+static long long* g_trace = nullptr;
+// Timing experiments only: a device buffer of 1024 int64 that the first CTA of the next launches
+// stamps with clock64() at its hand-off points (null: off).
+MS_EXPORT void ms_attn_tc_set_trace(long long* buffer) { g_trace = buffer; }
 
 MS_DEFINE_LAST_ERROR(ms_attn_tc_last_error)
 MS_DEFINE_PDL_SWITCH(ms_attn_tc_set_pdl)
@@ -499,17 +538,16 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     MS_CHECK_ARG(res == CUDA_SUCCESS, "attention_tc: encoding the cache map failed with code %d", (int)res);
   }
-  constexpr size_t smem = AtSmem::total + 1024;
-  static bool configured = false;
-  if (!configured) {
-    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
-  static const int dbg = getenv("MINISERVE_ATTN_TC_DEBUG") ? atoi(getenv("MINISERVE_ATTN_TC_DEBUG")) : 0;  // timing experiments only
-  dim3 grid(ceil_div(max_q_len, tpc), num_rows, nq / G);
-  MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q, q_start,
-            page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, dbg);
+  constexpr size_t smem_bytes = AtSmem::total + 1024;
+  static bool configured = false;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    configured = true;
+  }
+  dim3 grid(ceil_div(max_q_len, 2 * tpc), num_rows, nq / G);
+  MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, g_trace);
   return 0;
 }
