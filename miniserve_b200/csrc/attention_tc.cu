@@ -175,12 +175,36 @@ __device__ __forceinline__ void at_tmem_st16(uint32_t taddr, const uint32_t (&u)
       : "memory");
 }
 
+// eight float32 scaled by `inv`, as eight bfloat16
+__device__ __forceinline__ uint4 at_pack8(const float* v, float inv) {
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0] * inv, v[1] * inv), p1 = __floats2bfloat162_rn(v[2] * inv, v[3] * inv);
+  __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * inv, v[5] * inv), p3 = __floats2bfloat162_rn(v[6] * inv, v[7] * inv);
+  uint4 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&p0);
+  pk.y = *reinterpret_cast<uint32_t*>(&p1);
+  pk.z = *reinterpret_cast<uint32_t*>(&p2);
+  pk.w = *reinterpret_cast<uint32_t*>(&p3);
+  return pk;
+}
+// barriers of one softmax group (128 threads, hardware barrier `id`): plain, and with an OR over a flag
+__device__ __forceinline__ void at_group_sync(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id) : "memory"); }
+__device__ __forceinline__ bool at_group_any(int id, bool flag) {
+  uint32_t res;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+      "bar.red.or.pred q, %1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(res) : "r"(id), "r"((uint32_t)flag) : "memory");
+  return res != 0;
+}
+
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                        int page_shift, int G, int* __restrict__ status, long long* __restrict__ trace) {
+                        int page_shift, int G, int* __restrict__ status, long long* __restrict__ trace, int splits,
+                        int min_tiles_per_split, int num_tokens, float* __restrict__ part_o, float2* __restrict__ part_ml,
+                        int* __restrict__ tickets) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_final[2];
@@ -188,12 +212,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define AT_STAMP(slot) do { if (tracing) trace[(slot)] = clock64(); } while (0)
   __shared__ uint32_t tmem_slot;
+  __shared__ int ticket_of[2];
 
   pdl_prologue();
   const int r = blockIdx.y;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
   const int tpc = AT_ROWS / G;                                  // tokens per group
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * 2 * tpc;       // later tiles see more keys: start them first
+  const int q_tiles = gridDim.x / splits, split = blockIdx.x % splits;
+  const int m0 = (q_tiles - 1 - blockIdx.x / splits) * 2 * tpc;  // later tiles see more keys: start them first
   if (m0 >= q_len) return;
   const int start = q_start[r], kv_len = start + q_len;
   const int head0 = blockIdx.z * G, kvh = head0 / (nq / nkv);
@@ -209,9 +235,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     lo_g[g] = window > 0 ? max(0, q_first[g] - window + 1) : 0;
     lo_max[g] = window > 0 ? max(0, q_last[g] - window + 1) : 0;
   }
-  const int tile_begin = lo_g[0] / AT_KEYS;
+  int tile_begin = lo_g[0] / AT_KEYS;
   n_tiles[0] = (min(kv_len, q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin;
   n_tiles[1] = has_b ? (min(kv_len, q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin : 0;
+  // Long rows of keys are cut into splits that other CTAs take (the grid has `splits` CTAs per
+  // tile): this CTA keeps `per_split` key tiles from its split's first. A group whose keys lie in
+  // more than one split leaves a partial result (unnormalised O, the maximum it is scaled by, the
+  // sum), and the last of them to finish adds the partial results up in the order of the splits.
+  const int per_split = max(min_tiles_per_split, (max(n_tiles[0], n_tiles[1]) + splits - 1) / splits);
+  if (split * per_split >= max(n_tiles[0], n_tiles[1])) return;
+  int shares[2];  // in how many splits the group has keys
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    shares[g] = (n_tiles[g] + per_split - 1) / per_split;
+    n_tiles[g] = min(max(n_tiles[g] - split * per_split, 0), per_split);
+  }
+  tile_begin += split * per_split;
   const int n_all = max(n_tiles[0], n_tiles[1]);
 
   if (threadIdx.x == 0) {
@@ -305,7 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         at_commit(&s_full[g]);
         return true;
       };
-      if (ok) ok = issue_s(0, 0);
+      if (ok && n_tiles[0] > 0) ok = issue_s(0, 0);
       if (ok && n_tiles[1] > 0) ok = issue_s(1, 0);
       for (int j = 0; j < n_all && ok; ++j) {
         const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
@@ -434,26 +473,75 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
     if (!ok) atomicExch(status, 34);
     AT_FENCE_AFTER();
-    if (ok && n_mine > 0) {
-      const bool store = tok_in_req < q_len;
-      const float inv = 1.0f / l_sum;
-      __nv_bfloat16* dst = out + ((size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd) * AT_D;
+    const bool store = tok_in_req < q_len;
+    const size_t item = (size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd;  // (token, head) of this row
+    __nv_bfloat16* dst = out + item * AT_D;
+    if (shares[g] <= 1) {
+      if (ok && n_mine > 0) {
+        const float inv = 1.0f / l_sum;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float ov[32];
+          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (store) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(ov + i, inv);
+          }
+        }
+      }
+    } else if (n_mine > 0) {
+      // one of several splits of this group's keys: leave the partial result, take a ticket
+      const size_t items = (size_t)num_tokens * nq;
+      float* po = part_o + ((size_t)split * items + item) * AT_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float ov[32];
         at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (store) {
+        if (store && ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 pk;
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(ov[i] * inv, ov[i + 1] * inv), p1 = __floats2bfloat162_rn(ov[i + 2] * inv, ov[i + 3] * inv);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(ov[i + 4] * inv, ov[i + 5] * inv), p3 = __floats2bfloat162_rn(ov[i + 6] * inv, ov[i + 7] * inv);
-            pk.x = *reinterpret_cast<uint32_t*>(&p0);
-            pk.y = *reinterpret_cast<uint32_t*>(&p1);
-            pk.z = *reinterpret_cast<uint32_t*>(&p2);
-            pk.w = *reinterpret_cast<uint32_t*>(&p3);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = pk;
+          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(po + c * 32 + i) = make_float4(ov[i], ov[i + 1], ov[i + 2], ov[i + 3]);
+        }
+      }
+      if (store && ok) part_ml[(size_t)split * items + item] = make_float2(m_used, l_sum);
+      __threadfence();
+      // all 128 threads of the group meet here, also after a wait that gave up: then nobody merges
+      const bool bad = at_group_any(1 + g, !ok);
+      int* ticket = tickets + (size_t)(tok0 + m0 + g * tpc) * (nq / G) + blockIdx.z;
+      if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
+      at_group_sync(1 + g);
+      if (!bad && ticket_of[g] == shares[g] - 1) {
+        if (row == 0) *ticket = 0;  // left as it was found, for the next launch
+        __threadfence();
+        if (store) {
+          float m_all = -INFINITY;
+          for (int sp = 0; sp < shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&part_ml[(size_t)sp * items + item]).x);
+          float l_all = 0.f;
+          for (int sp = 0; sp < shares[g]; ++sp) {
+            const float2 ml = __ldcg(&part_ml[(size_t)sp * items + item]);
+            l_all += at_ex2((ml.x - m_all) * scale_log2) * ml.y;
+          }
+          const float inv = 1.0f / l_all;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+            for (int sp = 0; sp < shares[g]; ++sp) {
+              const float w = at_ex2((__ldcg(&part_ml[(size_t)sp * items + item]).x - m_all) * scale_log2);
+              const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)sp * items + item) * AT_D + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 v = __ldcg(src + i);
+                acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
+                acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
+                acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
+                acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
           }
         }
       }
@@ -501,17 +589,50 @@ MS_EXPORT int ms_attn_tc_supports(int head_dim, int page_size, int nq, int nkv) 
   return head_dim == AT_D && page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0 && nq % nkv == 0;
 }
 
+static int at_heads_per_cta(int nq, int nkv) {
+  const int group = nq / nkv;
+  int G = 1;
+  while (G * 2 <= 8 && group % (G * 2) == 0) G *= 2;  // the largest power of two up to 8 that divides the group
+  return G;
+}
+
+static int g_splits = 0, g_min_tiles = 16;
+// Tuning: force the number of key splits (0: chosen from the size of the step) and the least
+// number of key tiles that a split keeps.
+MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
+  g_splits = splits;
+  g_min_tiles = min_tiles > 0 ? min_tiles : 16;
+}
+
+// How many CTAs share the keys of one tile of queries. One CTA fills an SM, so a step with fewer
+// query tiles than SMs (a portion of a prompt far into a long context, above all) leaves SMs idle
+// while the others walk through thousands of keys: then the keys are cut so that the CTAs about
+// fill the GPU once. More CTAs than SMs only add a second wave and partial results (measured on
+// B200, 16 heads in 8 groups: 256 tokens behind 30,000: 653 us whole, 147 us in 8 splits; 512
+// behind 8,192: 193 -> 87 us in 4; 2,048 behind 2,048, which has 128 tiles: 96 us whole, 137 us
+// cut in three). Each split needs num_tokens * nq * (128 + 2) float32 of scratch.
+MS_EXPORT int ms_attn_tc_splits(int num_tokens, int nq, int nkv, int sm_count) {
+  if (g_splits > 0) return g_splits;
+  const int G = at_heads_per_cta(nq, nkv);
+  const long long ctas = (long long)ceil_div(num_tokens, 2 * (AT_ROWS / G)) * (nq / G);
+  const long long want = sm_count / ctas;
+  return (int)(want < 1 ? 1 : (want > 16 ? 16 : want));
+}
+
 MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
-                                 int window, int page_size, int* status, cudaStream_t stream) {
+                                 int window, int page_size, int* status, int splits, float* part_o, float* part_ml,
+                                 int* tickets, cudaStream_t stream) {
   if (num_rows == 0) return 0;
+  MS_CHECK_ARG(splits >= 1 && splits <= 64, "attention_tc: %d key splits", splits);
+  MS_CHECK_ARG(splits == 1 || (part_o != nullptr && part_ml != nullptr && tickets != nullptr && (uintptr_t)part_o % 16 == 0 &&
+                               (uintptr_t)part_ml % 8 == 0),
+               "attention_tc: key splits need scratch for the partial results and zeroed tickets");
   MS_CHECK_ARG(ms_attn_tc_supports(AT_D, page_size, nq, nkv), "attention_tc: unsupported shape (page_size=%d)", page_size);
   MS_CHECK_ARG(num_rows <= 65535, "attention_tc: too many rows (%d) for one launch", num_rows);
   MS_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0), "attention_tc: operands must be 16-byte aligned");
-  const int group = nq / nkv;
-  int G = 1;
-  while (G * 2 <= 8 && group % (G * 2) == 0) G *= 2;  // heads per CTA: the largest power of two up to 8 that divides the group
+  const int G = at_heads_per_cta(nq, nkv);
   const int tpc = AT_ROWS / G;
   AtEncodeFn encode;
   if (int rc = at_get_encode(&encode)) return rc;
@@ -546,8 +667,9 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
     MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured = true;
   }
-  dim3 grid(ceil_div(max_q_len, 2 * tpc), num_rows, nq / G);
+  dim3 grid(ceil_div(max_q_len, 2 * tpc) * splits, num_rows, nq / G);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, g_trace);
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, g_trace, splits,
+            g_min_tiles, num_tokens, part_o, reinterpret_cast<float2*>(part_ml), tickets);
   return 0;
 }

@@ -109,6 +109,7 @@ __global__ void qk_norm_rope_kv_kernel(
 // bfloat16 fast path for head sizes that are multiples of 64 with the whole head rotated: one
 // block per token, every warp takes a share of the heads, two adjacent elements per lane. What
 // depends on the token alone (position, page, cos/sin, norm weights) is fetched once per warp.
+template <int PER_LANE>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_bf16_token_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
@@ -118,7 +119,8 @@ qk_norm_rope_kv_bf16_token_kernel(
     const int* __restrict__ page_indices, int nq, int nkv, int d, float eps, int page_shift, int* __restrict__ status) {
   pdl_prologue();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int half = d >> 1, per_lane = half >> 6;  // iterations of 64 pairs (2 per lane)
+  const int half = d >> 1;
+  constexpr int per_lane = PER_LANE;  // iterations of 64 pairs (2 per lane): head size 128 or 256
   const int pos = positions[t];
   const bool has_kv = k_pool != nullptr;
   const int heads_total = nq + (has_kv ? 2 * nkv : 0);
@@ -134,10 +136,9 @@ qk_norm_rope_kv_bf16_token_kernel(
     slot_base = ((size_t)page * nkv * page_size + (pos & (page_size - 1))) * d;  // + kvh * page_size * d
   }
   // per-lane constants: cos/sin of its two pairs per iteration (at most 2 iterations: d <= 256)
-  float cs[2][2], sn[2][2];
+  float cs[per_lane][2], sn[per_lane][2];
 #pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    if (it >= per_lane) break;
+  for (int it = 0; it < per_lane; ++it) {
     const int j = it * 64 + 2 * lane;
     if (inv_freq == nullptr) {
       cs[it][0] = cs[it][1] = 1.f;
@@ -151,53 +152,86 @@ qk_norm_rope_kv_bf16_token_kernel(
       sincosf((float)pos * inv_freq[j + 1], &sn[it][1], &cs[it][1]);
     }
   }
-  for (int h = warp; h < heads_total; h += nwarps) {
-    const __nv_bfloat16* src = row_in + (size_t)h * d;
-    if (h >= nq + nkv) {  // a value head: copied as it is
-      const int kvh = h - nq - nkv;
-      __nv_bfloat16* dst = v_pool + slot_base + ((size_t)kvh << page_shift) * d;
-      for (int c = lane; c < (d >> 2); c += 32) reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
-      continue;
-    }
-    const bool is_q = h < nq;
-    __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * nq + h) * d : k_pool + slot_base + ((size_t)(h - nq) << page_shift) * d;
-    const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
-    float lo[2][2], hi[2][2];
-    float ss = 0.f;
+  // the norm weights of this lane's elements, the same for every head of a kind
+  __nv_bfloat162 wq[per_lane][2], wk[per_lane][2];
+  const bool normed = q_norm_w != nullptr;
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      if (it >= per_lane) break;
-      const int j = it * 64 + 2 * lane;
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + j));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + half + j));
-      lo[it][0] = a.x; lo[it][1] = a.y; hi[it][0] = b.x; hi[it][1] = b.y;
-      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  for (int it = 0; it < per_lane; ++it) {
+    if (!normed) continue;
+    const int j = it * 64 + 2 * lane;
+    wq[it][0] = *reinterpret_cast<const __nv_bfloat162*>(q_norm_w + j);
+    wq[it][1] = *reinterpret_cast<const __nv_bfloat162*>(q_norm_w + half + j);
+    if (has_kv) {
+      wk[it][0] = *reinterpret_cast<const __nv_bfloat162*>(k_norm_w + j);
+      wk[it][1] = *reinterpret_cast<const __nv_bfloat162*>(k_norm_w + half + j);
     }
-    float inv = 1.f;
-    if (nw) {
-      ss = warp_sum(ss);
-      inv = 1.0f / sqrtf(ss / (float)d + eps);
-    }
+  }
+  // Heads in batches of four per warp: all loads of a batch are issued before the first is
+  // used, so that a warp keeps several cache lines in flight instead of one head's two.
+  constexpr int HB = 4;
+  for (int h0 = warp; h0 < heads_total; h0 += HB * nwarps) {
+    __nv_bfloat162 raw[HB][per_lane][2];
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      if (it >= per_lane) break;
-      const int j = it * 64 + 2 * lane;
-      float wl[2] = {1.f, 1.f}, wh[2] = {1.f, 1.f};
-      if (nw) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + j));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + half + j));
-        wl[0] = a.x; wl[1] = a.y; wh[0] = b.x; wh[1] = b.y;
+    for (int b = 0; b < HB; ++b) {
+      const int h = min(h0 + b * nwarps, heads_total - 1);  // past the end: the last head again, unused
+      const __nv_bfloat16* src = row_in + (size_t)h * d;
+#pragma unroll
+      for (int it = 0; it < per_lane; ++it) {
+        const int j = it * 64 + 2 * lane;
+        raw[b][it][0] = *reinterpret_cast<const __nv_bfloat162*>(src + j);
+        raw[b][it][1] = *reinterpret_cast<const __nv_bfloat162*>(src + half + j);
       }
-      float ol[2], oh[2];
+    }
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float l = nw ? (lo[it][e] * inv) * wl[e] : lo[it][e];
-        const float hgh = nw ? (hi[it][e] * inv) * wh[e] : hi[it][e];
-        ol[e] = l * cs[it][e] - hgh * sn[it][e];
-        oh[e] = hgh * cs[it][e] + l * sn[it][e];
+    for (int b = 0; b < HB; ++b) {
+      const int h = h0 + b * nwarps;
+      if (h >= heads_total) continue;
+      if (h >= nq + nkv) {  // a value head: copied as it is
+        __nv_bfloat16* dst = v_pool + slot_base + ((size_t)(h - nq - nkv) << page_shift) * d;
+#pragma unroll
+        for (int it = 0; it < per_lane; ++it) {
+          const int j = it * 64 + 2 * lane;
+          *reinterpret_cast<__nv_bfloat162*>(dst + j) = raw[b][it][0];
+          *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = raw[b][it][1];
+        }
+        continue;
       }
-      *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(ol[0], ol[1]);
-      *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = __floats2bfloat162_rn(oh[0], oh[1]);
+      const bool is_q = h < nq;
+      __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * nq + h) * d : k_pool + slot_base + ((size_t)(h - nq) << page_shift) * d;
+      float lo[per_lane][2], hi[per_lane][2];
+      float ss = 0.f;
+#pragma unroll
+      for (int it = 0; it < per_lane; ++it) {
+        const float2 a = __bfloat1622float2(raw[b][it][0]);
+        const float2 c = __bfloat1622float2(raw[b][it][1]);
+        lo[it][0] = a.x; lo[it][1] = a.y; hi[it][0] = c.x; hi[it][1] = c.y;
+        ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+      }
+      float inv = 1.f;
+      if (normed) {
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)d + eps);
+      }
+#pragma unroll
+      for (int it = 0; it < per_lane; ++it) {
+        const int j = it * 64 + 2 * lane;
+        float wl[2] = {1.f, 1.f}, wh[2] = {1.f, 1.f};
+        if (normed) {
+          const float2 a = __bfloat1622float2(is_q ? wq[it][0] : wk[it][0]);
+          const float2 c = __bfloat1622float2(is_q ? wq[it][1] : wk[it][1]);
+          wl[0] = a.x; wl[1] = a.y; wh[0] = c.x; wh[1] = c.y;
+        }
+        float ol[2], oh[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float l = normed ? (lo[it][e] * inv) * wl[e] : lo[it][e];
+          const float hgh = normed ? (hi[it][e] * inv) * wh[e] : hi[it][e];
+          ol[e] = l * cs[it][e] - hgh * sn[it][e];
+          oh[e] = hgh * cs[it][e] + l * sn[it][e];
+        }
+        *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(ol[0], ol[1]);
+        *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = __floats2bfloat162_rn(oh[0], oh[1]);
+      }
     }
   }
 }
@@ -251,10 +285,16 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
       (k_pool == nullptr || (q_norm_w != nullptr) == (k_norm_w != nullptr)) && ((uintptr_t)qkv % 8 == 0) &&
       ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)k_pool % 8 == 0) && ((uintptr_t)v_pool % 8 == 0) &&
       (cos_sin == nullptr || (uintptr_t)cos_sin % 8 == 0)) {
-    MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-              (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
-              inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
-              head_dim, eps, page_shift, status);
+    if (head_dim == 128)
+      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<1>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
+                inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
+                head_dim, eps, page_shift, status);
+    else
+      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<2>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
+                inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
+                head_dim, eps, page_shift, status);
     return 0;
   }
   if (dtype == MS_F32)

@@ -35,6 +35,13 @@ class StepRow:
     fill_from: int | None = None
 
 
+def _leading_ones(q_len: np.ndarray, pad_rows: int) -> int:
+    """How many rows from the front bring exactly one token (padding rows, which follow the real
+    ones, bring one token each)."""
+    other = np.flatnonzero(q_len != 1)
+    return int(other[0]) if other.size else len(q_len) + pad_rows
+
+
 class StepError(RuntimeError):
     pass
 
@@ -208,7 +215,7 @@ class StepFunction:
             host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [1] * pad_rows,
             host_state_slot=slots.tolist() + [-1] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
-            decode_only=bool((q_len == 1).all()), sm_count=self.sm_count, scratch=self.persistent_scratch)
+            decode_only=bool((q_len == 1).all()), leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel flagged inconsistent input (a page that was given

@@ -436,14 +436,26 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
-    if q.dtype == torch.bfloat16 and not ctx.decode_only and attention_tc_ok(q, k_pool):
-        attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window)
-        return
-    if q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2]):
-        attention_bf16.run(out, q, k_pool, v_pool, ctx, group, scale, window)
-        return
+    if q.dtype == torch.bfloat16:
+        # rows at the front that bring one token each (a decode step, or the decoding requests
+        # of a mixed step) go to the split-key kernel, the rest to a tiled kernel
+        split_ok = attention_bf16.supports(q.shape[2], k_pool.shape[2])
+        single = ctx.leading_single_rows if split_ok else 0
+        if single:
+            attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+        if single == ctx.num_rows:
+            return
+        if attention_tc_ok(q, k_pool):
+            attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+            return
+        if split_ok:
+            attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+            return
     attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
                       ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream)
+
+
+_ATTN_TC_SCRATCH_LIMIT = 1 << 29  # bytes of partial results that a step's attention may ask for
 
 
 def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
@@ -456,12 +468,32 @@ def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
 
 
 def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-                         scale: float, window: int | None) -> None:
-    """Causal attention of prompts and mixed steps on the tcgen05 tensor cores (``csrc/attention_tc.cu``)."""
+                         scale: float, window: int | None, first_row: int = 0) -> None:
+    """Causal attention of rows [first_row, num_rows) of the step, any number of new tokens each,
+    on the tcgen05 tensor cores (``csrc/attention_tc.cu``)."""
     _check_dev(out, q, k_pool, v_pool)
     t, nq, d = q.shape
     lib = native.attn_tc()
+    skip = 4 * first_row  # the per-row tables are int32
+    # a short step cuts the keys of its last tiles between several CTAs, which leave partial results
+    items = t * nq
+    splits = lib.ms_attn_tc_splits(t - first_row, nq, k_pool.shape[1], ctx.sm_count)
+    while splits > 1 and splits * items * (d + 2) * 4 > _ATTN_TC_SCRATCH_LIMIT:
+        splits -= 1
+    part = tickets = None
+    if splits > 1:
+        part = ctx.scratch.get("attn_tc_partials")
+        if part is None or part.numel() < splits * items * (d + 2):
+            part = torch.empty(splits * items * (d + 2), dtype=torch.float32, device=q.device)
+            ctx.scratch["attn_tc_partials"] = part
+        tickets = ctx.scratch.get("attn_tc_tickets")
+        if tickets is None or tickets.numel() < items:
+            # zero before the first launch, left zero by every launch
+            tickets = torch.zeros(max(items, 1 << 16), dtype=torch.int32, device=q.device)
+            ctx.scratch["attn_tc_tickets"] = tickets
     native.kernel_check(lib.ms_attn_tc_prefill(
-        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.page_indptr[group]),
-        _ptr(ctx.page_indices[group]), ctx.num_rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), ctx.stream), lib=lib, errfn="ms_attn_tc_last_error")
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
+        _ptr(ctx.page_indices[group]), ctx.num_rows - first_row, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
+        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, _ptr(part),
+        None if part is None else part.data_ptr() + splits * items * d * 4, _ptr(tickets), ctx.stream),
+        lib=lib, errfn="ms_attn_tc_last_error")

@@ -77,28 +77,50 @@ def _scratch(ctx, rows: int, nq: int, splits: int, d: int, device) -> tuple[torc
 
 def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
         scale: float, window: int | None) -> None:
+    """The step's attention: rows at the front that bring one token each go to the split-key
+    decode kernel, the rest to the tiled kernel."""
+    single = ctx.leading_single_rows
+    if single:
+        run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+    if single < ctx.num_rows:
+        run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+
+
+def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+               scale: float, window: int | None, rows: int) -> None:
+    """Rows [0, rows) of the step, one new token each (so token i belongs to row i): keys split
+    across CTAs, partial results merged by the last CTA of each (row, head group) to finish."""
     t, nq, d = q.shape
     nkv, page_size = k_pool.shape[1], k_pool.shape[2]
     fns = _lib(d)
     indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
-    if ctx.decode_only:
-        chunks = nkv * -(-(nq // nkv) // 16)
-        splits = choose_splits(ctx.num_rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
-        part_o = part_ml = counters = None
-        if splits > 1:
-            part_o, part_ml = _scratch(ctx, ctx.num_rows, nq, splits, d, q.device)
-            counters = ctx.scratch.get("attn_counters")
-            if counters is None or counters.numel() < ctx.num_rows * chunks:
-                # tickets of the fused merge: zero before the first launch, left zero by every launch
-                counters = torch.zeros(max(4096, ctx.num_rows * chunks), dtype=torch.int32, device=q.device)
-                ctx.scratch["attn_counters"] = counters
-        _check(fns, fns["decode_fused"](
-            out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
-            None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
-            indices.data_ptr(), ctx.num_rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
-            launches=1)
-        return
+    chunks = nkv * -(-(nq // nkv) // 16)
+    splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
+    part_o = part_ml = counters = None
+    if splits > 1:
+        part_o, part_ml = _scratch(ctx, rows, nq, splits, d, q.device)
+        counters = ctx.scratch.get("attn_counters")
+        if counters is None or counters.numel() < rows * chunks:
+            # tickets of the fused merge: zero before the first launch, left zero by every launch
+            counters = torch.zeros(max(4096, rows * chunks), dtype=torch.int32, device=q.device)
+            ctx.scratch["attn_counters"] = counters
+    _check(fns, fns["decode_fused"](
+        out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
+        None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
+        launches=1)
+
+
+def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+                scale: float, window: int | None, first_row: int = 0) -> None:
+    """Rows [first_row, num_rows) of the step, any number of new tokens each: tiles of 64 queries
+    over the row's pages (``mma.sync``; the tcgen05 kernel of ``attention_tc.cu`` takes head size 128)."""
+    t, nq, d = q.shape
+    nkv, page_size = k_pool.shape[1], k_pool.shape[2]
+    fns = _lib(d)
+    indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
+    skip = 4 * first_row  # the per-row tables are int32
     _check(fns, fns["prefill"](
-        out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr(), ctx.q_start.data_ptr(),
-        indptr.data_ptr(), indices.data_ptr(), ctx.num_rows, ctx.max_q_len, nq, nkv, float(scale), int(window or 0),
+        out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr() + skip, ctx.q_start.data_ptr() + skip,
+        indptr.data_ptr() + skip, indices.data_ptr(), ctx.num_rows - first_row, ctx.max_q_len, nq, nkv, float(scale), int(window or 0),
         page_size, ctx.stream))

@@ -45,7 +45,8 @@ def _paged(rows, page, nkv, d, seed, device):
         q_start=torch.tensor([s for s, _ in rows], **i32), kv_len=torch.tensor([s + n for s, n in rows], **i32),
         page_indptr=[torch.tensor(indptr, **i32)], page_indices=[torch.tensor([p for t in tables for p in t], **i32)],
         max_q_len=max(n for _, n in rows), max_kv_len=max(s + n for s, n in rows),
-        decode_only=all(n == 1 for _, n in rows), graph_bucket=0, scratch={}, step_cache={},
+        decode_only=all(n == 1 for _, n in rows),
+        leading_single_rows=next((i for i, (_, n) in enumerate(rows) if n != 1), len(rows)), graph_bucket=0, scratch={}, step_cache={},
         sm_count=torch.cuda.get_device_properties(0).multi_processor_count, stream=0)
     return k, v, ctx
 
@@ -91,7 +92,9 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--splits", type=int, default=0, help="attn_decode: fixed number of key splits (0: the engine's choice)")
+    ap.add_argument("--splits", type=int, default=0, help="fixed number of key splits (0: the engine's choice)")
+    ap.add_argument("--prefix", type=int, default=0, help="attn_prefill: tokens already in the cache before the portion")
+    ap.add_argument("--min-tiles", type=int, default=0, help="attn_prefill with --splits: least key tiles per split (0: the kernel's default)")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -111,16 +114,19 @@ def main(argv=None) -> int:
             byts = args.batch * (args.context + 1) * nkv * d * 2 * 2
             work = dict(bytes=byts)
         else:
-            rows = [(0, args.tokens)]
-            flops = 4.0 * nq * d * args.tokens * (args.tokens + 1) / 2
-            byts = args.tokens * nkv * d * 4
+            rows = [(args.prefix, args.tokens)]  # a portion of a prompt behind `prefix` cached tokens
+            flops = 4.0 * nq * d * (args.tokens * (args.tokens + 1) / 2 + args.tokens * args.prefix)
+            byts = (args.prefix + args.tokens) * nkv * d * 4
             work = dict(flops=flops)
         copies = max(2, int(L2_BYTES // byts) + 1)
         sets = [_paged(rows, args.page_size, nkv, d, i, dev) for i in range(copies)]
         q = torch.randn(sum(n for _, n in rows), nq, d, device=dev).bfloat16()
         o = torch.empty_like(q)
-        if args.splits:
+        if args.splits and args.kernel == "attn_decode":
             attention_bf16.choose_splits = lambda *a, **k: args.splits
+        elif args.splits:
+            from ..ops import native
+            native.attn_tc().ms_attn_tc_set_splits(args.splits, args.min_tiles)
 
         def calls(i, stream):
             k, v, ctx = sets[i]

@@ -102,4 +102,6 @@ def make_context(pb: PagedBatch, logit_rows=None, device="cuda"):
         host_q_start=[s for s, _ in pb.rows], host_q_len=[n for _, n in pb.rows],
         host_state_slot=[-1] * len(pb.rows),
         max_q_len=max(n for _, n in pb.rows), max_kv_len=max(s + n for s, n in pb.rows),
-        decode_only=all(n == 1 for _, n in pb.rows), sm_count=props.multi_processor_count)
+        decode_only=all(n == 1 for _, n in pb.rows),
+        leading_single_rows=next((i for i, (_, n) in enumerate(pb.rows) if n != 1), len(pb.rows)),
+        sm_count=props.multi_processor_count)

@@ -395,12 +395,25 @@ def test_attention_bf16_decode_window_edge(window):
     assert torch.allclose(out.float(), ref, **BF16_TOL)
 
 
+@pytest.fixture(params=[None, (2, 1), (3, 2), (8, 1)], ids=lambda p: "auto" if p is None else f"splits{p[0]}x{p[1]}")
+def key_splits(request):
+    """Forces how the tcgen05 attention cuts a tile's keys between CTAs (None: its own choice, which
+    is no cut for steps as small as a test's): (splits, least key tiles per split)."""
+    from miniserve_b200.ops import native
+
+    lib = native.attn_tc()
+    if request.param is not None:
+        lib.ms_attn_tc_set_splits(*request.param)
+    yield request.param
+    lib.ms_attn_tc_set_splits(0, 0)
+
+
 TC_SHAPES = [(16, 8, 128, 16), (8, 8, 128, 8), (32, 8, 128, 32), (8, 1, 128, 16), (4, 2, 128, 128), (6, 2, 128, 64)]
 
 
 @pytest.mark.parametrize("nq, nkv, d, page", TC_SHAPES)
-def test_attention_tcgen05_prompts_and_mixed_steps(nq, nkv, d, page):
-    rows = [(0, 37), (52, 1), (15, 18), (0, 1), (63, 2), (0, 150), (100, 70), (64, 64), (0, 300), (250, 130)]
+def test_attention_tcgen05_prompts_and_mixed_steps(nq, nkv, d, page, key_splits):
+    rows = [(0, 37), (52, 1), (15, 18), (0, 1), (63, 2), (0, 150), (100, 70), (64, 64), (0, 300), (250, 130), (0, 700), (900, 260)]
     pb, q, ref, scale = _attention_case(torch.bfloat16, rows, nq, nkv, d, page)
     assert ops.attention_tc_ok(q, pb.k_pool)
     out = torch.full_like(q, float("nan"))
@@ -411,7 +424,7 @@ def test_attention_tcgen05_prompts_and_mixed_steps(nq, nkv, d, page):
 
 
 @pytest.mark.parametrize("window", [1, 7, 128, 129, 200])
-def test_attention_tcgen05_window_edge(window):
+def test_attention_tcgen05_window_edge(window, key_splits):
     rows = [(0, 400), (130, 3), (399, 1), (256, 128)]
     pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 128, 16, window=window)
     out = torch.full_like(q, float("nan"))
@@ -421,7 +434,7 @@ def test_attention_tcgen05_window_edge(window):
     assert torch.allclose(out.float(), ref, **BF16_TOL)
 
 
-def test_attention_tcgen05_finds_a_far_key_and_survives_poisoned_pages():
+def test_attention_tcgen05_finds_a_far_key_and_survives_poisoned_pages(key_splits):
     rows = [(0, 700), (900, 5)]
     pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 128, 16, needle=3)
     out = torch.full_like(q, float("nan"))  # pages past each request's end are NaN (PagedBatch poisons them)
@@ -432,7 +445,7 @@ def test_attention_tcgen05_finds_a_far_key_and_survives_poisoned_pages():
     assert torch.allclose(out.float(), ref, atol=0.3, rtol=2e-2)
 
 
-def test_attention_tcgen05_large_scores_keep_the_lazy_rescale_exact():
+def test_attention_tcgen05_large_scores_keep_the_lazy_rescale_exact(key_splits):
     """Scores that keep growing along the keys force the running maximum up tile after tile."""
     torch.manual_seed(3)
     nq, nkv, d, page, n = 2, 1, 128, 16, 600
@@ -450,6 +463,27 @@ def test_attention_tcgen05_large_scores_keep_the_lazy_rescale_exact():
     torch.cuda.synchronize()
     assert ops.device_status("cuda").item() == 0
     assert torch.allclose(out.float(), ref, **BF16_TOL)
+
+
+@pytest.mark.parametrize("nq, nkv, d, page", [(16, 8, 128, 16), (8, 2, 64, 16), (6, 2, 48, 8)])
+@pytest.mark.parametrize("window", [None, 33])
+def test_attention_of_a_mixed_step_uses_both_kernels(nq, nkv, d, page, window):
+    """Decoding requests come first in a mixed step: they go to the split-key kernel, the prompt
+    portions behind them (and a single token that follows a portion) to the tiled kernel."""
+    from miniserve_b200.ops import native
+
+    rows = [(700, 1), (15, 1), (0, 1), (0, 37), (100, 70), (52, 1), (0, 300)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, nq, nkv, d, page, window=window, needle=3)
+    ctx = make_context(pb)
+    assert ctx.leading_single_rows == 3 and not ctx.decode_only
+    out = torch.full_like(q, float("nan"))
+    before = native.LAUNCHES[0]
+    ops.attention(out, q, pb.k_pool, pb.v_pool, ctx, 0, scale, window)
+    assert native.LAUNCHES[0] - before == 2
+    torch.cuda.synchronize()
+    assert ops.device_status("cuda").item() == 0
+    assert torch.allclose(out.float()[1:], ref[1:], **BF16_TOL)
+    assert torch.allclose(out.float()[:1], ref[:1], atol=0.3, rtol=2e-2)  # the far key's value is 50
 
 
 def test_attention_bf16_refuses_other_head_sizes():
