@@ -34,6 +34,11 @@ PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+# --profile-range: the timed decode steps and the last timed prefill are bracketed by
+# cudaProfilerStart/Stop, so that a profiler started with --profile-from-start off sees only them
+PROFILE_RANGE = False
+
+
 def load_peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.is_file():
@@ -170,11 +175,15 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int):
     start_ctx = bench.caches[0].num_tokens
     launches0 = native.LAUNCHES[0] + (engine.graphs.replayed_launches if engine.graphs is not None else 0)
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if PROFILE_RANGE:
+        torch.cuda.profiler.start()
     t0.record()
     for _ in range(steps):
         bench.step_device()
     t1.record()
     torch.cuda.synchronize()
+    if PROFILE_RANGE:
+        torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1) / steps
     launches = native.LAUNCHES[0] + (engine.graphs.replayed_launches if engine.graphs is not None else 0) - launches0
     mean_ctx = start_ctx + (steps + 1) / 2
@@ -228,10 +237,14 @@ def time_prefill(engine, tokens: int, repeats: int = 5):
         rc = engine.cache.new_request()
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if PROFILE_RANGE and i == repeats + 1:
+            torch.cuda.profiler.start()
         t0.record()
         engine.step_fn.run([StepRow(rc, ids, (tokens - 1,))])
         t1.record()
         torch.cuda.synchronize()
+        if PROFILE_RANGE and i == repeats + 1:
+            torch.cuda.profiler.stop()
         if i >= 2:
             times.append(t0.elapsed_time(t1))
         engine.cache.release(rc)
@@ -374,6 +387,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -384,6 +399,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    global PROFILE_RANGE
+    PROFILE_RANGE = args.profile_range
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

@@ -41,19 +41,31 @@ def main(argv=None) -> int:
         prompt = [rng.randrange(vocab) for _ in range(rng.randint(*args.prompt_len))]
         params = SamplingParams(rng.randint(*args.max_new_tokens), frozenset(), args.temperature, args.top_p)
         reqs.append(eng.add_request(prompt, params))
+    import time
+
+    import torch
+
     steps = max_decode_batch = max_used = 0
+    phases = {"prefill": 0, "mixed": 0, "decode": 0}
+    torch.cuda.synchronize()
+    began = time.perf_counter()
     while eng.has_unfinished:
         if steps >= args.max_steps:
             print(f"not finished after {steps} steps", file=sys.stderr)
             return 1
         plan = eng.step()
         steps += 1
-        if plan is not None and plan.phase != "prefill":
-            max_decode_batch = max(max_decode_batch, plan.num_decode)
+        if plan is not None:
+            phases[plan.phase] += 1
+            if plan.phase != "prefill":
+                max_decode_batch = max(max_decode_batch, plan.num_decode)
         max_used = max(max_used, max(g.allocator.num_used for g in eng.cache.groups))
         eng.cache.check_invariants()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - began
     report = dict(
-        engine=engine_kwargs(args), num_requests=len(reqs),
+        engine=engine_kwargs(args), num_requests=len(reqs), seconds=round(seconds, 3), steps_by_phase=phases,
+        tokens_per_second=round(sum(len(r.prompt_ids) + len(r.output_ids) for r in reqs) / seconds, 1),
         prompt_tokens=sum(len(r.prompt_ids) for r in reqs), output_tokens=sum(len(r.output_ids) for r in reqs),
         steps=steps, max_decode_batch=max_decode_batch, max_pages_used=max_used, pool_pages=eng.cache.num_pages,
         preemptions=eng.scheduler.num_preemptions, preempted_requests=sum(r.num_preemptions > 0 for r in reqs),
