@@ -224,7 +224,7 @@ def time_e2e(llm, batch: int, context: int, steps: int, warmup: int):
     return batch * steps / dt, h2d, (batch + 1) * 4
 
 
-def time_prefill(engine, tokens: int, repeats: int = 5):
+def time_prefill(engine, tokens: int, repeats: int = 5, warmup: int = 6):
     import torch
 
     from miniserve_b200.engine.step import StepRow
@@ -233,19 +233,19 @@ def time_prefill(engine, tokens: int, repeats: int = 5):
     vocab = engine.model.spec.vocab_size
     ids = [rng.randrange(vocab) for _ in range(tokens)]
     times = []
-    for i in range(repeats + 2):
+    for i in range(repeats + warmup):
         rc = engine.cache.new_request()
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if PROFILE_RANGE and i == repeats + 1:
+        if PROFILE_RANGE and i == repeats + warmup - 1:
             torch.cuda.profiler.start()
         t0.record()
         engine.step_fn.run([StepRow(rc, ids, (tokens - 1,))])
         t1.record()
         torch.cuda.synchronize()
-        if PROFILE_RANGE and i == repeats + 1:
+        if PROFILE_RANGE and i == repeats + warmup - 1:
             torch.cuda.profiler.stop()
-        if i >= 2:
+        if i >= warmup:  # the host's first passes are slower and a prompt step is close to host-bound
             times.append(t0.elapsed_time(t1))
         engine.cache.release(rc)
     return statistics.median(times)

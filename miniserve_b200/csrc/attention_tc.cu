@@ -197,63 +197,125 @@ __device__ __forceinline__ bool at_group_any(int id, bool flag) {
   return res != 0;
 }
 
+// What one work item (a tile of 2 x 128 query rows, one group of heads, one split of the keys)
+// has to do. All threads of a CTA compute it from the item's index; the scheduler warp also
+// uses it to tell empty items from real ones.
+struct AtItem {
+  int r, tok0, q_len, m0, start, kv_len, head0, split;
+  int n_tiles[2], q_first[2], q_last[2], lo_g[2], lo_max[2], shares[2];
+  int tile_begin, n_all;
+  bool has_b;
+};
+
+struct AtGrid {
+  int q_tiles, rows, head_groups, splits, min_tiles_per_split, window, G;
+  __device__ __forceinline__ int total() const { return q_tiles * rows * head_groups * splits; }
+};
+
+// Items are numbered so that the tiles with the most keys (the last tiles of the longest rows)
+// come first: tile rank, then row, then head group, then split.
+__device__ __forceinline__ bool at_item(AtItem& it, int idx, const AtGrid& gr, const int* __restrict__ cu_q,
+                                        const int* __restrict__ q_start) {
+  it.split = idx % gr.splits;
+  idx /= gr.splits;
+  it.head0 = (idx % gr.head_groups) * gr.G;
+  idx /= gr.head_groups;
+  it.r = idx % gr.rows;
+  const int rank = idx / gr.rows;
+  const int tpc = AT_ROWS / gr.G;  // tokens per group
+  it.tok0 = cu_q[it.r];
+  it.q_len = cu_q[it.r + 1] - it.tok0;
+  it.m0 = (gr.q_tiles - 1 - rank) * 2 * tpc;
+  if (it.m0 >= it.q_len) return false;
+  it.start = q_start[it.r];
+  it.kv_len = it.start + it.q_len;
+  // per group: the key tiles it needs (B needs at least as many as A; B may have no rows at all)
+  it.has_b = it.m0 + tpc < it.q_len;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    it.q_first[g] = it.start + it.m0 + g * tpc;
+    it.q_last[g] = it.start + min(it.m0 + (g + 1) * tpc, it.q_len) - 1;
+    it.lo_g[g] = gr.window > 0 ? max(0, it.q_first[g] - gr.window + 1) : 0;
+    it.lo_max[g] = gr.window > 0 ? max(0, it.q_last[g] - gr.window + 1) : 0;
+  }
+  it.tile_begin = it.lo_g[0] / AT_KEYS;
+  it.n_tiles[0] = (min(it.kv_len, it.q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin;
+  it.n_tiles[1] = it.has_b ? (min(it.kv_len, it.q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin : 0;
+  // Long rows of keys are cut into splits that other items take: this one keeps `per_split` key
+  // tiles from its split's first. A group whose keys lie in more than one split leaves a partial
+  // result (unnormalised O, the maximum it is scaled by, the sum), and the last of them to finish
+  // adds the partial results up in the order of the splits.
+  const int n_full = max(it.n_tiles[0], it.n_tiles[1]);
+  const int per_split = max(gr.min_tiles_per_split, (n_full + gr.splits - 1) / gr.splits);
+  if (it.split * per_split >= n_full) return false;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    it.shares[g] = (it.n_tiles[g] + per_split - 1) / per_split;  // in how many splits the group has keys
+    it.n_tiles[g] = min(max(it.n_tiles[g] - it.split * per_split, 0), per_split);
+  }
+  it.tile_begin += it.split * per_split;
+  it.n_all = max(it.n_tiles[0], it.n_tiles[1]);
+  return true;
+}
+
+// The scheduler (all lanes of one warp): the CTA's first item is the one with its own number, the
+// others come off a counter in global memory. Empty items (tiles past a short row's end, splits
+// past a short key range) are stepped over: the lanes look at the 32 items from the claimed one
+// on, so a run of empty items costs one round trip. When nothing is left, the CTA signs off on a
+// second counter, and the last one to do so puts both back to zero for the next launch.
+__device__ __forceinline__ int at_claim(int* __restrict__ queue, const AtGrid& gr, const int* __restrict__ cu_q,
+                                        const int* __restrict__ q_start, int lane, bool first) {
+  const int total = gr.total();
+  for (;;) {
+    int idx = (int)blockIdx.x;
+    if (!first) {
+      if (lane == 0) idx = (int)gridDim.x + atomicAdd(queue, 1);
+      idx = __shfl_sync(0xffffffffu, idx, 0);
+    }
+    if (idx >= total) {
+      if (lane == 0 && atomicAdd(queue + 1, 1) == (int)gridDim.x - 1) {
+        queue[0] = 0;
+        queue[1] = 0;
+      }
+      return -1;
+    }
+    AtItem probe;
+    const bool work = idx + lane < total && at_item(probe, idx + lane, gr, cu_q, q_start);
+    const unsigned mask = __ballot_sync(0xffffffffu, work);
+    if (mask & 1u) return idx;
+    const int run = mask ? __ffs(mask) - 1 : 32;  // this many items from idx on are empty
+    if (!first && lane == 0 && run > 1) atomicMax(queue, idx + run - (int)gridDim.x);
+    first = false;
+  }
+}
+
+// Persistent: one CTA per SM takes items off a queue until none is left.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
-                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                        int page_shift, int G, int* __restrict__ status, long long* __restrict__ trace, int splits,
-                        int min_tiles_per_split, int num_tokens, float* __restrict__ part_o, float2* __restrict__ part_ml,
+                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int page_shift,
+                        const AtGrid gr, int* __restrict__ status, long long* __restrict__ trace, int num_tokens,
+                        float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
                         int* __restrict__ tickets) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_final[2];
-  // timing experiments only: the first CTA stamps clock64() at its hand-off points
-  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define AT_STAMP(slot) do { if (tracing) trace[(slot)] = clock64(); } while (0)
   __shared__ uint32_t tmem_slot;
   __shared__ int ticket_of[2];
-
-  pdl_prologue();
-  const int r = blockIdx.y;
-  const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
-  const int tpc = AT_ROWS / G;                                  // tokens per group
-  const int q_tiles = gridDim.x / splits, split = blockIdx.x % splits;
-  const int m0 = (q_tiles - 1 - blockIdx.x / splits) * 2 * tpc;  // later tiles see more keys: start them first
-  if (m0 >= q_len) return;
-  const int start = q_start[r], kv_len = start + q_len;
-  const int head0 = blockIdx.z * G, kvh = head0 / (nq / nkv);
+  __shared__ int item_slot;       // the item the CTA works on (-1: none left)
+  __shared__ int failed;          // a bounded wait gave up somewhere: the CTA winds down
+  const int G = gr.G, window = gr.window;
+  const int tpc = AT_ROWS / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // per group: the key tiles it needs (B needs at least as many as A; B may have no rows at all)
-  const bool has_b = m0 + tpc < q_len;
-  int n_tiles[2], q_first[2], q_last[2], lo_g[2], lo_max[2];
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    q_first[g] = start + m0 + g * tpc;
-    q_last[g] = start + min(m0 + (g + 1) * tpc, q_len) - 1;
-    lo_g[g] = window > 0 ? max(0, q_first[g] - window + 1) : 0;
-    lo_max[g] = window > 0 ? max(0, q_last[g] - window + 1) : 0;
+  pdl_prologue();
+  int next_item = -1;  // held by the scheduler warp
+  if (warp == 8) {
+    next_item = at_claim(queue, gr, cu_q, q_start, lane, true);
+    if (lane == 0) item_slot = next_item;
   }
-  int tile_begin = lo_g[0] / AT_KEYS;
-  n_tiles[0] = (min(kv_len, q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin;
-  n_tiles[1] = has_b ? (min(kv_len, q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - tile_begin : 0;
-  // Long rows of keys are cut into splits that other CTAs take (the grid has `splits` CTAs per
-  // tile): this CTA keeps `per_split` key tiles from its split's first. A group whose keys lie in
-  // more than one split leaves a partial result (unnormalised O, the maximum it is scaled by, the
-  // sum), and the last of them to finish adds the partial results up in the order of the splits.
-  const int per_split = max(min_tiles_per_split, (max(n_tiles[0], n_tiles[1]) + splits - 1) / splits);
-  if (split * per_split >= max(n_tiles[0], n_tiles[1])) return;
-  int shares[2];  // in how many splits the group has keys
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    shares[g] = (n_tiles[g] + per_split - 1) / per_split;
-    n_tiles[g] = min(max(n_tiles[g] - split * per_split, 0), per_split);
-  }
-  tile_begin += split * per_split;
-  const int n_all = max(n_tiles[0], n_tiles[1]);
-
-  if (threadIdx.x == 0) {
+  auto init_barriers = [&]() {
     at_mbar_init(&q_full, 1);
     for (int i = 0; i < 2; ++i) {
       at_mbar_init(&kv_full[i], 1);
@@ -263,6 +325,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       at_mbar_init(&o_final[i], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  };
+  if (threadIdx.x == 0) {
+    failed = 0;
+    init_barriers();
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(at_smem(&tmem_slot)), "r"(512u) : "memory");
@@ -272,280 +338,322 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   AT_FENCE_AFTER();
   const uint32_t tmem = tmem_slot;
+  bool first_item = true;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      at_expect_tx(&q_full, (has_b ? 4 : 2) * AT_BLOCK);
-      at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
-      at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
-      if (has_b) {
-        at_tma_3d(smem + AtSmem::q + 2 * AT_BLOCK, &map_q, &q_full, 0, head0, tok0 + m0 + tpc);
-        at_tma_3d(smem + AtSmem::q + 3 * AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0 + tpc);
-      }
-    }
-    const int* pages = page_indices + page_indptr[r];
-    const int page_size = 1 << page_shift;
-    const int box_rows = min(page_size, AT_KEYS);
-    bool ok = true;
-    for (int j = 0; j < n_all; ++j) {
-      const int s = j & 1;
-      const int key0 = (tile_begin + j) * AT_KEYS;
-      const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
-      int my_row = 0;
-      if (lane < boxes) {
-        const int key = key0 + lane * box_rows;
-        const int page = pages[key >> page_shift];
-        my_row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
-      }
-      if (j >= 2) {
-        if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) {
-          if (lane == 0) atomicExch(status, 31);
-          break;
+  for (;;) {
+    const int cur = item_slot;
+    if (cur < 0) break;
+    AtItem it;
+    at_item(it, cur, gr, cu_q, q_start);
+    const int r = it.r, tok0 = it.tok0, q_len = it.q_len, m0 = it.m0, start = it.start, kv_len = it.kv_len;
+    const int head0 = it.head0, kvh = head0 / (nq / nkv), split = it.split, tile_begin = it.tile_begin, n_all = it.n_all;
+    const bool has_b = it.has_b;
+    // timing experiments only: the first CTA stamps clock64() at the hand-off points of its first item
+    const bool tracing = trace != nullptr && blockIdx.x == 0 && first_item;
+#define AT_STAMP(slot) do { if (tracing) trace[(slot)] = clock64(); } while (0)
+
+    if (warp == 8) {
+      // ---------------------------------------------------------- TMA producer (and scheduler)
+      if (lane == 0) {
+        at_expect_tx(&q_full, (has_b ? 4 : 2) * AT_BLOCK);
+        at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
+        at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
+        if (has_b) {
+          at_tma_3d(smem + AtSmem::q + 2 * AT_BLOCK, &map_q, &q_full, 0, head0, tok0 + m0 + tpc);
+          at_tma_3d(smem + AtSmem::q + 3 * AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0 + tpc);
         }
       }
-      unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
-      unsigned char* vt = kt + 2 * AT_BLOCK;
-      if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
+      const int* pages = page_indices + page_indptr[r];
+      const int page_size = 1 << page_shift;
+      const int box_rows = min(page_size, AT_KEYS);
+      bool ok = true;
+      for (int j = 0; j < n_all; ++j) {
+        const int s = j & 1;
+        const int key0 = (tile_begin + j) * AT_KEYS;
+        const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
+        int my_row = 0;
+        if (lane < boxes) {
+          const int key = key0 + lane * box_rows;
+          const int page = pages[key >> page_shift];
+          my_row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
+        }
+        if (j >= 2) {
+          if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            if (lane == 0) {
+              atomicExch(status, 31);
+              failed = 1;
+            }
+            break;
+          }
+        }
+        unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
+        unsigned char* vt = kt + 2 * AT_BLOCK;
+        if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
+        __syncwarp();
+        if (lane < boxes) {
+          const int off = lane * box_rows * 128;
+          at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
+          at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
+          at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
+          at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
+        }
+      }
+      // all loads of this item are on their way: find the next one while the others compute
       __syncwarp();
-      if (lane < boxes) {
-        const int off = lane * box_rows * 128;
-        at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
-        at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
-        at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
-        at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
-      }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------ MMA issuer
-    if (at_elect()) {
-      constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
-      bool ok = at_wait(&q_full, 0);
-      int kv_ready = -1;  // the last tile whose kv_full this thread has waited for
-      auto need_kv = [&](int j) -> bool {
-        if (j <= kv_ready) return true;
-        if (!at_wait(&kv_full[j & 1], (j >> 1) & 1)) return false;
-        kv_ready = j;
-        AT_FENCE_AFTER();
-        return true;
-      };
-      auto issue_s = [&](int g, int j) -> bool {
-        if (!need_kv(j)) return false;
-        const unsigned char* kt = smem + AtSmem::kv + (j & 1) * AtSmem::stage;
-        const unsigned char* qt = smem + AtSmem::q + g * 2 * AT_BLOCK;
-#pragma unroll
-        for (int kk = 0; kk < AT_D / 16; ++kk) {
-          const uint64_t da = at_desc(qt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-          const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-          at_mma(tmem + (uint32_t)(g * 128), da, db, idesc_s, kk != 0);
-        }
-        at_commit(&s_full[g]);
-        return true;
-      };
-      if (ok && n_tiles[0] > 0) ok = issue_s(0, 0);
-      if (ok && n_tiles[1] > 0) ok = issue_s(1, 0);
-      for (int j = 0; j < n_all && ok; ++j) {
-        const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
-#pragma unroll 1
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (j >= n_tiles[g]) continue;
-          if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
+      next_item = at_claim(queue, gr, cu_q, q_start, lane, false);
+    } else if (warp == 9) {
+      // ---------------------------------------------------------- MMA issuer
+      if (at_elect()) {
+        constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
+        bool ok = at_wait(&q_full, 0);
+        int kv_ready = -1;  // the last tile whose kv_full this thread has waited for
+        auto need_kv = [&](int j) -> bool {
+          if (j <= kv_ready) return true;
+          if (!at_wait(&kv_full[j & 1], (j >> 1) & 1)) return false;
+          kv_ready = j;
           AT_FENCE_AFTER();
-          if (j < 40) AT_STAMP(16 * j + 1 + 2 * g);
+          return true;
+        };
+        auto issue_s = [&](int g, int j) -> bool {
+          if (!need_kv(j)) return false;
+          const unsigned char* kt = smem + AtSmem::kv + (j & 1) * AtSmem::stage;
+          const unsigned char* qt = smem + AtSmem::q + g * 2 * AT_BLOCK;
 #pragma unroll
-          for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
-            // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
-            // B = V [keys][d], MN-major
-            const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
-            at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
+          for (int kk = 0; kk < AT_D / 16; ++kk) {
+            const uint64_t da = at_desc(qt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+            const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+            at_mma(tmem + (uint32_t)(g * 128), da, db, idesc_s, kk != 0);
           }
-          if (j < 40) AT_STAMP(16 * j + 2 + 2 * g);
-          if (j + 1 < n_tiles[g]) {
-            ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
-          } else {
-            at_commit(&o_final[g]);
-          }
-        }
-        if (ok) at_commit(&kv_empty[j & 1]);
-      }
-      if (!ok) atomicExch(status, 33);
-    }
-  } else {
-    // ------------------------------------------------------------ softmax, thread = row of its group
-    const int g = warp >> 2;
-    const int row = threadIdx.x & 127;                // row within the group = tensor-memory lane
-    const int tok = row / G, hd = row - tok * G;
-    const int tok_in_req = m0 + g * tpc + tok;
-    const int qpos = start + tok_in_req;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
-    const int n_mine = n_tiles[g];
-    float m_used = -INFINITY, l_sum = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n_mine && ok; ++j) {
-      if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
-      AT_FENCE_AFTER();
-      if (row == 0 && j < 40) AT_STAMP(16 * j + 8 + 3 * g);
-      const int key0 = (tile_begin + j) * AT_KEYS;
-      const bool interior = key0 + AT_KEYS - 1 <= q_first[g] && key0 >= lo_max[g];
-      // the whole row of scores in registers: four loads in flight, one wait
-      float sv[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
-      asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (interior) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            const bool valid = key <= qpos && key >= lo_g[g] && (window <= 0 || key > qpos - window);
-            sv[c][i] = valid ? sv[c][i] : -INFINITY;
-            mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
-          }
-      }
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      if (row == 0 && j < 40) AT_STAMP(16 * j + 9 + 3 * g);
-      const float m_new = fmaxf(m_used, m_tile);
-      float alpha = 1.f;
-      bool rescale = false;
-      if (m_used == -INFINITY) {
-        m_used = m_new;
-      } else if ((m_new - m_used) * scale_log2 > 8.f) {
-        alpha = at_ex2((m_used - m_new) * scale_log2);
-        m_used = m_new;
-        rescale = true;
-      }
-      if (__any_sync(0xffffffffu, rescale)) {
-        // S(j) is complete, so the product P(j-1) V(j-1) issued before it is complete too: O is quiet
+          at_commit(&s_full[g]);
+          return true;
+        };
+        if (ok && it.n_tiles[0] > 0) ok = issue_s(0, 0);
+        if (ok && it.n_tiles[1] > 0) ok = issue_s(1, 0);
+        for (int j = 0; j < n_all && ok; ++j) {
+          const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float ov[32];
-          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          for (int g = 0; g < 2 && ok; ++g) {
+            if (j >= it.n_tiles[g]) continue;
+            if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
+            AT_FENCE_AFTER();
+            if (j < 40) AT_STAMP(16 * j + 1 + 2 * g);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-          at_tmem_st32(t_o + (uint32_t)(c * 32), ov);
-        }
-        l_sum *= alpha;
-      }
-      // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
-      // (masked scores are -inf and give 0)
-      const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
-      float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
-          const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
-          const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
-          part[(i >> 1) & 3] += e0 + e1;
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
-        }
-        at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
-      }
-      l_sum += (part[0] + part[1]) + (part[2] + part[3]);
-      const int valid_keys = kv_len - key0;
-      if (valid_keys < AT_KEYS && row >= valid_keys) {
-        unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(vt + h * AT_BLOCK + row * 128 + cc * 16) = make_uint4(0u, 0u, 0u, 0u);
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      }
-      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-      AT_FENCE_BEFORE();
-      at_arrive(&p_full[g]);
-      if (row == 0 && j < 40) AT_STAMP(16 * j + 10 + 3 * g);
-    }
-    if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
-    if (!ok) atomicExch(status, 34);
-    AT_FENCE_AFTER();
-    const bool store = tok_in_req < q_len;
-    const size_t item = (size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd;  // (token, head) of this row
-    __nv_bfloat16* dst = out + item * AT_D;
-    if (shares[g] <= 1) {
-      if (ok && n_mine > 0) {
-        const float inv = 1.0f / l_sum;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float ov[32];
-          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          if (store) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(ov + i, inv);
+            for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
+              // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
+              // B = V [keys][d], MN-major
+              const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
+              at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
+            }
+            if (j < 40) AT_STAMP(16 * j + 2 + 2 * g);
+            if (j + 1 < it.n_tiles[g]) {
+              ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
+            } else {
+              at_commit(&o_final[g]);
+            }
           }
+          // the producer waits for this only before tile j + 2: an arrival that nobody waits for
+          // must not be in flight when the barriers are set up again for the next item
+          if (ok && j + 2 < n_all) at_commit(&kv_empty[j & 1]);
+        }
+        if (!ok) {
+          atomicExch(status, 33);
+          failed = 1;
         }
       }
-    } else if (n_mine > 0) {
-      // one of several splits of this group's keys: leave the partial result, take a ticket
-      const size_t items = (size_t)num_tokens * nq;
-      float* po = part_o + ((size_t)split * items + item) * AT_D;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float ov[32];
-        at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+    } else {
+      // ---------------------------------------------------------- softmax, thread = row of its group
+      const int g = warp >> 2;
+      const int row = threadIdx.x & 127;                // row within the group = tensor-memory lane
+      const int tok = row / G, hd = row - tok * G;
+      const int tok_in_req = m0 + g * tpc + tok;
+      const int qpos = start + tok_in_req;
+      const int lo_mine = it.lo_g[g], lo_max_mine = it.lo_max[g], q_first_mine = it.q_first[g];
+      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+      const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
+      const int n_mine = it.n_tiles[g];
+      float m_used = -INFINITY, l_sum = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_mine && ok; ++j) {
+        if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
+        AT_FENCE_AFTER();
+        if (row == 0 && j < 40) AT_STAMP(16 * j + 8 + 3 * g);
+        const int key0 = (tile_begin + j) * AT_KEYS;
+        const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
+        // the whole row of scores in registers: four loads in flight, one wait
+        float sv[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (store && ok) {
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (interior) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(po + c * 32 + i) = make_float4(ov[i], ov[i + 1], ov[i + 2], ov[i + 3]);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c * 32 + i;
+              const bool valid = key <= qpos && key >= lo_mine && (window <= 0 || key > qpos - window);
+              sv[c][i] = valid ? sv[c][i] : -INFINITY;
+              mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
+            }
         }
-      }
-      if (store && ok) part_ml[(size_t)split * items + item] = make_float2(m_used, l_sum);
-      __threadfence();
-      // all 128 threads of the group meet here, also after a wait that gave up: then nobody merges
-      const bool bad = at_group_any(1 + g, !ok);
-      int* ticket = tickets + (size_t)(tok0 + m0 + g * tpc) * (nq / G) + blockIdx.z;
-      if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
-      at_group_sync(1 + g);
-      if (!bad && ticket_of[g] == shares[g] - 1) {
-        if (row == 0) *ticket = 0;  // left as it was found, for the next launch
-        __threadfence();
-        if (store) {
-          float m_all = -INFINITY;
-          for (int sp = 0; sp < shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&part_ml[(size_t)sp * items + item]).x);
-          float l_all = 0.f;
-          for (int sp = 0; sp < shares[g]; ++sp) {
-            const float2 ml = __ldcg(&part_ml[(size_t)sp * items + item]);
-            l_all += at_ex2((ml.x - m_all) * scale_log2) * ml.y;
-          }
-          const float inv = 1.0f / l_all;
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        if (row == 0 && j < 40) AT_STAMP(16 * j + 9 + 3 * g);
+        const float m_new = fmaxf(m_used, m_tile);
+        float alpha = 1.f;
+        bool rescale = false;
+        if (m_used == -INFINITY) {
+          m_used = m_new;
+        } else if ((m_new - m_used) * scale_log2 > 8.f) {
+          alpha = at_ex2((m_used - m_new) * scale_log2);
+          m_used = m_new;
+          rescale = true;
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+          // S(j) is complete, so the product P(j-1) V(j-1) issued before it is complete too: O is quiet
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            float acc[32];
+            float ov[32];
+            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-            for (int sp = 0; sp < shares[g]; ++sp) {
-              const float w = at_ex2((__ldcg(&part_ml[(size_t)sp * items + item]).x - m_all) * scale_log2);
-              const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)sp * items + item) * AT_D + c * 32);
+            for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+            at_tmem_st32(t_o + (uint32_t)(c * 32), ov);
+          }
+          l_sum *= alpha;
+        }
+        // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
+        // (masked scores are -inf and give 0)
+        const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 v = __ldcg(src + i);
-                acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
-                acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
-                acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
-                acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
-              }
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
+            const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
+            const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
+            part[(i >> 1) & 3] += e0 + e1;
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
+          }
+          at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
+        }
+        l_sum += (part[0] + part[1]) + (part[2] + part[3]);
+        const int valid_keys = kv_len - key0;
+        if (valid_keys < AT_KEYS && row >= valid_keys) {
+          unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(vt + h * AT_BLOCK + row * 128 + cc * 16) = make_uint4(0u, 0u, 0u, 0u);
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        AT_FENCE_BEFORE();
+        at_arrive(&p_full[g]);
+        if (row == 0 && j < 40) AT_STAMP(16 * j + 10 + 3 * g);
+      }
+      if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
+      if (!ok) {
+        atomicExch(status, 34);
+        failed = 1;
+      }
+      AT_FENCE_AFTER();
+      const bool store = tok_in_req < q_len;
+      const size_t item = (size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd;  // (token, head) of this row
+      __nv_bfloat16* dst = out + item * AT_D;
+      if (it.shares[g] <= 1) {
+        if (ok && n_mine > 0) {
+          const float inv = 1.0f / l_sum;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float ov[32];
+            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (store) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(ov + i, inv);
             }
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
           }
         }
+      } else if (n_mine > 0) {
+        // one of several splits of this group's keys: leave the partial result, take a ticket
+        const size_t items = (size_t)num_tokens * nq;
+        float* po = part_o + ((size_t)split * items + item) * AT_D;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float ov[32];
+          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (store && ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(po + c * 32 + i) = make_float4(ov[i], ov[i + 1], ov[i + 2], ov[i + 3]);
+          }
+        }
+        if (store && ok) part_ml[(size_t)split * items + item] = make_float2(m_used, l_sum);
+        __threadfence();
+        // all 128 threads of the group meet here, also after a wait that gave up: then nobody merges
+        const bool bad = at_group_any(1 + g, !ok);
+        int* ticket = tickets + (size_t)(tok0 + m0 + g * tpc) * (nq / G) + head0 / G;
+        if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
+        at_group_sync(1 + g);
+        if (!bad && ticket_of[g] == it.shares[g] - 1) {
+          if (row == 0) *ticket = 0;  // left as it was found, for the next launch
+          __threadfence();
+          if (store) {
+            float m_all = -INFINITY;
+            for (int sp = 0; sp < it.shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&part_ml[(size_t)sp * items + item]).x);
+            float l_all = 0.f;
+            for (int sp = 0; sp < it.shares[g]; ++sp) {
+              const float2 ml = __ldcg(&part_ml[(size_t)sp * items + item]);
+              l_all += at_ex2((ml.x - m_all) * scale_log2) * ml.y;
+            }
+            const float inv = 1.0f / l_all;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float acc[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+              for (int sp = 0; sp < it.shares[g]; ++sp) {
+                const float w = at_ex2((__ldcg(&part_ml[(size_t)sp * items + item]).x - m_all) * scale_log2);
+                const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)sp * items + item) * AT_D + c * 32);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 v = __ldcg(src + i);
+                  acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
+                  acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
+                  acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
+                  acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
+            }
+          }
+        }
+        at_group_sync(1 + g);  // ticket_of[g] is free for the next item
       }
     }
+    // ------------------------------------------------------------ between items
+    // Everything of this item is over: every product has completed (the softmax groups waited for
+    // the last ones), every arrival that was asked for has been waited for. The barriers start
+    // again from phase 0 and the scheduler publishes the next item.
+    AT_FENCE_BEFORE();
+    __syncthreads();
+    if (failed) break;
+    if (threadIdx.x == 0) init_barriers();
+    if (warp == 8 && lane == 0) item_slot = next_item;
+    first_item = false;
+    __syncthreads();
+    AT_FENCE_AFTER();
   }
   AT_FENCE_BEFORE();
   __syncthreads();
@@ -623,14 +731,15 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
                                  int window, int page_size, int* status, int splits, float* part_o, float* part_ml,
-                                 int* tickets, cudaStream_t stream) {
+                                 int* queue, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(splits >= 1 && splits <= 64, "attention_tc: %d key splits", splits);
-  MS_CHECK_ARG(splits == 1 || (part_o != nullptr && part_ml != nullptr && tickets != nullptr && (uintptr_t)part_o % 16 == 0 &&
-                               (uintptr_t)part_ml % 8 == 0),
-               "attention_tc: key splits need scratch for the partial results and zeroed tickets");
+  // queue: 2 + num_tokens * nq / G int32, zero before the first launch and left zero by every launch
+  // (the work queue's two counters, then the tickets of the groups whose keys are split)
+  MS_CHECK_ARG(queue != nullptr, "attention_tc: the work queue is missing");
+  MS_CHECK_ARG(splits == 1 || (part_o != nullptr && part_ml != nullptr && (uintptr_t)part_o % 16 == 0 && (uintptr_t)part_ml % 8 == 0),
+               "attention_tc: key splits need scratch for the partial results");
   MS_CHECK_ARG(ms_attn_tc_supports(AT_D, page_size, nq, nkv), "attention_tc: unsupported shape (page_size=%d)", page_size);
-  MS_CHECK_ARG(num_rows <= 65535, "attention_tc: too many rows (%d) for one launch", num_rows);
   MS_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0), "attention_tc: operands must be 16-byte aligned");
   const int G = at_heads_per_cta(nq, nkv);
   const int tpc = AT_ROWS / G;
@@ -667,9 +776,19 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
     MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured = true;
   }
-  dim3 grid(ceil_div(max_q_len, 2 * tpc) * splits, num_rows, nq / G);
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, g_min_tiles, window, G};
+  const long long total = (long long)gr.q_tiles * gr.rows * gr.head_groups * gr.splits;
+  MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
+  // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
+  const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, window, page_shift, G, status, g_trace, splits,
-            g_min_tiles, num_tokens, part_o, reinterpret_cast<float2*>(part_ml), tickets);
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status, g_trace, num_tokens,
+            part_o, reinterpret_cast<float2*>(part_ml), queue, queue + 2);
   return 0;
 }

@@ -43,4 +43,18 @@ class StepContext:
     sm_count: int = 148
     scratch: dict = field(default_factory=dict)  # per-step or persistent scratch buffers of kernels
     step_cache: dict = field(default_factory=dict)  # what parts compute once per step and share (e.g. the rotation table)
+    buffers: dict = field(default_factory=dict)  # activation buffers of this step, by (role, shape, dtype): see buffer()
     graph_bucket: int = 0  # > 0 while a CUDA graph for this padded batch size is captured or replayed
+
+    def buffer(self, role: str, shape: tuple, dtype: torch.dtype, device) -> torch.Tensor:
+        """An uninitialised activation tensor that lives for this step and is shared by every
+        layer: the first caller with this (role, shape, dtype) allocates it, later callers get the
+        same tensor. Kernels of one step run in stream order, so a part may take a role's buffer
+        again in the next layer once nothing of its own still reads it. A part names a role for
+        each tensor it has alive at the same time ("attn.qkv", "attn.q", ...)."""
+        key = (role, shape, dtype)
+        t = self.buffers.get(key)
+        if t is None:
+            t = torch.empty(shape, dtype=dtype, device=device)
+            self.buffers[key] = t
+        return t

@@ -11,7 +11,7 @@ import ctypes
 
 import torch
 
-from . import native
+from . import blas, native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
@@ -308,10 +308,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
     if tc_gemm_ok(x, weight):
         return linear_tc(x, weight, out, "f32" if out.dtype == torch.float32 else "bf16", stream=stream)
-    if out.dtype == torch.float32:
-        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
-    else:
-        torch.mm(x, weight.t(), out=out)
+    assert out.shape == (m, n) and out.dtype in (torch.float32, torch.bfloat16)
+    blas.gemm_bf16(out, x, weight, _stream(stream))
     return out
 
 
@@ -480,17 +478,17 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     splits = lib.ms_attn_tc_splits(t - first_row, nq, k_pool.shape[1], ctx.sm_count)
     while splits > 1 and splits * items * (d + 2) * 4 > _ATTN_TC_SCRATCH_LIMIT:
         splits -= 1
-    part = tickets = None
+    part = None
     if splits > 1:
         part = ctx.scratch.get("attn_tc_partials")
         if part is None or part.numel() < splits * items * (d + 2):
             part = torch.empty(splits * items * (d + 2), dtype=torch.float32, device=q.device)
             ctx.scratch["attn_tc_partials"] = part
-        tickets = ctx.scratch.get("attn_tc_tickets")
-        if tickets is None or tickets.numel() < items:
-            # zero before the first launch, left zero by every launch
-            tickets = torch.zeros(max(items, 1 << 16), dtype=torch.int32, device=q.device)
-            ctx.scratch["attn_tc_tickets"] = tickets
+    tickets = ctx.scratch.get("attn_tc_queue")
+    if tickets is None or tickets.numel() < items + 2:
+        # the work queue's counters and the merge tickets: zero before the first launch, left zero by every launch
+        tickets = torch.zeros(max(items + 2, 1 << 16), dtype=torch.int32, device=q.device)
+        ctx.scratch["attn_tc_queue"] = tickets
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), ctx.num_rows - first_row, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),

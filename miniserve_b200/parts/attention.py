@@ -79,8 +79,9 @@ class GQAttention(Part):
         """Returns the mixer's addend to the residual stream: a tensor [T, hidden], or float32
         partial sums of it that the next norm adds up (``ops.PartialSums``)."""
         t = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv, stream=ctx.stream)
-        q = torch.empty((t, self.heads, self.head_dim), dtype=x.dtype, device=x.device)
+        dt, dev = self.env.dtype, self.w_qkv.device
+        qkv = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
+        q = ctx.buffer("attn.q", (t, self.heads, self.head_dim), dt, dev)
         inv_freq, rotary_dim = self.position.kernel_table()
         indptr, indices = ctx.page_indptr[cache.group], ctx.page_indices[cache.group]
         ops.qk_norm_rope_kv(
@@ -88,7 +89,7 @@ class GQAttention(Part):
             self.w_q_norm, self.w_k_norm, inv_freq, rotary_dim, self.qk_norm_eps, ctx.positions,
             ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream,
             cos_sin=self.position.step_table(ctx))
-        out = torch.empty_like(q)
+        out = ctx.buffer("attn.out", (t, self.heads, self.head_dim), dt, dev)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
-        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream,
-                          partials=ops.SPLIT_K_PARTIALS)
+        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,
+                          out=None if ops.SPLIT_K_PARTIALS else ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))

@@ -33,11 +33,13 @@ class SwiGLU(Part):
     takes_lazy_input = True  # forward() starts with ops.linear, which can fuse the norm before it
 
     def forward(self, x, ctx) -> torch.Tensor:
-        gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream)
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
+        gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
         if ops.FUSE_SILU and ops.fusable_rows(gate_up.shape[0], self.inter, gate_up.dtype):
             # decode steps: SiLU(gate) * up runs while the down projection stages its input
             return ops.linear(ops.LazyAct(gate_up, stream=ctx.stream), self.w_down, stream=ctx.stream,
                               partials=ops.SPLIT_K_PARTIALS)
-        act = torch.empty((gate_up.shape[0], self.inter), dtype=gate_up.dtype, device=gate_up.device)
+        act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
         ops.silu_mul(act, gate_up, stream=ctx.stream)
-        return ops.linear(act, self.w_down, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS)
+        return ops.linear(act, self.w_down, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,
+                          out=None if ops.SPLIT_K_PARTIALS else ctx.buffer("mlp.down", (t, self.hidden), dt, dev))

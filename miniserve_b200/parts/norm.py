@@ -31,7 +31,7 @@ class RMSNorm(Part):
                 and ops.fusable_rows(residual.shape[0], self.size, self.env.dtype)):
             return ops.LazyNorm(residual, delta, self.w_weight, self.eps, stream=ctx.stream)
         n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
-        out = torch.empty((n, self.size), dtype=self.env.dtype, device=residual.device)
+        out = ctx.buffer("norm.out", (n, self.size), self.env.dtype, residual.device)
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,
                         write_residual=write_residual, stream=ctx.stream)
         return out
