@@ -106,131 +106,124 @@ __global__ void qk_norm_rope_kv_kernel(
   }
 }
 
-// bfloat16 fast path for head sizes that are multiples of 64 with the whole head rotated: one
-// block per token, every warp takes a share of the heads, two adjacent elements per lane. What
-// depends on the token alone (position, page, cos/sin, norm weights) is fetched once per warp.
-template <int PER_LANE>
+// bfloat16 fast path for head sizes 128 and 256 with the whole head rotated: one block per token,
+// D/16 lanes per head. A lane holds 8 consecutive elements of the head's first half and the 8 of
+// the second half that rotate with them (two 16-byte loads), so the rotation needs no exchange
+// between lanes; only the sum of squares goes round the head's lanes. What depends on the token
+// alone (position, page, cos/sin, norm weights) is fetched once per lane, and the loads of two
+// passes over the heads are in flight together.
+template <int D>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_bf16_token_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_norm_w,
     const __nv_bfloat16* __restrict__ k_norm_w, const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
     const int* __restrict__ positions, const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
-    const int* __restrict__ page_indices, int nq, int nkv, int d, float eps, int page_shift, int* __restrict__ status) {
+    const int* __restrict__ page_indices, int nq, int nkv, float eps, int page_shift, int* __restrict__ status) {
+  constexpr int LPH = D / 16;     // lanes per head
+  constexpr int HPW = 32 / LPH;   // heads per warp and pass
+  constexpr int HALF = D / 2;
+  constexpr int BATCH = 2;        // passes whose loads are issued together
   pdl_prologue();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int half = d >> 1;
-  constexpr int per_lane = PER_LANE;  // iterations of 64 pairs (2 per lane): head size 128 or 256
+  const int sub = lane % LPH, slot = lane / LPH, j0 = sub * 8;
   const int pos = positions[t];
   const bool has_kv = k_pool != nullptr;
   const int heads_total = nq + (has_kv ? 2 * nkv : 0);
-  const __nv_bfloat16* row_in = qkv + (size_t)t * heads_total * d;
+  const __nv_bfloat16* row_in = qkv + (size_t)t * heads_total * D;
+  // The page of the token hangs on a chain of three dependent loads; the first values of the
+  // token are asked for before the chain is followed, so that both are in flight together.
+  const int request = has_kv ? row_of_token[t] : 0;
+  const int stride = nwarps * HPW;  // heads per pass of the block
+  uint4 lo_raw[BATCH], hi_raw[BATCH];
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const int h = min(base + warp * HPW + slot + b * stride, heads_total - 1);  // past the end: the last head again, unused
+      const __nv_bfloat16* src = row_in + (size_t)h * D;
+      lo_raw[b] = *reinterpret_cast<const uint4*>(src + j0);
+      hi_raw[b] = *reinterpret_cast<const uint4*>(src + HALF + j0);
+    }
+  };
+  fetch(0);
+  float cs[8], sn[8];
+  if (inv_freq == nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { cs[i] = 1.f; sn[i] = 0.f; }
+  } else if (cos_sin) {
+    const float4* c4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * D + j0);
+    const float4* s4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * D + HALF + j0);
+    const float4 a = c4[0], b = c4[1], c = s4[0], d4 = s4[1];
+    cs[0] = a.x; cs[1] = a.y; cs[2] = a.z; cs[3] = a.w; cs[4] = b.x; cs[5] = b.y; cs[6] = b.z; cs[7] = b.w;
+    sn[0] = c.x; sn[1] = c.y; sn[2] = c.z; sn[3] = c.w; sn[4] = d4.x; sn[5] = d4.y; sn[6] = d4.z; sn[7] = d4.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sincosf((float)pos * inv_freq[j0 + i], &sn[i], &cs[i]);
+  }
+  // the norm weights of this lane's elements, the same for every head of a kind
+  const bool normed = q_norm_w != nullptr;
+  uint4 wq_lo = make_uint4(0u, 0u, 0u, 0u), wq_hi = wq_lo, wk_lo = wq_lo, wk_hi = wq_lo;
+  if (normed) {
+    wq_lo = *reinterpret_cast<const uint4*>(q_norm_w + j0);
+    wq_hi = *reinterpret_cast<const uint4*>(q_norm_w + HALF + j0);
+    if (has_kv) {
+      wk_lo = *reinterpret_cast<const uint4*>(k_norm_w + j0);
+      wk_hi = *reinterpret_cast<const uint4*>(k_norm_w + HALF + j0);
+    }
+  }
   size_t slot_base = 0;
   if (has_kv) {
-    const int page = page_indices[page_indptr[row_of_token[t]] + (pos >> page_shift)];
+    const int page = page_indices[page_indptr[request] + (pos >> page_shift)];
     if (page < 0) {
       if (threadIdx.x == 0) atomicExch(status, 2);
       return;
     }
     const int page_size = 1 << page_shift;
-    slot_base = ((size_t)page * nkv * page_size + (pos & (page_size - 1))) * d;  // + kvh * page_size * d
+    slot_base = ((size_t)page * nkv * page_size + (pos & (page_size - 1))) * D;  // + kvh * page_size * D
   }
-  // per-lane constants: cos/sin of its two pairs per iteration (at most 2 iterations: d <= 256)
-  float cs[per_lane][2], sn[per_lane][2];
+  for (int base = 0; base < heads_total; base += BATCH * stride) {  // the same trips for every lane: they exchange sums
+    const int h0 = base + warp * HPW + slot;
+    if (base > 0) fetch(base);
 #pragma unroll
-  for (int it = 0; it < per_lane; ++it) {
-    const int j = it * 64 + 2 * lane;
-    if (inv_freq == nullptr) {
-      cs[it][0] = cs[it][1] = 1.f;
-      sn[it][0] = sn[it][1] = 0.f;
-    } else if (cos_sin) {
-      const float2 c = *reinterpret_cast<const float2*>(cos_sin + (size_t)t * d + j);
-      const float2 s2 = *reinterpret_cast<const float2*>(cos_sin + (size_t)t * d + half + j);
-      cs[it][0] = c.x; cs[it][1] = c.y; sn[it][0] = s2.x; sn[it][1] = s2.y;
-    } else {
-      sincosf((float)pos * inv_freq[j], &sn[it][0], &cs[it][0]);
-      sincosf((float)pos * inv_freq[j + 1], &sn[it][1], &cs[it][1]);
-    }
-  }
-  // the norm weights of this lane's elements, the same for every head of a kind
-  __nv_bfloat162 wq[per_lane][2], wk[per_lane][2];
-  const bool normed = q_norm_w != nullptr;
-#pragma unroll
-  for (int it = 0; it < per_lane; ++it) {
-    if (!normed) continue;
-    const int j = it * 64 + 2 * lane;
-    wq[it][0] = *reinterpret_cast<const __nv_bfloat162*>(q_norm_w + j);
-    wq[it][1] = *reinterpret_cast<const __nv_bfloat162*>(q_norm_w + half + j);
-    if (has_kv) {
-      wk[it][0] = *reinterpret_cast<const __nv_bfloat162*>(k_norm_w + j);
-      wk[it][1] = *reinterpret_cast<const __nv_bfloat162*>(k_norm_w + half + j);
-    }
-  }
-  // Heads in batches of four per warp: all loads of a batch are issued before the first is
-  // used, so that a warp keeps several cache lines in flight instead of one head's two.
-  constexpr int HB = 4;
-  for (int h0 = warp; h0 < heads_total; h0 += HB * nwarps) {
-    __nv_bfloat162 raw[HB][per_lane][2];
-#pragma unroll
-    for (int b = 0; b < HB; ++b) {
-      const int h = min(h0 + b * nwarps, heads_total - 1);  // past the end: the last head again, unused
-      const __nv_bfloat16* src = row_in + (size_t)h * d;
-#pragma unroll
-      for (int it = 0; it < per_lane; ++it) {
-        const int j = it * 64 + 2 * lane;
-        raw[b][it][0] = *reinterpret_cast<const __nv_bfloat162*>(src + j);
-        raw[b][it][1] = *reinterpret_cast<const __nv_bfloat162*>(src + half + j);
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < HB; ++b) {
-      const int h = h0 + b * nwarps;
-      if (h >= heads_total) continue;
-      if (h >= nq + nkv) {  // a value head: copied as it is
-        __nv_bfloat16* dst = v_pool + slot_base + ((size_t)(h - nq - nkv) << page_shift) * d;
-#pragma unroll
-        for (int it = 0; it < per_lane; ++it) {
-          const int j = it * 64 + 2 * lane;
-          *reinterpret_cast<__nv_bfloat162*>(dst + j) = raw[b][it][0];
-          *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = raw[b][it][1];
-        }
-        continue;
-      }
-      const bool is_q = h < nq;
-      __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * nq + h) * d : k_pool + slot_base + ((size_t)(h - nq) << page_shift) * d;
-      float lo[per_lane][2], hi[per_lane][2];
+    for (int b = 0; b < BATCH; ++b) {
+      const int h = h0 + b * stride;
+      const bool live = h < heads_total;
+      const bool is_v = h >= nq + nkv, is_q = h < nq;
+      float lo[8], hi[8];
+      bf16x8_to_float(lo_raw[b], lo);
+      bf16x8_to_float(hi_raw[b], hi);
       float ss = 0.f;
 #pragma unroll
-      for (int it = 0; it < per_lane; ++it) {
-        const float2 a = __bfloat1622float2(raw[b][it][0]);
-        const float2 c = __bfloat1622float2(raw[b][it][1]);
-        lo[it][0] = a.x; lo[it][1] = a.y; hi[it][0] = c.x; hi[it][1] = c.y;
-        ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
-      }
-      float inv = 1.f;
-      if (normed) {
-        ss = warp_sum(ss);
-        inv = 1.0f / sqrtf(ss / (float)d + eps);
-      }
+      for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+      // every lane takes part in the exchange, also those past the last head
 #pragma unroll
-      for (int it = 0; it < per_lane; ++it) {
-        const int j = it * 64 + 2 * lane;
-        float wl[2] = {1.f, 1.f}, wh[2] = {1.f, 1.f};
+      for (int off = LPH / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      uint4 out_lo = lo_raw[b], out_hi = hi_raw[b];  // a value head is stored as it came
+      if (!is_v) {
+        float wl[8], wh[8];
+        float inv = 1.f;
         if (normed) {
-          const float2 a = __bfloat1622float2(is_q ? wq[it][0] : wk[it][0]);
-          const float2 c = __bfloat1622float2(is_q ? wq[it][1] : wk[it][1]);
-          wl[0] = a.x; wl[1] = a.y; wh[0] = c.x; wh[1] = c.y;
+          inv = 1.0f / sqrtf(ss / (float)D + eps);
+          bf16x8_to_float(is_q ? wq_lo : wk_lo, wl);
+          bf16x8_to_float(is_q ? wq_hi : wk_hi, wh);
         }
-        float ol[2], oh[2];
+        float ol[8], oh[8];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float l = normed ? (lo[it][e] * inv) * wl[e] : lo[it][e];
-          const float hgh = normed ? (hi[it][e] * inv) * wh[e] : hi[it][e];
-          ol[e] = l * cs[it][e] - hgh * sn[it][e];
-          oh[e] = hgh * cs[it][e] + l * sn[it][e];
+        for (int i = 0; i < 8; ++i) {
+          const float l = normed ? (lo[i] * inv) * wl[i] : lo[i];
+          const float hgh = normed ? (hi[i] * inv) * wh[i] : hi[i];
+          ol[i] = l * cs[i] - hgh * sn[i];
+          oh[i] = hgh * cs[i] + l * sn[i];
         }
-        *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(ol[0], ol[1]);
-        *reinterpret_cast<__nv_bfloat162*>(dst + half + j) = __floats2bfloat162_rn(oh[0], oh[1]);
+        out_lo = float_to_bf16x8(ol);
+        out_hi = float_to_bf16x8(oh);
+      }
+      if (live) {
+        __nv_bfloat16* dst = is_q ? q_out + ((size_t)t * nq + h) * D
+                                  : (is_v ? v_pool + slot_base + ((size_t)(h - nq - nkv) << page_shift) * D
+                                          : k_pool + slot_base + ((size_t)(h - nq) << page_shift) * D);
+        *reinterpret_cast<uint4*>(dst + j0) = out_lo;
+        *reinterpret_cast<uint4*>(dst + HALF + j0) = out_hi;
       }
     }
   }
@@ -282,19 +275,19 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   if (dtype == MS_BF16 && head_dim % 128 == 0 && head_dim <= 256 && (rotary_dim == head_dim || inv_freq == nullptr) &&
-      (k_pool == nullptr || (q_norm_w != nullptr) == (k_norm_w != nullptr)) && ((uintptr_t)qkv % 8 == 0) &&
-      ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)k_pool % 8 == 0) && ((uintptr_t)v_pool % 8 == 0) &&
-      (cos_sin == nullptr || (uintptr_t)cos_sin % 8 == 0)) {
+      (k_pool == nullptr || (q_norm_w != nullptr) == (k_norm_w != nullptr)) && ((uintptr_t)qkv % 16 == 0) &&
+      ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) &&
+      ((uintptr_t)q_norm_w % 16 == 0) && ((uintptr_t)k_norm_w % 16 == 0) && (cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0)) {
     if (head_dim == 128)
-      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<1>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<128>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
                 inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
-                head_dim, eps, page_shift, status);
+                eps, page_shift, status);
     else
-      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<2>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+      MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<256>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
                 inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
-                head_dim, eps, page_shift, status);
+                eps, page_shift, status);
     return 0;
   }
   if (dtype == MS_F32)
