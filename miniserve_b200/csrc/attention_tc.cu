@@ -201,7 +201,7 @@ __device__ __forceinline__ bool at_group_any(int id, bool flag) {
 // has to do. All threads of a CTA compute it from the item's index; the scheduler warp also
 // uses it to tell empty items from real ones.
 struct AtItem {
-  int r, tok0, q_len, m0, start, kv_len, head0, split;
+  int r, rank, tok0, q_len, m0, start, kv_len, head0, split;
   int n_tiles[2], q_first[2], q_last[2], lo_g[2], lo_max[2], shares[2];
   int tile_begin, n_all;
   bool has_b;
@@ -221,11 +221,11 @@ __device__ __forceinline__ bool at_item(AtItem& it, int idx, const AtGrid& gr, c
   it.head0 = (idx % gr.head_groups) * gr.G;
   idx /= gr.head_groups;
   it.r = idx % gr.rows;
-  const int rank = idx / gr.rows;
+  it.rank = idx / gr.rows;
   const int tpc = AT_ROWS / gr.G;  // tokens per group
   it.tok0 = cu_q[it.r];
   it.q_len = cu_q[it.r + 1] - it.tok0;
-  it.m0 = (gr.q_tiles - 1 - rank) * 2 * tpc;
+  it.m0 = (gr.q_tiles - 1 - it.rank) * 2 * tpc;
   if (it.m0 >= it.q_len) return false;
   it.start = q_start[it.r];
   it.kv_len = it.start + it.q_len;
@@ -295,7 +295,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int page_shift,
-                        const AtGrid gr, int* __restrict__ status, long long* __restrict__ trace, int num_tokens,
+                        const AtGrid gr, int* __restrict__ status, long long* __restrict__ trace,
                         float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
                         int* __restrict__ tickets) {
   extern __shared__ unsigned char smem_dyn[];
@@ -585,55 +585,60 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       } else if (n_mine > 0) {
-        // one of several splits of this group's keys: leave the partial result, take a ticket
-        const size_t items = (size_t)num_tokens * nq;
-        float* po = part_o + ((size_t)split * items + item) * AT_D;
+        // One of several splits of this group's keys: leave the partial result, take a ticket.
+        // Partial results are laid out [group of rows][split][4 columns][row], so that the 128
+        // threads of a group (one row each) write and read whole 512-byte lines together.
+        const size_t unit = ((size_t)(it.rank * gr.rows + r) * gr.head_groups + head0 / G) * 2 + g;
+        float4* po = reinterpret_cast<float4*>(part_o) + (unit * gr.splits + split) * (32 * 128) + row;
+        float2* pml = part_ml + unit * gr.splits * 128 + row;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float ov[32];
           at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          if (store && ok) {
+          if (ok) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(po + c * 32 + i) = make_float4(ov[i], ov[i + 1], ov[i + 2], ov[i + 3]);
+            for (int i = 0; i < 8; ++i) po[(c * 8 + i) * 128] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
           }
         }
-        if (store && ok) part_ml[(size_t)split * items + item] = make_float2(m_used, l_sum);
+        if (ok) pml[split * 128] = make_float2(m_used, l_sum);
         __threadfence();
         // all 128 threads of the group meet here, also after a wait that gave up: then nobody merges
         const bool bad = at_group_any(1 + g, !ok);
-        int* ticket = tickets + (size_t)(tok0 + m0 + g * tpc) * (nq / G) + head0 / G;
+        int* ticket = tickets + unit;
         if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
         at_group_sync(1 + g);
         if (!bad && ticket_of[g] == it.shares[g] - 1) {
           if (row == 0) *ticket = 0;  // left as it was found, for the next launch
           __threadfence();
-          if (store) {
-            float m_all = -INFINITY;
-            for (int sp = 0; sp < it.shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&part_ml[(size_t)sp * items + item]).x);
-            float l_all = 0.f;
-            for (int sp = 0; sp < it.shares[g]; ++sp) {
-              const float2 ml = __ldcg(&part_ml[(size_t)sp * items + item]);
-              l_all += at_ex2((ml.x - m_all) * scale_log2) * ml.y;
-            }
-            const float inv = 1.0f / l_all;
+          const float4* pall = reinterpret_cast<const float4*>(part_o) + unit * gr.splits * (32 * 128) + row;
+          float m_all = -INFINITY;
+          for (int sp = 0; sp < it.shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&pml[sp * 128]).x);
+          float l_all = 0.f;
+          for (int sp = 0; sp < it.shares[g]; ++sp) {
+            const float2 ml = __ldcg(&pml[sp * 128]);
+            l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
+          }
+          const float inv = 1.0f / l_all;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-              float acc[32];
+          for (int c = 0; c < 4; ++c) {
+            float acc[32];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-              for (int sp = 0; sp < it.shares[g]; ++sp) {
-                const float w = at_ex2((__ldcg(&part_ml[(size_t)sp * items + item]).x - m_all) * scale_log2);
-                const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)sp * items + item) * AT_D + c * 32);
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+            for (int sp = 0; sp < it.shares[g]; ++sp) {
+              const float2 ml = __ldcg(&pml[sp * 128]);
+              const float w = ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2);
+              const float4* src = pall + (size_t)sp * (32 * 128) + (c * 8) * 128;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float4 v = __ldcg(src + i);
-                  acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
-                  acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
-                  acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
-                  acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
-                }
+              for (int i = 0; i < 8; ++i) {
+                const float4 v = __ldcg(src + i * 128);
+                acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
+                acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
+                acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
+                acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
               }
+            }
+            if (store) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
             }
@@ -704,40 +709,53 @@ static int at_heads_per_cta(int nq, int nkv) {
   return G;
 }
 
-static int g_splits = 0, g_min_tiles = 16;
+static int g_splits = 0, g_min_tiles = 8;
 // Tuning: force the number of key splits (0: chosen from the size of the step) and the least
 // number of key tiles that a split keeps.
 MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
   g_splits = splits;
-  g_min_tiles = min_tiles > 0 ? min_tiles : 16;
+  g_min_tiles = min_tiles > 0 ? min_tiles : 8;
 }
 
-// How many CTAs share the keys of one tile of queries. One CTA fills an SM, so a step with fewer
+// How many items share the keys of one tile of queries. One CTA fills an SM, so a step with fewer
 // query tiles than SMs (a portion of a prompt far into a long context, above all) leaves SMs idle
-// while the others walk through thousands of keys: then the keys are cut so that the CTAs about
-// fill the GPU once. More CTAs than SMs only add a second wave and partial results (measured on
-// B200, 16 heads in 8 groups: 256 tokens behind 30,000: 653 us whole, 147 us in 8 splits; 512
-// behind 8,192: 193 -> 87 us in 4; 2,048 behind 2,048, which has 128 tiles: 96 us whole, 137 us
-// cut in three). Each split needs num_tokens * nq * (128 + 2) float32 of scratch.
+// while the others walk through thousands of keys: then the keys are cut so that the items about
+// fill the GPU once, in splits of at least 8 key tiles. With more tiles than SMs the queue evens
+// the load out by itself and splits only add partial results (3,072 tokens: 77 us whole, 85 us in
+// two). Measured on B200, 16 heads in 8 groups: 256 tokens behind 30,000: 645 us whole, 109 us in
+// 9 splits; 512 behind 8,192: 193 -> 72 us in 4; one prompt of 2,048 (128 tiles, the last of them
+// 16 key tiles long): 57 -> 47 us in 2. ms_attn_tc_scratch says how much scratch splits need.
 MS_EXPORT int ms_attn_tc_splits(int num_tokens, int nq, int nkv, int sm_count) {
   if (g_splits > 0) return g_splits;
   const int G = at_heads_per_cta(nq, nkv);
   const long long ctas = (long long)ceil_div(num_tokens, 2 * (AT_ROWS / G)) * (nq / G);
+  if (ctas > sm_count) return 1;
   const long long want = sm_count / ctas;
-  return (int)(want < 1 ? 1 : (want > 16 ? 16 : want));
+  return (int)(want < 2 ? 2 : (want > 16 ? 16 : want));
+}
+
+// What a launch needs besides its operands: float32 for the partial results of split key ranges
+// (none for one split) and int32 for the work queue and the merge tickets; the int32 must be zero
+// before the first launch and are left zero by every launch.
+MS_EXPORT void ms_attn_tc_scratch(int max_q_len, int num_rows, int nq, int nkv, int splits, long long* partial_floats,
+                                  long long* queue_ints) {
+  const int G = at_heads_per_cta(nq, nkv);
+  const long long units = (long long)ceil_div(max_q_len, 2 * (AT_ROWS / G)) * num_rows * (nq / G) * 2;  // groups of 128 rows
+  *partial_floats = splits > 1 ? units * splits * (AT_ROWS * AT_D + AT_ROWS * 2) : 0;
+  *queue_ints = 2 + units;
 }
 
 MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
-                                 int window, int page_size, int* status, int splits, float* part_o, float* part_ml,
-                                 int* queue, cudaStream_t stream) {
+                                 int window, int page_size, int* status, int splits, float* partials, int* queue,
+                                 cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(splits >= 1 && splits <= 64, "attention_tc: %d key splits", splits);
-  // queue: 2 + num_tokens * nq / G int32, zero before the first launch and left zero by every launch
-  // (the work queue's two counters, then the tickets of the groups whose keys are split)
+  // partials and queue: sized by ms_attn_tc_scratch (the work queue's two counters, then the tickets
+  // of the groups whose keys are split)
   MS_CHECK_ARG(queue != nullptr, "attention_tc: the work queue is missing");
-  MS_CHECK_ARG(splits == 1 || (part_o != nullptr && part_ml != nullptr && (uintptr_t)part_o % 16 == 0 && (uintptr_t)part_ml % 8 == 0),
+  MS_CHECK_ARG(splits == 1 || (partials != nullptr && (uintptr_t)partials % 16 == 0),
                "attention_tc: key splits need scratch for the partial results");
   MS_CHECK_ARG(ms_attn_tc_supports(AT_D, page_size, nq, nkv), "attention_tc: unsupported shape (page_size=%d)", page_size);
   MS_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0), "attention_tc: operands must be 16-byte aligned");
@@ -788,7 +806,8 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
   const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status, g_trace, num_tokens,
-            part_o, reinterpret_cast<float2*>(part_ml), queue, queue + 2);
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status, g_trace,
+            partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
+            queue + 2);
   return 0;
 }

@@ -473,25 +473,33 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     t, nq, d = q.shape
     lib = native.attn_tc()
     skip = 4 * first_row  # the per-row tables are int32
-    # a short step cuts the keys of its last tiles between several CTAs, which leave partial results
-    items = t * nq
-    splits = lib.ms_attn_tc_splits(t - first_row, nq, k_pool.shape[1], ctx.sm_count)
-    while splits > 1 and splits * items * (d + 2) * 4 > _ATTN_TC_SCRATCH_LIMIT:
-        splits -= 1
+    # a step with few query tiles cuts long key ranges between several CTAs, which leave partial results
+    rows = ctx.num_rows - first_row
+    plan = ctx.step_cache.get(("attn_tc_plan", first_row, nq, k_pool.shape[1]))
+    if plan is None:  # the same for every layer of the step
+        splits = lib.ms_attn_tc_splits(t - first_row, nq, k_pool.shape[1], ctx.sm_count)
+        need_f, need_i = ctypes.c_longlong(), ctypes.c_longlong()
+        while True:
+            lib.ms_attn_tc_scratch(ctx.max_q_len, rows, nq, k_pool.shape[1], splits, ctypes.byref(need_f), ctypes.byref(need_i))
+            if splits == 1 or need_f.value * 4 <= _ATTN_TC_SCRATCH_LIMIT:
+                break
+            splits -= 1
+        plan = (splits, need_f.value, need_i.value)
+        ctx.step_cache[("attn_tc_plan", first_row, nq, k_pool.shape[1])] = plan
+    splits, need_floats, need_ints = plan
     part = None
     if splits > 1:
         part = ctx.scratch.get("attn_tc_partials")
-        if part is None or part.numel() < splits * items * (d + 2):
-            part = torch.empty(splits * items * (d + 2), dtype=torch.float32, device=q.device)
+        if part is None or part.numel() < need_floats:
+            part = torch.empty(need_floats, dtype=torch.float32, device=q.device)
             ctx.scratch["attn_tc_partials"] = part
-    tickets = ctx.scratch.get("attn_tc_queue")
-    if tickets is None or tickets.numel() < items + 2:
+    queue = ctx.scratch.get("attn_tc_queue")
+    if queue is None or queue.numel() < need_ints:
         # the work queue's counters and the merge tickets: zero before the first launch, left zero by every launch
-        tickets = torch.zeros(max(items + 2, 1 << 16), dtype=torch.int32, device=q.device)
-        ctx.scratch["attn_tc_queue"] = tickets
+        queue = torch.zeros(max(need_ints, 1 << 16), dtype=torch.int32, device=q.device)
+        ctx.scratch["attn_tc_queue"] = queue
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
-        _ptr(ctx.page_indices[group]), ctx.num_rows - first_row, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, _ptr(part),
-        None if part is None else part.data_ptr() + splits * items * d * 4, _ptr(tickets), ctx.stream),
+        _ptr(ctx.page_indices[group]), rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
+        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, _ptr(part), _ptr(queue), ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")
