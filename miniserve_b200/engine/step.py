@@ -223,5 +223,10 @@ class StepFunction:
         code = int(self.status.item())
         if code:
             self.status.zero_()
+            # a kernel that gave up may have left its tickets and work-queue counters half counted:
+            # they go back to zero (in place: CUDA graphs hold their addresses)
+            for buf in self.persistent_scratch.values():
+                if isinstance(buf, torch.Tensor) and buf.dtype == torch.int32:
+                    buf.zero_()
             raise StepError(f"a kernel reported a fault it caught itself (code {code}: 2-3 inconsistent cache "
-                            f"metadata, 11-13 a bounded wait in the tensor-core pipeline ran out)")
+                            f"metadata; 11-13, 21-24, 31-34 a bounded wait in a tensor-core pipeline ran out)")
