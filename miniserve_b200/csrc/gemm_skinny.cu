@@ -49,14 +49,18 @@ struct SkinnyFused {
 };
 
 
-// MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: float32 partials [splits, M, N]
+// MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: float32 partials [splits, M, N];
+// MODE 3: W is a stacked gate|up weight [2N, K] and out [M, N] = silu(x Wg^T) * (x Wu^T) in bf16
+// (miniserve/model/qwen3.py:128-131): the CTA takes 8 gate rows as the lower half of its fragments
+// and the 8 up rows that belong to them as the upper half, so both factors of an output meet in it.
+// Both products are rounded to bfloat16 before the activation, as when they are stored in between.
 template <int MT, int MODE, int PRO>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                    int M, int N, int K, int k_per_split, SkinnyFused fused) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * SK_ROWS;
+  const int n0 = blockIdx.x * (MODE == 3 ? 8 : SK_ROWS);
   const int k_begin = blockIdx.y * k_per_split, k_end = min(K, k_begin + k_per_split);
   const int k_len = k_end - k_begin;
   const int xs_stride = k_per_split + 32;  // bf16 elements: rows 64 bytes apart modulo 128, so 16-byte reads of two rows do not collide
@@ -65,9 +69,10 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
   // this warp's part of the slice, in chunks of 32 k (8 per lane of a quad)
   const int per_warp = ((k_len + SK_WARPS * 32 - 1) / (SK_WARPS * 32)) * 32;
   const int wk_begin = warp * per_warp, wk_end = min(k_len, wk_begin + per_warp);
-  const bool row_a = n0 + g < N, row_b = n0 + g + 8 < N;
+  const int upper = MODE == 3 ? N : 8;  // where the fragments' upper rows come from, relative to the lower ones
+  const bool row_a = n0 + g < N, row_b = MODE == 3 ? row_a : n0 + g + 8 < N;
   const __nv_bfloat16* wa_ptr = W + (size_t)(n0 + (row_a ? g : 0)) * K + k_begin + 8 * t;
-  const __nv_bfloat16* wb_ptr = W + (size_t)(n0 + (row_b ? g + 8 : 0)) * K + k_begin + 8 * t;
+  const __nv_bfloat16* wb_ptr = W + (size_t)(n0 + (row_b ? g + upper : 0)) * K + k_begin + 8 * t;
 
   uint4 wa[SK_UNROLL], wb[SK_UNROLL];
   auto fetch = [&](int k) {
@@ -83,6 +88,13 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
   // wait for the kernels launched earlier (which produce X)
   pdl_launch_dependents();
   fetch(wk_begin);
+  // what does not fit into the registers is asked into L2 meanwhile (one 128-byte line = 64 k of a row)
+  if (t == 0) {
+    for (int kk = wk_begin + 32 * SK_UNROLL; kk < wk_end; kk += 64) {
+      if (row_a) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wa_ptr + kk));
+      if (row_b) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wb_ptr + kk));
+    }
+  }
   pdl_wait();
 
   // activations of this K slice: [MT * 8][k_len], rows past M are zero
@@ -192,6 +204,20 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
     base[(g + 8) * TOK + 8 * j + 2 * t + 1] = acc[j][3];
   }
   __syncthreads();
+  if (MODE == 3) {
+    for (int idx = tid; idx < 8 * TOK; idx += SK_THREADS) {
+      const int tok = idx >> 3, row = idx & 7;
+      if (tok >= M || n0 + row >= N) continue;
+      float sg = 0.f, su = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) {
+        sg += red[(size_t)w * SK_ROWS * TOK + row * TOK + tok];
+        su += red[(size_t)w * SK_ROWS * TOK + (row + 8) * TOK + tok];
+      }
+      const float gt = __bfloat162float(__float2bfloat16_rn(sg)), up = __bfloat162float(__float2bfloat16_rn(su));
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * N + n0 + row] = __float2bfloat16_rn(gt / (1.0f + expf(-gt)) * up);
+    }
+  } else
   for (int idx = tid; idx < SK_ROWS * TOK; idx += SK_THREADS) {
     const int tok = idx / SK_ROWS, row = idx - tok * SK_ROWS;  // consecutive threads: consecutive n
     if (tok >= M || n0 + row >= N) continue;
@@ -226,7 +252,7 @@ static int launch_skinny(void* out, const void* X, const void* W, int M, int N, 
     MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(ceil_div(N, SK_ROWS), splits);
+  dim3 grid(ceil_div(N, MODE == 3 ? 8 : SK_ROWS), splits);
   MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split, fused);
   return 0;
 }
@@ -264,6 +290,16 @@ MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M
   MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
   const SkinnyFused fused = {};
   MS_SK_DISPATCH(PRO_PLAIN);
+}
+
+// out [M, N] bfloat16 = silu(X Wg^T) * (X Wu^T) for the stacked weight W = [Wg; Wu] of 2N rows.
+MS_EXPORT int ms_gemm_skinny_gate_up_bf16(void* out, const void* X, const void* W, int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (int rc = check_skinny(W, M, N, K, 1, 0)) return rc;
+  MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
+  const SkinnyFused fused = {};
+  return M > 8 ? launch_skinny<2, 3, PRO_PLAIN>(out, X, W, M, N, K, 1, fused, stream)
+               : launch_skinny<1, 3, PRO_PLAIN>(out, X, W, M, N, K, 1, fused, stream);
 }
 
 // out = rmsnorm(res_in + delta) * norm_w times W^T; res_out (a buffer other than res_in, or null)

@@ -15,7 +15,7 @@ from . import blas, native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
-    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear",
+    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul",
     "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
@@ -310,6 +310,24 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         return linear_tc(x, weight, out, "f32" if out.dtype == torch.float32 else "bf16", stream=stream)
     assert out.shape == (m, n) and out.dtype in (torch.float32, torch.bfloat16)
     blas.gemm_bf16(out, x, weight, _stream(stream))
+    return out
+
+
+def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch=None, stream=None) -> torch.Tensor:
+    """out [M, I] = silu(x Wg^T) * (x Wu^T) for the stacked weight [2I, K] (gate rows, then up rows;
+    miniserve/model/qwen3.py:128-131). bfloat16 with at most 16 rows: one weight-streaming kernel
+    whose CTAs hold a gate row and its up row together. Otherwise the product into ``scratch``
+    ([M, 2I], allocated if None) and the activation kernel."""
+    m, kdim = x.shape
+    inter = out.shape[1]
+    assert weight.shape == (2 * inter, kdim) and out.shape[0] == m and out.dtype == x.dtype
+    if x.dtype == torch.bfloat16 and _skinny_ok(x, weight):
+        _check_dev(x, weight, out)
+        native.kernel_check(native.kernels().ms_gemm_skinny_gate_up_bf16(_ptr(out), _ptr(x), _ptr(weight), m, inter, kdim,
+                                                                        _stream(stream)))
+        return out
+    gate_up = linear(x, weight, out=scratch, stream=stream)
+    silu_mul(out, gate_up, stream=stream)
     return out
 
 

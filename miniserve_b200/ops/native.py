@@ -98,6 +98,7 @@ def kernels():
     _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _i, _ll, _p, _p, _f, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_norm_bf16", [_p, _p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_silu_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_skinny_gate_up_bf16", [_p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])

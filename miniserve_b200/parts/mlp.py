@@ -34,12 +34,16 @@ class SwiGLU(Part):
 
     def forward(self, x, ctx) -> torch.Tensor:
         t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
-        gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
-        if ops.FUSE_SILU and ops.fusable_rows(gate_up.shape[0], self.inter, gate_up.dtype):
-            # decode steps: SiLU(gate) * up runs while the down projection stages its input
+        if ops.FUSE_SILU and ops.fusable_rows(t, self.inter, dt):
+            # (measured slower than what follows) SiLU(gate) * up runs while the down projection stages its input
+            gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
             return ops.linear(ops.LazyAct(gate_up, stream=ctx.stream), self.w_down, stream=ctx.stream,
                               partials=ops.SPLIT_K_PARTIALS)
         act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
-        ops.silu_mul(act, gate_up, stream=ctx.stream)
+        if isinstance(x, torch.Tensor) and t <= ops.SKINNY_MAX_M and dt == torch.bfloat16:
+            ops.linear_silu_mul(x, self.w_gate_up, act, stream=ctx.stream)  # decode steps: the activation in the product's epilogue
+        else:
+            gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
+            ops.silu_mul(act, gate_up, stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,
                           out=None if ops.SPLIT_K_PARTIALS else ctx.buffer("mlp.down", (t, self.hidden), dt, dev))

@@ -13,6 +13,12 @@ from tests.kernel_util import PagedBatch, make_context, reference_attention
 from tests.plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
+
+
+def native_launches() -> int:
+    from miniserve_b200.ops import native
+
+    return native.LAUNCHES[0]
 DEV = "cuda"
 DTYPES = [torch.float32, torch.bfloat16]
 
@@ -181,6 +187,25 @@ def test_skinny_gemm_with_silu_mul_in_its_prologue(m, n, inter):
     parts = ops.linear(ops.LazyAct(gu), w, partials=True)
     assert torch.allclose(ops.materialize(parts).float(), expect, atol=0.05 * (inter ** 0.5), rtol=2e-2)
     assert torch.allclose(ops.LazyAct(gu).materialize().float(), act.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m, inter, k", [(1, 3072, 1024), (8, 3072, 1024), (13, 224, 96), (16, 136, 64), (5, 12288, 4096)])
+def test_skinny_gate_up_with_the_activation_in_its_epilogue(m, inter, k):
+    """One kernel for silu(x Wg^T) * (x Wu^T) at decode sizes: the same numbers as the product into a
+    [M, 2I] tensor followed by the activation kernel (both round the products to bfloat16 first)."""
+    torch.manual_seed(m + inter)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(2 * inter, k, device=DEV) * k ** -0.5).bfloat16()
+    gate_up = ops.linear(x, w)
+    want = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+    ops.silu_mul(want, gate_up)
+    got = torch.full((m, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+    before = native_launches()
+    ops.linear_silu_mul(x, w, got)
+    assert native_launches() - before == 1
+    assert torch.equal(got, want)
+    ref = torch.nn.functional.silu(x.float() @ w[:inter].float().t()) * (x.float() @ w[inter:].float().t())
+    assert torch.allclose(got.float(), ref, atol=3e-2, rtol=3e-2)
 
 
 def test_add_rmsnorm_takes_partial_sums():
