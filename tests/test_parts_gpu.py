@@ -203,3 +203,127 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
     finally:
         unregister_part("mixer", "running_mean")
         unregister_architecture("ToyStateLM")
+
+
+# ------------------------------------------------------------------ a toy routed feed-forward and a toy position encoding
+class TopOneExperts(Part):
+    """y = p_e * W2_e relu(W1_e x) for the expert e with the largest router logit (float32 logits and
+    softmax over the experts), token by token."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.inter, self.experts = spec["hidden"], spec["intermediate"], spec["experts"]
+        self.chosen = []  # what the router picked, for the test to look at
+
+    def weights(self):
+        w = {"router.weight": WeightDecl((self.experts, self.hidden), precision="float32")}
+        for e in range(self.experts):
+            w[f"experts.{e}.w1"] = WeightDecl((self.inter, self.hidden))
+            w[f"experts.{e}.w2"] = WeightDecl((self.hidden, self.inter))
+        return w
+
+    def bind(self, tensors):
+        self.router = tensors["router.weight"]
+        assert self.router.dtype == torch.float32  # kept in 32-bit whatever the run's dtype
+        self.w1 = [tensors[f"experts.{e}.w1"] for e in range(self.experts)]
+        self.w2 = [tensors[f"experts.{e}.w2"] for e in range(self.experts)]
+
+    def forward(self, x, ctx):
+        from miniserve_b200 import ops
+
+        x = ops.materialize(x)
+        logits = x.float() @ self.router.T
+        prob, expert = torch.softmax(logits, -1).max(-1)
+        self.chosen.append(expert.cpu())
+        out = torch.zeros_like(x)
+        for e in range(self.experts):
+            rows = (expert == e).nonzero().flatten()
+            if rows.numel():
+                h = torch.relu(ops.linear(x[rows].contiguous(), self.w1[e], stream=ctx.stream))
+                y = ops.linear(h, self.w2[e], stream=ctx.stream)
+                out[rows] = (y.float() * prob[rows, None]).to(x.dtype)
+        return out
+
+
+class HalvedPositions(Part):
+    """A rotary encoding whose angle is floor(position / 2) * inv_freq: neighbours share an angle.
+    The framework's q/k kernel takes it as a table of cos and sin per token."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        d = spec["head_dim"]
+        self.rotary_dim = d
+        self.inv_freq = (1.0 / (spec["theta"] ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(env.device)
+
+    def kernel_table(self):
+        return self.inv_freq, self.rotary_dim
+
+    def step_table(self, ctx):
+        angle = (ctx.positions[:ctx.num_tokens] // 2).float()[:, None] * self.inv_freq[None, :]
+        return torch.cat((angle.cos(), angle.sin()), dim=1).contiguous()
+
+
+def _toy_routed_spec(raw):
+    hidden = raw["hidden_size"]
+    norm = PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"]))
+    block = PartSpec("prenorm", dict(names=dict(mixer="mixer.", feed_forward="ffn.", norm1="ln1.", norm2="ln2.")))
+    dense = PartSpec("swiglu", dict(hidden=hidden, intermediate=raw["inter"]))
+    routed = PartSpec("top_one_experts", dict(hidden=hidden, intermediate=raw["inter"], experts=3))
+
+    def attention(position):
+        return PartSpec("gqa_attention", dict(hidden=hidden, heads=4, kv_heads=2, head_dim=16, qk_norm=True, qk_norm_eps=raw["eps"],
+                                              position=position))
+
+    halved = attention(PartSpec("halved_positions", dict(head_dim=16, theta=50.0)))
+    plain_rope = attention(PartSpec("rope_neox", dict(head_dim=16, theta=100.0)))
+    layers = (LayerSpec("layers.0.", block, halved, routed, dict(norm1=norm, norm2=norm)),
+              LayerSpec("layers.1.", block, plain_rope, dense, dict(norm1=norm, norm2=norm)))
+    return ModelSpec("ToyRoutedLM", hidden, raw["vocab"],
+                     PartSpec("token_embedding", dict(vocab=raw["vocab"], hidden=hidden, name="embed.weight")),
+                     layers, (RunEntry(0), RunEntry(1)),
+                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"], name="final.")),
+                     PartSpec("linear_head", dict(vocab=raw["vocab"], hidden=hidden, tied=False, name="head.weight")))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_routed_feed_forward_and_toy_positions_register_build_and_step(dtype):
+    register_part("feed_forward", "top_one_experts")(TopOneExperts)
+    register_part("position", "halved_positions")(HalvedPositions)
+    register_architecture(Architecture("ToyRoutedLM", lambda raw: raw, _toy_routed_spec))
+    try:
+        raw = dict(architectures=["ToyRoutedLM"], hidden_size=32, inter=48, vocab=67, eps=1e-5)
+        _, _, spec = resolve(raw)
+        model = DecoderModel(spec, dtype, DEV)
+        tensors = random_tensors(model.weight_decls(), 5, dtype=dtype, std=0.3, device=DEV)
+        assert tensors["layers.0.ffn.router.weight"].dtype == torch.float32
+        model.bind(tensors)
+        cache = CacheManager(model.entry_caches, 12, 8, max_requests=2, dtype=dtype, device=DEV)
+        step = StepFunction(model, cache)
+        routed = model.layers[0].feed_forward
+        ids = torch.randint(0, 67, (30,)).tolist()
+        a = cache.new_request()
+        whole = step.run([StepRow(a, ids, range(30))])
+        cache.release(a)
+        picked = routed.chosen[-1]
+        assert len(set(picked.tolist())) > 1, "the router sent every token to one expert: the test shows nothing"
+        # neighbours share an angle: swapping nothing else, position 2k and 2k+1 rotate alike, so
+        # the encoding differs from the framework's own; the cut below must not change a logit
+        b, c = cache.new_request(), cache.new_request()
+        outs, i = [], 0
+        for n in (5, 2, 1, 14, 8):
+            rows = [StepRow(b, ids[i:i + n], range(n))]
+            if i < 20:
+                rows.append(StepRow(c, ids[::-1][i:i + n], []))
+            outs.append(step.run(rows)[:n])
+            i += n
+        step.check_status()
+        got = torch.cat(outs)
+        tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=6e-2, rtol=6e-2)
+        assert torch.allclose(got, whole, **tol)
+        cache.release(b)
+        cache.release(c)
+        assert cache.is_idle()
+    finally:
+        unregister_part("feed_forward", "top_one_experts")
+        unregister_part("position", "halved_positions")
+        unregister_architecture("ToyRoutedLM")
