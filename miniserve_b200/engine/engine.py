@@ -114,6 +114,16 @@ class Engine:
         return pages
 
     # ------------------------------------------------------------------ requests
+    def capture_graphs(self, modes=("greedy",)) -> int:
+        """Capture the decode graphs of every batch bucket now (while the engine is idle) instead
+        of at their first use; returns how many were captured. ``modes``: of "greedy",
+        "temperature", "top_p"."""
+        if self.graphs is None:
+            return 0
+        if self.has_unfinished:
+            raise RuntimeError("graphs are captured at the start, before any request is submitted")
+        return self.graphs.capture_all(modes)
+
     def add_request(self, prompt_ids: Sequence[int], params: SamplingParams) -> Request:
         req = Request(next(self._rids), list(prompt_ids), params)
         req.seed = params.seed if params.seed is not None else self._seeds.randrange(2 ** 32)

@@ -93,6 +93,28 @@ class DecodeGraphs:
             sf.cache.trim(r.cache)
         return cap.tokens[:n]
 
+    def capture_all(self, modes: Sequence[str] = ("greedy",)) -> int:
+        """Capture the graphs of every batch bucket now instead of at their first use (the reference
+        captures at start-up, miniserve/engine/cuda_graph.py). Needs an idle cache: it steps
+        ``max_batch`` one-token requests that it creates and releases. Returns how many it captured."""
+        sf = self.step_fn
+        sampling_for = {
+            "greedy": lambda n: None,
+            "temperature": lambda n: dict(temperatures=[1.0] * n, top_ps=[1.0] * n, seeds=[0] * n, counters=[0] * n),
+            "top_p": lambda n: dict(temperatures=[1.0] * n, top_ps=[0.5] * n, seeds=[0] * n, counters=[0] * n),
+        }
+        before = len(self._graphs)
+        for mode in modes:
+            for bucket in self.buckets:
+                caches = [sf.cache.new_request() for _ in range(bucket)]
+                try:
+                    self.run([StepRow(c, [0], (0,)) for c in caches], sampling_for[mode](bucket))
+                finally:
+                    for c in caches:
+                        sf.cache.release(c)
+        torch.cuda.current_stream(sf.device).synchronize()
+        return len(self._graphs) - before
+
     def _forward(self, ctx, bucket: int, mode: str, f32, i64):
         sf = self.step_fn
         ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream

@@ -27,6 +27,8 @@ def main(argv=None) -> int:
     ap.add_argument("--workload-seed", type=int, default=0)
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--capture-graphs-at-start", action="store_true",
+                    help="capture the decode graphs before the clock starts (else each at its first use, inside the timed run)")
     ap.add_argument("--max-steps", type=int, default=1_000_000, help="fail if not done after this many steps")
     args = ap.parse_args(argv)
 
@@ -34,6 +36,8 @@ def main(argv=None) -> int:
 
     llm = LLM(args.model, random=args.random, weights_seed=args.weights_seed, dtype=args.dtype, **engine_kwargs(args))
     eng = llm.engine
+    if args.capture_graphs_at_start:
+        eng.capture_graphs(("greedy",) if args.temperature == 0 else ("temperature", "top_p") if args.top_p < 1 else ("temperature",))
     vocab = llm.model.spec.vocab_size
     rng = random.Random(args.workload_seed)
     reqs = []
