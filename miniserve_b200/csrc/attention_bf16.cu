@@ -261,6 +261,11 @@ struct DecodeSmem {
   static constexpr size_t bytes = bytes_pipe > bytes_merge ? bytes_pipe : bytes_merge;
 };
 
+// Timing experiments only: a buffer of 64 int64 that thread 0 of the first CTA stamps with clock64()
+// at the kernel's stages (null: off).
+__device__ long long* dc_trace = nullptr;
+#define DC_STAMP(slot) do { if (tracing) dc_trace[(slot)] = clock64(); } while (0)
+
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
@@ -271,6 +276,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   // the keys and values of older tokens. So the CTA may start streaming them while the kernels
   // before it (the q/k/v projection, the rotation and cache write) are still running.
   pdl_launch_dependents();
+  const bool tracing = dc_trace != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0;
+  DC_STAMP(0);
   const int split = blockIdx.x, r = blockIdx.y;
   const int group = nq / nkv, chunks_per_group = (group + 15) / 16;
   const int kvh = blockIdx.z / chunks_per_group, head0 = kvh * group + (blockIdx.z % chunks_per_group) * 16;
@@ -327,7 +334,9 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     if (issued < my_count && my_first + issued * DC_WARPS >= newest_slice) break;
     issue(issued);
   }
+  DC_STAMP(1);
   pdl_wait();
+  DC_STAMP(2);
   for (int idx = tid; idx < 16 * CHUNKS; idx += DC_THREADS) {
     const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -336,6 +345,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   }
   for (; issued < DC_STAGES - 1; ++issued) issue(issued);
   __syncthreads();
+  DC_STAMP(3);
   uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
   if (Q_IN_REGS) {
 #pragma unroll
@@ -410,8 +420,10 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
     __syncwarp();
+    if (i < 16) DC_STAMP(4 + i);
   }
   cp_async_wait<0>();
+  DC_STAMP(24);
 #pragma unroll
   for (int j = 0; j < 2; ++j) l_run[j] = quad_sum(l_run[j]);
   __syncthreads();  // the pipelines are drained: shared memory becomes the merge area
@@ -456,6 +468,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       }
     }
   }
+  DC_STAMP(25);
   if (num_splits == 1 || counters == nullptr) return;
   // The split that finishes last merges them all (a ticket per (request, head chunk); no waiting):
   // out = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m).
@@ -469,23 +482,44 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     if (last_one) *ticket = 0;  // ready for the next launch
   }
   __syncthreads();
+  DC_STAMP(26);
   if (!last_one) return;
   __threadfence();
   for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
     const int row = idx / D, c = idx - row * D;
     const size_t item = (size_t)r * nq + head0 + row;
-    const float* ml = part_ml + item * num_splits * 2;
-    float m = -INFINITY;
-    for (int sp = 0; sp < num_splits; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
-    float acc = 0.f, l = 0.f;
-    for (int sp = 0; sp < num_splits; ++sp) {
-      const float ms_ = __ldcg(ml + 2 * sp);
-      const float wgt = ms_ == -INFINITY ? 0.f : exp2f(ms_ - m);
-      acc += wgt * __ldcg(part_o + (item * num_splits + sp) * D + c);
-      l += wgt * __ldcg(ml + 2 * sp + 1);
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + item * num_splits;
+    const float* po = part_o + item * num_splits * D + c;
+    float acc = 0.f, l = 0.f, m = -INFINITY;
+    // splits in groups of eight: the loads of a group are in flight together (they are what this
+    // tail waits for); the result is rescaled when a later group raises the maximum
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+      float2 mls[8];
+      float os[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool in = s0 + i < num_splits;
+        mls[i] = in ? __ldcg(ml + s0 + i) : make_float2(-INFINITY, 0.f);
+        os[i] = in ? __ldcg(po + (size_t)(s0 + i) * D) : 0.f;
+      }
+      float m_new = m;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, mls[i].x);
+      if (m_new == -INFINITY) continue;
+      const float keep = m == -INFINITY ? 0.f : exp2f(m - m_new);
+      acc *= keep;
+      l *= keep;
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float wgt = mls[i].x == -INFINITY ? 0.f : exp2f(mls[i].x - m);
+        acc += wgt * os[i];
+        l += wgt * mls[i].y;
+      }
     }
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
+  DC_STAMP(27);
 }
 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
@@ -520,6 +554,12 @@ MS_DEFINE_LAST_ERROR(MS_ATTN_FN(last_error))
 MS_DEFINE_PDL_SWITCH(MS_ATTN_FN(set_pdl))
 
 MS_EXPORT int MS_ATTN_FN(head_dim)() { return D; }
+
+// Timing experiments only: see dc_trace.
+MS_EXPORT int MS_ATTN_FN(set_trace)(long long* buffer) {
+  MS_CHECK_CUDA(cudaMemcpyToSymbol(dc_trace, &buffer, sizeof(buffer)));
+  return 0;
+}
 
 static int shift_of(int page_size) {
   int s = 0;
