@@ -136,6 +136,8 @@ def _flag(name: str, default: str) -> bool:
 # predecessor and weights are prefetched before the wait, a separate small kernel costs less than
 # the serial work a prologue adds to every CTA of the product.
 FUSE_NORM = _flag("MINISERVE_FUSE_NORM", "0")      # norm inside the next product's prologue
+TC_GEMM = _flag("MINISERVE_TC_GEMM", "0")          # plain products with more than 16 rows on this package's tcgen05 kernel
+TC_ATTENTION = _flag("MINISERVE_TC_ATTENTION", "1")  # prompts on the tcgen05 attention kernel (head size 128)
 FUSE_SILU = _flag("MINISERVE_FUSE_SILU", "0")      # SiLU * up inside the down projection's prologue
 SPLIT_K_PARTIALS = _flag("MINISERVE_SPLIT_K", "0")  # narrow products hand float32 partial sums to the norm
 
@@ -205,9 +207,7 @@ def tc_gemm_enabled() -> bool:
     """Plain products with more than 16 rows go to the vendor library unless MINISERVE_TC_GEMM=1:
     this package's tcgen05 kernel is correct but, with one CTA per 128 x 128 tile and no operand
     sharing between SMs, reaches about 60-75 % of the library's rate at prefill sizes."""
-    import os
-
-    return os.environ.get("MINISERVE_TC_GEMM", "0") == "1"
+    return TC_GEMM
 
 
 TC_EPILOGUE = {"bf16": 0, "f32": 1, "silu_mul": 2}
@@ -484,9 +484,7 @@ _ATTN_TC_SCRATCH_LIMIT = 1 << 29  # bytes of partial results that a step's atten
 
 def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
     """Whether the tcgen05 prefill attention takes this shape (head size 128, pages of 8..128)."""
-    import os
-
-    if os.environ.get("MINISERVE_TC_ATTENTION", "1") == "0" or q.shape[2] != 128:
+    if not TC_ATTENTION or q.shape[2] != 128:
         return False
     return bool(native.attn_tc().ms_attn_tc_supports(q.shape[2], k_pool.shape[2], q.shape[1], k_pool.shape[1]))
 

@@ -24,7 +24,7 @@ _DEFAULT_MATH, _NO_REDUCED_PRECISION_REDUCTION = 0, 16
 _WORKSPACE_BYTES = 32 << 20
 
 _lib = None
-_handles: dict[int, tuple[c_void_p, torch.Tensor]] = {}
+_handles: dict[int, list] = {}  # device index -> [handle, workspace, stream last set]
 _one = ctypes.c_float(1.0)
 _zero = ctypes.c_float(0.0)
 _p_one, _p_zero = ctypes.addressof(_one), ctypes.addressof(_zero)
@@ -69,9 +69,9 @@ def _handle(device: torch.device):
             workspace = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
             _check(lib.cublasSetWorkspace_v2(handle, workspace.data_ptr(), _WORKSPACE_BYTES), "cublasSetWorkspace")
             _check(lib.cublasSetMathMode(handle, _DEFAULT_MATH | _NO_REDUCED_PRECISION_REDUCTION), "cublasSetMathMode")
-        got = (handle, workspace)
+        got = [handle, workspace, None]
         _handles[idx] = got
-    return got[0]
+    return got
 
 
 def gemm_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stream: int) -> None:
@@ -79,8 +79,13 @@ def gemm_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stream: 
     m, k = x.shape
     n = weight.shape[0]
     lib = _library()
-    handle = _handle(x.device)
-    _check(lib.cublasSetStream_v2(handle, stream), "cublasSetStream")
+    entry = _handle(x.device)
+    handle = entry[0]
+    if entry[2] != stream:
+        _check(lib.cublasSetStream_v2(handle, stream), "cublasSetStream")
+        # the library drops a workspace of the user's when the stream changes: give it again
+        _check(lib.cublasSetWorkspace_v2(handle, entry[1].data_ptr(), _WORKSPACE_BYTES), "cublasSetWorkspace")
+        entry[2] = stream
     # column-major view: out^T [N, M] = weight (as [K, N], transposed) times x^T [K, M]
     _check(lib.cublasGemmEx(handle, _OP_T, _OP_N, n, m, k, _p_one, weight.data_ptr(), _R_16BF, k, x.data_ptr(), _R_16BF, k,
                             _p_zero, out.data_ptr(), _R_32F if out.dtype == torch.float32 else _R_16BF, n, _COMPUTE_32F,
