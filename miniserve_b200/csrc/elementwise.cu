@@ -59,6 +59,69 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __r
   }
 }
 
+// The same for bfloat16 activations whose rows are a multiple of 8 wide: eight elements per thread
+// and trip (two 16-byte loads of the residual, one of the addend), the sum kept in registers when
+// a row is at most 8 * THREADS wide, else in shared memory.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual, float* __restrict__ residual_out,
+                          const __nv_bfloat16* __restrict__ delta, const float* __restrict__ parts, int num_parts,
+                          size_t part_stride, const __nv_bfloat16* __restrict__ w, const int* __restrict__ rows, float eps,
+                          int hidden, int write_residual) {
+  extern __shared__ float row_buf[];  // hidden floats, used only by rows wider than 8 * THREADS
+  __shared__ float red[32];
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const __nv_bfloat16* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  const int chunks = hidden >> 3;
+  const bool in_regs = chunks <= THREADS;
+  float h[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    const float4 a = *reinterpret_cast<const float4*>(res + 8 * c), b = *reinterpret_cast<const float4*>(res + 8 * c + 4);
+    h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b.x; h[5] = b.y; h[6] = b.z; h[7] = b.w;
+    if (dl) {
+      float d[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + 8 * c), d);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) h[e] += d[e];
+    }
+    for (int p = 0; p < num_parts; ++p) {
+      const float* src = parts + p * part_stride + (size_t)r * hidden + 8 * c;
+      const float4 pa = *reinterpret_cast<const float4*>(src), pb = *reinterpret_cast<const float4*>(src + 4);
+      h[0] += pa.x; h[1] += pa.y; h[2] += pa.z; h[3] += pa.w; h[4] += pb.x; h[5] += pb.y; h[6] += pb.z; h[7] += pb.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += h[e] * h[e];
+    if (!in_regs) {
+      *reinterpret_cast<float4*>(row_buf + 8 * c) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(row_buf + 8 * c + 4) = make_float4(h[4], h[5], h[6], h[7]);
+    }
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  __nv_bfloat16* o = out + (size_t)i * hidden;
+  const bool store_sum = residual_out != nullptr || (write_residual && (dl || num_parts));
+  float* sum_to = residual_out ? residual_out + (size_t)r * hidden : res;
+  for (int c = threadIdx.x; c < chunks; c += THREADS) {
+    if (!in_regs) {
+      const float4 a = *reinterpret_cast<const float4*>(row_buf + 8 * c), b = *reinterpret_cast<const float4*>(row_buf + 8 * c + 4);
+      h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b.x; h[5] = b.y; h[6] = b.z; h[7] = b.w;
+    }
+    if (store_sum) {
+      *reinterpret_cast<float4*>(sum_to + 8 * c) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(sum_to + 8 * c + 4) = make_float4(h[4], h[5], h[6], h[7]);
+    }
+    float wv[8], y[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(w + 8 * c), wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = (h[e] * inv) * wv[e];
+    *reinterpret_cast<uint4*>(o + 8 * c) = float_to_bf16x8(y);
+  }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
@@ -156,6 +219,16 @@ MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, void* residual_out, 
     auto k = add_rmsnorm_kernel<float, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (float*)residual_out, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
+  } else if (hidden % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual_f32 % 16 == 0) && ((uintptr_t)residual_out % 16 == 0) &&
+             ((uintptr_t)delta % 16 == 0) && ((uintptr_t)parts % 16 == 0) && (part_stride % 4 == 0) && ((uintptr_t)weight % 16 == 0)) {
+    if (hidden <= 8 * 128) {
+      MS_LAUNCH((add_rmsnorm_bf16x8_kernel<128>), num_out_rows, 128, 0, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    } else {
+      auto k = add_rmsnorm_bf16x8_kernel<256>;
+      const size_t need = hidden <= 8 * 256 ? 0 : smem;
+      if (need > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+      MS_LAUNCH(k, num_out_rows, 256, need, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    }
   } else {
     auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
