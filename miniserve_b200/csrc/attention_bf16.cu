@@ -14,6 +14,8 @@
 // end of a request are zero-filled, never read.
 #include <cfloat>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 #ifndef MS_HEAD_DIM
@@ -257,7 +259,7 @@ struct DecodeSmem {
   static constexpr int stage_elems = 2 * DC_SLICE * DPAD;  // K slice then V slice
   static constexpr int pipe_elems = DC_WARPS * DC_STAGES * stage_elems;
   static constexpr size_t bytes_pipe = (size_t)(q_elems + pipe_elems) * 2;
-  static constexpr size_t bytes_merge = (size_t)DC_WARPS * 16 * (D + 2) * 4 + (size_t)q_elems * 2;
+  static constexpr size_t bytes_merge = (size_t)(DC_WARPS + 1) * 16 * (D + 2) * 4 + (size_t)q_elems * 2;
   static constexpr size_t bytes = bytes_pipe > bytes_merge ? bytes_pipe : bytes_merge;
 };
 
@@ -271,7 +273,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
-                   float scale_log2, int window, int page_shift, int num_splits, int* __restrict__ counters) {
+                   float scale_log2, int window, int page_shift, int num_splits, int* __restrict__ counters,
+                   int cluster_merge) {
   // Until pdl_wait() below, only data written before this step is touched: the step's metadata and
   // the keys and values of older tokens. So the CTA may start streaming them while the kernels
   // before it (the q/k/v projection, the rotation and cache write) are still running.
@@ -429,6 +432,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   __syncthreads();  // the pipelines are drained: shared memory becomes the merge area
 
   float* merge = reinterpret_cast<float*>(smem_raw + (size_t)DecodeSmem::q_elems * 2);  // [warps][16][D + 2]
+  float* cta_out = merge + (size_t)DC_WARPS * 16 * (D + 2);                              // [16][D + 2]
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     float* row = merge + ((size_t)warp * 16 + g + 8 * j) * (D + 2);
@@ -459,6 +463,14 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     const int head = head0 + row;
     if (num_splits == 1) {
       out[((size_t)r * nq + head) * D + c] = __float2bfloat16_rn(acc / l);
+    } else if (cluster_merge) {
+      // the splits of a (request, head group) are one thread-block cluster: the partial result
+      // stays in this CTA's shared memory, where the cluster's first CTA reads it
+      cta_out[row * (D + 2) + c] = acc;
+      if (c == 0) {
+        cta_out[row * (D + 2) + D] = m;
+        cta_out[row * (D + 2) + D + 1] = l;
+      }
     } else {
       const size_t p = ((size_t)r * nq + head) * num_splits + split;
       part_o[p * D + c] = acc;
@@ -469,6 +481,29 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     }
   }
   DC_STAMP(25);
+  if (num_splits > 1 && cluster_merge) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every split's partial result is in its shared memory
+    if (cluster.block_rank() == 0) {
+      for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
+        const int row = idx / D, c = idx - row * D;
+        float m = -INFINITY;
+        for (int sp = 0; sp < num_splits; ++sp) m = fmaxf(m, cluster.map_shared_rank(cta_out, sp)[row * (D + 2) + D]);
+        float acc = 0.f, l = 0.f;
+        for (int sp = 0; sp < num_splits; ++sp) {
+          const float* src = cluster.map_shared_rank(cta_out, sp) + row * (D + 2);
+          const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
+          acc += wgt * src[c];
+          l += wgt * src[D + 1];
+        }
+        out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
+      }
+    }
+    DC_STAMP(27);
+    cluster.sync();  // the others' shared memory lives until the first CTA has read it
+    return;
+  }
   if (num_splits == 1 || counters == nullptr) return;
   // The split that finishes last merges them all (a ticket per (request, head chunk); no waiting):
   // out = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m).
@@ -626,11 +661,36 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
   MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
       (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
       (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
-      shift_of(page_size), num_splits, counters);
+      shift_of(page_size), num_splits, counters, 0);
   if (num_splits > 1 && counters == nullptr) {
     MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
               (const float*)part_o, (const float*)part_ml, num_splits);
   }
+  return 0;
+}
+
+// The same with the splits of a (request, head group) as one thread-block cluster (2 to 8 splits):
+// partial results stay in shared memory and the cluster's first CTA adds them up through
+// distributed shared memory, so no scratch, no fence and no ticket are needed.
+MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* kv_len,
+                                         const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
+                                         float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
+  MS_CHECK_ARG(num_splits >= 2 && num_splits <= 8, "attention: a cluster takes 2 to 8 splits, not %d", num_splits);
+  MS_CHECK_ARG(num_rows <= 65535, "attention: too many rows (%d) for one launch", num_rows);
+  const int group = nq / nkv;
+  static bool configured = false;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DecodeSmem::bytes));
+    configured = true;
+  }
+  dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
+  MS_LAUNCH_CLUSTERED(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream, num_splits,
+      (__nv_bfloat16*)out, (float*)nullptr, (float*)nullptr, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
+      shift_of(page_size), num_splits, (int*)nullptr, 1);
   return 0;
 }
 

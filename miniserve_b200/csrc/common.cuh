@@ -111,20 +111,38 @@ inline int& pdl_switch() {
   return on;
 }
 
+// cluster_x > 1: thread-block clusters of that many CTAs along x (the grid's x must be a multiple).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                          Args&&... args) {
+inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_x, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (pdl_switch()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_switch() ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  return launch_clustered(kernel, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 
 }  // namespace ms
@@ -149,3 +167,5 @@ enum MsDtype : int { MS_F32 = 0, MS_BF16 = 1 };
   MS_EXPORT void name(int on) { ::ms::pdl_switch() = on; }
 #define MS_LAUNCH(kernel, grid, block, smem, stream, ...) \
   MS_CHECK_CUDA(::ms::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__))
+#define MS_LAUNCH_CLUSTERED(kernel, grid, block, smem, stream, cluster_x, ...) \
+  MS_CHECK_CUDA(::ms::launch_clustered(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, (unsigned)(cluster_x), __VA_ARGS__))

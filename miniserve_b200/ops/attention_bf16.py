@@ -14,6 +14,15 @@ from . import build, native
 _p, _i, _f = c_void_p, c_int, c_float
 
 
+def _flag(name: str, default: str) -> bool:
+    import os
+
+    return os.environ.get(name, default) == "1"
+
+
+CLUSTER_MERGE = _flag("MINISERVE_CLUSTER_MERGE", "1")  # 2 to 8 key splits of a decode step as one thread-block cluster
+
+
 def supports(head_dim: int, page_size: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size & (page_size - 1) == 0
 
@@ -34,6 +43,7 @@ def _lib(head_dim: int):
         ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _p], c_int),
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
         ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
     ):
         fn = getattr(lib, pre + name)
         fn.argtypes, fn.restype = args, res
@@ -97,6 +107,12 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
     chunks = nkv * -(-(nq // nkv) // 16)
     splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
+    if CLUSTER_MERGE and 2 <= splits <= 8:
+        # the splits as one thread-block cluster: merged through distributed shared memory
+        _check(fns, fns["decode_cluster"](
+            out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream))
+        return
     part_o = part_ml = counters = None
     if splits > 1:
         part_o, part_ml = _scratch(ctx, rows, nq, splits, d, q.device)
