@@ -208,7 +208,7 @@ struct AtItem {
 };
 
 struct AtGrid {
-  int q_tiles, rows, head_groups, splits, min_tiles_per_split, window, G;
+  int q_tiles, rows, head_groups, splits, max_tiles_per_item, window, G;
   __device__ __forceinline__ int total() const { return q_tiles * rows * head_groups * splits; }
 };
 
@@ -241,12 +241,14 @@ __device__ __forceinline__ bool at_item(AtItem& it, int idx, const AtGrid& gr, c
   it.tile_begin = it.lo_g[0] / AT_KEYS;
   it.n_tiles[0] = (min(it.kv_len, it.q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin;
   it.n_tiles[1] = it.has_b ? (min(it.kv_len, it.q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin : 0;
-  // Long rows of keys are cut into splits that other items take: this one keeps `per_split` key
-  // tiles from its split's first. A group whose keys lie in more than one split leaves a partial
-  // result (unnormalised O, the maximum it is scaled by, the sum), and the last of them to finish
-  // adds the partial results up in the order of the splits.
+  // Key ranges longer than `max_tiles_per_item` are cut into pieces of that length (the last one
+  // shorter; measured faster than equal pieces, whose items all start late in the queue's order)
+  // that other items take, at most `splits` of them: this one keeps `per_split` key tiles from its
+  // piece's first. A group whose keys lie in more than one piece leaves a partial result
+  // (unnormalised O, the maximum it is scaled by, the sum), and the last of them to finish adds
+  // the partial results up in the order of the pieces.
   const int n_full = max(it.n_tiles[0], it.n_tiles[1]);
-  const int per_split = max(gr.min_tiles_per_split, (n_full + gr.splits - 1) / gr.splits);
+  const int per_split = max(gr.max_tiles_per_item, (n_full + gr.splits - 1) / gr.splits);
   if (it.split * per_split >= n_full) return false;
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
@@ -709,7 +711,7 @@ static int at_heads_per_cta(int nq, int nkv) {
   return G;
 }
 
-static int g_splits = 0, g_min_tiles = 8;
+static int g_splits = 0, g_min_tiles = 8;  // forced by ms_attn_tc_set_splits (0: planned per launch)
 // Tuning: force the number of key splits (0: chosen from the size of the step) and the least
 // number of key tiles that a split keeps.
 MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
@@ -717,21 +719,43 @@ MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
   g_min_tiles = min_tiles > 0 ? min_tiles : 8;
 }
 
-// How many items share the keys of one tile of queries. One CTA fills an SM, so a step with fewer
-// query tiles than SMs (a portion of a prompt far into a long context, above all) leaves SMs idle
-// while the others walk through thousands of keys: then the keys are cut so that the items about
-// fill the GPU once, in splits of at least 8 key tiles. With more tiles than SMs the queue evens
-// the load out by itself and splits only add partial results (3,072 tokens: 77 us whole, 85 us in
-// two). Measured on B200, 16 heads in 8 groups: 256 tokens behind 30,000: 645 us whole, 109 us in
-// 9 splits; 512 behind 8,192: 193 -> 72 us in 4; one prompt of 2,048 (128 tiles, the last of them
-// 16 key tiles long): 57 -> 47 us in 2. ms_attn_tc_scratch says how much scratch splits need.
-MS_EXPORT int ms_attn_tc_splits(int num_tokens, int nq, int nkv, int sm_count) {
-  if (g_splits > 0) return g_splits;
-  const int G = at_heads_per_cta(nq, nkv);
-  const long long ctas = (long long)ceil_div(num_tokens, 2 * (AT_ROWS / G)) * (nq / G);
-  if (ctas > sm_count) return 1;
-  const long long want = sm_count / ctas;
-  return (int)(want < 2 ? 2 : (want > 16 ? 16 : want));
+// How the keys of a tile of queries are shared out, from the step's geometry on the host (q_start
+// and q_len of the rows the launch covers): key ranges longer than *min_tiles key tiles are cut into
+// pieces of that length, at most *splits of them. One CTA fills an SM, so a step with at most one query tile per SM cannot even its load
+// out through the queue (nor can one with up to two): the last tiles of a long prompt, or the few tiles of a portion far into a
+// long context, walk many more keys than the rest while other SMs idle. Then key ranges longer
+// than about 1.2 times the work per SM are cut. With many more tiles than SMs the queue evens the
+// load out by itself and splits only add partial results.
+// Measured on B200, 16 heads in 8 groups: 256 tokens behind 30,000: 645 us whole, 109 us cut;
+// 512 behind 8,192: 193 -> 72 us; one prompt of 2,048 (128 tiles, the last 16 key tiles long):
+// 57 us whole, 47 us with ranges over 8 tiles cut in two, 42 us with ranges over 9.
+// ms_attn_tc_scratch says how much scratch the splits need.
+MS_EXPORT void ms_attn_tc_plan(const int* q_start, const int* q_len, int num_rows, int nq, int nkv, int window, int sm_count,
+                               int* splits, int* min_tiles) {
+  *splits = 1;
+  *min_tiles = g_min_tiles;
+  if (g_splits > 0) {
+    *splits = g_splits;
+    return;
+  }
+  const int G = at_heads_per_cta(nq, nkv), span = 2 * (AT_ROWS / G), head_groups = nq / G;
+  long long ctas = 0, steps = 0;
+  int longest = 0;
+  for (int r = 0; r < num_rows; ++r) {
+    for (int m0 = 0; m0 < q_len[r]; m0 += span) {
+      const int last = q_start[r] + (m0 + span < q_len[r] ? m0 + span : q_len[r]) - 1;
+      const int lo = window > 0 && q_start[r] + m0 - window + 1 > 0 ? q_start[r] + m0 - window + 1 : 0;
+      const int n = (last + AT_KEYS) / AT_KEYS - lo / AT_KEYS;
+      ctas += head_groups;
+      steps += (long long)n * head_groups;
+      longest = n > longest ? n : longest;
+    }
+  }
+  if (ctas == 0 || ctas > 2LL * sm_count) return;
+  const long long fair = (steps * 12 + 10LL * sm_count - 1) / (10LL * sm_count);  // 1.2 x the work per SM, rounded up
+  *min_tiles = (int)(fair < 4 ? 4 : fair);
+  const int want = ceil_div(longest, *min_tiles);
+  *splits = want < 1 ? 1 : (want > 16 ? 16 : want);
 }
 
 // What a launch needs besides its operands: float32 for the partial results of split key ranges
@@ -748,10 +772,10 @@ MS_EXPORT void ms_attn_tc_scratch(int max_q_len, int num_rows, int nq, int nkv, 
 MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
-                                 int window, int page_size, int* status, int splits, float* partials, int* queue,
-                                 cudaStream_t stream) {
+                                 int window, int page_size, int* status, int splits, int min_tiles, float* partials,
+                                 int* queue, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  MS_CHECK_ARG(splits >= 1 && splits <= 64, "attention_tc: %d key splits", splits);
+  MS_CHECK_ARG(splits >= 1 && splits <= 64 && min_tiles >= 1, "attention_tc: %d key splits of at least %d tiles", splits, min_tiles);
   // partials and queue: sized by ms_attn_tc_scratch (the work queue's two counters, then the tickets
   // of the groups whose keys are split)
   MS_CHECK_ARG(queue != nullptr, "attention_tc: the work queue is missing");
@@ -800,7 +824,7 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
     MS_CHECK_CUDA(cudaGetDevice(&dev));
     MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, g_min_tiles, window, G};
+  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, min_tiles, window, G};
   const long long total = (long long)gr.q_tiles * gr.rows * gr.head_groups * gr.splits;
   MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left

@@ -499,18 +499,24 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     skip = 4 * first_row  # the per-row tables are int32
     # a step with few query tiles cuts long key ranges between several CTAs, which leave partial results
     rows = ctx.num_rows - first_row
-    plan = ctx.step_cache.get(("attn_tc_plan", first_row, nq, k_pool.shape[1]))
-    if plan is None:  # the same for every layer of the step
-        splits = lib.ms_attn_tc_splits(t - first_row, nq, k_pool.shape[1], ctx.sm_count)
+    key = ("attn_tc_plan", first_row, nq, k_pool.shape[1], int(window or 0))
+    plan = ctx.step_cache.get(key)
+    if plan is None:  # the same for every layer of the step that has this window
+        starts = (ctypes.c_int * rows)(*ctx.host_q_start[first_row:first_row + rows])
+        lens = (ctypes.c_int * rows)(*ctx.host_q_len[first_row:first_row + rows])
+        splits, min_tiles = ctypes.c_int(), ctypes.c_int()
+        lib.ms_attn_tc_plan(starts, lens, rows, nq, k_pool.shape[1], int(window or 0), ctx.sm_count, ctypes.byref(splits),
+                            ctypes.byref(min_tiles))
+        splits = splits.value
         need_f, need_i = ctypes.c_longlong(), ctypes.c_longlong()
         while True:
             lib.ms_attn_tc_scratch(ctx.max_q_len, rows, nq, k_pool.shape[1], splits, ctypes.byref(need_f), ctypes.byref(need_i))
             if splits == 1 or need_f.value * 4 <= _ATTN_TC_SCRATCH_LIMIT:
                 break
             splits -= 1
-        plan = (splits, need_f.value, need_i.value)
-        ctx.step_cache[("attn_tc_plan", first_row, nq, k_pool.shape[1])] = plan
-    splits, need_floats, need_ints = plan
+        plan = (splits, min_tiles.value, need_f.value, need_i.value)
+        ctx.step_cache[key] = plan
+    splits, min_tiles, need_floats, need_ints = plan
     part = None
     if splits > 1:
         part = ctx.scratch.get("attn_tc_partials")
@@ -525,5 +531,5 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, _ptr(part), _ptr(queue), ctx.stream),
+        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")

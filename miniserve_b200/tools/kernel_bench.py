@@ -45,7 +45,7 @@ def _paged(rows, page, nkv, d, seed, device):
         q_start=torch.tensor([s for s, _ in rows], **i32), kv_len=torch.tensor([s + n for s, n in rows], **i32),
         page_indptr=[torch.tensor(indptr, **i32)], page_indices=[torch.tensor([p for t in tables for p in t], **i32)],
         max_q_len=max(n for _, n in rows), max_kv_len=max(s + n for s, n in rows),
-        decode_only=all(n == 1 for _, n in rows),
+        decode_only=all(n == 1 for _, n in rows), host_q_start=[s for s, _ in rows], host_q_len=[n for _, n in rows],
         leading_single_rows=next((i for i, (_, n) in enumerate(rows) if n != 1), len(rows)), graph_bucket=0, scratch={}, step_cache={},
         sm_count=torch.cuda.get_device_properties(0).multi_processor_count, stream=0)
     return k, v, ctx
