@@ -35,6 +35,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -269,6 +272,188 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// One 32-column chunk of a row of the accumulator (and of the up half for SiLU * up), to global memory.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(void* __restrict__ out, const uint32_t (&acc)[32], const uint32_t (&up)[32], int row,
+                                            int col0, int N_out) {
+  if (EPI == TC_OUT_F32) {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)row * N_out + col0;
+    if (col0 + 32 <= N_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    } else {
+      for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __uint_as_float(acc[j]);
+    }
+    return;
+  }
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __uint_as_float(acc[j]);
+    if (EPI == TC_SILU_MUL) x = x / (1.0f + expf(-x)) * __uint_as_float(up[j]);
+    v[j] = x;
+  }
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N_out + col0;
+  if (col0 + 32 <= N_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 pk;
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+      pk.x = *reinterpret_cast<uint32_t*>(&p0);
+      pk.y = *reinterpret_cast<uint32_t*>(&p1);
+      pk.z = *reinterpret_cast<uint32_t*>(&p2);
+      pk.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(dst + j) = pk;
+    }
+  } else {
+    for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+// The persistent form: one CTA per SM walks over tiles (tile = CTA index, + grid size, ...), the
+// ring of shared-memory stages keeps running from one tile into the next, and tensor memory holds
+// two accumulators, so that the epilogue of a tile overlaps the products of the next one.
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          void* __restrict__ out, int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  static_assert(BN <= 256, "two accumulators of BN columns must fit 512 columns of tensor memory");
+  constexpr uint32_t ACC_COLS = BN <= 64 ? 64 : BN <= 128 ? 128 : 256;  // columns of one accumulator
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;                // output columns per tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_iters = (K + TC_BK - 1) / TC_BK;
+  const int n_tiles = (N_out + COLS - 1) / COLS, m_tiles = (M + TC_BM - 1) / TC_BM;
+  const int num_tiles = n_tiles * m_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(2 * ACC_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int kb = 0;  // k-blocks loaded so far, over all tiles: the ring does not restart between tiles
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int n0 = (tile % n_tiles) * COLS, m0 = (tile / n_tiles) * TC_BM;
+        bool ok = true;
+        for (int it = 0; it < k_iters; ++it, ++kb) {
+          const int s = kb % STAGES;
+          if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1)) {
+            atomicExch(status, 11);
+            ok = false;
+            break;
+          }
+          unsigned char* a_tile = smem + (size_t)s * TcSmem<BN>::stage_bytes;
+          unsigned char* b_tile = a_tile + TcSmem<BN>::a_bytes;
+          mbar_expect_tx(&full_bar[s], TcSmem<BN>::stage_bytes);
+          tma_load_2d(a_tile, &map_a, &full_bar[s], it * TC_BK, m0);
+          if (EPI == TC_SILU_MUL) {
+            tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
+            tma_load_2d(b_tile + TcSmem<BN>::b_bytes / 2, &map_w, &full_bar[s], it * TC_BK, up_row_offset + n0);
+          } else {
+            tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      int kb = 0, tc = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tc) {
+        const int buf = tc & 1;
+        // the epilogue warps must have read this accumulator's previous tile
+        if (tc >= 2 && !mbar_wait(&acc_empty[buf], ((tc >> 1) - 1) & 1)) {
+          atomicExch(status, 14);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t tmem_acc = tmem_base + (uint32_t)buf * ACC_COLS;
+        for (int it = 0; it < k_iters; ++it, ++kb) {
+          const int s = kb % STAGES;
+          if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
+            atomicExch(status, 12);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned char* a_tile = smem + (size_t)s * TcSmem<BN>::stage_bytes;
+          const unsigned char* b_tile = a_tile + TcSmem<BN>::a_bytes;
+          const uint64_t da = make_smem_desc(a_tile), db = make_smem_desc(b_tile);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) umma_bf16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quad = warp & 3;
+    int tc = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tc) {
+      const int buf = tc & 1;
+      const int n0 = (tile % n_tiles) * COLS, m0 = (tile / n_tiles) * TC_BM;
+      const int row = m0 + quad * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (tc >> 1) & 1)) {
+        atomicExch(status, 13);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t lane_addr = tmem_base + (uint32_t)buf * ACC_COLS + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < COLS; c += 32) {
+        uint32_t acc[32];
+        tmem_ld32(lane_addr + (uint32_t)c, acc);
+        if constexpr (EPI == TC_SILU_MUL) {
+          uint32_t up[32];
+          tmem_ld32(lane_addr + (uint32_t)(COLS + c), up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (row < M) store_chunk<EPI>(out, acc, up, row, n0 + c, N_out);
+        } else {
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (row < M) store_chunk<EPI>(out, acc, acc, row, n0 + c, N_out);
+        }
+      }
+      // this accumulator may be overwritten by the tile after the next
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * ACC_COLS) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -321,6 +506,32 @@ static int launch_tc(void* out, const void* A, const void* W, int M, int N_out, 
   return 0;
 }
 
+template <int BN, int STAGES, int EPI>
+static int launch_tc_persistent(void* out, const void* A, const void* W, int M, int N_out, int w_rows, int K, int up_row_offset,
+                                int* status, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(&map_a, A, M, K, TC_BM)) return rc;
+  if (int rc = make_map(&map_w, W, w_rows, K, EPI == TC_SILU_MUL ? BN / 2 : BN)) return rc;
+  constexpr size_t smem = (size_t)STAGES * TcSmem<BN>::stage_bytes + 1024;
+  static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
+  auto kernel = gemm_tc_persistent_kernel<BN, STAGES, EPI>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    configured = true;
+  }
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;
+  const long long tiles = (long long)ceil_div(N_out, COLS) * ceil_div(M, TC_BM);
+  MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
+  const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+  MS_LAUNCH(kernel, grid, TC_THREADS, smem, stream, map_a, map_w, out, M, N_out, K, up_row_offset, status);
+  return 0;
+}
+
 }  // namespace ms
 
 using namespace ms;
@@ -331,7 +542,8 @@ MS_DEFINE_PDL_SWITCH(ms_gemm_tc_set_pdl)
 // epilogue 0: out bf16 [M, N]; 1: out float32 [M, N]; 2: W is [2 * N, K] (gate rows then up rows),
 // out bf16 [M, N] = silu(A gate^T) * (A up^T). status: a device int the kernel raises if a wait ran out.
 static int g_tc_config = 0;
-// Tile configuration for experiments: 0 = default.
+// Tile configuration for experiments and tests: 0 = chosen from the shape, 5 = one CTA per tile,
+// 10 = persistent with 256-column tiles, 11 = persistent with 128-column tiles.
 MS_EXPORT void ms_gemm_tc_set_config(int config) { g_tc_config = config; }
 
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,
@@ -342,15 +554,34 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
   MS_CHECK_ARG(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
   MS_CHECK_ARG(status != nullptr, "gemm_tc: needs a status word");
   MS_CHECK_ARG(ceil_div(M, TC_BM) <= 65535, "gemm_tc: M=%d too large for one launch", M);
+  // Enough 128 x 256 tiles to give every SM one: the persistent kernel (measured on B200: 1,366 against
+  // 1,093 TFLOP/s for 8192 x 4096 x 4096, 740 against 582 for 2048 x 4096 x 1024; cuBLAS: 1,527 and
+  // 1,048). Fewer: one CTA per 128 x 128 tile, which spreads a narrow output over more SMs.
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const bool wide = (long long)ceil_div(M, TC_BM) * ceil_div(N, 256) >= sm_count;
   switch (epilogue) {
     case TC_OUT_BF16:
       if (g_tc_config == 1) return launch_tc<128, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 2) return launch_tc<256, 2, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 3) return launch_tc<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 4) return launch_tc<64, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 11) return launch_tc_persistent<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 12) return launch_tc_persistent<256, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 10 || wide) return launch_tc_persistent<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-    case TC_OUT_F32: return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
-    case TC_SILU_MUL: return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+    case TC_OUT_F32:
+      if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 10 || wide) return launch_tc_persistent<256, 4, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+      return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+    case TC_SILU_MUL:
+      if (g_tc_config == 5) return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+      return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }
 }

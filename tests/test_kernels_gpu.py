@@ -91,9 +91,16 @@ def test_gemm_f32_is_true_32bit_and_row_independent(m, n, k):
     assert torch.equal(alone[0], out[m // 2])
 
 
-@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (17, 200, 72), (333, 1000, 1000), (2048, 1024, 2048), (130, 503, 96)])
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (17, 200, 72), (333, 1000, 1000), (2048, 1024, 2048), (130, 503, 96), (4096, 6144, 256)])
 @pytest.mark.parametrize("epilogue", ["bf16", "f32", "silu_mul"])
-def test_tcgen05_gemm(m, n, k, epilogue):
+@pytest.mark.parametrize("config", [0, 5, 10, 11], ids=["by_shape", "tile_per_cta", "persistent_256", "persistent_128"])
+def test_tcgen05_gemm(m, n, k, epilogue, config):
+    """config: 0 chosen from the shape; 5 one CTA per tile; 10 and 11 the persistent kernel (tiles of 256 and 128 columns) whose ring
+    of stages runs on from tile to tile and whose two accumulators take turns."""
+    from miniserve_b200.ops import native
+
+    if config == 11 and epilogue != "bf16":
+        pytest.skip("the 128-column persistent tile is built for the plain bfloat16 epilogue only")
     torch.manual_seed(m + n)
     x = torch.randn(m, k, device=DEV).bfloat16()
     if epilogue == "silu_mul":
@@ -105,8 +112,12 @@ def test_tcgen05_gemm(m, n, k, epilogue):
         w = torch.randn(n, k, device=DEV).bfloat16()
         expect = x.float() @ w.float().T
         out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.float32 if epilogue == "f32" else torch.bfloat16)
-    ops.linear_tc(x, w, out, epilogue)
-    torch.cuda.synchronize()
+    native.gemm_tc().ms_gemm_tc_set_config(config)
+    try:
+        ops.linear_tc(x, w, out, epilogue)
+        torch.cuda.synchronize()
+    finally:
+        native.gemm_tc().ms_gemm_tc_set_config(0)
     assert ops.device_status(DEV).item() == 0
     scale = expect.abs().max().item()
     tol = 1e-4 * scale if epilogue == "f32" else 8e-3 * scale
