@@ -284,8 +284,7 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const uint32
     } else {
       for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __uint_as_float(acc[j]);
     }
-    return;
-  }
+  } else {
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -308,6 +307,7 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ out, const uint32
     }
   } else {
     for (int j = 0; j < 32 && col0 + j < N_out; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+  }
   }
 }
 
@@ -454,6 +454,269 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 }
 
+// ---------------------------------------------------------------- two CTAs per tile (cta_group::2)
+// A pair of CTAs (a cluster of two, on neighbouring SMs) computes one 256 x 256 tile: each CTA
+// loads its own 128 rows of A and 128 of the tile's 256 rows of W, the tensor cores of both read
+// both halves of W (the peer's through distributed shared memory), and each accumulates its own
+// 128 x 256 half in its own tensor memory. An SM thus stages 32 KB per k-block of 64 instead of
+// 48 KB for the same products. The first CTA of the pair issues the products for both and owns
+// the "stage is full" barriers, which the TMA copies of both CTAs report to; "stage is empty"
+// and "accumulator is full" reach both CTAs at once (tcgen05.commit with a cluster mask).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// TMA copy whose bytes are reported to the barrier of the pair's first CTA (address bit 24 cleared)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+// arrives on this barrier in both CTAs of the pair when the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+// arrive on the same barrier in the pair's first CTA
+__device__ __forceinline__ void mbar_arrive_first_cta(uint64_t* bar) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0u));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
+}
+
+// AND of a flag over the 128 threads of the epilogue warps (hardware barrier 1)
+__device__ __forceinline__ bool epilogue_all(bool flag) {
+  uint32_t res;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(res) : "r"((uint32_t)flag) : "memory");
+  return res != 0;
+}
+
+constexpr int PAIR_BN = 256, PAIR_STAGES = 5;
+constexpr int PAIR_OUT_BYTES = TC_BM * 64 * 2;  // one [128][64] bfloat16 tile of the epilogue's two
+constexpr int PAIR_STAGE_BYTES = (TC_BM + PAIR_BN / 2) * TC_BK * 2;  // per CTA: 128 rows of A and 128 of W
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
+                    int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[PAIR_STAGES], empty_bar[PAIR_STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  constexpr int COLS = EPI == TC_SILU_MUL ? PAIR_BN / 2 : PAIR_BN;  // output columns per tile
+  constexpr int A_BYTES = TC_BM * TC_BK * 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: the CTA that issues the products
+  const int k_iters = (K + TC_BK - 1) / TC_BK;
+  const int n_tiles = (N_out + COLS - 1) / COLS, m_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+  const int num_tiles = n_tiles * m_tiles;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  // Tiles that run at the same time share the larger operand: with fewer rows in A than in W the
+  // row tiles change fastest, so that a tile of W is fetched from memory once and serves every row
+  // tile while it is in L2 (24,576 x 4,096 weights do not fit L2; walking them once per row tile
+  // took 339 us against the library's 271 for 2,048 rows).
+  const bool m_fastest = M <= N_out;
+  auto tile_m = [&](int tile) { return m_fastest ? tile % m_tiles : tile / n_tiles; };
+  auto tile_n = [&](int tile) { return m_fastest ? tile / m_tiles : tile % n_tiles; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is reported to them
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int kb = 0;
+      for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+        const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
+        // this CTA's 128 of the tile's 256 rows of W: for SiLU * up the first CTA brings the gate rows, the second the up rows
+        const int w_row = EPI == TC_SILU_MUL ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + (int)rank * (PAIR_BN / 2);
+        bool ok = true;
+        for (int it = 0; it < k_iters; ++it, ++kb) {
+          const int s = kb % PAIR_STAGES;
+          if (kb >= PAIR_STAGES && !mbar_wait(&empty_bar[s], ((kb / PAIR_STAGES) - 1) & 1)) {
+            atomicExch(status, 11);
+            ok = false;
+            break;
+          }
+          unsigned char* a_tile = smem + (size_t)s * PAIR_STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);  // both CTAs' bytes
+          tma_load_2d_pair(a_tile, &map_a, &full_bar[s], it * TC_BK, m0);
+          tma_load_2d_pair(a_tile + A_BYTES, &map_w, &full_bar[s], it * TC_BK, w_row);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc(2 * TC_BM, PAIR_BN);
+      int kb = 0, tc = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
+        const int buf = tc & 1;
+        if (tc >= 2 && !mbar_wait(&acc_empty[buf], ((tc >> 1) - 1) & 1)) {
+          atomicExch(status, 14);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t tmem_acc = tmem_base + (uint32_t)buf * PAIR_BN;
+        for (int it = 0; it < k_iters; ++it, ++kb) {
+          const int s = kb % PAIR_STAGES;
+          if (!mbar_wait(&full_bar[s], (kb / PAIR_STAGES) & 1)) {
+            atomicExch(status, 12);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned char* a_tile = smem + (size_t)s * PAIR_STAGE_BYTES;
+          const uint64_t da = make_smem_desc(a_tile), db = make_smem_desc(a_tile + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) umma_bf16_pair(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0);
+          umma_commit_pair(&empty_bar[s]);
+        }
+        if (ok) umma_commit_pair(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    int tc = 0, out_buf = 0;
+    const bool tma_out = EPI != TC_OUT_F32 && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tc) {
+      const int buf = tc & 1;
+      const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
+      const int row = m0 + quad * 32 + lane;
+      // the four epilogue warps go on together or stop together (they meet at barriers below)
+      if (!epilogue_all(mbar_wait(&acc_full[buf], (tc >> 1) & 1))) {
+        atomicExch(status, 13);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t lane_addr = tmem_base + (uint32_t)buf * PAIR_BN + ((uint32_t)(quad * 32) << 16);
+      if constexpr (EPI == TC_OUT_F32) {
+#pragma unroll 1
+        for (int c = 0; c < COLS; c += 32) {
+          uint32_t acc[32];
+          tmem_ld32(lane_addr + (uint32_t)c, acc);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (row < M) store_chunk<EPI>(out, acc, acc, row, n0 + c, N_out);
+        }
+      } else if (!tma_out) {
+#pragma unroll 1
+        for (int c = 0; c < COLS; c += 32) {
+          uint32_t acc[32];
+          tmem_ld32(lane_addr + (uint32_t)c, acc);
+          if constexpr (EPI == TC_SILU_MUL) {
+            uint32_t up[32];
+            tmem_ld32(lane_addr + (uint32_t)(COLS + c), up);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (row < M) store_chunk<EPI>(out, acc, up, row, n0 + c, N_out);
+          } else {
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (row < M) store_chunk<EPI>(out, acc, acc, row, n0 + c, N_out);
+          }
+        }
+      } else {
+        // bfloat16 out: 64 columns at a time go through a swizzled shared-memory tile [128][64] and
+        // leave with one TMA store, which writes whole lines and clips at the matrix's edge; two
+        // tiles take turns so that a store is still reading one while the next is being filled
+        const int r = quad * 32 + lane;
+#pragma unroll 1
+        for (int cb = 0; cb < COLS; cb += 64) {
+          unsigned char* stage_out = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + (size_t)out_buf * PAIR_OUT_BYTES;
+          if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");  // this tile's last store has read it
+          asm volatile("bar.sync 1, 128;\n" ::: "memory");
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t acc[32];
+            float v[32];
+            tmem_ld32(lane_addr + (uint32_t)(cb + 32 * h), acc);
+            if constexpr (EPI == TC_SILU_MUL) {
+              uint32_t up[32];
+              tmem_ld32(lane_addr + (uint32_t)(COLS + cb + 32 * h), up);
+              asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                const float x = __uint_as_float(acc[q]);
+                v[q] = x / (1.0f + expf(-x)) * __uint_as_float(up[q]);
+              }
+            } else {
+              asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+              for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(acc[q]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), p1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), p3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+              pk.x = *reinterpret_cast<uint32_t*>(&p0);
+              pk.y = *reinterpret_cast<uint32_t*>(&p1);
+              pk.z = *reinterpret_cast<uint32_t*>(&p2);
+              pk.w = *reinterpret_cast<uint32_t*>(&p3);
+              const int chunk = 4 * h + q;  // 16-byte chunk of the 128-byte row; the swizzle XORs it with the row
+              *reinterpret_cast<uint4*>(stage_out + r * 128 + ((chunk ^ (r & 7)) << 4)) = pk;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          asm volatile("bar.sync 1, 128;\n" ::: "memory");
+          if (threadIdx.x == 64) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                         ::"l"(&map_out), "r"(smem_u32(stage_out)), "r"(n0 + cb), "r"(m0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+          }
+          out_buf ^= 1;
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_first_cta(&acc_empty[buf]);
+    }
+    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // every store has landed
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // neither CTA's shared or tensor memory goes away while the other may still use it
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -532,6 +795,37 @@ static int launch_tc_persistent(void* out, const void* A, const void* W, int M, 
   return 0;
 }
 
+template <int EPI>
+static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_out, int w_rows, int K, int up_row_offset,
+                          int* status, cudaStream_t stream) {
+  CUtensorMap map_a, map_w, map_out;
+  if (int rc = make_map(&map_a, A, M, K, TC_BM)) return rc;
+  if (int rc = make_map(&map_w, W, w_rows, K, PAIR_BN / 2)) return rc;
+  map_out = map_a;  // a valid map also when the kernel does not store through it (float32 out, odd widths)
+  if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
+    if (int rc = make_map(&map_out, out, M, N_out, TC_BM)) return rc;
+  }
+  constexpr size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 2 * PAIR_OUT_BYTES + 1024;
+  static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
+  auto kernel = gemm_tc_pair_kernel<EPI>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    configured = true;
+  }
+  constexpr int COLS = EPI == TC_SILU_MUL ? PAIR_BN / 2 : PAIR_BN;
+  const long long tiles = (long long)ceil_div(N_out, COLS) * ceil_div(M, 2 * TC_BM);
+  MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
+  const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), TC_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K, up_row_offset,
+                      status);
+  return 0;
+}
+
 }  // namespace ms
 
 using namespace ms;
@@ -543,8 +837,27 @@ MS_DEFINE_PDL_SWITCH(ms_gemm_tc_set_pdl)
 // out bf16 [M, N] = silu(A gate^T) * (A up^T). status: a device int the kernel raises if a wait ran out.
 static int g_tc_config = 0;
 // Tile configuration for experiments and tests: 0 = chosen from the shape, 5 = one CTA per tile,
-// 10 = persistent with 256-column tiles, 11 = persistent with 128-column tiles.
+// 10 = persistent with 256-column tiles, 11 = persistent with 128-column tiles, 20 = pairs of CTAs on 256 x 256 tiles.
 MS_EXPORT void ms_gemm_tc_set_config(int config) { g_tc_config = config; }
+
+// 1 if this package's kernel is the faster choice for the product (measured on B200 against
+// cuBLAS): bfloat16 out, at least one 256 x 256 tile for every pair of SMs, and rounds of tiles
+// that are mostly full of output. Then the 2-CTA kernel runs 2048 x 4096 x 1024 in 16.0 us
+// (cuBLAS 16.3), 2048 x 6144 x 1024 in 21.5 (22.8), 2048 x 24576 x 4096 in 261 (272) and
+// 8192 x 4096 x 4096 in 167 (180). A narrow output (2048 x 1024: 32 tiles) leaves SMs idle and
+// the library's smaller tiles win (14.2 against 8.9 us), as they do for 1,000 rows (4 row tiles,
+// the last a quarter full: 56 against 42 us at 6144 x 4096).
+MS_EXPORT int ms_gemm_tc_prefers(int M, int N, int K, int epilogue) {
+  int dev = 0, sm_count = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (epilogue != TC_OUT_BF16 || K % 8 != 0 || N % 8 != 0) return 0;
+  const long long pairs = sm_count / 2, tiles = (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN);
+  const long long rounds = (tiles + pairs - 1) / pairs;
+  // the share of the tiles' area that is output, and of the rounds' slots that hold a tile
+  const double useful = (double)M * N / ((double)tiles * 2 * TC_BM * PAIR_BN), filled = (double)tiles / (double)(rounds * pairs);
+  // a long k with a half-empty last round: the library cuts k there and wins (145 against 130 us for 2100 x 4096 x 12288)
+  return tiles >= pairs && useful * filled >= (K > 8192 ? 0.95 : 0.8);
+}
 
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,
                               cudaStream_t stream) {
@@ -563,7 +876,8 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
     MS_CHECK_CUDA(cudaGetDevice(&dev));
     MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const bool wide = (long long)ceil_div(M, TC_BM) * ceil_div(N, 256) >= sm_count;
+  const bool wide = (long long)ceil_div(M, TC_BM) * ceil_div(N, 256) >= sm_count;           // a 128 x 256 tile per SM
+  const bool pairs = (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN) >= sm_count / 2;  // a 256 x 256 tile per pair of SMs
   switch (epilogue) {
     case TC_OUT_BF16:
       if (g_tc_config == 1) return launch_tc<128, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
@@ -571,16 +885,19 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
       if (g_tc_config == 3) return launch_tc<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 4) return launch_tc<64, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 10) return launch_tc_persistent<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 11) return launch_tc_persistent<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 12) return launch_tc_persistent<256, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 10 || wide) return launch_tc_persistent<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 20 || pairs) return launch_tc_pair<TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_OUT_F32:
       if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 20) return launch_tc_pair<TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 10 || wide) return launch_tc_persistent<256, 4, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_SILU_MUL:
       if (g_tc_config == 5) return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+      if (g_tc_config == 20) return launch_tc_pair<TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
       return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }

@@ -136,7 +136,13 @@ def _flag(name: str, default: str) -> bool:
 # predecessor and weights are prefetched before the wait, a separate small kernel costs less than
 # the serial work a prologue adds to every CTA of the product.
 FUSE_NORM = _flag("MINISERVE_FUSE_NORM", "0")      # norm inside the next product's prologue
-TC_GEMM = _flag("MINISERVE_TC_GEMM", "0")          # plain products with more than 16 rows on this package's tcgen05 kernel
+def _setting(name: str, default: str) -> str:
+    import os
+
+    return os.environ.get(name, default)
+
+
+TC_GEMM = _setting("MINISERVE_TC_GEMM", "auto")   # products with more than 16 rows on the tcgen05 kernels: auto, 1 or 0
 TC_ATTENTION = _flag("MINISERVE_TC_ATTENTION", "1")  # prompts on the tcgen05 attention kernel (head size 128)
 FUSE_SILU = _flag("MINISERVE_FUSE_SILU", "0")      # SiLU * up inside the down projection's prologue
 SPLIT_K_PARTIALS = _flag("MINISERVE_SPLIT_K", "0")  # narrow products hand float32 partial sums to the norm
@@ -204,10 +210,10 @@ def device_status(device: torch.device | str = "cuda") -> torch.Tensor:
 
 
 def tc_gemm_enabled() -> bool:
-    """Plain products with more than 16 rows go to the vendor library unless MINISERVE_TC_GEMM=1:
-    this package's tcgen05 kernel is correct but, with one CTA per 128 x 128 tile and no operand
-    sharing between SMs, reaches about 60-75 % of the library's rate at prefill sizes."""
-    return TC_GEMM
+    """Whether plain bfloat16 products with more than 16 rows may run on this package's tcgen05
+    kernels (``MINISERVE_TC_GEMM``: ``auto``, the default, where they are the faster choice;
+    ``1`` always; ``0`` never)."""
+    return TC_GEMM != "0"
 
 
 TC_EPILOGUE = {"bf16": 0, "f32": 1, "silu_mul": 2}
@@ -230,8 +236,26 @@ def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
-def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return (tc_gemm_enabled() and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+_TC_PREFERS: dict[tuple, bool] = {}
+
+
+def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> bool:
+    """Whether ``linear`` sends this product to the tcgen05 kernels rather than to the vendor
+    library: always where they are forced, else where they were measured faster (wide bfloat16
+    outputs, see ``ms_gemm_tc_prefers``)."""
+    if TC_GEMM == "0" or x.shape[1] % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return False
+    if TC_GEMM == "1":
+        return True
+    if out is not None and (out.dtype != torch.bfloat16 or out.data_ptr() % 16):
+        return False
+    key = (x.shape[0], weight.shape[0], x.shape[1])
+    known = _TC_PREFERS.get(key)
+    if known is None:
+        if len(_TC_PREFERS) > 65536:
+            _TC_PREFERS.clear()
+        known = _TC_PREFERS[key] = bool(native.gemm_tc().ms_gemm_tc_prefers(key[0], key[1], key[2], TC_EPILOGUE["bf16"]))
+    return known
 
 
 SKINNY_MAX_M = 16
@@ -314,7 +338,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         return out
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    if tc_gemm_ok(x, weight):
+    if tc_gemm_ok(x, weight, out):
         return linear_tc(x, weight, out, "f32" if out.dtype == torch.float32 else "bf16", stream=stream)
     assert out.shape == (m, n) and out.dtype in (torch.float32, torch.bfloat16)
     blas.gemm_bf16(out, x, weight, _stream(stream))
