@@ -495,22 +495,24 @@ __device__ __forceinline__ void mbar_arrive_first_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
 }
 
-// AND of a flag over the 128 threads of the epilogue warps (hardware barrier 1)
-__device__ __forceinline__ bool epilogue_all(bool flag) {
+// AND of a flag over the 128 threads of a group of epilogue warps (hardware barrier `id`), and their plain barrier
+__device__ __forceinline__ bool epilogue_all(int id, bool flag) {
   uint32_t res;
   asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-      : "=r"(res) : "r"((uint32_t)flag) : "memory");
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+      "bar.red.and.pred q, %1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(res) : "r"(id), "r"((uint32_t)flag) : "memory");
   return res != 0;
 }
+__device__ __forceinline__ void epilogue_sync(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id) : "memory"); }
 
+constexpr int PAIR_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int PAIR_BN = 256, PAIR_STAGES = 5;
 constexpr int PAIR_OUT_BYTES = TC_BM * 64 * 2;  // one [128][64] bfloat16 tile of the epilogue's two
 constexpr int PAIR_STAGE_BYTES = (TC_BM + PAIR_BN / 2) * TC_BK * 2;  // per CTA: 128 rows of A and 128 of W
 
 template <int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
                     int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
@@ -542,7 +544,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp of both CTAs
+      mbar_init(&acc_empty[b], 16);  // one arrival per epilogue warp of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -614,7 +616,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    const int quad = warp & 3;
+    // eight epilogue warps in two groups of four; a group's warps cover the 128 lanes of tensor
+    // memory (warp w may touch lanes 32 * (w % 4) .. + 31) and the groups share out the columns
+    const int quad = warp & 3, eg = (warp - 2) >> 2;
+    const bool issuer = (int)threadIdx.x == 64 + 128 * eg;
     int tc = 0, out_buf = 0;
     const bool tma_out = EPI != TC_OUT_F32 && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tc) {
@@ -622,7 +627,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
       const int row = m0 + quad * 32 + lane;
       // the four epilogue warps go on together or stop together (they meet at barriers below)
-      if (!epilogue_all(mbar_wait(&acc_full[buf], (tc >> 1) & 1))) {
+      if (!epilogue_all(1 + eg, mbar_wait(&acc_full[buf], (tc >> 1) & 1))) {
         atomicExch(status, 13);
         break;
       }
@@ -630,7 +635,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * PAIR_BN + ((uint32_t)(quad * 32) << 16);
       if constexpr (EPI == TC_OUT_F32) {
 #pragma unroll 1
-        for (int c = 0; c < COLS; c += 32) {
+        for (int c = 32 * eg; c < COLS; c += 64) {
           uint32_t acc[32];
           tmem_ld32(lane_addr + (uint32_t)c, acc);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
@@ -638,7 +643,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       } else if (!tma_out) {
 #pragma unroll 1
-        for (int c = 0; c < COLS; c += 32) {
+        for (int c = 32 * eg; c < COLS; c += 64) {
           uint32_t acc[32];
           tmem_ld32(lane_addr + (uint32_t)c, acc);
           if constexpr (EPI == TC_SILU_MUL) {
@@ -653,14 +658,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       } else {
         // bfloat16 out: 64 columns at a time go through a swizzled shared-memory tile [128][64] and
-        // leave with one TMA store, which writes whole lines and clips at the matrix's edge; two
-        // tiles take turns so that a store is still reading one while the next is being filled
+        // leave with one TMA store, which writes whole lines and clips at the matrix's edge; each
+        // group of warps has two such tiles that take turns, so that a store is still reading one
+        // while the next is being filled
         const int r = quad * 32 + lane;
 #pragma unroll 1
-        for (int cb = 0; cb < COLS; cb += 64) {
-          unsigned char* stage_out = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + (size_t)out_buf * PAIR_OUT_BYTES;
-          if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");  // this tile's last store has read it
-          asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        for (int cb = 64 * eg; cb < COLS; cb += 128) {
+          unsigned char* stage_out = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + (size_t)(2 * eg + out_buf) * PAIR_OUT_BYTES;
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");  // this tile's last store has read it
+          epilogue_sync(1 + eg);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t acc[32];
@@ -694,8 +700,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-          asm volatile("bar.sync 1, 128;\n" ::: "memory");
-          if (threadIdx.x == 64) {
+          epilogue_sync(1 + eg);
+          if (issuer) {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
                          ::"l"(&map_out), "r"(smem_u32(stage_out)), "r"(n0 + cb), "r"(m0) : "memory");
             asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
@@ -707,7 +713,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive_first_cta(&acc_empty[buf]);
     }
-    if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // every store has landed
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // every store has landed
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
@@ -805,7 +811,7 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
     if (int rc = make_map(&map_out, out, M, N_out, TC_BM)) return rc;
   }
-  constexpr size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 2 * PAIR_OUT_BYTES + 1024;
+  constexpr size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 4 * PAIR_OUT_BYTES + 1024;
   static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
   auto kernel = gemm_tc_pair_kernel<EPI>;
   static bool configured = false;
@@ -821,7 +827,7 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   const long long tiles = (long long)ceil_div(N_out, COLS) * ceil_div(M, 2 * TC_BM);
   MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
   const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), TC_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K, up_row_offset,
+  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), PAIR_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K, up_row_offset,
                       status);
   return 0;
 }
@@ -850,13 +856,18 @@ MS_EXPORT void ms_gemm_tc_set_config(int config) { g_tc_config = config; }
 MS_EXPORT int ms_gemm_tc_prefers(int M, int N, int K, int epilogue) {
   int dev = 0, sm_count = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-  if (epilogue != TC_OUT_BF16 || K % 8 != 0 || N % 8 != 0) return 0;
-  const long long pairs = sm_count / 2, tiles = (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN);
+  if (epilogue == TC_OUT_F32 || K % 8 != 0 || N % 8 != 0) return 0;
+  // SiLU * up: a tile's 256 columns are 128 gate and 128 up columns, i.e. 128 columns of output; the fused
+  // kernel beats the library's product followed by the activation kernel by more (28 against 34 us for
+  // 2048 x 2*3072 x 1024, 261 against 295 us for 2048 x 2*12288 x 4096)
+  const int cols = epilogue == TC_SILU_MUL ? PAIR_BN / 2 : PAIR_BN;
+  const long long pairs = sm_count / 2, tiles = (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, cols);
   const long long rounds = (tiles + pairs - 1) / pairs;
   // the share of the tiles' area that is output, and of the rounds' slots that hold a tile
-  const double useful = (double)M * N / ((double)tiles * 2 * TC_BM * PAIR_BN), filled = (double)tiles / (double)(rounds * pairs);
+  const double useful = (double)M * N / ((double)tiles * 2 * TC_BM * cols), filled = (double)tiles / (double)(rounds * pairs);
+  const double need = epilogue == TC_SILU_MUL ? 0.7 : (K > 8192 ? 0.95 : 0.8);
   // a long k with a half-empty last round: the library cuts k there and wins (145 against 130 us for 2100 x 4096 x 12288)
-  return tiles >= pairs && useful * filled >= (K > 8192 ? 0.95 : 0.8);
+  return tiles >= pairs && useful * filled >= need;
 }
 
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,
@@ -897,7 +908,9 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
       return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_SILU_MUL:
       if (g_tc_config == 5) return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
-      if (g_tc_config == 20) return launch_tc_pair<TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+      if (g_tc_config == 10) return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+      if (g_tc_config == 20 || (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN / 2) >= sm_count / 2)
+        return launch_tc_pair<TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
       return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }

@@ -15,7 +15,7 @@ from . import blas, native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
-    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul",
+    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul", "silu_mul_is_fused",
     "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
@@ -239,22 +239,23 @@ def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue
 _TC_PREFERS: dict[tuple, bool] = {}
 
 
-def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> bool:
-    """Whether ``linear`` sends this product to the tcgen05 kernels rather than to the vendor
-    library: always where they are forced, else where they were measured faster (wide bfloat16
-    outputs, see ``ms_gemm_tc_prefers``)."""
+def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16") -> bool:
+    """Whether ``linear`` (or ``linear_silu_mul``) sends this product to the tcgen05 kernels rather
+    than to the vendor library: always where they are forced, else where they were measured faster
+    (wide bfloat16 outputs, see ``ms_gemm_tc_prefers``)."""
     if TC_GEMM == "0" or x.shape[1] % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
         return False
     if TC_GEMM == "1":
         return True
     if out is not None and (out.dtype != torch.bfloat16 or out.data_ptr() % 16):
         return False
-    key = (x.shape[0], weight.shape[0], x.shape[1])
+    n = weight.shape[0] // 2 if epilogue == "silu_mul" else weight.shape[0]
+    key = (x.shape[0], n, x.shape[1], epilogue)
     known = _TC_PREFERS.get(key)
     if known is None:
         if len(_TC_PREFERS) > 65536:
             _TC_PREFERS.clear()
-        known = _TC_PREFERS[key] = bool(native.gemm_tc().ms_gemm_tc_prefers(key[0], key[1], key[2], TC_EPILOGUE["bf16"]))
+        known = _TC_PREFERS[key] = bool(native.gemm_tc().ms_gemm_tc_prefers(key[0], key[1], key[2], TC_EPILOGUE[epilogue]))
     return known
 
 
@@ -345,11 +346,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def silu_mul_is_fused(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether ``linear_silu_mul`` runs as one kernel for these operands (then it needs no scratch)."""
+    if x.dtype != torch.bfloat16:
+        return False
+    return _skinny_ok(x, weight) or (x.shape[0] > SKINNY_MAX_M and tc_gemm_ok(x, weight, out, "silu_mul"))
+
+
 def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch=None, stream=None) -> torch.Tensor:
     """out [M, I] = silu(x Wg^T) * (x Wu^T) for the stacked weight [2I, K] (gate rows, then up rows;
     miniserve/model/qwen3.py:128-131). bfloat16 with at most 16 rows: one weight-streaming kernel
-    whose CTAs hold a gate row and its up row together. Otherwise the product into ``scratch``
-    ([M, 2I], allocated if None) and the activation kernel."""
+    whose CTAs hold a gate row and its up row together. More rows: the 2-CTA tcgen05 kernel with
+    the activation in its epilogue where that is the faster choice (``tc_gemm_ok``); otherwise the
+    product into ``scratch`` ([M, 2I], allocated if None) and the activation kernel."""
     m, kdim = x.shape
     inter = out.shape[1]
     assert weight.shape == (2 * inter, kdim) and out.shape[0] == m and out.dtype == x.dtype
@@ -358,6 +367,8 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, sc
         native.kernel_check(native.kernels().ms_gemm_skinny_gate_up_bf16(_ptr(out), _ptr(x), _ptr(weight), m, inter, kdim,
                                                                         _stream(stream)))
         return out
+    if x.dtype == torch.bfloat16 and m > SKINNY_MAX_M and tc_gemm_ok(x, weight, out, "silu_mul"):
+        return linear_tc(x, weight, out, "silu_mul", stream=stream)  # the activation in the tcgen05 kernel's epilogue
     gate_up = linear(x, weight, out=scratch, stream=stream)
     silu_mul(out, gate_up, stream=stream)
     return out

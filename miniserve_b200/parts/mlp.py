@@ -40,8 +40,11 @@ class SwiGLU(Part):
             return ops.linear(ops.LazyAct(gate_up, stream=ctx.stream), self.w_down, stream=ctx.stream,
                               partials=ops.SPLIT_K_PARTIALS)
         act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
-        if isinstance(x, torch.Tensor) and t <= ops.SKINNY_MAX_M and dt == torch.bfloat16:
-            ops.linear_silu_mul(x, self.w_gate_up, act, stream=ctx.stream)  # decode steps: the activation in the product's epilogue
+        if isinstance(x, torch.Tensor) and dt == torch.bfloat16:
+            # one kernel with the activation in its epilogue where there is one (decode steps, wide prompt steps)
+            fused = ops.silu_mul_is_fused(x, self.w_gate_up, act)
+            scratch = None if fused else ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev)
+            ops.linear_silu_mul(x, self.w_gate_up, act, scratch=scratch, stream=ctx.stream)
         else:
             gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
             ops.silu_mul(act, gate_up, stream=ctx.stream)
