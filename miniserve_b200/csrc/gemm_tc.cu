@@ -507,20 +507,23 @@ __device__ __forceinline__ bool epilogue_all(int id, bool flag) {
 __device__ __forceinline__ void epilogue_sync(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id) : "memory"); }
 
 constexpr int PAIR_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
-constexpr int PAIR_BN = 256, PAIR_STAGES = 5;
-constexpr int PAIR_OUT_BYTES = TC_BM * 64 * 2;  // one [128][64] bfloat16 tile of the epilogue's two
-constexpr int PAIR_STAGE_BYTES = (TC_BM + PAIR_BN / 2) * TC_BK * 2;  // per CTA: 128 rows of A and 128 of W
+constexpr int PAIR_BN = 256;                    // the wide tile; outputs too narrow for it take 128 columns
+constexpr int PAIR_OUT_BYTES = TC_BM * 64 * 2;  // one [128][64] bfloat16 tile of the epilogue's four
+// per CTA and stage: 128 rows of A and half of the tile's BN rows of W, 64 k each
+__host__ __device__ constexpr int pair_stage_bytes(int bn) { return (TC_BM + bn / 2) * TC_BK * 2; }
 
-template <int EPI>
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
                     int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t full_bar[PAIR_STAGES], empty_bar[PAIR_STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
-  constexpr int COLS = EPI == TC_SILU_MUL ? PAIR_BN / 2 : PAIR_BN;  // output columns per tile
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;  // output columns per tile
+  constexpr int STAGE_BYTES = pair_stage_bytes(BN);
+  constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators (512 or 256 columns)
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -538,7 +541,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   auto tile_n = [&](int tile) { return m_fastest ? tile / m_tiles : tile % n_tiles; };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PAIR_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -549,7 +552,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -567,17 +570,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int tile = pair; tile < num_tiles; tile += num_pairs) {
         const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
         // this CTA's 128 of the tile's 256 rows of W: for SiLU * up the first CTA brings the gate rows, the second the up rows
-        const int w_row = EPI == TC_SILU_MUL ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + (int)rank * (PAIR_BN / 2);
+        const int w_row = EPI == TC_SILU_MUL ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + (int)rank * (BN / 2);
         bool ok = true;
         for (int it = 0; it < k_iters; ++it, ++kb) {
-          const int s = kb % PAIR_STAGES;
-          if (kb >= PAIR_STAGES && !mbar_wait(&empty_bar[s], ((kb / PAIR_STAGES) - 1) & 1)) {
+          const int s = kb % STAGES;
+          if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1)) {
             atomicExch(status, 11);
             ok = false;
             break;
           }
-          unsigned char* a_tile = smem + (size_t)s * PAIR_STAGE_BYTES;
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);  // both CTAs' bytes
+          unsigned char* a_tile = smem + (size_t)s * STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);  // both CTAs' bytes
           tma_load_2d_pair(a_tile, &map_a, &full_bar[s], it * TC_BK, m0);
           tma_load_2d_pair(a_tile + A_BYTES, &map_w, &full_bar[s], it * TC_BK, w_row);
         }
@@ -586,7 +589,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else if (warp == 1) {
     if (rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = make_idesc(2 * TC_BM, PAIR_BN);
+      constexpr uint32_t idesc = make_idesc(2 * TC_BM, BN);
       int kb = 0, tc = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tc) {
@@ -597,16 +600,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t tmem_acc = tmem_base + (uint32_t)buf * PAIR_BN;
+        const uint32_t tmem_acc = tmem_base + (uint32_t)buf * BN;
         for (int it = 0; it < k_iters; ++it, ++kb) {
-          const int s = kb % PAIR_STAGES;
-          if (!mbar_wait(&full_bar[s], (kb / PAIR_STAGES) & 1)) {
+          const int s = kb % STAGES;
+          if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
             atomicExch(status, 12);
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const unsigned char* a_tile = smem + (size_t)s * PAIR_STAGE_BYTES;
+          const unsigned char* a_tile = smem + (size_t)s * STAGE_BYTES;
           const uint64_t da = make_smem_desc(a_tile), db = make_smem_desc(a_tile + A_BYTES);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) umma_bf16_pair(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (it | k) != 0);
@@ -632,7 +635,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const uint32_t lane_addr = tmem_base + (uint32_t)buf * PAIR_BN + ((uint32_t)(quad * 32) << 16);
+      const uint32_t lane_addr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quad * 32) << 16);
       if constexpr (EPI == TC_OUT_F32) {
 #pragma unroll 1
         for (int c = 32 * eg; c < COLS; c += 64) {
@@ -664,7 +667,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int r = quad * 32 + lane;
 #pragma unroll 1
         for (int cb = 64 * eg; cb < COLS; cb += 128) {
-          unsigned char* stage_out = smem + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + (size_t)(2 * eg + out_buf) * PAIR_OUT_BYTES;
+          unsigned char* stage_out = smem + (size_t)STAGES * STAGE_BYTES + (size_t)(2 * eg + out_buf) * PAIR_OUT_BYTES;
           if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");  // this tile's last store has read it
           epilogue_sync(1 + eg);
 #pragma unroll
@@ -719,7 +722,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   cluster_sync_all();  // neither CTA's shared or tensor memory goes away while the other may still use it
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -801,19 +804,19 @@ static int launch_tc_persistent(void* out, const void* A, const void* W, int M, 
   return 0;
 }
 
-template <int EPI>
+template <int BN, int STAGES, int EPI>
 static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_out, int w_rows, int K, int up_row_offset,
                           int* status, cudaStream_t stream) {
   CUtensorMap map_a, map_w, map_out;
   if (int rc = make_map(&map_a, A, M, K, TC_BM)) return rc;
-  if (int rc = make_map(&map_w, W, w_rows, K, PAIR_BN / 2)) return rc;
+  if (int rc = make_map(&map_w, W, w_rows, K, BN / 2)) return rc;
   map_out = map_a;  // a valid map also when the kernel does not store through it (float32 out, odd widths)
   if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
     if (int rc = make_map(&map_out, out, M, N_out, TC_BM)) return rc;
   }
-  constexpr size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 4 * PAIR_OUT_BYTES + 1024;
+  constexpr size_t smem = (size_t)STAGES * pair_stage_bytes(BN) + 4 * PAIR_OUT_BYTES + 1024;
   static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
-  auto kernel = gemm_tc_pair_kernel<EPI>;
+  auto kernel = gemm_tc_pair_kernel<BN, STAGES, EPI>;
   static bool configured = false;
   static int sm_count = 0;
   if (!configured) {
@@ -823,7 +826,7 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
     MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
     configured = true;
   }
-  constexpr int COLS = EPI == TC_SILU_MUL ? PAIR_BN / 2 : PAIR_BN;
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;
   const long long tiles = (long long)ceil_div(N_out, COLS) * ceil_div(M, 2 * TC_BM);
   MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
   const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
@@ -899,18 +902,19 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
       if (g_tc_config == 10) return launch_tc_persistent<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 11) return launch_tc_persistent<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 12) return launch_tc_persistent<256, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 20 || pairs) return launch_tc_pair<TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 21) return launch_tc_pair<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 20 || pairs) return launch_tc_pair<256, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_OUT_F32:
       if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 20) return launch_tc_pair<TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
+      if (g_tc_config == 20) return launch_tc_pair<256, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 10 || wide) return launch_tc_persistent<256, 4, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_F32>(out, A, W, M, N, N, K, 0, status, stream);
     case TC_SILU_MUL:
       if (g_tc_config == 5) return launch_tc<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
       if (g_tc_config == 10) return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
       if (g_tc_config == 20 || (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN / 2) >= sm_count / 2)
-        return launch_tc_pair<TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
+        return launch_tc_pair<256, 5, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
       return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }

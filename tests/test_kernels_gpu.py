@@ -93,13 +93,13 @@ def test_gemm_f32_is_true_32bit_and_row_independent(m, n, k):
 
 @pytest.mark.parametrize("m, n, k", [(128, 128, 64), (17, 200, 72), (333, 1000, 1000), (2048, 1024, 2048), (130, 503, 96), (4096, 6144, 256)])
 @pytest.mark.parametrize("epilogue", ["bf16", "f32", "silu_mul"])
-@pytest.mark.parametrize("config", [0, 5, 10, 11, 20], ids=["by_shape", "tile_per_cta", "persistent_256", "persistent_128", "two_cta_tiles"])
+@pytest.mark.parametrize("config", [0, 5, 10, 11, 20, 21], ids=["by_shape", "tile_per_cta", "persistent_256", "persistent_128", "two_cta_256", "two_cta_128"])
 def test_tcgen05_gemm(m, n, k, epilogue, config):
     """config: 0 chosen from the shape; 5 one CTA per tile; 10 and 11 the persistent kernel (tiles of 256 and 128 columns) whose ring
     of stages runs on from tile to tile and whose two accumulators take turns; 20 the same with pairs of CTAs on 256 x 256 tiles."""
     from miniserve_b200.ops import native
 
-    if config == 11 and epilogue != "bf16":
+    if config in (11, 21) and epilogue != "bf16":
         pytest.skip("the 128-column persistent tile is built for the plain bfloat16 epilogue only")
     torch.manual_seed(m + n)
     x = torch.randn(m, k, device=DEV).bfloat16()
