@@ -28,7 +28,24 @@ constexpr int TC_BM = 128, TC_BK = 64;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;  // polls of an mbarrier before giving up (far beyond any real wait)
 
-enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_SILU_MUL = 2 };
+enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_SILU_MUL = 2, TC_QKV_ROPE = 3 };
+
+// What the q|k|v epilogue (TC_QKV_ROPE) needs besides the product: per-head RMSNorm of q and k, rotation
+// by position and the write of q to [T, nq, 128] and of k, v into their cache pages, as the separate
+// kernel of rope_kv.cu does (miniserve/model/qwen3.py:118-123, miniserve/model/attention.py:139). Head size 128.
+struct QkvEpilogue {
+  __nv_bfloat16* k_pool;            // [pages + 1, nkv, page_size, 128]
+  __nv_bfloat16* v_pool;
+  const __nv_bfloat16* q_norm_w;    // [128] or null (no norm)
+  const __nv_bfloat16* k_norm_w;
+  const float* cos_sin;             // [T, 128]: cos then sin of every rotation pair of a token, or null (no rotation)
+  const int* positions;
+  const int* row_of_token;
+  const int* page_indptr;
+  const int* page_indices;
+  int nq, nkv, page_shift;
+  float eps;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -516,11 +533,12 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, void* __restrict__ out,
-                    int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+                    int M, int N_out, int K, int up_row_offset, int* __restrict__ status, const QkvEpilogue qe) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int row_dst[2][TC_BM];  // TC_QKV_ROPE: the pool row (page, kv head, slot) each row of a k or v head goes to (-1: none)
   constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;  // output columns per tile
   constexpr int STAGE_BYTES = pair_stage_bytes(BN);
   constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators (512 or 256 columns)
@@ -624,7 +642,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quad = warp & 3, eg = (warp - 2) >> 2;
     const bool issuer = (int)threadIdx.x == 64 + 128 * eg;
     int tc = 0, out_buf = 0;
-    const bool tma_out = EPI != TC_OUT_F32 && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const bool tma_out = EPI != TC_OUT_F32 && EPI != TC_QKV_ROPE && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tc) {
       const int buf = tc & 1;
       const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
@@ -636,7 +654,120 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quad * 32) << 16);
-      if constexpr (EPI == TC_OUT_F32) {
+      if constexpr (EPI == TC_QKV_ROPE) {
+        // A tile's 256 columns are two whole heads; each group of warps takes one. A thread owns a
+        // token's row of its head: it reads the 128 values twice from tensor memory (once for the
+        // sum of squares, once to normalise and rotate), puts the result into the group's two
+        // swizzled [128][64] tiles, and the tiles leave by TMA (q) or by row copies into the
+        // token's cache page (k, v).
+        const int r = quad * 32 + lane, tok = m0 + r;
+        const int head = n0 / 128 + eg;
+        const bool is_q = head < qe.nq, is_v = head >= qe.nq + qe.nkv;
+        const __nv_bfloat16* nw = is_v ? nullptr : (is_q ? qe.q_norm_w : qe.k_norm_w);
+        const uint32_t head_addr = lane_addr + (uint32_t)(128 * eg);
+        unsigned char* stage_lo = smem + (size_t)STAGES * STAGE_BYTES + (size_t)(2 * eg) * PAIR_OUT_BYTES;
+        unsigned char* stage_hi = stage_lo + PAIR_OUT_BYTES;
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // the stores of the tile before have read both
+        epilogue_sync(1 + eg);
+        float inv = 1.f;
+        if (nw) {
+          float ss = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t acc[32];
+            tmem_ld32(head_addr + (uint32_t)(32 * c), acc);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+            for (int q = 0; q < 32; ++q) {
+              const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[q])));  // the product is rounded to bfloat16 first, as when it is stored
+              ss += x * x;
+            }
+          }
+          inv = 1.0f / sqrtf(ss / 128.f + qe.eps);
+        }
+        const float* table = (qe.cos_sin && !is_v && tok < M) ? qe.cos_sin + (size_t)tok * 128 : nullptr;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t lo[32], hi[32];
+          tmem_ld32(head_addr + (uint32_t)(32 * hh), lo);
+          tmem_ld32(head_addr + (uint32_t)(64 + 32 * hh), hi);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // eight rotation pairs at a time
+            float l[8], h[8], cs[8], sn[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              l[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[8 * q + e])));
+              h[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[8 * q + e])));
+              cs[e] = 1.f;
+              sn[e] = 0.f;
+            }
+            if (nw) {
+              float wl[8], wh[8];
+              bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 32 * hh + 8 * q), wl);
+              bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 64 + 32 * hh + 8 * q), wh);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                l[e] = (l[e] * inv) * wl[e];
+                h[e] = (h[e] * inv) * wh[e];
+              }
+            }
+            if (table) {
+              const float4 c0 = *reinterpret_cast<const float4*>(table + 32 * hh + 8 * q), c1 = *reinterpret_cast<const float4*>(table + 32 * hh + 8 * q + 4);
+              const float4 s0 = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 8 * q), s1 = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 8 * q + 4);
+              cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+              sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+            }
+            float ol[8], oh[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              ol[e] = l[e] * cs[e] - h[e] * sn[e];
+              oh[e] = h[e] * cs[e] + l[e] * sn[e];
+            }
+            const int chunk = 4 * hh + q;  // elements 32 hh + 8 q .. + 7 of the head's first half, and of its second
+            *reinterpret_cast<uint4*>(stage_lo + r * 128 + ((chunk ^ (r & 7)) << 4)) = float_to_bf16x8(ol);
+            *reinterpret_cast<uint4*>(stage_hi + r * 128 + ((chunk ^ (r & 7)) << 4)) = float_to_bf16x8(oh);
+          }
+        }
+        if (!is_q) {
+          // where this token's row of the head goes in the pool
+          int dst = -1;
+          if (tok < M) {
+            const int pos = qe.positions[tok];
+            const int page = qe.page_indices[qe.page_indptr[qe.row_of_token[tok]] + (pos >> qe.page_shift)];
+            if (page < 0) {
+              atomicExch(status, 2);
+            } else {
+              const int kvh = head - qe.nq - (is_v ? qe.nkv : 0);
+              dst = ((page * qe.nkv + kvh) << qe.page_shift) + (pos & ((1 << qe.page_shift) - 1));
+            }
+          }
+          row_dst[eg][r] = dst;
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        epilogue_sync(1 + eg);
+        if (is_q) {
+          if (issuer) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                         ::"l"(&map_out), "r"(smem_u32(stage_lo)), "r"(head * 128), "r"(m0) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                         ::"l"(&map_out), "r"(smem_u32(stage_hi)), "r"(head * 128 + 64), "r"(m0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+          }
+        } else {
+          // two rows per warp and trip: 16 lanes copy a row's 256 bytes (8 chunks from each tile) in whole lines
+          __nv_bfloat16* pool = is_v ? qe.v_pool : qe.k_pool;
+          const int sub = lane & 15, c = sub & 7;
+          const unsigned char* from = sub < 8 ? stage_lo : stage_hi;
+#pragma unroll 4
+          for (int trip = 0; trip < 16; ++trip) {
+            const int rr = quad * 32 + 2 * trip + (lane >> 4);
+            const int dst = row_dst[eg][rr];
+            if (dst >= 0)
+              *reinterpret_cast<uint4*>(pool + (size_t)dst * 128 + (sub >> 3) * 64 + c * 8) = *reinterpret_cast<const uint4*>(from + rr * 128 + ((c ^ (rr & 7)) << 4));
+          }
+        }
+      } else if constexpr (EPI == TC_OUT_F32) {
 #pragma unroll 1
         for (int c = 32 * eg; c < COLS; c += 64) {
           uint32_t acc[32];
@@ -806,12 +937,14 @@ static int launch_tc_persistent(void* out, const void* A, const void* W, int M, 
 
 template <int BN, int STAGES, int EPI>
 static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_out, int w_rows, int K, int up_row_offset,
-                          int* status, cudaStream_t stream) {
+                          int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{}) {
   CUtensorMap map_a, map_w, map_out;
   if (int rc = make_map(&map_a, A, M, K, TC_BM)) return rc;
   if (int rc = make_map(&map_w, W, w_rows, K, BN / 2)) return rc;
   map_out = map_a;  // a valid map also when the kernel does not store through it (float32 out, odd widths)
-  if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
+  if (EPI == TC_QKV_ROPE) {
+    if (int rc = make_map(&map_out, out, M, (long long)qe.nq * 128, TC_BM)) return rc;  // q alone goes out through it
+  } else if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
     if (int rc = make_map(&map_out, out, M, N_out, TC_BM)) return rc;
   }
   constexpr size_t smem = (size_t)STAGES * pair_stage_bytes(BN) + 4 * PAIR_OUT_BYTES + 1024;
@@ -831,7 +964,7 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
   const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), PAIR_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K, up_row_offset,
-                      status);
+                      status, qe);
   return 0;
 }
 
@@ -871,6 +1004,31 @@ MS_EXPORT int ms_gemm_tc_prefers(int M, int N, int K, int epilogue) {
   const double need = epilogue == TC_SILU_MUL ? 0.7 : (K > 8192 ? 0.95 : 0.8);
   // a long k with a half-empty last round: the library cuts k there and wins (145 against 130 us for 2100 x 4096 x 12288)
   return tiles >= pairs && useful * filled >= need;
+}
+
+// q_out [M, nq, 128], k_pool / v_pool [pages + 1, nkv, page_size, 128] from x [M, K] and the stacked
+// weight [(nq + 2 nkv) * 128, K]: the q|k|v product with the per-head norm, the rotation and the cache
+// write in its epilogue (the 2-CTA kernel). nq and nkv even, head size 128, the whole head rotated.
+MS_EXPORT int ms_gemm_tc_qkv_bf16(void* q_out, const void* x, const void* w_qkv, int M, int K, int nq, int nkv, void* k_pool,
+                                  void* v_pool, const void* q_norm_w, const void* k_norm_w, const float* cos_sin,
+                                  const int* positions, const int* row_of_token, const int* page_indptr,
+                                  const int* page_indices, int page_size, float eps, int* status, cudaStream_t stream) {
+  if (M == 0) return 0;
+  MS_CHECK_ARG(M > 0 && K > 0 && K % 8 == 0, "gemm_tc: bad sizes M=%d K=%d", M, K);
+  MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % 2 == 0 && nkv % 2 == 0, "gemm_tc: the q|k|v epilogue takes even head counts, not %d and %d", nq, nkv);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "gemm_tc: page_size=%d must be a power of two", page_size);
+  MS_CHECK_ARG((q_norm_w != nullptr) == (k_norm_w != nullptr), "gemm_tc: q and k are normed together or not at all");
+  MS_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w_qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
+                   ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)q_norm_w % 16 == 0) && ((uintptr_t)k_norm_w % 16 == 0) &&
+                   ((uintptr_t)cos_sin % 16 == 0),
+               "gemm_tc: operands must be 16-byte aligned");
+  MS_CHECK_ARG(status != nullptr && k_pool != nullptr && v_pool != nullptr, "gemm_tc: the q|k|v epilogue needs the pools and a status word");
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  const QkvEpilogue qe = {(__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
+                          cos_sin, positions, row_of_token, page_indptr, page_indices, nq, nkv, shift, eps};
+  const int n_total = (nq + 2 * nkv) * 128;
+  return launch_tc_pair<256, 5, TC_QKV_ROPE>(q_out, x, w_qkv, M, n_total, n_total, K, 0, status, stream, qe);
 }
 
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,

@@ -15,7 +15,7 @@ from . import blas, native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
-    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul", "silu_mul_is_fused",
+    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul", "silu_mul_is_fused", "qkv_fused_ok", "qkv_norm_rope_kv",
     "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
@@ -143,6 +143,7 @@ def _setting(name: str, default: str) -> str:
 
 
 TC_GEMM = _setting("MINISERVE_TC_GEMM", "auto")   # products with more than 16 rows on the tcgen05 kernels: auto, 1 or 0
+QKV_EPILOGUE = _flag("MINISERVE_QKV_EPILOGUE", "1")  # q/k norm, rotation and cache write in the q|k|v product's epilogue
 TC_ATTENTION = _flag("MINISERVE_TC_ATTENTION", "1")  # prompts on the tcgen05 attention kernel (head size 128)
 FUSE_SILU = _flag("MINISERVE_FUSE_SILU", "0")      # SiLU * up inside the down projection's prologue
 SPLIT_K_PARTIALS = _flag("MINISERVE_SPLIT_K", "0")  # narrow products hand float32 partial sums to the norm
@@ -432,6 +433,43 @@ def qk_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: to
         _ptr(cos_sin if inv_freq is not None else None), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, d,
         rotary_dim if inv_freq is not None else 0, float(eps), page_size, _ptr(status), dtype_code(qkv.dtype),
         _stream(stream)))
+
+
+def qkv_fused_ok(x: torch.Tensor, w_qkv: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, k_pool, q_norm_w, k_norm_w) -> bool:
+    """Whether ``qkv_norm_rope_kv`` takes this projection: a step wide enough for the 2-CTA tcgen05
+    kernel to be the faster choice for the q|k|v product, bfloat16, head size 128 rotated whole (or
+    not at all), even head counts (a tile's 256 columns are then two whole heads of one kind)."""
+    if TC_GEMM == "0" or not QKV_EPILOGUE or x.dtype != torch.bfloat16 or k_pool is None:
+        return False
+    if d != 128 or rotary_dim not in (0, 128) or nq % 2 or nkv % 2 or (q_norm_w is None) != (k_norm_w is None):
+        return False
+    # the epilogue's work per tile does not depend on k: it hides behind the products of the next tile
+    # when k is long (measured at 2,048 rows: 76 against 83 us for 4096 -> 6144 columns, 148 against
+    # 164 us for 5120 -> 10240) and does not when k is short (30 against 25 us for 1024 -> 4096)
+    if x.shape[0] <= SKINNY_MAX_M or x.shape[1] < 2048:
+        return False
+    return TC_GEMM == "1" or tc_gemm_ok(x, w_qkv)
+
+
+def qkv_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, x: torch.Tensor, w_qkv: torch.Tensor,
+                     q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, cos_sin: torch.Tensor | None, eps: float,
+                     positions: torch.Tensor, row_of_token: torch.Tensor, page_indptr: torch.Tensor,
+                     page_indices: torch.Tensor, page_size: int, stream=None) -> None:
+    """The q|k|v projection of x [T, K] with what follows it in its epilogue: per-head norm of q and
+    k, rotation by position (``cos_sin``: the step's float32 table [T, 128], None for no rotation),
+    q to ``q_out`` [T, nq, 128] and the new k, v into their pages. The same arithmetic as
+    ``linear`` followed by ``qk_norm_rope_kv``, without the [T, (nq + 2 nkv) * 128] tensor in between."""
+    _check_dev(q_out, k_pool, v_pool, x, w_qkv, q_norm_w, k_norm_w, cos_sin, positions, row_of_token, page_indptr, page_indices)
+    t, nq, d = q_out.shape
+    nkv = k_pool.shape[1]
+    assert d == 128 and k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
+    assert x.dtype == torch.bfloat16 and w_qkv.shape == ((nq + 2 * nkv) * d, x.shape[1]) and x.shape[0] == t
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (t, d))
+    lib = native.gemm_tc()
+    native.kernel_check(lib.ms_gemm_tc_qkv_bf16(
+        _ptr(q_out), _ptr(x), _ptr(w_qkv), t, x.shape[1], nq, nkv, _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w), _ptr(k_norm_w),
+        _ptr(cos_sin), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), page_size, float(eps),
+        _ptr(device_status(x.device)), _stream(stream)), lib=lib, errfn="ms_gemm_tc_last_error")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, num_tokens: int, rotary_dim: int, stream=None) -> torch.Tensor:

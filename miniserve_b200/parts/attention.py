@@ -80,15 +80,23 @@ class GQAttention(Part):
         partial sums of it that the next norm adds up (``ops.PartialSums``)."""
         t = x.shape[0]
         dt, dev = self.env.dtype, self.w_qkv.device
-        qkv = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
         q = ctx.buffer("attn.q", (t, self.heads, self.head_dim), dt, dev)
         inv_freq, rotary_dim = self.position.kernel_table()
         indptr, indices = ctx.page_indptr[cache.group], ctx.page_indices[cache.group]
-        ops.qk_norm_rope_kv(
-            q, cache.k if self.owns_cache else None, cache.v if self.owns_cache else None, qkv,
-            self.w_q_norm, self.w_k_norm, inv_freq, rotary_dim, self.qk_norm_eps, ctx.positions,
-            ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream,
-            cos_sin=self.position.step_table(ctx))
+        if (self.owns_cache and isinstance(x, torch.Tensor)
+                and ops.qkv_fused_ok(x, self.w_qkv, self.heads, self.kv_heads, self.head_dim, rotary_dim if inv_freq is not None else 0,
+                                     cache.k, self.w_q_norm, self.w_k_norm)):
+            # prompt steps: norm, rotation and cache write in the product's epilogue
+            ops.qkv_norm_rope_kv(q, cache.k, cache.v, x, self.w_qkv, self.w_q_norm, self.w_k_norm,
+                                 self.position.step_table(ctx) if inv_freq is not None else None, self.qk_norm_eps,
+                                 ctx.positions, ctx.row_of_token, indptr, indices, cache.page_size, stream=ctx.stream)
+        else:
+            qkv = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
+            ops.qk_norm_rope_kv(
+                q, cache.k if self.owns_cache else None, cache.v if self.owns_cache else None, qkv,
+                self.w_q_norm, self.w_k_norm, inv_freq, rotary_dim, self.qk_norm_eps, ctx.positions,
+                ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream,
+                cos_sin=self.position.step_table(ctx))
         out = ctx.buffer("attn.out", (t, self.heads, self.head_dim), dt, dev)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
         return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,

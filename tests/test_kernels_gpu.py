@@ -275,6 +275,40 @@ def test_qk_norm_rope_kv_write(dtype, nq, nkv, d, page, theta, eps):
     assert torch.equal(~torch.isnan(pb.k_pool[:, 0, :, 0]).cpu(), written)
 
 
+@pytest.mark.parametrize("nq, nkv, page, rotate, normed", [(16, 8, 16, True, True), (4, 2, 8, True, False), (2, 2, 64, False, True),
+                                                          (6, 4, 16, True, True)])
+@pytest.mark.parametrize("rows", [[(0, 300), (13, 1), (500, 213)], [(0, 1000)], [(3, 129), (0, 127), (40, 2), (0, 70)]])
+def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nq, nkv, page, rotate, normed, rows):
+    """The 2-CTA tcgen05 kernel's q|k|v epilogue against the product followed by the separate kernel:
+    the same q, the same new keys and values in the same slots, nothing else touched."""
+    d, hidden, eps = 128, 256, 1e-6
+    torch.manual_seed(nq * 100 + len(rows))
+    a = PagedBatch(rows, page, nkv, d, torch.bfloat16, seed=3)
+    b = PagedBatch(rows, page, nkv, d, torch.bfloat16, seed=3)
+    t = a.num_tokens
+    x = torch.randn(t, hidden, device=DEV).bfloat16()
+    w = (torch.randn((nq + 2 * nkv) * d, hidden, device=DEV) * hidden ** -0.5).bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16() if normed else None
+    kw = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16() if normed else None
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))).to(DEV) if rotate else None
+    table = ops.rope_table(a.positions, inv_freq, t, d) if rotate else None
+    q1 = torch.full((t, nq, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    q2 = torch.full_like(q1, float("nan"))
+    ops.qk_norm_rope_kv(q1, a.k_pool, a.v_pool, ops.linear(x, w), qw, kw, inv_freq, d if rotate else 0, eps, a.positions, a.row_of_token,
+                        a.page_indptr, a.page_indices, page, a.status, cos_sin=table)
+    ops.qkv_norm_rope_kv(q2, b.k_pool, b.v_pool, x, w, qw, kw, table, eps, b.positions, b.row_of_token, b.page_indptr, b.page_indices, page)
+    torch.cuda.synchronize()
+    assert a.status.item() == 0 and ops.device_status(DEV).item() == 0
+    tol = dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(q2.float(), q1.float(), **tol)
+    # the pools: NaN (never written) in the same places, close values in the others, values bit-equal
+    for p1, p2, exact in ((a.k_pool, b.k_pool, False), (a.v_pool, b.v_pool, True)):
+        assert torch.equal(torch.isnan(p1), torch.isnan(p2))
+        x1, x2 = torch.nan_to_num(p1.float()), torch.nan_to_num(p2.float())
+        assert torch.equal(x1, x2) if exact else torch.allclose(x2, x1, **tol)
+    assert (~torch.isnan(b.k_pool[:, 0, :, 0])).sum().item() == t
+
+
 def test_rope_angles_at_far_positions_are_32bit():
     d, theta, page = 32, 1e6, 16
     pb = PagedBatch([(40000, 3)], page, 1, d, torch.float32)
