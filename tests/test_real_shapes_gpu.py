@@ -84,3 +84,42 @@ def test_real_vocabulary_sampling_matches_the_plain_sampler(real):
     for r in range(2):
         assert got[r] == plain.sample_token(logits[r].cpu(), [0.8, 1.0][r], [7, 9][r], [39, 40][r])
     cache.release(rc)
+
+
+def test_wide_hidden_size_runs_the_tcgen05_products_and_their_epilogues(tmp_path, monkeypatch):
+    """A hidden size of 2,048 with this package's tcgen05 kernels forced for every product with more
+    than 16 rows: the q|k|v product then carries the per-head norm, the rotation and the cache write
+    in its epilogue and the gate|up product SiLU * up. Whole, in portions and decoded, against the
+    plain implementation."""
+    from miniserve_b200 import ops
+
+    monkeypatch.setattr(ops, "TC_GEMM", "1")
+    raw = dict(plain.tiny_config_b(), hidden_size=2048, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+               intermediate_size=512, vocab_size=777, num_hidden_layers=2, tie_word_embeddings=False)
+    plain.write_random_model(tmp_path, raw, seed=9, std=0.02, dtype=torch.bfloat16)
+    rng = random.Random(8)
+    ids = [rng.randrange(raw["vocab_size"]) for _ in range(330)]
+    cfg, w = plain.read_config(tmp_path), plain.read_weights(tmp_path)
+    expect = plain.all_logits(cfg, w, ids)
+    _, _, model = load_model(tmp_path, "bfloat16", "cuda:0")
+    assert ops.qkv_fused_ok(torch.empty(300, 2048, device="cuda", dtype=torch.bfloat16), model.layers[0].mixer.w_qkv, 4, 2, 128, 128,
+                            True, model.layers[0].mixer.w_q_norm, model.layers[0].mixer.w_k_norm)
+    cache = CacheManager(model.entry_caches, 48, 16, 4, dtype=model.dtype, device=model.device, poison=True)
+    step = StepFunction(model, cache)
+    n = len(ids)
+    rc = cache.new_request()
+    whole = step.run([StepRow(rc, ids, range(n))])
+    cache.release(rc)
+    a, b = cache.new_request(), cache.new_request()
+    outs = [step.run([StepRow(a, ids[:257], range(257))])]
+    for i in range(257, 270):
+        outs.append(step.run([StepRow(a, ids[i:i + 1], [0]), StepRow(b, ids[(i - 257) * 19:(i - 256) * 19], [])])[:1])
+    outs.append(step.run([StepRow(b, ids[:40], []), StepRow(a, ids[270:], range(n - 270))])[:n - 270])
+    step.check_status()
+    cut = torch.cat(outs)
+    cache.release(a)
+    cache.release(b)
+    assert cache.is_idle()
+    noise = bfloat16_noise(tmp_path, {"x": ids}, {"x": expect})
+    for name, got in (("whole", whole), ("cut", cut)):
+        check_bfloat16((got.cpu() - expect).abs().max(dim=1).values, noise, name)
