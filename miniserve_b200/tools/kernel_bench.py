@@ -84,7 +84,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -99,6 +99,8 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--legacy", action="store_true", help="attention: force the mma.sync kernels")
+    ap.add_argument("--gemm", choices=["auto", "tcgen05", "library"], default="auto",
+                    help="gemm, gate_up: this package's tcgen05 kernels, the vendor library, or the engine's choice")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -135,6 +137,22 @@ def main(argv=None) -> int:
                 attention_bf16.run(o, q, k, v, ctx, 0, d ** -0.5, None)
             else:
                 ops.attention(o, q, k, v, ctx, 0, d ** -0.5, None)
+    elif args.kernel in ("gemm", "gate_up"):
+        # gemm: x [m, k] times w [n, k]^T; gate_up: silu(x Wg^T) * (x Wu^T) with the stacked weight [2 n, k]
+        ops.TC_GEMM = {"auto": "auto", "tcgen05": "1", "library": "0"}[args.gemm]
+        rows = args.n * (2 if args.kernel == "gate_up" else 1)
+        work = dict(flops=2.0 * args.m * rows * args.k)
+        copies = max(2, int(L2_BYTES // (rows * args.k * 2)) + 1)
+        ws = [(torch.randn(rows, args.k, device=dev) * args.k ** -0.5).bfloat16() for _ in range(copies)]
+        x = torch.randn(args.m, args.k, device=dev).bfloat16()
+        o = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+        scratch = torch.empty(args.m, rows, device=dev, dtype=torch.bfloat16)
+
+        def calls(i, stream):
+            if args.kernel == "gemm":
+                ops.linear(x, ws[i], out=o, stream=stream)
+            else:
+                ops.linear_silu_mul(x, ws[i], o, scratch=scratch, stream=stream)
     elif args.kernel == "skinny":
         byts = args.n * args.k * 2
         work = dict(bytes=byts)
