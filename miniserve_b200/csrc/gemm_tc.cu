@@ -688,19 +688,32 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const float* table = (qe.cos_sin && !is_v && tok < M) ? qe.cos_sin + (size_t)tok * 128 : nullptr;
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
+          // the half's cos and sin first: their way from memory overlaps the reads of tensor memory
+          float4 cs4[8], sn4[8];
+          if (table) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              cs4[q] = *reinterpret_cast<const float4*>(table + 32 * hh + 4 * q);
+              sn4[q] = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 4 * q);
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              cs4[q] = make_float4(1.f, 1.f, 1.f, 1.f);
+              sn4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
           uint32_t lo[32], hi[32];
           tmem_ld32(head_addr + (uint32_t)(32 * hh), lo);
           tmem_ld32(head_addr + (uint32_t)(64 + 32 * hh), hi);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
           for (int q = 0; q < 4; ++q) {  // eight rotation pairs at a time
-            float l[8], h[8], cs[8], sn[8];
+            float l[8], h[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               l[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[8 * q + e])));
               h[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[8 * q + e])));
-              cs[e] = 1.f;
-              sn[e] = 0.f;
             }
             if (nw) {
               float wl[8], wh[8];
@@ -712,12 +725,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 h[e] = (h[e] * inv) * wh[e];
               }
             }
-            if (table) {
-              const float4 c0 = *reinterpret_cast<const float4*>(table + 32 * hh + 8 * q), c1 = *reinterpret_cast<const float4*>(table + 32 * hh + 8 * q + 4);
-              const float4 s0 = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 8 * q), s1 = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 8 * q + 4);
-              cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-              sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-            }
+            const float cs[8] = {cs4[2 * q].x, cs4[2 * q].y, cs4[2 * q].z, cs4[2 * q].w, cs4[2 * q + 1].x, cs4[2 * q + 1].y, cs4[2 * q + 1].z, cs4[2 * q + 1].w};
+            const float sn[8] = {sn4[2 * q].x, sn4[2 * q].y, sn4[2 * q].z, sn4[2 * q].w, sn4[2 * q + 1].x, sn4[2 * q + 1].y, sn4[2 * q + 1].z, sn4[2 * q + 1].w};
             float ol[8], oh[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
