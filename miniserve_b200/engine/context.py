@@ -47,8 +47,8 @@ class StepContext:
     graph_bucket: int = 0  # > 0 while a CUDA graph for this padded batch size is captured or replayed
 
     def buffer(self, role: str, shape: tuple, dtype: torch.dtype, device) -> torch.Tensor:
-        """An uninitialised activation tensor that lives for this step and is shared by every
-        layer: the first caller with this (role, shape, dtype) allocates it, later callers get the
+        """An uninitialised activation tensor that lives for one pass of the model over this step
+        (the model empties ``buffers`` when a pass begins) and is shared by every layer: the first caller with this (role, shape, dtype) allocates it, later callers get the
         same tensor. Kernels of one step run in stream order, so a part may take a role's buffer
         again in the next layer once nothing of its own still reads it. A part names a role for
         each tensor it has alive at the same time ("attn.qkv", "attn.q", ...)."""

@@ -28,11 +28,12 @@ def graph_buckets(max_bs: int) -> list[int]:
 
 
 class _Captured:
-    __slots__ = ("graph", "tokens", "logits", "f32", "i64", "launches")
+    __slots__ = ("graph", "tokens", "logits", "f32", "i64", "launches", "sampler_scratch")
 
-    def __init__(self, graph, tokens, logits, f32, i64, launches):
+    def __init__(self, graph, tokens, logits, f32, i64, launches, sampler_scratch):
         self.graph, self.tokens, self.logits, self.f32, self.i64 = graph, tokens, logits, f32, i64
         self.launches = launches  # launches of this package's kernels inside the graph
+        self.sampler_scratch = sampler_scratch  # the sampler's scratch tensor whose address the graph holds (None: none)
 
 
 class DecodeGraphs:
@@ -74,6 +75,8 @@ class DecodeGraphs:
             self._graphs.clear()
             self._generation = sf.arena_generation
         cap = self._graphs.get((bucket, mode))
+        if cap is not None and cap.sampler_scratch is not None and cap.sampler_scratch is not self.sampler._scratch:
+            cap = None  # the sampler has moved to a larger scratch since: the graph's address is stale
         if cap is None:
             cap = self._capture(ctx, bucket, mode)
             self._graphs[(bucket, mode)] = cap
@@ -152,4 +155,4 @@ class DecodeGraphs:
         native.LAUNCHES[0] = before  # a capture launches nothing
         if self._pool is None:
             self._pool = graph.pool()
-        return _Captured(graph, tokens, logits, f32, i64, launches)
+        return _Captured(graph, tokens, logits, f32, i64, launches, self.sampler._scratch if mode == "top_p" else None)

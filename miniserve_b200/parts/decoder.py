@@ -106,7 +106,12 @@ class DecoderModel:
         of run entry i. Returns float32 logits at ``ctx.logit_rows``: [wanted, vocab]."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet (bind() was not called)")
-        ctx.step_cache.clear()  # what parts share within one pass is made anew by every pass
+        # What parts share within one pass is made anew by every pass. That holds for the activation
+        # buffers too: a pass that is captured into a CUDA graph must allocate them itself (from the
+        # graph's memory pool); tensors left by an earlier pass over the same context are ordinary
+        # memory that goes back to the allocator while the graph still holds their addresses.
+        ctx.step_cache.clear()
+        ctx.buffers.clear()
         stream = ResidualStream(self.embedding.forward(ctx))
         for i, entry in enumerate(self.spec.run_order):
             stream = self.layers[entry.layer].forward(stream, ctx, caches[i])

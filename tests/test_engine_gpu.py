@@ -131,3 +131,24 @@ def test_long_decoding_and_first_tokens(folder, dtype):
     assert (first - expect[:3]).abs().max().item() <= tol
     cache.release(rc)
     assert cache.is_idle()
+
+
+def test_a_graph_replays_rightly_after_later_captures_and_a_trimmed_allocator(folder):
+    """A capture empties the allocator's cache, and so may anyone: a graph captured earlier must
+    hold no address of memory that went back to the allocator (everything its pass allocated
+    comes from the graphs' own pool)."""
+    raw = folder["raw"]
+    llm = LLM(folder["path"], dtype="float32", kv_pool_tokens=1024, page_size=folder["page"], max_running=4,
+              chunked_prefill_size=24, cuda_graph=True)
+    first = _prompts(raw, [6, 11], 21)
+    lengths = [5, 14]  # two requests decode together, then one alone: the graphs for 2 rows and for 1
+    outs = llm.generate(first, [SamplingParams(max_new_tokens=n) for n in lengths])
+    assert len(llm.engine.graphs._graphs) >= 2
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    scribble = [torch.full((1 << 18,), float("nan"), device="cuda:0") for _ in range(8)]  # takes what was given back
+    second = _prompts(raw, [9, 4], 22)
+    outs += llm.generate(second, [SamplingParams(max_new_tokens=n) for n in lengths])  # the first graphs again
+    del scribble
+    for p, o, n in zip(first + second, outs, lengths * 2):
+        assert o == plain.generate(folder["cfg"], folder["w"], p, n)
