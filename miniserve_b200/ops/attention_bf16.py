@@ -119,6 +119,8 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
         counters = ctx.scratch.get("attn_counters")
         if counters is None or counters.numel() < rows * chunks:
             # tickets of the fused merge: zero before the first launch, left zero by every launch
+            if counters is not None:  # captured graphs may hold the smaller one's address: it stays alive
+                ctx.scratch.setdefault("retired", []).append(counters)
             counters = torch.zeros(max(4096, rows * chunks), dtype=torch.int32, device=q.device)
             ctx.scratch["attn_counters"] = counters
     _check(fns, fns["decode_fused"](
