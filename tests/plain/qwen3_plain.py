@@ -76,7 +76,17 @@ def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, dtype) ->
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).to(torch.float32) / head_dim))
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     ang = torch.cat((ang, ang), dim=-1)
-    return ang.cos().to(dtype), ang.sin().to(dtype)
+    # The cosine and sine of the float32 angle are taken by numpy in float64 and rounded to float32:
+    # the value an exact float32 cosine gives. torch's own float32 cosine on the CPU is within an
+    # ulp of it almost always, but its first call in a process was seen to return values off by
+    # 1.5e-4 at angles of tens of radians (about one process in fifty, on two machines), which
+    # moves logits by a thousand times the float32 tolerance of the tests.
+    import numpy as np
+
+    wide = ang.to(torch.float64).numpy()
+    cos = torch.from_numpy(np.cos(wide)).to(torch.float32)
+    sin = torch.from_numpy(np.sin(wide)).to(torch.float32)
+    return cos.to(dtype), sin.to(dtype)
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
