@@ -235,6 +235,141 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
   }
 }
 
+// The same product for an output with many more row tiles than the GPU holds CTAs (the head over
+// the vocabulary: 9,496 tiles): a CTA stages X once and walks the tiles blockIdx.x, + gridDim.x, ...
+// The weights of the next tile (or of the tile's next k group) are requested before the current
+// ones are multiplied, so a CTA always has a tile's rows in flight, and the staging of X and the
+// start of a CTA are paid once per CTA instead of once per tile. The sums are formed in the same
+// order as in gemm_skinny_kernel, so both kernels give the same bits.
+// MODE 0: bfloat16 out [M, N]; 1: float32 out [M, N].
+template <int MT, int MODE>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_stream_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
+                          int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int TOK = MT * 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int xs_stride = K + 32;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  // two areas for the warps' partial sums, taken in turn: a tile's sums are still being read while the next tile's are written
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)TOK * xs_stride * 2);
+  const int n_tiles = (N + SK_ROWS - 1) / SK_ROWS;
+  const int per_warp = ((K + SK_WARPS * 32 - 1) / (SK_WARPS * 32)) * 32;
+  const int wk_begin = warp * per_warp, wk_end = min(K, wk_begin + per_warp);
+
+  uint4 wa[SK_UNROLL], wb[SK_UNROLL];
+  auto fetch = [&](int tile, int k) {
+    const int n0 = tile * SK_ROWS;
+    const bool row_a = n0 + g < N, row_b = n0 + g + 8 < N;
+    const __nv_bfloat16* pa = W + (size_t)(n0 + (row_a ? g : 0)) * K + 8 * t;
+    const __nv_bfloat16* pb = W + (size_t)(n0 + (row_b ? g + 8 : 0)) * K + 8 * t;
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int kk = k + 32 * u;
+      const bool in = kk + 8 * t < wk_end;
+      wa[u] = (in && row_a) ? ldg_stream(pa + kk) : make_uint4(0u, 0u, 0u, 0u);
+      wb[u] = (in && row_b) ? ldg_stream(pb + kk) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  int tile = blockIdx.x;  // the grid never has more CTAs than there are tiles
+  pdl_launch_dependents();
+  fetch(tile, wk_begin);
+  pdl_wait();
+
+  const int chunks = K >> 3;
+  for (int idx = tid; idx < TOK * chunks; idx += SK_THREADS) {
+    const int row = idx / chunks, c = idx - row * chunks;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < M) v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + c * 8);
+    *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
+  }
+  __syncthreads();
+
+  int turn = 0;
+  for (; tile < n_tiles; tile += gridDim.x) {
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int k = wk_begin; k < wk_end; k += 32 * SK_UNROLL) {
+      uint4 ca[SK_UNROLL], cb[SK_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        ca[u] = wa[u];
+        cb[u] = wb[u];
+      }
+      if (k + 32 * SK_UNROLL < wk_end) {
+        fetch(tile, k + 32 * SK_UNROLL);
+      } else if (tile + (int)gridDim.x < n_tiles) {
+        fetch(tile + (int)gridDim.x, wk_begin);
+      }
+#pragma unroll
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        const int kk = k + 32 * u;
+        if (kk >= wk_end) break;
+        const bool in = kk + 8 * t < wk_end;
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+          if (in) xb = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * xs_stride + kk + 8 * t);
+          mma_bf16_16816(acc[j], ca[u].x, cb[u].x, ca[u].y, cb[u].y, xb.x, xb.y);
+          mma_bf16_16816(acc[j], ca[u].z, cb[u].z, ca[u].w, cb[u].w, xb.z, xb.w);
+        }
+      }
+    }
+    float* mine = red + (size_t)turn * SK_WARPS * SK_ROWS * TOK;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      float* base = mine + (size_t)warp * SK_ROWS * TOK;
+      base[g * TOK + 8 * j + 2 * t] = acc[j][0];
+      base[g * TOK + 8 * j + 2 * t + 1] = acc[j][1];
+      base[(g + 8) * TOK + 8 * j + 2 * t] = acc[j][2];
+      base[(g + 8) * TOK + 8 * j + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();  // also: everyone has finished reading the other area (the tile before)
+    const int n0 = tile * SK_ROWS;
+    for (int idx = tid; idx < SK_ROWS * TOK; idx += SK_THREADS) {
+      const int tok = idx / SK_ROWS, row = idx - tok * SK_ROWS;  // consecutive threads: consecutive n
+      if (tok >= M || n0 + row >= N) continue;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) s += mine[(size_t)w * SK_ROWS * TOK + row * TOK + tok];
+      const size_t o = (size_t)tok * N + n0 + row;
+      if (MODE == 0) {
+        reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(s);
+      } else {
+        reinterpret_cast<float*>(out)[o] = s;
+      }
+    }
+    turn ^= 1;
+  }
+}
+
+// Outputs with at least this many row tiles per SM go to the kernel that walks tiles.
+constexpr int SK_STREAM_TILES_PER_SM = 8;
+
+template <int MT, int MODE>
+static int launch_skinny_stream(void* out, const void* X, const void* W, int M, int N, int K, int sm_count, cudaStream_t stream) {
+  const size_t smem = (size_t)MT * 8 * (K + 32) * 2 + 2 * (size_t)SK_WARPS * SK_ROWS * MT * 8 * 4;
+  MS_CHECK_ARG(smem <= 200 * 1024, "gemm_skinny: K=%d needs %zu bytes of shared memory", K, smem);
+  auto kernel = gemm_skinny_stream_kernel<MT, MODE>;
+  static size_t configured = 0;
+  static int per_sm = 0;
+  if (smem > configured) {
+    if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+    per_sm = 0;
+  }
+  if (per_sm == 0) {
+    // CTAs that are resident together for the largest shared-memory size seen so far
+    MS_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SK_THREADS, configured));
+    MS_CHECK_ARG(per_sm > 0, "gemm_skinny: the kernel does not fit an SM with %zu bytes of shared memory", configured);
+  }
+  const long long tiles = ceil_div(N, SK_ROWS), resident = (long long)sm_count * per_sm;
+  MS_LAUNCH(kernel, (unsigned)(tiles < resident ? tiles : resident), SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X,
+            (const __nv_bfloat16*)W, M, N, K);
+  return 0;
+}
+
 template <int MT, int MODE, int PRO>
 static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, int splits, const SkinnyFused& fused,
                          cudaStream_t stream) {
@@ -282,12 +417,31 @@ static int check_skinny(const void* W, int M, int N, int K, int splits, int out_
                 : launch_skinny<1, 2, PRO>(out, X, W, M, N, K, splits, fused, stream);                        \
   } while (0)
 
+static int g_skinny_stream = 1;
+// Tuning and tests: 0 keeps outputs with very many row tiles on the kernel with one tile per CTA.
+MS_EXPORT void ms_gemm_skinny_set_stream(int on) { g_skinny_stream = on; }
+
 // out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
 MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,
                                   cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
   MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
+  if (splits == 1 && out_mode != 2) {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+      int dev = 0;
+      MS_CHECK_CUDA(cudaGetDevice(&dev));
+      MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (g_skinny_stream && ceil_div(N, SK_ROWS) >= (long long)SK_STREAM_TILES_PER_SM * sm_count) {
+      const bool wide = M > 8;
+      if (out_mode == 0) return wide ? launch_skinny_stream<2, 0>(out, X, W, M, N, K, sm_count, stream)
+                                     : launch_skinny_stream<1, 0>(out, X, W, M, N, K, sm_count, stream);
+      return wide ? launch_skinny_stream<2, 1>(out, X, W, M, N, K, sm_count, stream)
+                  : launch_skinny_stream<1, 1>(out, X, W, M, N, K, sm_count, stream);
+    }
+  }
   const SkinnyFused fused = {};
   MS_SK_DISPATCH(PRO_PLAIN);
 }

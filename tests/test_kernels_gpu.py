@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from miniserve_b200 import ops
-from miniserve_b200.ops import attention_bf16
+from miniserve_b200.ops import attention_bf16, native
 from tests.kernel_util import PagedBatch, make_context, reference_attention
 from tests.plain import qwen3_plain as plain
 
@@ -135,7 +135,8 @@ def test_bf16_linear_accumulates_in_float32():
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n, k", [(16, 32), (503, 96), (1000, 1024), (72, 3072), (151936, 64)])
+@pytest.mark.parametrize("n, k", [(16, 32), (503, 96), (1000, 1024), (72, 3072), (151936, 64), (40000, 1024), (33333, 264),
+                                  (20008, 3072)])
 def test_skinny_gemm_bf16(m, n, k):
     torch.manual_seed(m * 1000 + n)
     x = torch.randn(m, k, device=DEV).bfloat16()
@@ -155,6 +156,15 @@ def test_skinny_gemm_bf16(m, n, k):
     alone = torch.empty(1, n, device=DEV)
     ops.linear(x[m - 1:m].contiguous(), w, out=alone)
     assert torch.equal(alone[0], out32[m - 1])
+    # very wide outputs go to the kernel whose CTAs walk many row tiles: the same bits as one tile per CTA
+    k_lib = native.kernels()
+    k_lib.ms_gemm_skinny_set_stream(0)
+    try:
+        one_tile = torch.full((m, n), float("nan"), device=DEV)
+        ops.linear(x, w, out=one_tile)
+    finally:
+        k_lib.ms_gemm_skinny_set_stream(1)
+    assert torch.equal(one_tile, out32)
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
