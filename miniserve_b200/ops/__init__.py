@@ -276,13 +276,18 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     stages the whole of x, so with a long k the staging costs as much as the weights: measured on
     B200 against cuBLAS the kernel wins for k up to 3,072 at any n (3.0 against 5.4 us for 4096 x
     1024 at 8 rows, 4.5 against 9.1 us for 1024 x 3072) and for 4096 x 4096 up to 8 rows (7.8
-    against 12.4 us), and loses beyond (43 against 36 us for 24576 x 4096, twice that at 16 rows)."""
+    against 12.4 us), and loses beyond (43 against 36 us for 24576 x 4096, twice that at 16 rows).
+    Outputs with at least 8 row tiles of 16 per SM (the head over the vocabulary) run on CTAs that
+    stage x once and walk the tiles: up to 8 rows that wins for k up to 4,096 too (151,936 x 4,096:
+    187 against 208 us; x 2,048: 95 against 106; x 5,120: 292 against 255, so not beyond)."""
     m, k = x.shape
     n = weight.shape[0]
     if not (0 < m <= SKINNY_MAX_M and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
             and 16 * (k + 32) * 2 <= 200 * 1024):
         return False
-    return k <= 3072 or (k <= 4096 and n <= 4096 and m <= 8)
+    if k <= 3072:
+        return True
+    return k <= 4096 and m <= 8 and (n <= 4096 or n >= 8 * 16 * _sm_count(x.device))
 
 
 def skinny_splits(n: int, k: int, sm_count: int) -> int:
