@@ -346,6 +346,7 @@ gemm_skinny_stream_kernel(void* __restrict__ out, const __nv_bfloat16* __restric
 
 // Outputs with at least this many row tiles per SM go to the kernel that walks tiles.
 constexpr int SK_STREAM_TILES_PER_SM = 8;
+static int g_stream_mode = 1;  // 2 (measurements only): launched with the programmatic-dependent-launch attribute
 
 template <int MT, int MODE>
 static int launch_skinny_stream(void* out, const void* X, const void* W, int M, int N, int K, int sm_count, cudaStream_t stream) {
@@ -365,8 +366,18 @@ static int launch_skinny_stream(void* out, const void* X, const void* W, int M, 
     MS_CHECK_ARG(per_sm > 0, "gemm_skinny: the kernel does not fit an SM with %zu bytes of shared memory", configured);
   }
   const long long tiles = ceil_div(N, SK_ROWS), resident = (long long)sm_count * per_sm;
-  MS_LAUNCH(kernel, (unsigned)(tiles < resident ? tiles : resident), SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X,
-            (const __nv_bfloat16*)W, M, N, K);
+  // Launched without the programmatic-dependent-launch attribute (the kernel's griddepcontrol
+  // instructions then do nothing and it starts when the kernel before it has completed): its
+  // CTAs fill every SM's registers for the whole of its time, and when they became resident
+  // early, behind the last layers' kernels, the step was slower than with no overlap at all
+  // (a decode step of Qwen3-0.6B at batch 8: 1.359 ms with the attribute, 1.301 ms without,
+  // 1.329 ms with one row tile per CTA).
+  const int pdl_was = pdl_switch();
+  if (g_stream_mode != 2) pdl_switch() = 0;
+  const cudaError_t err = launch(kernel, dim3((unsigned)(tiles < resident ? tiles : resident)), dim3(SK_THREADS), smem, stream, out,
+                                (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K);
+  pdl_switch() = pdl_was;
+  MS_CHECK_CUDA(err);
   return 0;
 }
 
@@ -418,8 +429,9 @@ static int check_skinny(const void* W, int M, int N, int K, int splits, int out_
   } while (0)
 
 static int g_skinny_stream = 1;
-// Tuning and tests: 0 keeps outputs with very many row tiles on the kernel with one tile per CTA.
-MS_EXPORT void ms_gemm_skinny_set_stream(int on) { g_skinny_stream = on; }
+// Tuning and tests: 0 keeps outputs with very many row tiles on the kernel with one tile per CTA;
+// 2 launches the tile-walking kernel with the dependent-launch attribute (see launch_skinny_stream).
+MS_EXPORT void ms_gemm_skinny_set_stream(int on) { g_skinny_stream = on; ms::g_stream_mode = on; }
 
 // out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
 MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,

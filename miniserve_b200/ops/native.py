@@ -104,7 +104,8 @@ def kernels():
     import os
 
     # MINISERVE_SKINNY_STREAM=0: very wide outputs (the head) stay on the kernel with one row tile per CTA
-    lib.ms_gemm_skinny_set_stream(int(os.environ.get("MINISERVE_SKINNY_STREAM", "1") != "0"))
+    # (2: the tile-walking kernel with the dependent-launch attribute, for measurements)
+    lib.ms_gemm_skinny_set_stream(int(os.environ.get("MINISERVE_SKINNY_STREAM", "1")))
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
     _declare(lib, "ms_qk_norm_rope_kv",
