@@ -346,7 +346,7 @@ gemm_skinny_stream_kernel(void* __restrict__ out, const __nv_bfloat16* __restric
 
 // Outputs with at least this many row tiles per SM go to the kernel that walks tiles.
 constexpr int SK_STREAM_TILES_PER_SM = 8;
-static int g_stream_mode = 1;  // 2 (measurements only): launched with the programmatic-dependent-launch attribute
+static int g_stream_mode = 1;  // 0: off; 1: on; 2 (measurements only): on, launched with the programmatic-dependent-launch attribute
 
 template <int MT, int MODE>
 static int launch_skinny_stream(void* out, const void* X, const void* W, int M, int N, int K, int sm_count, cudaStream_t stream) {
@@ -428,10 +428,9 @@ static int check_skinny(const void* W, int M, int N, int K, int splits, int out_
                 : launch_skinny<1, 2, PRO>(out, X, W, M, N, K, splits, fused, stream);                        \
   } while (0)
 
-static int g_skinny_stream = 1;
 // Tuning and tests: 0 keeps outputs with very many row tiles on the kernel with one tile per CTA;
 // 2 launches the tile-walking kernel with the dependent-launch attribute (see launch_skinny_stream).
-MS_EXPORT void ms_gemm_skinny_set_stream(int on) { g_skinny_stream = on; ms::g_stream_mode = on; }
+MS_EXPORT void ms_gemm_skinny_set_stream(int mode) { ms::g_stream_mode = mode; }
 
 // out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
 MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,
@@ -446,7 +445,7 @@ MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M
       MS_CHECK_CUDA(cudaGetDevice(&dev));
       MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
     }
-    if (g_skinny_stream && ceil_div(N, SK_ROWS) >= (long long)SK_STREAM_TILES_PER_SM * sm_count) {
+    if (g_stream_mode != 0 && ceil_div(N, SK_ROWS) >= (long long)SK_STREAM_TILES_PER_SM * sm_count) {
       const bool wide = M > 8;
       if (out_mode == 0) return wide ? launch_skinny_stream<2, 0>(out, X, W, M, N, K, sm_count, stream)
                                      : launch_skinny_stream<1, 0>(out, X, W, M, N, K, sm_count, stream);
