@@ -216,14 +216,14 @@ def sample_token(logits: torch.Tensor, temperature: float, seed: int, counter: i
 
 
 def generate(cfg: dict, w: dict, prompt: list[int], max_new_tokens: int, temperature: float = 0.0,
-             seed: int = 0, stop: frozenset[int] = frozenset()) -> list[int]:
+             seed: int = 0, stop: frozenset[int] = frozenset(), top_p: float = 1.0) -> list[int]:
     """Recompute the whole sequence for every new token (no cache); the token sampled at
     index ``len(sequence)`` uses that index as the noise counter
     (miniserve/engine/sampler.py:73-76, miniserve/engine/request.py:151-155)."""
     seq, out = list(prompt), []
     for _ in range(max_new_tokens):
         logits = all_logits(cfg, w, seq)[-1]
-        tok = sample_token(logits, temperature, seed, len(seq))
+        tok = sample_token(logits, temperature, seed, len(seq), top_p)
         out.append(tok)
         seq.append(tok)
         if tok in stop:

@@ -152,3 +152,25 @@ def test_a_graph_replays_rightly_after_later_captures_and_a_trimmed_allocator(fo
     del scribble
     for p, o, n in zip(first + second, outs, lengths * 2):
         assert o == plain.generate(folder["cfg"], folder["w"], p, n)
+
+
+def test_graphs_captured_at_the_start_in_every_mode(folder):
+    """Every batch bucket in all three sampling modes captured before any request, one after the
+    other (each capture empties the allocator's cache under the ones before it), then generation."""
+    raw = folder["raw"]
+    llm = LLM(folder["path"], dtype="float32", kv_pool_tokens=1024, page_size=folder["page"], max_running=4,
+              chunked_prefill_size=24, cuda_graph=True)
+    captured = llm.engine.capture_graphs(("greedy", "temperature", "top_p"))
+    assert captured == 3 * len(llm.engine.graphs.buckets)
+    assert llm.engine.cache.is_idle()
+    prompts = _prompts(raw, [7, 19, 3], 31)
+    greedy = llm.generate(prompts, SamplingParams(max_new_tokens=9))
+    for p, o in zip(prompts, greedy):
+        assert o == plain.generate(folder["cfg"], folder["w"], p, 9)
+    sampled = llm.generate(prompts[:1], SamplingParams(9, temperature=0.8, seed=3))[0]
+    assert sampled == plain.generate(folder["cfg"], folder["w"], prompts[0], 9, temperature=0.8, seed=3)
+    nucleus = llm.generate(prompts[:1], SamplingParams(9, temperature=0.8, top_p=0.8, seed=3))[0]
+    eager = LLM(folder["path"], dtype="float32", kv_pool_tokens=1024, page_size=folder["page"], max_running=4,
+                chunked_prefill_size=24, cuda_graph=False)
+    assert nucleus == eager.generate(prompts[:1], SamplingParams(9, temperature=0.8, top_p=0.8, seed=3))[0]
+    assert len(llm.engine.graphs._graphs) == captured  # nothing was captured again
