@@ -18,7 +18,10 @@
 //    larger calls are refused with an error (return code 1, text from ..._last_error()) and
 //    nothing is launched. A call with splits == 1 needs no scratch at all.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-//    that device current) and remembers it. Make that first call outside any stream capture.
+//    that device current), sets the kernel's shared-memory attribute for that device and remembers
+//    both. Make that first call outside any stream capture, and from one thread: the tables that
+//    remember are filled without a lock, so the first call on a device must not run beside another
+//    call of this library; later calls may come from any thread.
 //  * The call allocates nothing: no cudaMalloc, cudaFree or allocating library routine.
 //  * All calls share the one array, and it keeps what the last call left. Nothing in it has to
 //    start at zero: every partial result that the merge reads was written by the same call

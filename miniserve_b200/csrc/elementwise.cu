@@ -24,13 +24,12 @@ __global__ void embed_gather_kernel(float* __restrict__ residual, const T* __res
 
 // ---------------------------------------------------------------- (add +) RMSNorm (+ gather)
 // For output row i: r = rows ? rows[i] : i.
-//   h = residual[r] (+ delta[r] if delta) (+ parts[0][r] + parts[1][r] + ... in that order)   float32
+//   h = residual[r] (+ delta[r] if delta)            float32
 //   if (write_residual) residual[r] = h              (only without a gather)
 //   out[i] = h / sqrt(mean(h^2) + eps) * w           rounded once to T
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __restrict__ residual_out, const T* __restrict__ delta,
-                   const float* __restrict__ parts, int num_parts, size_t part_stride,
+add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta,
                    const T* __restrict__ w, const int* __restrict__ rows, float eps, int hidden,
                    int write_residual) {
   extern __shared__ float row_buf[];  // hidden floats
@@ -44,7 +43,6 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __r
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     float h = res[c];
     if (dl) h += Elem<T>::load(dl + c);
-    for (int p = 0; p < num_parts; ++p) h += parts[p * part_stride + (size_t)r * hidden + c];
     row_buf[c] = h;
     ss += h * h;
   }
@@ -53,8 +51,7 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __r
   T* o = out + (size_t)i * hidden;
   for (int c = threadIdx.x; c < hidden; c += THREADS) {
     const float h = row_buf[c];
-    if (residual_out) residual_out[(size_t)r * hidden + c] = h;
-    else if (write_residual && (dl || num_parts)) res[c] = h;
+    if (write_residual && dl) res[c] = h;
     Elem<T>::store(o + c, (h * inv) * Elem<T>::load(w + c));
   }
 }
@@ -64,10 +61,9 @@ add_rmsnorm_kernel(T* __restrict__ out, float* __restrict__ residual, float* __r
 // a row is at most 8 * THREADS wide, else in shared memory.
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
-add_rmsnorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual, float* __restrict__ residual_out,
-                          const __nv_bfloat16* __restrict__ delta, const float* __restrict__ parts, int num_parts,
-                          size_t part_stride, const __nv_bfloat16* __restrict__ w, const int* __restrict__ rows, float eps,
-                          int hidden, int write_residual) {
+add_rmsnorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual,
+                          const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ w,
+                          const int* __restrict__ rows, float eps, int hidden, int write_residual) {
   extern __shared__ float row_buf[];  // hidden floats, used only by rows wider than 8 * THREADS
   __shared__ float red[32];
   pdl_prologue();
@@ -88,11 +84,6 @@ add_rmsnorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ r
 #pragma unroll
       for (int e = 0; e < 8; ++e) h[e] += d[e];
     }
-    for (int p = 0; p < num_parts; ++p) {
-      const float* src = parts + p * part_stride + (size_t)r * hidden + 8 * c;
-      const float4 pa = *reinterpret_cast<const float4*>(src), pb = *reinterpret_cast<const float4*>(src + 4);
-      h[0] += pa.x; h[1] += pa.y; h[2] += pa.z; h[3] += pa.w; h[4] += pb.x; h[5] += pb.y; h[6] += pb.z; h[7] += pb.w;
-    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += h[e] * h[e];
     if (!in_regs) {
@@ -103,8 +94,8 @@ add_rmsnorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ r
   const float total = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   __nv_bfloat16* o = out + (size_t)i * hidden;
-  const bool store_sum = residual_out != nullptr || (write_residual && (dl || num_parts));
-  float* sum_to = residual_out ? residual_out + (size_t)r * hidden : res;
+  const bool store_sum = write_residual && dl;
+  float* sum_to = res;
   for (int c = threadIdx.x; c < chunks; c += THREADS) {
     if (!in_regs) {
       const float4 a = *reinterpret_cast<const float4*>(row_buf + 8 * c), b = *reinterpret_cast<const float4*>(row_buf + 8 * c + 4);
@@ -201,38 +192,34 @@ MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* 
   return 0;
 }
 
-// delta: an addend in the activation dtype, or null. parts: float32 partial sums
-// [num_parts][..][hidden] that are `part_stride` floats apart (the split-K output of the skinny
-// matrix product), or null. Both are added to the residual before the norm.
-// residual_out: if given, the sum goes there and `residual_f32` is left as it was.
-MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, void* residual_out, const void* delta, const float* parts, int num_parts,
-                             long long part_stride, const void* weight, const int* rows,
+// delta: an addend in the activation dtype, or null; it is added to the residual before the norm.
+MS_EXPORT int ms_add_rmsnorm(void* out, void* residual_f32, const void* delta, const void* weight, const int* rows,
                              float eps, int num_out_rows, int hidden, int write_residual, int dtype,
                              cudaStream_t stream) {
   if (num_out_rows == 0) return 0;
   MS_CHECK_ARG(num_out_rows > 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d H=%d", num_out_rows, hidden);
-  MS_CHECK_ARG(!(rows && (write_residual || residual_out)), "add_rmsnorm: a gathered norm cannot write the residual back");
+  MS_CHECK_ARG(!(rows && write_residual), "add_rmsnorm: a gathered norm cannot write the residual back");
   const size_t smem = (size_t)hidden * sizeof(float);
   MS_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", hidden, smem);
   constexpr int THREADS = 256;
   if (dtype == MS_F32) {
     auto k = add_rmsnorm_kernel<float, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (float*)residual_out, (const float*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const float*)weight, rows, eps, hidden, write_residual);
-  } else if (hidden % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual_f32 % 16 == 0) && ((uintptr_t)residual_out % 16 == 0) &&
-             ((uintptr_t)delta % 16 == 0) && ((uintptr_t)parts % 16 == 0) && (part_stride % 4 == 0) && ((uintptr_t)weight % 16 == 0)) {
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (float*)out, (float*)residual_f32, (const float*)delta, (const float*)weight, rows, eps, hidden, write_residual);
+  } else if (hidden % 8 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual_f32 % 16 == 0) &&
+             ((uintptr_t)delta % 16 == 0) && ((uintptr_t)weight % 16 == 0)) {
     if (hidden <= 8 * 128) {
-      MS_LAUNCH((add_rmsnorm_bf16x8_kernel<128>), num_out_rows, 128, 0, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+      MS_LAUNCH((add_rmsnorm_bf16x8_kernel<128>), num_out_rows, 128, 0, stream, (__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
     } else {
       auto k = add_rmsnorm_bf16x8_kernel<256>;
       const size_t need = hidden <= 8 * 256 ? 0 : smem;
       if (need > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
-      MS_LAUNCH(k, num_out_rows, 256, need, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+      MS_LAUNCH(k, num_out_rows, 256, need, stream, (__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
     }
   } else {
     auto k = add_rmsnorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (__nv_bfloat16*)out, (float*)residual_f32, (float*)residual_out, (const __nv_bfloat16*)delta, parts, parts ? num_parts : 0, (size_t)part_stride, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
+    MS_LAUNCH(k, num_out_rows, THREADS, smem, stream, (__nv_bfloat16*)out, (float*)residual_f32, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, rows, eps, hidden, write_residual);
   }
   return 0;
 }

@@ -6,9 +6,7 @@
 // eight warps streams its part of that slice straight from global memory into tensor-core
 // fragments with 16-byte loads (eight in flight per lane), multiplies it with the matching
 // activations from shared memory, and the warps' partial sums are added in shared memory in a
-// fixed order. With `splits` > 1 the K dimension is also cut across CTAs and each split writes
-// float32 partial sums [splits, M, N]; the consumer (the fused residual-add + RMSNorm kernel) adds
-// them, so narrow outputs (N = hidden) still fill the machine without atomics.
+// fixed order.
 // Stands where the reference's decode step calls F.linear (miniserve/model/qwen3.py:115-131,186).
 #include "common.cuh"
 
@@ -31,39 +29,20 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
-// What the kernel does while it stages its activations (the weights are already in flight):
-//   PRO_PLAIN  X is bf16 [M, K], copied as it is;
-//   PRO_NORM   X = rmsnorm(res_in + delta) * norm_w, the fused residual-add + RMSNorm
-//              (miniserve/model/fused.py:170,192: fused_add_rmsnorm): every CTA recomputes the M rows
-//              (a few KB), the first CTA also stores the sum to res_out (a buffer other than res_in,
-//              since other CTAs still read res_in);
-//   PRO_SILU   X = silu(gate) * up of a stacked [M, 2K] gate|up tensor (miniserve/model/qwen3.py:128-131).
-enum SkinnyPrologue : int { PRO_PLAIN = 0, PRO_NORM = 1, PRO_SILU = 2 };
-
-struct SkinnyFused {
-  const float* res_in;           // PRO_NORM: [M, K] float32
-  const __nv_bfloat16* delta;    // PRO_NORM: [M, K] addend or null
-  float* res_out;                // PRO_NORM: [M, K] receives res_in + delta (may be null: not stored)
-  const __nv_bfloat16* norm_w;   // PRO_NORM: [K]
-  float eps;
-};
-
-
-// MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: float32 partials [splits, M, N];
+// MODE 0: bf16 out [M, N]; 1: float32 out [M, N];
 // MODE 3: W is a stacked gate|up weight [2N, K] and out [M, N] = silu(x Wg^T) * (x Wu^T) in bf16
 // (miniserve/model/qwen3.py:128-131): the CTA takes 8 gate rows as the lower half of its fragments
 // and the 8 up rows that belong to them as the upper half, so both factors of an output meet in it.
 // Both products are rounded to bfloat16 before the activation, as when they are stored in between.
-template <int MT, int MODE, int PRO>
+template <int MT, int MODE>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
-                   int M, int N, int K, int k_per_split, SkinnyFused fused) {
+                   int M, int N, int K) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * (MODE == 3 ? 8 : SK_ROWS);
-  const int k_begin = blockIdx.y * k_per_split, k_end = min(K, k_begin + k_per_split);
-  const int k_len = k_end - k_begin;
-  const int xs_stride = k_per_split + 32;  // bf16 elements: rows 64 bytes apart modulo 128, so 16-byte reads of two rows do not collide
+  const int k_begin = 0, k_len = K;
+  const int xs_stride = K + 32;  // bf16 elements: rows 64 bytes apart modulo 128, so 16-byte reads of two rows do not collide
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
 
   // this warp's part of the slice, in chunks of 32 k (8 per lane of a quad)
@@ -99,68 +78,11 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
 
   // activations of this K slice: [MT * 8][k_len], rows past M are zero
   const int chunks = k_len >> 3;
-  if (PRO == PRO_NORM) {
-    // one warp per row (rows warp, warp + 8); K is whole here (no split)
-    for (int row = warp; row < MT * 8; row += SK_WARPS) {
-      if (row >= M) {
-        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-        continue;
-      }
-      const float* rin = fused.res_in + (size_t)row * K;
-      const __nv_bfloat16* dl = fused.delta ? fused.delta + (size_t)row * K : nullptr;
-      float ss = 0.f;
-      for (int c = lane; c < chunks; c += 32) {
-        float h[8], d[8];
-        *reinterpret_cast<float4*>(h) = *reinterpret_cast<const float4*>(rin + c * 8);
-        *reinterpret_cast<float4*>(h + 4) = *reinterpret_cast<const float4*>(rin + c * 8 + 4);
-        if (dl) {
-          bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + c * 8), d);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) h[i] += d[i];
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss += h[i] * h[i];
-        if (blockIdx.x == 0 && fused.res_out) {
-          *reinterpret_cast<float4*>(fused.res_out + (size_t)row * K + c * 8) = *reinterpret_cast<float4*>(h);
-          *reinterpret_cast<float4*>(fused.res_out + (size_t)row * K + c * 8 + 4) = *reinterpret_cast<float4*>(h + 4);
-        }
-      }
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)K + fused.eps);
-      for (int c = lane; c < chunks; c += 32) {
-        float h[8], d[8], wv[8];
-        *reinterpret_cast<float4*>(h) = *reinterpret_cast<const float4*>(rin + c * 8);
-        *reinterpret_cast<float4*>(h + 4) = *reinterpret_cast<const float4*>(rin + c * 8 + 4);
-        if (dl) {
-          bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + c * 8), d);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) h[i] += d[i];
-        }
-        bf16x8_to_float(*reinterpret_cast<const uint4*>(fused.norm_w + c * 8), wv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = (h[i] * inv) * wv[i];
-        *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = float_to_bf16x8(h);
-      }
-    }
-  } else {
-    for (int idx = tid; idx < MT * 8 * chunks; idx += SK_THREADS) {
-      const int row = idx / chunks, c = idx - row * chunks;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row < M) {
-        if (PRO == PRO_SILU) {
-          // X is the stacked gate|up tensor [M, 2K]: silu(gate) * up in float32, rounded once
-          float gt[8], up[8];
-          bf16x8_to_float(*reinterpret_cast<const uint4*>(X + (size_t)row * 2 * K + k_begin + c * 8), gt);
-          bf16x8_to_float(*reinterpret_cast<const uint4*>(X + (size_t)row * 2 * K + K + k_begin + c * 8), up);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) gt[i] = gt[i] / (1.0f + expf(-gt[i])) * up[i];
-          v = float_to_bf16x8(gt);
-        } else {
-          v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + k_begin + c * 8);
-        }
-      }
-      *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
-    }
+  for (int idx = tid; idx < MT * 8 * chunks; idx += SK_THREADS) {
+    const int row = idx / chunks, c = idx - row * chunks;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < M) v = *reinterpret_cast<const uint4*>(X + (size_t)row * K + c * 8);
+    *reinterpret_cast<uint4*>(xs + row * xs_stride + c * 8) = v;
   }
   __syncthreads();
 
@@ -227,10 +149,8 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
     const size_t o = (size_t)tok * N + n0 + row;
     if (MODE == 0) {
       reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(s);
-    } else if (MODE == 1) {
-      reinterpret_cast<float*>(out)[o] = s;
     } else {
-      reinterpret_cast<float*>(out)[(size_t)blockIdx.y * M * N + o] = s;
+      reinterpret_cast<float*>(out)[o] = s;
     }
   }
 }
@@ -346,7 +266,7 @@ gemm_skinny_stream_kernel(void* __restrict__ out, const __nv_bfloat16* __restric
 
 // Outputs with at least this many row tiles per SM go to the kernel that walks tiles.
 constexpr int SK_STREAM_TILES_PER_SM = 8;
-static int g_stream_mode = 1;  // 0: off; 1: on; 2 (measurements only): on, launched with the programmatic-dependent-launch attribute
+static int g_stream_mode = 1;  // 0: off (one row tile per CTA); 1: on
 
 template <int MT, int MODE>
 static int launch_skinny_stream(void* out, const void* X, const void* W, int M, int N, int K, int sm_count, cudaStream_t stream) {
@@ -373,7 +293,7 @@ static int launch_skinny_stream(void* out, const void* X, const void* W, int M, 
   // (a decode step of Qwen3-0.6B at batch 8: 1.359 ms with the attribute, 1.301 ms without,
   // 1.329 ms with one row tile per CTA).
   const int pdl_was = pdl_switch();
-  if (g_stream_mode != 2) pdl_switch() = 0;
+  pdl_switch() = 0;
   const cudaError_t err = launch(kernel, dim3((unsigned)(tiles < resident ? tiles : resident)), dim3(SK_THREADS), smem, stream, out,
                                 (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K);
   pdl_switch() = pdl_was;
@@ -381,25 +301,20 @@ static int launch_skinny_stream(void* out, const void* X, const void* W, int M, 
   return 0;
 }
 
-template <int MT, int MODE, int PRO>
-static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, int splits, const SkinnyFused& fused,
-                         cudaStream_t stream) {
-  // whole multiples of 8 warps x 32 k per split keep every warp's range aligned
-  int k_per_split = ceil_div(ceil_div(K, splits), 32) * 32;
-  const int used_splits = ceil_div(K, k_per_split);
-  MS_CHECK_ARG(used_splits == splits, "gemm_skinny: %d splits leave some without work (K=%d)", splits, K);
-  const size_t smem_x = (size_t)MT * 8 * (k_per_split + 32) * 2;
+template <int MT, int MODE>
+static int launch_skinny(void* out, const void* X, const void* W, int M, int N, int K, cudaStream_t stream) {
+  const size_t smem_x = (size_t)MT * 8 * (K + 32) * 2;
   const size_t smem_red = (size_t)SK_WARPS * SK_ROWS * MT * 8 * 4;
   const size_t smem = smem_x > smem_red ? smem_x : smem_red;
-  MS_CHECK_ARG(smem <= 200 * 1024, "gemm_skinny: K slice of %d needs %zu bytes of shared memory", k_per_split, smem);
-  auto kernel = gemm_skinny_kernel<MT, MODE, PRO>;
+  MS_CHECK_ARG(smem <= 200 * 1024, "gemm_skinny: K=%d needs %zu bytes of shared memory", K, smem);
+  auto kernel = gemm_skinny_kernel<MT, MODE>;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(ceil_div(N, MODE == 3 ? 8 : SK_ROWS), splits);
-  MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, k_per_split, fused);
+  dim3 grid(ceil_div(N, MODE == 3 ? 8 : SK_ROWS));
+  MS_LAUNCH(kernel, grid, SK_THREADS, smem, stream, out, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K);
   return 0;
 }
 
@@ -407,89 +322,45 @@ static int launch_skinny(void* out, const void* X, const void* W, int M, int N, 
 
 using namespace ms;
 
-static int check_skinny(const void* W, int M, int N, int K, int splits, int out_mode) {
+static int check_skinny(const void* W, int M, int N, int K, int out_mode) {
   MS_CHECK_ARG(M > 0 && M <= 16, "gemm_skinny: M=%d is outside 1..16", M);
   MS_CHECK_ARG(K > 0 && K % 8 == 0, "gemm_skinny: K=%d must be a multiple of 8", K);
   MS_CHECK_ARG((uintptr_t)W % 16 == 0, "gemm_skinny: the weight must be 16-byte aligned");
-  MS_CHECK_ARG(splits >= 1 && (splits == 1 || out_mode == 2), "gemm_skinny: only partial sums can be split over K");
-  MS_CHECK_ARG(out_mode >= 0 && out_mode <= 2, "gemm_skinny: bad output mode %d", out_mode);
-  MS_CHECK_ARG(ceil_div(N, SK_ROWS) <= 2147483647 && splits <= 65535, "gemm_skinny: grid too large");
+  MS_CHECK_ARG(out_mode == 0 || out_mode == 1, "gemm_skinny: bad output mode %d", out_mode);
+  MS_CHECK_ARG(ceil_div(N, SK_ROWS) <= 2147483647, "gemm_skinny: grid too large");
   return 0;
 }
 
-#define MS_SK_DISPATCH(PRO)                                                                                   \
-  do {                                                                                                        \
-    const bool wide = M > 8;                                                                                  \
-    if (out_mode == 0) return wide ? launch_skinny<2, 0, PRO>(out, X, W, M, N, K, splits, fused, stream)      \
-                                   : launch_skinny<1, 0, PRO>(out, X, W, M, N, K, splits, fused, stream);     \
-    if (out_mode == 1) return wide ? launch_skinny<2, 1, PRO>(out, X, W, M, N, K, splits, fused, stream)      \
-                                   : launch_skinny<1, 1, PRO>(out, X, W, M, N, K, splits, fused, stream);     \
-    return wide ? launch_skinny<2, 2, PRO>(out, X, W, M, N, K, splits, fused, stream)                         \
-                : launch_skinny<1, 2, PRO>(out, X, W, M, N, K, splits, fused, stream);                        \
-  } while (0)
-
-// Tuning and tests: 0 keeps outputs with very many row tiles on the kernel with one tile per CTA;
-// 2 launches the tile-walking kernel with the dependent-launch attribute (see launch_skinny_stream).
+// 0 keeps outputs with very many row tiles on the kernel with one tile per CTA (tests compare the two).
 MS_EXPORT void ms_gemm_skinny_set_stream(int mode) { ms::g_stream_mode = mode; }
 
-// out_mode 0: bfloat16 [M, N]; 1: float32 [M, N]; 2: float32 partials [splits, M, N].
-MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int splits, int out_mode,
+// out_mode 0: bfloat16 [M, N]; 1: float32 [M, N].
+MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M, int N, int K, int out_mode,
                                   cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
+  if (int rc = check_skinny(W, M, N, K, out_mode)) return rc;
   MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
-  if (splits == 1 && out_mode != 2) {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-      int dev = 0;
-      MS_CHECK_CUDA(cudaGetDevice(&dev));
-      MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-    }
-    if (g_stream_mode != 0 && ceil_div(N, SK_ROWS) >= (long long)SK_STREAM_TILES_PER_SM * sm_count) {
-      const bool wide = M > 8;
-      if (out_mode == 0) return wide ? launch_skinny_stream<2, 0>(out, X, W, M, N, K, sm_count, stream)
-                                     : launch_skinny_stream<1, 0>(out, X, W, M, N, K, sm_count, stream);
-      return wide ? launch_skinny_stream<2, 1>(out, X, W, M, N, K, sm_count, stream)
-                  : launch_skinny_stream<1, 1>(out, X, W, M, N, K, sm_count, stream);
-    }
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const SkinnyFused fused = {};
-  MS_SK_DISPATCH(PRO_PLAIN);
+  const bool wide = M > 8;
+  if (g_stream_mode != 0 && ceil_div(N, SK_ROWS) >= (long long)SK_STREAM_TILES_PER_SM * sm_count) {
+    if (out_mode == 0) return wide ? launch_skinny_stream<2, 0>(out, X, W, M, N, K, sm_count, stream)
+                                   : launch_skinny_stream<1, 0>(out, X, W, M, N, K, sm_count, stream);
+    return wide ? launch_skinny_stream<2, 1>(out, X, W, M, N, K, sm_count, stream)
+                : launch_skinny_stream<1, 1>(out, X, W, M, N, K, sm_count, stream);
+  }
+  if (out_mode == 0) return wide ? launch_skinny<2, 0>(out, X, W, M, N, K, stream) : launch_skinny<1, 0>(out, X, W, M, N, K, stream);
+  return wide ? launch_skinny<2, 1>(out, X, W, M, N, K, stream) : launch_skinny<1, 1>(out, X, W, M, N, K, stream);
 }
 
 // out [M, N] bfloat16 = silu(X Wg^T) * (X Wu^T) for the stacked weight W = [Wg; Wu] of 2N rows.
 MS_EXPORT int ms_gemm_skinny_gate_up_bf16(void* out, const void* X, const void* W, int M, int N, int K, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  if (int rc = check_skinny(W, M, N, K, 1, 0)) return rc;
+  if (int rc = check_skinny(W, M, N, K, 0)) return rc;
   MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
-  const SkinnyFused fused = {};
-  return M > 8 ? launch_skinny<2, 3, PRO_PLAIN>(out, X, W, M, N, K, 1, fused, stream)
-               : launch_skinny<1, 3, PRO_PLAIN>(out, X, W, M, N, K, 1, fused, stream);
-}
-
-// out = rmsnorm(res_in + delta) * norm_w times W^T; res_out (a buffer other than res_in, or null)
-// receives res_in + delta. delta may be null.
-MS_EXPORT int ms_gemm_skinny_norm_bf16(void* out, const float* res_in, const void* delta, float* res_out, const void* norm_w,
-                                       float eps, const void* W, int M, int N, int K, int out_mode, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-  const int splits = 1;
-  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
-  MS_CHECK_ARG(out_mode != 2, "gemm_skinny: the fused norm needs the whole K in one CTA (no partial sums)");
-  MS_CHECK_ARG(res_in != nullptr && norm_w != nullptr && res_out != res_in, "gemm_skinny: the fused norm needs res_in, norm_w and a separate res_out");
-  MS_CHECK_ARG(((uintptr_t)res_in % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)res_out % 16 == 0) && ((uintptr_t)norm_w % 16 == 0),
-               "gemm_skinny: fused-norm operands must be 16-byte aligned");
-  const void* X = nullptr;
-  const SkinnyFused fused = {res_in, (const __nv_bfloat16*)delta, res_out, (const __nv_bfloat16*)norm_w, eps};
-  MS_SK_DISPATCH(PRO_NORM);
-}
-
-// out = (silu(gate_up[:, :K]) * gate_up[:, K:]) times W^T for gate_up [M, 2K].
-MS_EXPORT int ms_gemm_skinny_silu_bf16(void* out, const void* gate_up, const void* W, int M, int N, int K, int splits,
-                                       int out_mode, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-  if (int rc = check_skinny(W, M, N, K, splits, out_mode)) return rc;
-  MS_CHECK_ARG((uintptr_t)gate_up % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
-  const void* X = gate_up;
-  const SkinnyFused fused = {};
-  MS_SK_DISPATCH(PRO_SILU);
+  return M > 8 ? launch_skinny<2, 3>(out, X, W, M, N, K, stream) : launch_skinny<1, 3>(out, X, W, M, N, K, stream);
 }

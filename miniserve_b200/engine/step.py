@@ -215,7 +215,10 @@ class StepFunction:
             host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [1] * pad_rows,
             host_state_slot=slots.tolist() + [-1] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
-            decode_only=bool((q_len == 1).all()), leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
+            decode_only=bool((q_len == 1).all()),
+            logit_rows_in_order=(len(want) == int(q_len.sum()) and want == list(range(len(want)))
+                                 and (pad_rows == 0 or want_pad_rows)),
+            leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel flagged inconsistent input (a page that was given

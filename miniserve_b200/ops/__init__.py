@@ -15,8 +15,9 @@ from . import blas, native
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
-    "NativeError", "OutOfBlocks", "PartialSums", "LazyNorm", "LazyAct", "materialize", "fusable_rows", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul", "silu_mul_is_fused", "qkv_fused_ok", "qkv_norm_rope_kv",
-    "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
+    "NativeError", "OutOfBlocks", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul",
+    "silu_mul_is_fused", "qkv_fused_ok", "qkv_norm_rope_kv", "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table",
+    "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -59,83 +60,12 @@ def embed_gather(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
                                           dtype_code(table.dtype), _stream(stream)))
 
 
-class PartialSums:
-    """The output of a matrix product whose K dimension was cut across CTAs: float32 partial
-    sums ``parts`` [splits, M, N] that the consumer adds up (the fused add + RMSNorm kernel takes
-    them as they are)."""
-
-    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
-        self.parts = parts
-        self.dtype = dtype  # the activation dtype the sum stands for
-
-    @property
-    def shape(self):
-        return self.parts.shape[1:]
-
-    def float(self) -> torch.Tensor:
-        return self.parts.sum(dim=0)
-
-    def materialize(self) -> torch.Tensor:
-        return self.parts.sum(dim=0).to(self.dtype)
-
-
-class LazyNorm:
-    """A residual-add + RMSNorm that has not run yet: ``rmsnorm(residual_in + delta) * weight``, with
-    the sum going to ``residual_out``. ``linear`` fuses it into the weight-streaming product of a
-    decode step (the norm is recomputed while the weights are in flight); ``materialize`` runs it
-    as a kernel of its own for any other consumer."""
-
-    def __init__(self, residual_in: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, stream=None):
-        self.residual_in, self.delta, self.weight, self.eps, self.stream = residual_in, delta, weight, eps, stream
-        self.residual_out = torch.empty_like(residual_in)
-        self.shape = residual_in.shape
-        self.dtype = weight.dtype
-        self.device = residual_in.device
-        self._value: torch.Tensor | None = None
-
-    def materialize(self) -> torch.Tensor:
-        if self._value is None:
-            out = torch.empty(self.residual_in.shape, dtype=self.weight.dtype, device=self.residual_in.device)
-            add_rmsnorm(out, self.residual_in, self.delta, self.weight, self.eps, stream=self.stream,
-                        residual_out=self.residual_out)
-            self._value = out
-        return self._value
-
-
-class LazyAct:
-    """silu(gate) * up of a stacked [M, 2I] tensor that has not run yet; ``linear`` fuses it into
-    the staging of the product that consumes it."""
-
-    def __init__(self, gate_up: torch.Tensor, stream=None):
-        self.gate_up, self.stream = gate_up, stream
-        self.shape = (gate_up.shape[0], gate_up.shape[1] // 2)
-        self.dtype = gate_up.dtype
-        self.device = gate_up.device
-
-    def materialize(self) -> torch.Tensor:
-        out = torch.empty(self.shape, dtype=self.gate_up.dtype, device=self.gate_up.device)
-        silu_mul(out, self.gate_up, stream=self.stream)
-        return out
-
-
-def materialize(x):
-    """The tensor behind a lazy or partial result (a plain tensor is returned as it is)."""
-    return x.materialize() if isinstance(x, (LazyNorm, LazyAct, PartialSums)) else x
-
-
 def _flag(name: str, default: str) -> bool:
     import os
 
     return os.environ.get(name, default) == "1"
 
 
-# Decode-step fusions the parts may ask for. All three are built and tested, and all three are off
-# by default: measured on B200 (Qwen3-0.6B shapes, batch 8, CUDA graph with programmatic dependent
-# launch) a step took 1.47 ms with none of them, 1.53 ms with split-K partial sums, 1.56 ms with the
-# SiLU prologue as well, and 1.85 ms with the norm prologue: once a kernel's launch overlaps its
-# predecessor and weights are prefetched before the wait, a separate small kernel costs less than
-# the serial work a prologue adds to every CTA of the product.
-FUSE_NORM = _flag("MINISERVE_FUSE_NORM", "0")      # norm inside the next product's prologue
 def _setting(name: str, default: str) -> str:
     import os
 
@@ -145,26 +75,15 @@ def _setting(name: str, default: str) -> str:
 TC_GEMM = _setting("MINISERVE_TC_GEMM", "auto")   # products with more than 16 rows on the tcgen05 kernels: auto, 1 or 0
 QKV_EPILOGUE = _flag("MINISERVE_QKV_EPILOGUE", "1")  # q/k norm, rotation and cache write in the q|k|v product's epilogue
 TC_ATTENTION = _flag("MINISERVE_TC_ATTENTION", "1")  # prompts on the tcgen05 attention kernel (head size 128)
-FUSE_SILU = _flag("MINISERVE_FUSE_SILU", "0")      # SiLU * up inside the down projection's prologue
-SPLIT_K_PARTIALS = _flag("MINISERVE_SPLIT_K", "0")  # narrow products hand float32 partial sums to the norm
+DECODE_CHAIN = _flag("MINISERVE_DECODE_CHAIN", "1")  # decode steps of up to 16 requests as chains of products in persistent kernels
 
 
-def fusable_rows(num_rows: int, width: int, dtype: torch.dtype) -> bool:
-    """Whether a norm or activation of this shape can ride in the decode product's prologue."""
-    return dtype == torch.bfloat16 and 0 < num_rows <= SKINNY_MAX_M and width % 8 == 0 and 16 * (width + 32) * 2 <= 200 * 1024
-
-
-def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: "torch.Tensor | PartialSums | None",
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None,
                 weight: torch.Tensor, eps: float, rows: torch.Tensor | None = None, num_rows: int | None = None,
-                write_residual: bool = True, stream=None, residual_out: torch.Tensor | None = None) -> None:
+                write_residual: bool = True, stream=None) -> None:
     """out[i] = rmsnorm(residual[r] + delta[r]) * weight with r = rows[i] (or i); the sum is
-    written back to ``residual`` when there is no gather. Statistics in float32. ``delta`` may be
-    a tensor in the activation dtype or the float32 partial sums of a split matrix product."""
-    parts = None
-    if isinstance(delta, PartialSums):
-        parts, delta = delta.parts, None
-        assert parts.dtype == torch.float32 and parts.is_contiguous() and parts.shape[-1] == residual.shape[-1]
-    _check_dev(out, residual, delta, weight, rows, parts)
+    written back to ``residual`` when there is no gather. Statistics in float32."""
+    _check_dev(out, residual, delta, weight, rows)
     assert residual.dtype == torch.float32 and out.dtype == weight.dtype
     assert delta is None or delta.dtype == out.dtype
     hidden = residual.shape[-1]
@@ -173,10 +92,7 @@ def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: "torch.Tensor 
     if rows is None:
         assert residual.shape[0] >= n
     k = native.kernels()
-    native.kernel_check(k.ms_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(residual_out), _ptr(delta), _ptr(parts),
-                                         0 if parts is None else parts.shape[0],
-                                         0 if parts is None else parts.shape[1] * parts.shape[2],
-                                         _ptr(weight), _ptr(rows),
+    native.kernel_check(k.ms_add_rmsnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(rows),
                                          float(eps), n, hidden, int(write_residual and rows is None),
                                          dtype_code(out.dtype), _stream(stream)))
 
@@ -290,31 +206,15 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return k <= 4096 and m <= 8 and (n <= 4096 or n >= 8 * 16 * _sm_count(x.device))
 
 
-def skinny_splits(n: int, k: int, sm_count: int) -> int:
-    """K splits for a narrow output: enough CTAs (16 rows of W each) for two per SM, every split
-    at least 256 wide and all of them non-empty."""
-    tiles = -(-n // 16)
-    want = max(1, min(-(-2 * sm_count // tiles), k // 256))
-    while want > 1:
-        per = -(-(-(-k // want)) // 32) * 32
-        if -(-k // per) == want:
-            break
-        want -= 1
-    return want
-
-
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None,
-           partials: bool = False) -> "torch.Tensor | PartialSums":
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """x [M, K] times weight[N, K]^T -> [M, N].
 
     float32: this package's FFMA kernel (true 32-bit, fixed summation order per element).
-    bfloat16 with at most 16 rows (decode steps): this package's weight-streaming kernel; with
-    ``partials`` the result may come back as float32 ``PartialSums`` for a fused consumer.
-    bfloat16 otherwise: the vendor library's matrix product with float32 accumulation. ``out``
-    may be float32 (logits) or bfloat16.
+    bfloat16 with at most 16 rows (decode steps): this package's weight-streaming kernel.
+    bfloat16 otherwise: this package's tcgen05 kernel where it is the faster choice
+    (``tc_gemm_ok``), else the vendor library's matrix product with float32 accumulation.
+    ``out`` may be float32 (logits) or bfloat16.
     """
-    if isinstance(x, (LazyNorm, LazyAct)):
-        return _linear_fused(x, weight, out, stream, partials)
     _check_dev(x, weight, out)
     m, kdim = x.shape
     n = weight.shape[0]
@@ -330,17 +230,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
     if _skinny_ok(x, weight):
         k = native.kernels()
-        if partials and out is None:
-            splits = skinny_splits(n, kdim, _sm_count(x.device))
-            if splits > 1:
-                parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-                native.kernel_check(k.ms_gemm_skinny_bf16(_ptr(parts), _ptr(x), _ptr(weight), m, n, kdim, splits, 2,
-                                                          _stream(stream)))
-                return PartialSums(parts, torch.bfloat16)
         if out is None:
             out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
         assert out.shape == (m, n)
-        native.kernel_check(k.ms_gemm_skinny_bf16(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, 1,
+        native.kernel_check(k.ms_gemm_skinny_bf16(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim,
                                                   1 if out.dtype == torch.float32 else 0, _stream(stream)))
         return out
     if out is None:
@@ -377,37 +270,6 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, sc
         return linear_tc(x, weight, out, "silu_mul", stream=stream)  # the activation in the tcgen05 kernel's epilogue
     gate_up = linear(x, weight, out=scratch, stream=stream)
     silu_mul(out, gate_up, stream=stream)
-    return out
-
-
-def _linear_fused(x, weight: torch.Tensor, out: torch.Tensor | None, stream, partials: bool):
-    """``linear`` for a lazy input: the norm or activation runs inside the product's prologue."""
-    m, kdim = x.shape
-    n = weight.shape[0]
-    ok = (weight.dtype == torch.bfloat16 and weight.shape[1] == kdim and fusable_rows(m, kdim, weight.dtype)
-          and weight.data_ptr() % 16 == 0 and weight.is_cuda and weight.is_contiguous())
-    if not ok:
-        return linear(x.materialize(), weight, out=out, stream=stream, partials=partials)
-    k = native.kernels()
-    if isinstance(x, LazyNorm):
-        if out is None:
-            out = torch.empty((m, n), dtype=torch.bfloat16, device=weight.device)
-        assert out.shape == (m, n)
-        native.kernel_check(k.ms_gemm_skinny_norm_bf16(
-            _ptr(out), _ptr(x.residual_in), _ptr(x.delta), _ptr(x.residual_out), _ptr(x.weight), float(x.eps), _ptr(weight),
-            m, n, kdim, 1 if out.dtype == torch.float32 else 0, _stream(stream)))
-        return out
-    if partials and out is None:
-        splits = skinny_splits(n, kdim, _sm_count(weight.device))
-        if splits > 1:
-            parts = torch.empty((splits, m, n), dtype=torch.float32, device=weight.device)
-            native.kernel_check(k.ms_gemm_skinny_silu_bf16(_ptr(parts), _ptr(x.gate_up), _ptr(weight), m, n, kdim, splits, 2,
-                                                           _stream(stream)))
-            return PartialSums(parts, torch.bfloat16)
-    if out is None:
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=weight.device)
-    native.kernel_check(k.ms_gemm_skinny_silu_bf16(_ptr(out), _ptr(x.gate_up), _ptr(weight), m, n, kdim, 1,
-                                                   1 if out.dtype == torch.float32 else 0, _stream(stream)))
     return out
 
 

@@ -95,17 +95,16 @@ def kernels():
     _declare(lib, "ms_device_arch", [_i, POINTER(c_int), POINTER(c_int)])
     _declare(lib, "ms_fill_tokens", [_p, _p, _p, _p, _i, _p])
     _declare(lib, "ms_embed_gather", [_p, _p, _p, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _i, _ll, _p, _p, _f, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_gemm_skinny_norm_bf16", [_p, _p, _p, _p, _p, _f, _p, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_gemm_skinny_silu_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_gate_up_bf16", [_p, _p, _p, _i, _i, _i, _p])
-    _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_set_stream", [_i], None)
-    import os
-
-    # MINISERVE_SKINNY_STREAM=0: very wide outputs (the head) stay on the kernel with one row tile per CTA
-    # (2: the tile-walking kernel with the dependent-launch attribute, for measurements)
-    lib.ms_gemm_skinny_set_stream(int(os.environ.get("MINISERVE_SKINNY_STREAM", "1")))
+    _declare(lib, "ms_decode_chain", [_p, _p, _p, _i, _p])
+    _declare(lib, "ms_decode_chain_wrows", [_i, _i, _i])
+    _declare(lib, "ms_decode_chain_tiles", [_i, _i, _i])
+    _declare(lib, "ms_decode_chain_grid", [POINTER(c_int)])
+    _declare(lib, "ms_decode_chain_fits", [_i, _i])
+    _declare(lib, "ms_chain_embed", [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
     _declare(lib, "ms_qk_norm_rope_kv",

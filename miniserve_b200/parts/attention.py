@@ -41,8 +41,6 @@ class GQAttention(Part):
         pos_spec = spec.get("position") or PartSpec("none")
         self.position = build_part("position", pos_spec, env)
 
-    takes_lazy_input = True  # forward() starts with ops.linear, which can fuse the norm before it
-
     @property
     def owns_cache(self) -> bool:
         return self.kv_source == "own"
@@ -76,14 +74,13 @@ class GQAttention(Part):
         self.w_k_norm = tensors["k_norm.weight"].contiguous() if self.qk_norm and self.owns_cache else None
 
     def forward(self, x: torch.Tensor, ctx, cache):
-        """Returns the mixer's addend to the residual stream: a tensor [T, hidden], or float32
-        partial sums of it that the next norm adds up (``ops.PartialSums``)."""
+        """Returns the mixer's addend to the residual stream: a tensor [T, hidden]."""
         t = x.shape[0]
         dt, dev = self.env.dtype, self.w_qkv.device
         q = ctx.buffer("attn.q", (t, self.heads, self.head_dim), dt, dev)
         inv_freq, rotary_dim = self.position.kernel_table()
         indptr, indices = ctx.page_indptr[cache.group], ctx.page_indices[cache.group]
-        if (self.owns_cache and isinstance(x, torch.Tensor)
+        if (self.owns_cache
                 and ops.qkv_fused_ok(x, self.w_qkv, self.heads, self.kv_heads, self.head_dim, rotary_dim if inv_freq is not None else 0,
                                      cache.k, self.w_q_norm, self.w_k_norm)):
             # prompt steps: norm, rotation and cache write in the product's epilogue
@@ -99,5 +96,27 @@ class GQAttention(Part):
                 cos_sin=self.position.step_table(ctx))
         out = ctx.buffer("attn.out", (t, self.heads, self.head_dim), dt, dev)
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
-        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,
-                          out=None if ops.SPLIT_K_PARTIALS else ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))
+        return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream,
+                          out=ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))
+
+    def chain_mixer(self, ctx, cache):
+        """This mixer for a decode chain (``parts/decode_chain.py``): the q|k|v product, then one
+        kernel that norms and rotates q and the new k, writes the new k, v into the cache and attends
+        over it, then the output product."""
+        from ..ops import attention_bf16
+        from .decode_chain import ChainMixer
+
+        if (self.env.dtype != torch.bfloat16 or not self.owns_cache or self.hidden % 8 or (self.heads * self.head_dim) % 8
+                or not attention_bf16.supports(self.head_dim, cache.page_size)):
+            return None
+        inv_freq, rotary_dim = self.position.kernel_table()
+
+        def run(projection: torch.Tensor, out: torch.Tensor) -> None:
+            rows = projection.shape[0]
+            table = self.position.step_table(ctx) if inv_freq is not None else None
+            attention_bf16.run_decode(
+                out.view(rows, self.heads, self.head_dim), None, cache.k, cache.v, ctx, cache.group, self.scale, self.window, rows,
+                projection=dict(qkv=projection, q_norm_w=self.w_q_norm, k_norm_w=self.w_k_norm, cos_sin=table,
+                                rot=rotary_dim if table is not None else 0, eps=self.qk_norm_eps))
+
+        return ChainMixer(self.w_qkv, self.w_o, run)

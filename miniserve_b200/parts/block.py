@@ -2,7 +2,6 @@
 
 from __future__ import annotations
 
-from .. import ops
 from ..config.spec import LayerSpec
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part
 
@@ -30,17 +29,24 @@ class PreNormBlock(Part):
                 self.names["norm1"]: self.norm1, self.names["norm2"]: self.norm2}
 
     def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
-        # A mixer or feed-forward that sets ``takes_lazy_input`` starts with ops.linear, which can
-        # run the norm inside its own prologue (decode steps); the sum then lands in a new buffer.
         total = stream.total
-        x = self.norm1.forward(total, stream.pending, ctx, lazy=getattr(self.mixer, "takes_lazy_input", False))
-        if isinstance(x, ops.LazyNorm):
-            total = x.residual_out
+        x = self.norm1.forward(total, stream.pending, ctx)
         a = self.mixer.forward(x, ctx, cache)
-        x = self.norm2.forward(total, a, ctx, lazy=getattr(self.feed_forward, "takes_lazy_input", False))
-        if isinstance(x, ops.LazyNorm):
-            total = x.residual_out
+        x = self.norm2.forward(total, a, ctx)
         return ResidualStream(total, self.feed_forward.forward(x, ctx))
+
+    def chain_layer(self, ctx, cache):
+        """This layer for a decode chain (``parts/decode_chain.py``), or None if one of its parts
+        does not take part in chains."""
+        from .decode_chain import ChainLayer
+
+        ask = lambda part, name, *args: getattr(part, name)(*args) if hasattr(part, name) else None  # noqa: E731
+        n1, n2 = ask(self.norm1, "chain_norm"), ask(self.norm2, "chain_norm")
+        mixer = ask(self.mixer, "chain_mixer", ctx, cache)
+        ff = ask(self.feed_forward, "chain_feed_forward")
+        if n1 is None or n2 is None or mixer is None or ff is None:
+            return None
+        return ChainLayer(n1, mixer, n2, ff)
 
 
 def build_block(layer: LayerSpec, env: BuildEnv) -> Part:

@@ -30,17 +30,10 @@ class SwiGLU(Part):
         self.w_gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
-    takes_lazy_input = True  # forward() starts with ops.linear, which can fuse the norm before it
-
     def forward(self, x, ctx) -> torch.Tensor:
         t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
-        if ops.FUSE_SILU and ops.fusable_rows(t, self.inter, dt):
-            # (measured slower than what follows) SiLU(gate) * up runs while the down projection stages its input
-            gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
-            return ops.linear(ops.LazyAct(gate_up, stream=ctx.stream), self.w_down, stream=ctx.stream,
-                              partials=ops.SPLIT_K_PARTIALS)
         act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
-        if isinstance(x, torch.Tensor) and dt == torch.bfloat16:
+        if dt == torch.bfloat16:
             # one kernel with the activation in its epilogue where there is one (decode steps, wide prompt steps)
             fused = ops.silu_mul_is_fused(x, self.w_gate_up, act)
             scratch = None if fused else ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev)
@@ -48,5 +41,12 @@ class SwiGLU(Part):
         else:
             gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
             ops.silu_mul(act, gate_up, stream=ctx.stream)
-        return ops.linear(act, self.w_down, stream=ctx.stream, partials=ops.SPLIT_K_PARTIALS,
-                          out=None if ops.SPLIT_K_PARTIALS else ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
+        return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
+
+    def chain_feed_forward(self):
+        """The two products of this feed-forward for a decode chain (``parts/decode_chain.py``)."""
+        from .decode_chain import ChainFeedForward
+
+        if self.env.dtype != torch.bfloat16 or self.hidden % 8 or self.inter % 8:
+            return None
+        return ChainFeedForward(self.w_gate_up, self.w_down)

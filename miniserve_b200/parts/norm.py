@@ -22,16 +22,16 @@ class RMSNorm(Part):
         return {"weight": WeightDecl((self.size,), init="ones_normal")}
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
-                num_rows: int | None = None, write_residual: bool = True, lazy: bool = False):
+                num_rows: int | None = None, write_residual: bool = True) -> torch.Tensor:
         """Normalise ``residual (+ delta)``; without ``rows`` the sum is stored back into
-        ``residual``. With ``rows`` (int32 indices) only those rows are produced. ``lazy``: the
-        caller's consumer takes an ``ops.LazyNorm`` (decode steps: the norm then runs inside the
-        product that consumes it, and the sum goes to ``LazyNorm.residual_out``)."""
-        if (lazy and ops.FUSE_NORM and rows is None and write_residual and (delta is None or isinstance(delta, torch.Tensor))
-                and ops.fusable_rows(residual.shape[0], self.size, self.env.dtype)):
-            return ops.LazyNorm(residual, delta, self.w_weight, self.eps, stream=ctx.stream)
+        ``residual``. With ``rows`` (int32 indices) only those rows are produced."""
         n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = ctx.buffer("norm.out", (n, self.size), self.env.dtype, residual.device)
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,
                         write_residual=write_residual, stream=ctx.stream)
         return out
+
+    def chain_norm(self):
+        """(weight, eps) for a decode chain (``parts/decode_chain.py``), which applies the norm inside
+        the products around it."""
+        return (self.w_weight, self.eps) if self.env.dtype == torch.bfloat16 else None

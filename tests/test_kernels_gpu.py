@@ -148,10 +148,6 @@ def test_skinny_gemm_bf16(m, n, k):
     assert torch.allclose(out32, expect, **tol)
     out16 = ops.linear(x, w)
     assert out16.dtype == torch.bfloat16 and torch.allclose(out16.float(), expect, atol=0.05 * (k ** 0.5), rtol=2e-2)
-    parts = ops.linear(x, w, partials=True)
-    if isinstance(parts, ops.PartialSums):
-        assert parts.parts.shape[0] > 1 and parts.parts.shape[1:] == (m, n)
-        assert torch.allclose(parts.float(), expect, **tol)
     # a row's result does not depend on the rows beside it (where both shapes go to this kernel:
     # with k beyond 3,072 more than 8 rows go to the library)
     if ops._skinny_ok(x, w):
@@ -167,49 +163,6 @@ def test_skinny_gemm_bf16(m, n, k):
     finally:
         k_lib.ms_gemm_skinny_set_stream(1)
     assert torch.equal(one_tile, out32)
-
-
-@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
-@pytest.mark.parametrize("n, k", [(72, 96), (4096, 1024), (503, 1000)])
-def test_skinny_gemm_with_the_norm_in_its_prologue(m, n, k):
-    torch.manual_seed(m + n)
-    res = torch.randn(m, k, device=DEV) * 2
-    delta = torch.randn(m, k, device=DEV).bfloat16()
-    nw = (1 + 0.1 * torch.randn(k, device=DEV)).bfloat16()
-    w = (torch.randn(n, k, device=DEV) / 4).bfloat16()
-    eps = 1e-6
-    total = res + delta.float()
-    xn = (total * torch.rsqrt((total * total).mean(-1, keepdim=True) + eps) * nw.float()).bfloat16()
-    expect = xn.float() @ w.float().T
-    for d in (delta, None):
-        lazy = ops.LazyNorm(res.clone(), d, nw, eps)
-        keep = lazy.residual_in.clone()
-        out = ops.linear(lazy, w)
-        tot = total if d is not None else res
-        xr = (tot * torch.rsqrt((tot * tot).mean(-1, keepdim=True) + eps) * nw.float()).bfloat16()
-        exp = xr.float() @ w.float().T
-        assert torch.allclose(out.float(), exp, atol=0.05 * (k ** 0.5), rtol=2e-2)
-        assert torch.allclose(lazy.residual_out, tot, atol=1e-6)       # the sum went to the new buffer
-        assert torch.equal(lazy.residual_in, keep)                      # and the old one is untouched
-        # the stand-alone norm gives the same activations
-        assert torch.allclose(ops.LazyNorm(res.clone(), d, nw, eps).materialize().float(), xr.float(), atol=2e-2, rtol=2e-2)
-    assert expect.shape == (m, n)
-
-
-@pytest.mark.parametrize("m", [1, 8, 16])
-@pytest.mark.parametrize("n, inter", [(1024, 3072), (96, 224), (503, 72)])
-def test_skinny_gemm_with_silu_mul_in_its_prologue(m, n, inter):
-    torch.manual_seed(m + n)
-    gu = (torch.randn(m, 2 * inter, device=DEV) * 2).bfloat16()
-    w = (torch.randn(n, inter, device=DEV) / 4).bfloat16()
-    g, u = gu[:, :inter].float(), gu[:, inter:].float()
-    act = (g * torch.sigmoid(g) * u).bfloat16()
-    expect = act.float() @ w.float().T
-    out = ops.linear(ops.LazyAct(gu), w)
-    assert torch.allclose(out.float(), expect, atol=0.05 * (inter ** 0.5), rtol=2e-2)
-    parts = ops.linear(ops.LazyAct(gu), w, partials=True)
-    assert torch.allclose(ops.materialize(parts).float(), expect, atol=0.05 * (inter ** 0.5), rtol=2e-2)
-    assert torch.allclose(ops.LazyAct(gu).materialize().float(), act.float(), atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("m, inter, k", [(1, 3072, 1024), (8, 3072, 1024), (13, 224, 96), (16, 136, 64), (5, 2048, 4096)])
@@ -229,24 +182,6 @@ def test_skinny_gate_up_with_the_activation_in_its_epilogue(m, inter, k):
     assert torch.equal(got, want)
     ref = torch.nn.functional.silu(x.float() @ w[:inter].float().t()) * (x.float() @ w[inter:].float().t())
     assert torch.allclose(got.float(), ref, atol=3e-2, rtol=3e-2)
-
-
-def test_add_rmsnorm_takes_partial_sums():
-    hidden, rows, eps = 1000, 5, 1e-6
-    res = torch.randn(rows, hidden, device=DEV)
-    parts = torch.randn(3, rows, hidden, device=DEV)
-    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).bfloat16()
-    total = res + parts[0] + parts[1] + parts[2]
-    expect = total * torch.rsqrt((total * total).mean(-1, keepdim=True) + eps) * w.float()
-    out = torch.empty(rows, hidden, device=DEV, dtype=torch.bfloat16)
-    got = res.clone()
-    ops.add_rmsnorm(out, got, ops.PartialSums(parts, torch.bfloat16), w, eps)
-    assert torch.allclose(got, total, atol=1e-6) and torch.allclose(out.float(), expect, atol=2e-2, rtol=2e-2)
-    idx = torch.tensor([4, 1], device=DEV, dtype=torch.int32)
-    out2 = torch.empty(2, hidden, device=DEV, dtype=torch.bfloat16)
-    keep = res.clone()
-    ops.add_rmsnorm(out2, keep, ops.PartialSums(parts, torch.bfloat16), w, eps, rows=idx)
-    assert torch.equal(keep, res) and torch.allclose(out2.float(), expect[idx.long()], atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
