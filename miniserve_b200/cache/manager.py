@@ -59,7 +59,8 @@ class KVEntryView:
 @dataclass
 class StateEntryView:
     """What a mixer with fixed-size state gets: ``state[slot]`` belongs to the request whose
-    slot id is ``ctx.state_slot[row]``."""
+    slot id is ``ctx.state_slot[row]``. The tensor has one slot more than the cache has requests:
+    the padding rows of a captured graph carry that slot's id, so a mixer needs no mask for them."""
 
     state: torch.Tensor | None
     shape: tuple[int, ...]
@@ -80,20 +81,53 @@ class RequestCache:
     _tokens_without_tables: int = 0
 
 
+def group_needs(entry_caches: Sequence[EntryCache]) -> tuple[list[tuple[PagedKV, int]], list[FixedState]]:
+    """What a model's run entries ask of the cache: ``[(need, number of entries)]`` for the paged
+    groups (entries with equal needs share a group), and the fixed-size states, one per owning
+    entry. The order of the groups is the one ``CacheManager`` uses."""
+    groups: dict[PagedKV, int] = {}
+    states: list[FixedState] = []
+    for i, ec in enumerate(entry_caches):
+        if ec.owner != i or ec.need is None:
+            continue
+        if isinstance(ec.need, PagedKV):
+            groups[ec.need] = groups.get(ec.need, 0) + 1
+        elif isinstance(ec.need, FixedState):
+            states.append(ec.need)
+    return list(groups.items()), states
+
+
+def window_pages(window: int, page_size: int, step_tokens: int) -> int:
+    """The most pages a request holds in a group that looks ``window`` keys back, when a step brings
+    it at most ``step_tokens`` tokens: the window and the step's tokens (pages are given back after
+    the step), plus the pages both ends cut into."""
+    return -(-(window + step_tokens) // page_size) + 1
+
+
 class CacheManager:
-    def __init__(self, entry_caches: Sequence[EntryCache], num_pages: int, page_size: int, max_requests: int,
+    def __init__(self, entry_caches: Sequence[EntryCache], num_pages: "int | Sequence[int]", page_size: int, max_requests: int,
                  dtype: torch.dtype = torch.bfloat16, device: torch.device | str | None = None,
-                 poison: bool = False):
-        """``entry_caches``: one per run entry (``DecoderModel.entry_caches``). ``num_pages``
-        pages of ``page_size`` tokens per group. ``device`` None keeps everything on the host
-        (bookkeeping only, for tests). ``poison`` fills the pools with NaN so that a read of a
-        slot nobody wrote shows up."""
+                 poison: bool = False, poison_on_free: bool = False, step_tokens: int | None = None):
+        """``entry_caches``: one per run entry (``DecoderModel.entry_caches``). ``num_pages``:
+        pages of ``page_size`` tokens, one number for every group or one per group (in the order
+        of ``group_needs``). ``device`` None keeps everything on the host (bookkeeping only, for
+        tests). ``poison`` fills the pools with NaN so that a read of a slot nobody wrote shows
+        up; ``poison_on_free`` also fills a request's pages with NaN when it gives them back, so
+        that a stale key read through a reused page shows up (a debugging aid: it launches a fill
+        per release). ``step_tokens``: the most tokens a step brings one request; with it,
+        ``pages_for`` knows that a windowed group never holds a whole long request."""
         if page_size < 1 or page_size & (page_size - 1):
             raise ValueError(f"page_size must be a power of two, got {page_size}")
-        if num_pages < 1:
+        needs, _ = group_needs(entry_caches)
+        per_group = [int(num_pages)] * len(needs) if isinstance(num_pages, int) else [int(n) for n in num_pages]
+        if len(per_group) != len(needs):
+            raise ValueError(f"{len(per_group)} page counts for {len(needs)} cache groups")
+        if any(n < 1 for n in per_group) or (isinstance(num_pages, int) and num_pages < 1):
             raise ValueError(f"the pool needs at least one page, got {num_pages}")
         self.page_size = page_size
-        self.num_pages = num_pages
+        self.num_pages = max(per_group) if per_group else (num_pages if isinstance(num_pages, int) else 0)
+        self.step_tokens = step_tokens
+        self.poison_on_free = poison_on_free
         self.max_requests = max_requests
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
@@ -110,7 +144,7 @@ class CacheManager:
                 if g is None:
                     g = len(self.groups)
                     by_need[ec.need] = g
-                    self.groups.append(CacheGroup(ec.need, [], BlockAllocator(num_pages, page_size), page_size))
+                    self.groups.append(CacheGroup(ec.need, [], BlockAllocator(per_group[g], page_size), page_size))
                 owners[i] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
             elif isinstance(ec.need, FixedState):
@@ -119,13 +153,14 @@ class CacheManager:
                 raise TypeError(f"run entry {i} asks for an unknown kind of cache: {ec.need!r}")
         if self.device is not None:
             for grp in self.groups:
-                shape = (len(grp.entries), num_pages + 1, grp.need.kv_heads, page_size, grp.need.head_dim)
+                shape = (len(grp.entries), grp.allocator.num_blocks + 1, grp.need.kv_heads, page_size, grp.need.head_dim)
                 fill = float("nan") if poison else 0.0
                 grp.k = torch.full(shape, fill, dtype=dtype, device=self.device)
                 grp.v = torch.full(shape, fill, dtype=dtype, device=self.device)
         state_tensors: dict[int, torch.Tensor | None] = {}
         for i, need in self._state_entries:
-            state_tensors[i] = (torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=self.device)
+            # one slot more than there are requests: the padding rows of a captured graph read and write it
+            state_tensors[i] = (torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=self.device)
                                 if self.device is not None else None)
         for i, ec in enumerate(entry_caches):
             if ec.need is None:
@@ -142,6 +177,11 @@ class CacheManager:
 
     # ------------------------------------------------------------------ views and sizes
     @property
+    def pad_state_slot(self) -> int:
+        """A state slot outside the ones requests get, for padding rows (as ``pad_page`` is for pages)."""
+        return self.max_requests
+
+    @property
     def entry_views(self) -> list:
         return self._entry_view
 
@@ -156,6 +196,11 @@ class CacheManager:
     def pool_bytes(self) -> int:
         return sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups if g.k is not None)
 
+    def state_bytes(self) -> int:
+        """Bytes of the per-request state tensors (one slot per request the cache can hold)."""
+        return sum(v.state.numel() * v.state.element_size() for v in self._entry_view
+                   if isinstance(v, StateEntryView) and v.state is not None)
+
     # ------------------------------------------------------------------ requests
     def new_request(self) -> RequestCache:
         """Empty tables and a state slot for a request that is being admitted."""
@@ -169,6 +214,13 @@ class CacheManager:
         """Give back everything ``rc`` holds (request finished, aborted, preempted or refused)."""
         if rc.released:
             raise ValueError("request cache released twice")
+        if self.poison_on_free and self.device is not None:
+            for g, t in zip(self.groups, rc.tables):
+                held = [b for b in t.blocks if b >= 0]
+                if held and g.k is not None:
+                    idx = torch.tensor(held, dtype=torch.long, device=self.device)
+                    g.k[:, idx] = float("nan")
+                    g.v[:, idx] = float("nan")
         for t in rc.tables:
             t.release()
         if rc.state_slot >= 0:
@@ -186,15 +238,39 @@ class CacheManager:
         return tuple(g.allocator.num_free for g in self.groups)
 
     def pages_for(self, num_tokens: int) -> tuple[int, ...]:
-        """Pages per group that a request of ``num_tokens`` tokens may hold at its largest."""
-        return tuple(-(-num_tokens // g.page_size) for g in self.groups)
+        """Pages per group that a request of ``num_tokens`` tokens may hold at its largest: all of
+        them, or, in a windowed group (when the step size is known), the window and a step's tokens."""
+        out = []
+        for g in self.groups:
+            n = -(-num_tokens // g.page_size)
+            if g.need.window and self.step_tokens:
+                n = min(n, window_pages(g.need.window, g.page_size, self.step_tokens))
+            out.append(n)
+        return tuple(out)
+
+    def group_pages(self) -> tuple[int, ...]:
+        """Pages each group's pool has."""
+        return tuple(g.allocator.num_blocks for g in self.groups)
 
     def pages_needed(self, rc: RequestCache, new_tokens: int) -> tuple[int, ...]:
         """Pages per group that appending ``new_tokens`` to ``rc`` would allocate."""
         return tuple(t.blocks_needed(new_tokens) for t in rc.tables)
 
     def pages_held(self, rc: RequestCache) -> tuple[int, ...]:
-        return tuple(t.num_entries for t in rc.tables)
+        """Pages per group that ``rc`` holds now (a windowed group has given the older ones back)."""
+        return tuple(t.num_blocks for t in rc.tables)
+
+    def pages_outstanding(self, rc: RequestCache, upto_tokens: int) -> tuple[int, ...]:
+        """Pages per group that ``rc`` may still take, net of what it gives back, before its
+        sequence reaches ``upto_tokens`` tokens: the pages not yet allocated, but in a windowed
+        group (when the step size is known) no more than brings it to the most it ever holds."""
+        out = []
+        for g, t in zip(self.groups, rc.tables):
+            n = max(0, -(-upto_tokens // g.page_size) - t.num_entries)
+            if g.need.window and self.step_tokens:
+                n = min(n, max(0, window_pages(g.need.window, g.page_size, self.step_tokens) - t.num_blocks))
+            out.append(n)
+        return tuple(out)
 
     def fits(self, need: Sequence[int], margin: Sequence[int] | None = None) -> bool:
         free = self.num_free()

@@ -59,6 +59,26 @@ class RunEntry:
 
 
 @dataclass(frozen=True)
+class TensorRule:
+    """How one tensor of a checkpoint maps onto the tensors the parts declare, where the two do not
+    simply carry the same name. ``source`` is the checkpoint's name; ``targets`` lists (declared
+    name, rows): one target with rows -1 renames the tensor; several cut it along its first axis
+    into that many rows each, in order (a checkpoint that stores q, k and v as one matrix, or
+    experts as one stack). Renaming and splitting are data of the architecture, not loader code."""
+
+    source: str
+    targets: tuple[tuple[str, int], ...]
+
+    @classmethod
+    def rename(cls, source: str, target: str) -> "TensorRule":
+        return cls(source, ((target, -1),))
+
+    @classmethod
+    def split(cls, source: str, *targets: tuple[str, int]) -> "TensorRule":
+        return cls(source, tuple((name, int(rows)) for name, rows in targets))
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     hidden_size: int
@@ -68,6 +88,8 @@ class ModelSpec:
     run_order: tuple[RunEntry, ...]
     final_norm: PartSpec
     head: PartSpec
+    final_norm_prefix: str  # tensor-name prefix of the norm before the head (e.g. ``model.norm.``)
+    checkpoint_rules: tuple[TensorRule, ...] = ()
 
     def __post_init__(self):
         for i, e in enumerate(self.run_order):

@@ -29,7 +29,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          const int* __restrict__ positions, const int* __restrict__ row_of_token,
                          const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
                          int num_tokens, int nq, int nkv, int d, float scale, int window, int page_shift,
-                         int* __restrict__ status) {
+                         int num_pages, int* __restrict__ status) {
   extern __shared__ float q_smem[];  // [warps][d]
   pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -60,9 +60,13 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     size_t base = 0;
     if (valid) {
       const int page = pages[kj >> page_shift];
-      if (page < 0) {
-        atomicExch(status, 3);
-      } else {
+      bool usable = page >= 0;
+      if (!usable) atomicExch(status, 3);
+      MS_DEBUG_ONLY(if (usable && (page >= num_pages || row < 0)) {
+        atomicExch(status, 5);
+        usable = false;
+      })
+      if (usable) {
         base = (((size_t)page * nkv + kvh) * page_size + (kj & (page_size - 1))) * d;
         const T* kr = k_pool + base;
         float dot = 0.f;
@@ -105,7 +109,7 @@ using namespace ms;
 MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool, const void* v_pool,
                                    const int* positions, const int* row_of_token, const int* page_indptr,
                                    const int* page_indices, int num_tokens, int nq, int nkv, int head_dim, float scale,
-                                   int window, int page_size, int* status, int dtype, cudaStream_t stream) {
+                                   int window, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(head_dim > 0 && head_dim <= ROWWISE_MAX_D, "attention: head_dim=%d is outside 1..%d", head_dim, ROWWISE_MAX_D);
@@ -119,11 +123,11 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
   if (dtype == MS_F32)
     MS_LAUNCH(attention_rowwise_kernel<float>, blocks, warps * 32, smem, stream,
         (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, row_of_token, page_indptr,
-        page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift, status);
+        page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift, num_pages, status);
   else
     MS_LAUNCH(attention_rowwise_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream,
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift,
-        status);
+        num_pages, status);
   return 0;
 }

@@ -297,7 +297,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int page_shift,
-                        const AtGrid gr, int* __restrict__ status, long long* __restrict__ trace,
+                        const AtGrid gr, int* __restrict__ status,
                         float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
                         int* __restrict__ tickets) {
   extern __shared__ unsigned char smem_dyn[];
@@ -340,7 +340,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   AT_FENCE_AFTER();
   const uint32_t tmem = tmem_slot;
-  bool first_item = true;
 
   for (;;) {
     const int cur = item_slot;
@@ -351,8 +350,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int head0 = it.head0, kvh = head0 / (nq / nkv), split = it.split, tile_begin = it.tile_begin, n_all = it.n_all;
     const bool has_b = it.has_b;
     // timing experiments only: the first CTA stamps clock64() at the hand-off points of its first item
-    const bool tracing = trace != nullptr && blockIdx.x == 0 && first_item;
-#define AT_STAMP(slot) do { if (tracing) trace[(slot)] = clock64(); } while (0)
 
     if (warp == 8) {
       // ---------------------------------------------------------- TMA producer (and scheduler)
@@ -440,7 +437,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (j >= it.n_tiles[g]) continue;
             if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
             AT_FENCE_AFTER();
-            if (j < 40) AT_STAMP(16 * j + 1 + 2 * g);
 #pragma unroll
             for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
               // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
@@ -448,7 +444,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
               at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
             }
-            if (j < 40) AT_STAMP(16 * j + 2 + 2 * g);
             if (j + 1 < it.n_tiles[g]) {
               ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
             } else {
@@ -480,7 +475,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; j < n_mine && ok; ++j) {
         if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
         AT_FENCE_AFTER();
-        if (row == 0 && j < 40) AT_STAMP(16 * j + 8 + 3 * g);
         const int key0 = (tile_begin + j) * AT_KEYS;
         const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
         // the whole row of scores in registers: four loads in flight, one wait
@@ -506,7 +500,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
         const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        if (row == 0 && j < 40) AT_STAMP(16 * j + 9 + 3 * g);
         const float m_new = fmaxf(m_used, m_tile);
         float alpha = 1.f;
         bool rescale = false;
@@ -561,7 +554,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
         AT_FENCE_BEFORE();
         at_arrive(&p_full[g]);
-        if (row == 0 && j < 40) AT_STAMP(16 * j + 10 + 3 * g);
       }
       if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
       if (!ok) {
@@ -658,7 +650,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (failed) break;
     if (threadIdx.x == 0) init_barriers();
     if (warp == 8 && lane == 0) item_slot = next_item;
-    first_item = false;
     __syncthreads();
     AT_FENCE_AFTER();
   }
@@ -691,11 +682,6 @@ static int at_get_encode(AtEncodeFn* out) {
 
 using namespace ms;
 
-static long long* g_trace = nullptr;
-// Timing experiments only: a device buffer of 1024 int64 that the first CTA of the next launches
-// stamps with clock64() at its hand-off points (null: off).
-MS_EXPORT void ms_attn_tc_set_trace(long long* buffer) { g_trace = buffer; }
-
 MS_DEFINE_LAST_ERROR(ms_attn_tc_last_error)
 MS_DEFINE_PDL_SWITCH(ms_attn_tc_set_pdl)
 
@@ -711,13 +697,7 @@ static int at_heads_per_cta(int nq, int nkv) {
   return G;
 }
 
-static int g_splits = 0, g_min_tiles = 8;  // forced by ms_attn_tc_set_splits (0: planned per launch)
-// Tuning: force the number of key splits (0: chosen from the size of the step) and the least
-// number of key tiles that a split keeps.
-MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
-  g_splits = splits;
-  g_min_tiles = min_tiles > 0 ? min_tiles : 8;
-}
+constexpr int AT_MIN_TILES = 8;  // the least number of key tiles that a split keeps
 
 // How the keys of a tile of queries are shared out, from the step's geometry on the host (q_start
 // and q_len of the rows the launch covers): key ranges longer than *min_tiles key tiles are cut into
@@ -733,11 +713,7 @@ MS_EXPORT void ms_attn_tc_set_splits(int splits, int min_tiles) {
 MS_EXPORT void ms_attn_tc_plan(const int* q_start, const int* q_len, int num_rows, int nq, int nkv, int window, int sm_count,
                                int* splits, int* min_tiles) {
   *splits = 1;
-  *min_tiles = g_min_tiles;
-  if (g_splits > 0) {
-    *splits = g_splits;
-    return;
-  }
+  *min_tiles = AT_MIN_TILES;
   const int G = at_heads_per_cta(nq, nkv), span = 2 * (AT_ROWS / G), head_groups = nq / G;
   long long ctas = 0, steps = 0;
   int longest = 0;
@@ -830,7 +806,7 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
   const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status, g_trace,
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status,
             partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
             queue + 2);
   return 0;

@@ -156,6 +156,16 @@ inline int ms::fail(const char* fmt, ...) {
   return 1;
 }
 
+// Checks that only a debug build carries (MINISERVE_DEBUG=1 compiles the libraries with
+// -DMS_DEBUG_CHECKS under names of their own): indices that the host is trusted to have got right
+// are checked against their bounds, and a kernel that finds one out of range raises the status word
+// (code 5) and skips the access instead of making it.
+#ifdef MS_DEBUG_CHECKS
+#define MS_DEBUG_ONLY(...) __VA_ARGS__
+#else
+#define MS_DEBUG_ONLY(...)
+#endif
+
 // dtype codes shared with Python
 enum MsDtype : int { MS_F32 = 0, MS_BF16 = 1 };
 

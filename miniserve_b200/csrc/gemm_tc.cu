@@ -987,8 +987,9 @@ MS_DEFINE_PDL_SWITCH(ms_gemm_tc_set_pdl)
 // epilogue 0: out bf16 [M, N]; 1: out float32 [M, N]; 2: W is [2 * N, K] (gate rows then up rows),
 // out bf16 [M, N] = silu(A gate^T) * (A up^T). status: a device int the kernel raises if a wait ran out.
 static int g_tc_config = 0;
-// Tile configuration for experiments and tests: 0 = chosen from the shape, 5 = one CTA per tile,
-// 10 = persistent with 256-column tiles, 11 = persistent with 128-column tiles, 20 = pairs of CTAs on 256 x 256 tiles.
+// Which of the kernel's forms runs: 0 = chosen from the shape (what serving uses); the tests force each form at
+// every shape: 5 = one CTA per tile, 10 / 11 = persistent with 256- / 128-column tiles, 20 / 21 = pairs of CTAs on
+// 256- / 128-column tiles.
 MS_EXPORT void ms_gemm_tc_set_config(int config) { g_tc_config = config; }
 
 // 1 if this package's kernel is the faster choice for the product (measured on B200 against
@@ -1061,14 +1062,9 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
   const bool pairs = (long long)ceil_div(M, 2 * TC_BM) * ceil_div(N, PAIR_BN) >= sm_count / 2;  // a 256 x 256 tile per pair of SMs
   switch (epilogue) {
     case TC_OUT_BF16:
-      if (g_tc_config == 1) return launch_tc<128, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 2) return launch_tc<256, 2, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 3) return launch_tc<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 4) return launch_tc<64, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 5) return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 10) return launch_tc_persistent<256, 4, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 11) return launch_tc_persistent<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
-      if (g_tc_config == 12) return launch_tc_persistent<256, 3, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 21) return launch_tc_pair<128, 6, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       if (g_tc_config == 20 || pairs) return launch_tc_pair<256, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);
       return launch_tc<128, 5, TC_OUT_BF16>(out, A, W, M, N, N, K, 0, status, stream);

@@ -225,8 +225,14 @@ MS_EXPORT int ms_table_copy_blocks(void* h, int* out, int cap) {
 // Arena layout (int32 entries; every field starts on a multiple of 4 entries):
 //   token_ids[T'] positions[T'] row_of_token[T'] cu_q[R'+1] q_start[R'] kv_len[R'] state_slot[R']
 //   logit_rows[W] then for each cache group g: page_indptr_g[R'+1] page_indices_g[P_g]
-// with R' = rows + pad_rows and T' = tokens + pad_rows. A padding row is one token 0 at
-// position 0 whose single page is `pad_page` (a page outside the allocator); with want_pad_rows its
+// with R' = rows + pad_rows and T' = tokens + pad_rows. Of a table only the pages it still holds
+// are packed (and the entry just below them, which reads -1): page_indptr_g[r] is the index that
+// the table's entry 0 WOULD have, so that page_indices_g[page_indptr_g[r] + (position / page_size)]
+// is right for every position a kernel may ask for (those the window still reaches), whatever a
+// windowed group has given back; it can be negative. So a step never packs more entries than
+// the pool has pages, plus one per row. A padding row is one token 0 at
+// position 0 whose single page is `pad_page` (a page outside the allocator) and whose state slot is
+// `pad_state_slot` (a slot no request gets, so that a mixer with state needs no mask); with want_pad_rows its
 // logits are wanted too, so that the layout depends on R' alone. indices_cap > 0 gives every
 // group's page_indices exactly that many entries (a layout that does not move with the number of
 // pages, as a captured CUDA graph needs); 0 packs them tightly.
@@ -237,7 +243,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
                                  const int* q_start, const int* q_len, const int* token_ids,
                                  const int* state_slot, const int* logit_rows, int num_logit_rows, int groups,
                                  void* const* tables /* [groups][rows] */, const int* pad_page /* [groups] */,
-                                 long long indices_cap, int want_pad_rows) {
+                                 long long indices_cap, int want_pad_rows, int pad_state_slot) {
   if (rows < 0 || pad_rows < 0 || groups < 0) return -err(VALUE_ERROR, "pack_step: negative count");
   long long T = 0;
   for (int r = 0; r < rows; ++r) {
@@ -263,7 +269,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
       if (t->num_tokens != (long long)q_start[r] + q_len[r])
         return -err(VALUE_ERROR, "pack_step: row %d, group %d: the table holds %lld tokens, the step ends at %d", r, g,
                     t->num_tokens, q_start[r] + q_len[r]);
-      pages += (long long)t->blocks.size();
+      pages += (long long)t->blocks.size() - std::max(t->first_live - 1, 0);
     }
     if (indices_cap > 0 && pages > indices_cap)
       return -err(VALUE_ERROR, "pack_step: group %d needs %lld page entries, the fixed layout has %lld", g, pages, indices_cap);
@@ -286,7 +292,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
     arena[o_cu + r + 1] = (int32_t)t;
     arena[o_qs + r] = s;
     arena[o_kv + r] = s + n;
-    arena[o_ss + r] = pad ? -1 : (state_slot ? state_slot[r] : -1);
+    arena[o_ss + r] = pad ? pad_state_slot : (state_slot ? state_slot[r] : -1);
   }
   for (int i = 0; i < num_logit_rows; ++i) {
     if (logit_rows[i] < 0 || logit_rows[i] >= T) return -err(INDEX_ERROR, "pack_step: logit row %d outside [0, %lld)", logit_rows[i], T);
@@ -296,17 +302,19 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
     for (int i = 0; i < pad_rows; ++i) arena[o_lr + num_logit_rows + i] = (int32_t)(T + i);
   for (int g = 0; g < groups; ++g) {
     long long p = 0;
-    arena[o_indptr[g]] = 0;
     for (int r = 0; r < Rp; ++r) {
       if (r < rows) {
         auto* tb = static_cast<Table*>(tables[(size_t)g * rows + r]);
-        std::copy(tb->blocks.begin(), tb->blocks.end(), arena + o_indices[g] + p);
-        p += (long long)tb->blocks.size();
+        const int from = std::max(tb->first_live - 1, 0);
+        arena[o_indptr[g] + r] = (int32_t)(p - from);
+        std::copy(tb->blocks.begin() + from, tb->blocks.end(), arena + o_indices[g] + p);
+        p += (long long)tb->blocks.size() - from;
       } else {
+        arena[o_indptr[g] + r] = (int32_t)p;
         arena[o_indices[g] + p++] = pad_page[g];
       }
-      arena[o_indptr[g] + r + 1] = (int32_t)p;
     }
+    arena[o_indptr[g] + Rp] = (int32_t)p;
   }
   return off;
 }

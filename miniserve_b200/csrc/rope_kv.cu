@@ -26,7 +26,7 @@ __global__ void qk_norm_rope_kv_kernel(
     const float* __restrict__ cos_sin,   // [T, rot]: cos then sin of every (token, pair), or null (computed here)
     const int* __restrict__ positions, const int* __restrict__ row_of_token,
     const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
-    int num_tokens, int nq, int nkv, int d, int rot, float eps, int page_shift, int* __restrict__ status) {
+    int num_tokens, int nq, int nkv, int d, int rot, float eps, int page_shift, int num_pages, int* __restrict__ status) {
   pdl_prologue();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -55,6 +55,10 @@ __global__ void qk_norm_rope_kv_kernel(
       if (lane == 0) atomicExch(status, 2);
       return;
     }
+    MS_DEBUG_ONLY(if (page >= num_pages || row < 0) {
+      if (lane == 0) atomicExch(status, 5);
+      return;
+    })
     T* pool = is_v ? v_pool : k_pool;
     dst = pool + (((size_t)page * nkv + kvh) * page_size + (pos & (page_size - 1))) * d;
     if (is_v) {
@@ -119,7 +123,7 @@ qk_norm_rope_kv_bf16_token_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_norm_w,
     const __nv_bfloat16* __restrict__ k_norm_w, const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
     const int* __restrict__ positions, const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
-    const int* __restrict__ page_indices, int nq, int nkv, float eps, int page_shift, int* __restrict__ status) {
+    const int* __restrict__ page_indices, int nq, int nkv, float eps, int page_shift, int num_pages, int* __restrict__ status) {
   constexpr int LPH = D / 16;     // lanes per head
   constexpr int HPW = 32 / LPH;   // heads per warp and pass
   constexpr int HALF = D / 2;
@@ -178,6 +182,10 @@ qk_norm_rope_kv_bf16_token_kernel(
       if (threadIdx.x == 0) atomicExch(status, 2);
       return;
     }
+    MS_DEBUG_ONLY(if (page >= num_pages || request < 0) {
+      if (threadIdx.x == 0) atomicExch(status, 5);
+      return;
+    })
     const int page_size = 1 << page_shift;
     slot_base = ((size_t)page * nkv * page_size + (pos & (page_size - 1))) * D;  // + kvh * page_size * D
   }
@@ -262,7 +270,7 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
                                  const void* k_norm_w, const float* inv_freq, const float* cos_sin, const int* positions,
                                  const int* row_of_token, const int* page_indptr, const int* page_indices,
                                  int num_tokens, int nq, int nkv, int head_dim, int rotary_dim, float eps,
-                                 int page_size, int* status, int dtype, cudaStream_t stream) {
+                                 int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && head_dim > 0, "qk_norm_rope_kv: bad sizes nq=%d nkv=%d d=%d", nq, nkv, head_dim);
   MS_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
@@ -282,23 +290,23 @@ MS_EXPORT int ms_qk_norm_rope_kv(void* q_out, void* k_pool, void* v_pool, const 
       MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<128>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
                 inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
-                eps, page_shift, status);
+                eps, page_shift, num_pages, status);
     else
       MS_LAUNCH(qk_norm_rope_kv_bf16_token_kernel<256>, num_tokens, 128, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
                 inv_freq, inv_freq ? cos_sin : (const float*)nullptr, positions, row_of_token, page_indptr, page_indices, nq, nkv,
-                eps, page_shift, status);
+                eps, page_shift, num_pages, status);
     return 0;
   }
   if (dtype == MS_F32)
     MS_LAUNCH(qk_norm_rope_kv_kernel<float>, blocks, warps * 32, 0, stream,
         (float*)q_out, (float*)k_pool, (float*)v_pool, (const float*)qkv, (const float*)q_norm_w, (const float*)k_norm_w,
         inv_freq, cos_sin, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps,
-        page_shift, status);
+        page_shift, num_pages, status);
   else
     MS_LAUNCH(qk_norm_rope_kv_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream,
         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)qkv,
         (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, inv_freq, cos_sin, positions, row_of_token, page_indptr,
-        page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps, page_shift, status);
+        page_indices, num_tokens, nq, nkv, head_dim, rotary_dim, eps, page_shift, num_pages, status);
   return 0;
 }

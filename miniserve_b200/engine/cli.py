@@ -13,30 +13,33 @@ import argparse
 
 def add_engine_args(parser: argparse.ArgumentParser) -> None:
     g = parser.add_argument_group("engine")
-    g.add_argument("--max-running", type=int, default=64, help="max requests in the running batch")
-    g.add_argument("--max-prefill-tokens", type=int, default=8192, help="token budget of one prefill batch")
+    g.add_argument("--max-running", type=int, default=64, help="how many requests may be admitted at the same time")
+    g.add_argument("--max-prefill-tokens", type=int, default=8192,
+                   help="without chunking (--chunked-prefill-size 0): the most prompt tokens one step takes")
     g.add_argument("--kv-pool-tokens", type=int, default=None,
-                   help="exact KV pool size in tokens (rounded down to whole pages); "
-                        "default: as large as GPU memory allows")
-    g.add_argument("--page-size", type=int, default=16, help="tokens per KV page (a power of two)")
-    g.add_argument("--seed", type=int, default=0, help="seeds sampling for requests that bring no seed of their own")
+                   help="size of the key/value cache in tokens, cut down to whole pages; unset: what the device has left")
+    g.add_argument("--page-size", type=int, default=16, help="tokens in one cache page; a power of two")
+    g.add_argument("--seed", type=int, default=0, help="where requests without a seed of their own get theirs from")
     g.add_argument("--chunked-prefill-size", type=int, default=None,
-                   help="tokens per step, decodes included, with prefills cut into chunks batched with decodes; "
-                        "0: whole prefills in prefill-only steps (default: 2048)")
-    g.add_argument("--disable-cuda-graph", action="store_true", help="run decode steps eagerly (no CUDA Graphs)")
+                   help="token budget of a step: decoding requests first, the rest filled with portions of prompts; "
+                        "0 runs every prompt whole, in steps without decoding (default: 2048)")
+    g.add_argument("--disable-cuda-graph", action="store_true", help="launch the kernels of decode steps one by one")
     g.add_argument("--cuda-graph-max-bs", type=int, default=None,
-                   help="largest decode batch captured in a CUDA Graph (default: --max-running); "
-                        "graphs are captured for powers of two below it and for it")
+                   help="decode steps up to this many requests replay a captured graph, padded to the next power of two "
+                        "or to this number (default: --max-running)")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                    help="bfloat16: the serving kernels; float32: the whole model in true 32-bit")
-    # accepted for compatibility with the reference's command lines; one valid value each
-    g.add_argument("--attention", choices=["paged"], default="paged", help="KV storage (only paged here)")
-    g.add_argument("--schedule-policy", choices=["fcfs"], default="fcfs", help="admission order (only fcfs here)")
-    g.add_argument("--block-backend", choices=["cpp"], default="cpp", help="block bookkeeping (C++ here)")
-    g.add_argument("--disable-radix", action="store_true", help="no prefix cache (this engine has none)")
     g.add_argument("--disable-overlap", action="store_true",
-                   help="read back each step's tokens before scheduling the next (no CPU-GPU overlap)")
-    g.add_argument("--fused-ops", action="store_true", help="fused operators (this engine always uses its fused kernels)")
+                   help="wait for a step's tokens before planning the next one (the host then idles while the GPU works)")
+    g.add_argument("--poison-on-free", action="store_true",
+                   help="debugging: fill the pages a request gives back with NaN, so that a stale read shows")
+    # options of miniserve/engine/cli.py that choose between implementations of which this engine has one:
+    # taken, with their single value, so that a command line written for that engine still parses
+    g.add_argument("--attention", choices=["paged"], default="paged", help="the cache is always paged here")
+    g.add_argument("--schedule-policy", choices=["fcfs"], default="fcfs", help="requests are always admitted in arrival order here")
+    g.add_argument("--block-backend", choices=["cpp"], default="cpp", help="page bookkeeping is always the C++ one here")
+    g.add_argument("--disable-radix", action="store_true", help="accepted and ignored: there is no prefix cache here")
+    g.add_argument("--fused-ops", action="store_true", help="accepted and ignored: the fused kernels are the only ones here")
 
 
 def engine_kwargs(args: argparse.Namespace) -> dict:
@@ -50,12 +53,13 @@ def engine_kwargs(args: argparse.Namespace) -> dict:
         cuda_graph=not args.disable_cuda_graph,
         cuda_graph_max_bs=args.cuda_graph_max_bs,
         overlap=not args.disable_overlap,
+        poison_on_free=args.poison_on_free,
     )
 
 
 def add_model_args(parser: argparse.ArgumentParser) -> None:
     g = parser.add_argument_group("model")
-    g.add_argument("--model", default=None, help="folder with config.json and *.safetensors")
+    g.add_argument("--model", default=None, help="a model folder: config.json and safetensors files")
     g.add_argument("--random", default=None, metavar="PRESET",
-                   help="instead of --model: random weights for a preset (tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b)")
-    g.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
+                   help="no folder: a model of these sizes with random weights (tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b)")
+    g.add_argument("--weights-seed", type=int, default=0, help="the random weights are drawn from this seed")

@@ -27,7 +27,7 @@ class StepContext:
     cu_q: torch.Tensor  # [R + 1] first flat token of each row
     q_start: torch.Tensor  # [R] tokens of the row already in the cache
     kv_len: torch.Tensor  # [R] tokens in the cache after this step
-    state_slot: torch.Tensor  # [R] slot of the row's fixed-size state (-1: none)
+    state_slot: torch.Tensor  # [R] slot of the row's fixed-size state (padding rows: the spare slot no request gets)
     logit_rows: torch.Tensor  # [W] flat token indices whose logits are wanted
     page_indptr: list[torch.Tensor]  # per cache group: [R + 1]
     page_indices: list[torch.Tensor]  # per cache group: page ids, -1 where a window gave one back

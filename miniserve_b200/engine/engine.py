@@ -24,7 +24,7 @@ from typing import Sequence
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, group_needs, window_pages
 from ..parts.decoder import DecoderModel
 from ..sampling.sampler import Sampler
 from .request import PLACEHOLDER, Request, RequestState, SamplingParams
@@ -32,6 +32,33 @@ from .scheduler import Plan, Scheduler
 from .step import StepError, StepFunction, StepRow
 
 DEFAULT_CHUNKED_PREFILL = 2048
+
+
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
+class _range:
+    """An NVTX range around a phase of a step when ``MINISERVE_NVTX=1`` (a profiler's timeline then shows
+    schedule / launch / read back per step, as miniserve/bench/offline.py:235-241 brackets its steps);
+    nothing otherwise."""
+
+    enabled = __import__("os").environ.get("MINISERVE_NVTX", "0") == "1"
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if self.enabled:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            torch.cuda.nvtx.range_pop()
+        return False
 
 
 class _Launched:
@@ -50,7 +77,7 @@ class Engine:
                  max_running: int = 64, max_prefill_tokens: int = 8192, chunked_prefill_size: int | None = None,
                  seed: int = 0, cuda_graph: bool = True, cuda_graph_max_bs: int | None = None,
                  kv_mem_fraction: float = 0.9, overlap: bool = True, cache: CacheManager | None = None, step_fn=None,
-                 sampler=None):
+                 sampler=None, poison_on_free: bool = False):
         """``kv_pool_tokens``: exact size of the cache pool in tokens, rounded down to whole pages
         (default: ``kv_mem_fraction`` of the memory the device has free after the weights, less a
         reserve for activations). ``chunked_prefill_size``: tokens per step, decode tokens included,
@@ -61,17 +88,20 @@ class Engine:
         ``overlap``: launch each step before reading back the previous one.
         Names and meanings follow miniserve/engine/engine.py:42-77. ``cache``, ``step_fn`` and
         ``sampler`` replace the ones the engine would build (a test can run the whole loop on the
-        host against a stand-in step function this way)."""
+        host against a stand-in step function this way). ``poison_on_free``: a debugging aid, see
+        ``CacheManager``."""
         self.model = model
         if chunked_prefill_size is None:
             chunked_prefill_size = DEFAULT_CHUNKED_PREFILL
+        step_tokens = chunked_prefill_size if chunked_prefill_size else max_prefill_tokens
         if cache is None:
-            num_pages = self._pool_pages(model, kv_pool_tokens, page_size, kv_mem_fraction,
-                                         chunked_prefill_size if chunked_prefill_size else max_prefill_tokens,
-                                         max_running)
+            num_pages = self._pool_pages(model, kv_pool_tokens, page_size, kv_mem_fraction, step_tokens, max_running)
             cache = CacheManager(model.entry_caches, num_pages, page_size, max_running, dtype=model.dtype,
-                                 device=model.device)
+                                 device=model.device, poison_on_free=poison_on_free, step_tokens=step_tokens)
         self.cache = cache
+        self.settings = dict(kv_pool_tokens=kv_pool_tokens, page_size=page_size, max_running=max_running,
+                             max_prefill_tokens=max_prefill_tokens, chunked_prefill_size=chunked_prefill_size, seed=seed,
+                             cuda_graph=cuda_graph, cuda_graph_max_bs=cuda_graph_max_bs or max_running, overlap=overlap)
         self.step_fn = step_fn if step_fn is not None else StepFunction(model, self.cache)
         self.scheduler = Scheduler(self.cache, max_running, max_prefill_tokens, chunked_prefill_size)
         self.sampler = sampler if sampler is not None else Sampler(model.device, model.spec.vocab_size, max_running)
@@ -86,32 +116,52 @@ class Engine:
             self.graphs = DecodeGraphs(self.step_fn, self.sampler, cuda_graph_max_bs or max_running)
         self.overlap = overlap
         self.num_steps = 0
+        self.stalled = False  # the last step() neither launched a step nor read one back
         self.launched: Plan | None = None  # the plan the last step() launched
         self._inflight: _Launched | None = None
         self._pinned: list[torch.Tensor] = []
 
     @staticmethod
-    def _pool_pages(model, kv_pool_tokens, page_size, fraction, step_tokens, max_running) -> int:
-        per_token = 0
+    def _pool_pages(model, kv_pool_tokens, page_size, fraction, step_tokens, max_running) -> list[int]:
+        """Pages for each cache group (in ``group_needs`` order). A group that keeps every key gets
+        ``kv_pool_tokens`` worth of pages, or its share of the device memory that is left after the
+        weights, the per-request state tensors and a reserve for a step's activations; a windowed
+        group never needs more than ``max_running`` requests' windows, and gets no more."""
         item = torch.empty((), dtype=model.dtype).element_size()
-        seen = set()
-        for ec in model.entry_caches:
-            if ec.need is not None and ec.owner not in seen and hasattr(ec.need, "kv_heads"):
-                seen.add(ec.owner)
-                per_token += 2 * ec.need.kv_heads * ec.need.head_dim * item
+        needs, states = group_needs(model.entry_caches)
+        page_bytes = [2 * count * need.kv_heads * need.head_dim * item * page_size for need, count in needs]
+        bound = [max_running * window_pages(need.window, page_size, step_tokens) if need.window else None for need, _ in needs]
         if kv_pool_tokens is not None:
             if kv_pool_tokens < page_size:
                 raise ValueError(f"kv_pool_tokens={kv_pool_tokens} is smaller than one page ({page_size})")
-            return kv_pool_tokens // page_size
+            want = kv_pool_tokens // page_size
+            return [want if b is None else min(want, b) for b in bound]
         free, _ = torch.cuda.mem_get_info(model.device)
+        state_bytes = sum(max_running * torch.empty((), dtype=st.dtype).element_size() * _numel(st.shape) for st in states)
         # activations of the largest step: a few [tokens, widest] buffers, and float32 logits of every row
         widest = max(model.spec.hidden_size * 8, 1)
         reserve = step_tokens * widest * 4 * 4 + max_running * model.spec.vocab_size * 4 * 3 + (1 << 30)
-        usable = int(fraction * (free - reserve))
-        pages = usable // max(per_token * page_size, 1)
-        if pages < 1:
+        usable = int(fraction * (free - reserve - state_bytes))
+        windowed = sum(b * pb for b, pb in zip(bound, page_bytes) if b is not None)
+        whole = sum(pb for b, pb in zip(bound, page_bytes) if b is None)
+        pages = (usable - windowed) // max(whole, 1) if whole else 0
+        if usable <= windowed or (whole and pages < 1):
             raise RuntimeError(f"no device memory left for the cache pool ({free} bytes free)")
-        return pages
+        return [pages if b is None else b for b in bound]
+
+    def describe(self) -> dict:
+        """The configuration in effect, as plain data (what a benchmark records beside its numbers;
+        miniserve/engine/describe.py:22-44 serves the same purpose)."""
+        m, c = self.model, self.cache
+        return dict(
+            architecture=m.spec.architecture, dtype=str(m.dtype).replace("torch.", ""), device=str(m.device),
+            layers=len(m.spec.run_order), hidden_size=m.spec.hidden_size, vocab_size=m.spec.vocab_size,
+            weight_bytes=m.weight_bytes() if m.bound else None,
+            cache_groups=[dict(entries=len(g.entries), kv_heads=g.need.kv_heads, head_dim=g.need.head_dim, window=g.need.window,
+                               pages=g.allocator.num_blocks, page_size=g.page_size) for g in c.groups],
+            cache_bytes=c.pool_bytes(), cache_bytes_per_token=c.bytes_per_token(), state_bytes=c.state_bytes(),
+            request_slots=c.max_requests, graph_buckets=list(self.graphs.buckets) if self.graphs is not None else [],
+            **self.settings)
 
     # ------------------------------------------------------------------ requests
     def capture_graphs(self, modes=("greedy",)) -> int:
@@ -154,14 +204,19 @@ class Engine:
     def step(self) -> Plan | None:
         """Run one step. Returns the plan launched by this call (None if nothing could run). With
         overlap the tokens it samples are read back by the NEXT call."""
-        plan = self.scheduler.schedule()
+        with _range("schedule"):
+            plan = self.scheduler.schedule()
         prev = self._inflight
         self.launched = plan
-        self._inflight = self._launch(plan, prev) if plan is not None else None
+        with _range(f"launch {plan.phase} rows={len(plan.rows)} tokens={plan.num_tokens}" if plan is not None else "launch none"):
+            self._inflight = self._launch(plan, prev) if plan is not None else None
         if not self.overlap:
             prev, self._inflight = self._inflight, None
         if prev is not None:
-            self._process(prev)
+            with _range("read back"):
+                self._process(prev)
+        # a step that neither launched nor read anything back changed nothing: the next would do the same
+        self.stalled = plan is None and prev is None
         return plan
 
     def _launch(self, plan: Plan, prev: _Launched | None) -> _Launched:
@@ -224,7 +279,10 @@ class Engine:
         values = launched.host.tolist()
         status = values.pop()
         if status:
-            self.step_fn.status.zero_()
+            # the step after this one is already launched: let it drain, then put the status word and the
+            # kernels' tickets back to zero (as StepFunction.check_status does), so that a caller who
+            # catches the error can go on
+            self.step_fn.reset_after_fault()
             raise StepError(f"a kernel reported a fault it caught itself (code {status})")
         for (req, slot), tok in zip(launched.slots, values):
             if req.is_done:  # ended before (this token lies past its end)
@@ -236,12 +294,34 @@ class Engine:
                 req.transition(RequestState.FINISHED)
                 self._retire(req)
 
-    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams]) -> list[list[int]]:
-        """Submit all prompts (token ids) at once and run to completion; output token ids per prompt."""
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],
+                 on_step=None, max_steps: int | None = None) -> list[list[int]]:
+        """Submit all prompts (token ids) at once and run to completion; output token ids per prompt.
+        ``on_step(engine, plan)`` is called after every step with the plan that step launched (None if it
+        launched nothing): a place to count, time or check. ``max_steps``: raise if not done by then."""
         if isinstance(params, SamplingParams):
             params = [params] * len(prompts)
-        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        if len(params) != len(prompts):
+            raise ValueError(f"{len(prompts)} prompts but {len(params)} sampling parameters")
+        reqs: list[Request] = []
+        try:
+            for p, sp in zip(prompts, params):
+                reqs.append(self.add_request(p, sp))
+        except Exception:
+            # a prompt was refused: none of this call's requests stays behind in the queues
+            for r in reqs:
+                self.abort(r.rid)
+            raise
+        steps = 0
         while self.has_unfinished:
-            if self.step() is None and self._inflight is None and self.scheduler.has_unfinished:
+            if max_steps is not None and steps >= max_steps:
+                raise RuntimeError(f"not finished after {steps} steps")
+            plan = self.step()
+            steps += 1
+            # (a step may launch nothing and still move on: with overlap, a preempted request waits for its
+            # newest token to be read back before it is admitted again, and this step read it)
+            if self.stalled and self.scheduler.has_unfinished:
                 raise RuntimeError("the scheduler produced no step although requests are unfinished")
+            if on_step is not None:
+                on_step(self, plan)
         return [r.output_ids for r in reqs]

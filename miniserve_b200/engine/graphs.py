@@ -43,7 +43,8 @@ class DecodeGraphs:
         self.buckets = graph_buckets(max_bs)
         self.max_batch = self.buckets[-1]
         cache = step_fn.cache
-        self.indices_cap = cache.num_pages + self.max_batch + 4
+        # a step packs the pages its rows hold (at most the pool), one guard entry per row, and the padding rows' page
+        self.indices_cap = max(g.allocator.num_blocks for g in cache.groups) + 2 * self.max_batch + 4 if cache.groups else 4
         step_fn.reserve_arena(16 * (self.max_batch + 8) + cache.num_groups * (self.indices_cap + self.max_batch + 16) + 256)
         self._generation = step_fn.arena_generation
         self._graphs: dict[tuple[int, str], _Captured] = {}
@@ -142,9 +143,22 @@ class DecodeGraphs:
         self.sampler._ensure(bucket)
         torch.cuda.current_stream(sf.device).synchronize()
         s = self.capture_stream
+        # A warm-up pass outside the capture (first-use set-up of kernels and libraries must not happen while
+        # capturing). It runs the step's real rows, so what it changes has to be put back: rewriting the same
+        # keys and values is harmless, but a mixer's per-request state would otherwise advance twice (by the
+        # warm-up and again by the first replay).
+        from ..cache.manager import StateEntryView
+
+        slots = ctx.state_slot.long()
+        states = {id(v.state): v.state for v in sf.cache.entry_views if isinstance(v, StateEntryView) and v.state is not None}
+        kept = [(st, st[slots].clone()) for st in states.values()]
         with torch.cuda.stream(s):
-            self._forward(ctx, bucket, mode, f32, i64)  # warm-up outside the capture
+            s.wait_stream(torch.cuda.current_stream(sf.device))
+            self._forward(ctx, bucket, mode, f32, i64)
         s.synchronize()
+        for st, value in kept:
+            st[slots] = value
+        torch.cuda.current_stream(sf.device).synchronize()
         from ..ops import native
 
         graph = torch.cuda.CUDAGraph()

@@ -38,7 +38,8 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",
     raw = load_config_dict(model_dir)
     _, cfg, spec = resolve(raw)
     model = DecoderModel(spec, parse_dtype(dtype), device)
-    tensors = load_weights(model_dir, model.weight_decls(), model.dtype, model.device, ignorable=_ignorable(model))
+    tensors = load_weights(model_dir, model.weight_decls(), model.dtype, model.device, ignorable=_ignorable(model),
+                           rules=spec.checkpoint_rules, stacks=model.weight_stacks())
     model.bind(tensors)
     return raw, cfg, model
 
@@ -51,5 +52,5 @@ def random_model(raw_config: Mapping[str, Any], seed: int, dtype: str | torch.dt
     _, cfg, spec = resolve(raw)
     model = DecoderModel(spec, parse_dtype(dtype), device)
     model.bind(random_tensors(model.weight_decls(), seed, dtype=model.dtype, std=std, device=model.device,
-                              draw_on_device=draw_on_device))
+                              draw_on_device=draw_on_device, stacks=model.weight_stacks()))
     return raw, cfg, model

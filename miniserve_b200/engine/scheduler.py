@@ -79,6 +79,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []  # admission order
         self.num_preemptions = 0
+        self.num_preempted_requests = 0  # requests preempted at least once
         self.stats = dict(first_tokens=0, re_tokens=0)
 
     # ------------------------------------------------------------------ queues
@@ -86,7 +87,7 @@ class Scheduler:
         if req.state is not RequestState.WAITING:
             raise ValueError(f"request {req.rid} is {req.state.name}, expected WAITING")
         need = self.cache.pages_for(req.max_len)
-        if any(n > self.cache.num_pages for n in need):
+        if any(n > have for n, have in zip(need, self.cache.group_pages())):
             raise ValueError(f"request {req.rid} needs up to {req.max_len} tokens of cache, "
                              f"the pool holds {self.cache.num_pages * self.cache.page_size}")
         self.waiting.append(req)
@@ -120,9 +121,7 @@ class Scheduler:
             if self._decodes(r):
                 need = _add(need, self.cache.pages_needed(r.cache, 1))
             elif r.state is RequestState.PREFILL:
-                whole = self.cache.pages_for(r.seq_len + 1)
-                held = self.cache.pages_held(r.cache)
-                need = _add(need, tuple(max(0, w - h) for w, h in zip(whole, held)))
+                need = _add(need, self.cache.pages_outstanding(r.cache, r.seq_len + 1))
         return need
 
     def _admission_need(self, req: Request) -> tuple[int, ...]:
@@ -135,6 +134,7 @@ class Scheduler:
         req.cache = None
         self.running.remove(req)
         self.waiting.appendleft(req)  # victims are taken newest first, so arrival order is kept
+        self.num_preempted_requests += req.num_preemptions == 0
         req.num_preemptions += 1
         self.num_preemptions += 1
 

@@ -164,7 +164,7 @@ class StepFunction:
         total = self._host_lib.ms_pack_step(
             pinned.data_ptr(), self._arena_ints, offsets, len(rows), pad_rows, q_start.ctypes.data,
             q_len.ctypes.data, ids.ctypes.data, slots.ctypes.data, want_arr.ctypes.data, len(want), groups, tables,
-            pad_page.ctypes.data, indices_cap, int(want_pad_rows))
+            pad_page.ctypes.data, indices_cap, int(want_pad_rows), self.cache.pad_state_slot)
         if total < 0:
             # undo the reservation so that a failed step leaves the tables as they were
             for r, n in zip(rows, q_len):
@@ -213,23 +213,29 @@ class StepFunction:
             logit_rows=view(o[7], max(len(want) + (pad_rows if want_pad_rows else 0), 1)),
             page_indptr=page_indptr, page_indices=page_indices, status=self.status,
             host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [1] * pad_rows,
-            host_state_slot=slots.tolist() + [-1] * pad_rows,
+            host_state_slot=slots.tolist() + [self.cache.pad_state_slot] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
             decode_only=bool((q_len == 1).all()),
             logit_rows_in_order=(len(want) == int(q_len.sum()) and want == list(range(len(want)))
                                  and (pad_rows == 0 or want_pad_rows)),
             leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
 
+    def reset_after_fault(self) -> None:
+        """After a kernel raised the status word: wait for what is in flight, then zero the word and
+        the kernels' persistent counters. A kernel that gave up may have left its tickets, work-queue
+        counters or barrier state half counted; they go back to zero in place, because CUDA graphs
+        hold their addresses."""
+        torch.cuda.current_stream(self.device).synchronize()
+        self.status.zero_()
+        for buf in self.persistent_scratch.values():
+            if isinstance(buf, torch.Tensor) and buf.dtype == torch.int32:
+                buf.zero_()
+
     def check_status(self) -> None:
         """Synchronise and raise if a kernel flagged inconsistent input (a page that was given
         back, a table too short)."""
         code = int(self.status.item())
         if code:
-            self.status.zero_()
-            # a kernel that gave up may have left its tickets and work-queue counters half counted:
-            # they go back to zero (in place: CUDA graphs hold their addresses)
-            for buf in self.persistent_scratch.values():
-                if isinstance(buf, torch.Tensor) and buf.dtype == torch.int32:
-                    buf.zero_()
+            self.reset_after_fault()
             raise StepError(f"a kernel reported a fault it caught itself (code {code}: 2-3 inconsistent cache "
                             f"metadata; 11-13, 21-24, 31-34 a bounded wait in a tensor-core pipeline ran out)")

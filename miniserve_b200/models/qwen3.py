@@ -38,7 +38,8 @@ def qwen3_model_spec(cfg: Qwen3Config) -> ModelSpec:
         embedding=PartSpec("token_embedding", dict(vocab=cfg.vocab_size, hidden=cfg.hidden_size, name=EMBED_NAME)),
         layers=layers,
         run_order=tuple(RunEntry(i) for i in range(cfg.num_hidden_layers)),
-        final_norm=PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps, name="model.norm.")),
+        final_norm=PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)),
+        final_norm_prefix="model.norm.",
         head=PartSpec("linear_head", dict(vocab=cfg.vocab_size, hidden=cfg.hidden_size,
                                           tied=cfg.tie_word_embeddings, name=HEAD_NAME, tied_to=EMBED_NAME)),
     )

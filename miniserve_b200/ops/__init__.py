@@ -298,8 +298,8 @@ def qk_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor | None, v_pool: to
     native.kernel_check(k.ms_qk_norm_rope_kv(
         _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
         _ptr(cos_sin if inv_freq is not None else None), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, d,
-        rotary_dim if inv_freq is not None else 0, float(eps), page_size, _ptr(status), dtype_code(qkv.dtype),
-        _stream(stream)))
+        rotary_dim if inv_freq is not None else 0, float(eps), page_size, 0 if k_pool is None else k_pool.shape[0],
+        _ptr(status), dtype_code(qkv.dtype), _stream(stream)))
 
 
 def qkv_fused_ok(x: torch.Tensor, w_qkv: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, k_pool, q_norm_w, k_norm_w) -> bool:
@@ -361,7 +361,7 @@ def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, 
     k = native.kernels()
     native.kernel_check(k.ms_attention_rowwise(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
-        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), page_size, _ptr(status),
+        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), page_size, k_pool.shape[0], _ptr(status),
         dtype_code(q.dtype), _stream(stream)))
 
 
@@ -420,6 +420,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
 
 
 _ATTN_TC_SCRATCH_LIMIT = 1 << 29  # bytes of partial results that a step's attention may ask for
+ATTN_TC_SPLITS: tuple[int, int] | None = None  # tests: (key splits, least key tiles per split) instead of the planned ones
 
 
 def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
@@ -447,14 +448,16 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
         splits, min_tiles = ctypes.c_int(), ctypes.c_int()
         lib.ms_attn_tc_plan(starts, lens, rows, nq, k_pool.shape[1], int(window or 0), ctx.sm_count, ctypes.byref(splits),
                             ctypes.byref(min_tiles))
-        splits = splits.value
+        splits, least = splits.value, min_tiles.value
+        if ATTN_TC_SPLITS is not None:
+            splits, least = ATTN_TC_SPLITS[0], ATTN_TC_SPLITS[1] or least
         need_f, need_i = ctypes.c_longlong(), ctypes.c_longlong()
         while True:
             lib.ms_attn_tc_scratch(ctx.max_q_len, rows, nq, k_pool.shape[1], splits, ctypes.byref(need_f), ctypes.byref(need_i))
             if splits == 1 or need_f.value * 4 <= _ATTN_TC_SCRATCH_LIMIT:
                 break
             splits -= 1
-        plan = (splits, min_tiles.value, need_f.value, need_i.value)
+        plan = (splits, least, need_f.value, need_i.value)
         ctx.step_cache[key] = plan
     splits, min_tiles, need_floats, need_ints = plan
     part = None

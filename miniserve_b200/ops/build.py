@@ -126,8 +126,31 @@ def _run(cmd: list[str], what: str) -> None:
     log(f"compiled {what} in {time.time() - t0:.1f} s")
 
 
+def debug_checks() -> bool:
+    """MINISERVE_DEBUG=1: the CUDA libraries are compiled with -DMS_DEBUG_CHECKS (bounds checks that raise
+    the status word, see ``csrc/common.cuh``) under names of their own, beside the ordinary ones."""
+    return os.environ.get("MINISERVE_DEBUG", "0") == "1"
+
+
+def host_sanitizers() -> bool:
+    """MINISERVE_HOST_SANITIZE=1: the host core is compiled with AddressSanitizer and
+    UndefinedBehaviorSanitizer (the process that loads it must have the sanitizer's runtime preloaded)."""
+    return os.environ.get("MINISERVE_HOST_SANITIZE", "0") == "1"
+
+
+def _variant(mod: Module) -> tuple[Module, list[str]]:
+    """The module as it is built under the debugging switches, and extra compiler flags."""
+    if mod.cuda and debug_checks():
+        return Module(mod.name + "_dbg", mod.sources, mod.defines + ("MS_DEBUG_CHECKS",), mod.cuda, mod.extra_deps), []
+    if not mod.cuda and host_sanitizers():
+        return (Module(mod.name + "_san", mod.sources, mod.defines, mod.cuda, mod.extra_deps),
+                ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g"])
+    return mod, []
+
+
 def ensure_built(mod: Module, verbose_ptxas: bool = False) -> Path:
     """Path of the module's shared library, compiling it first if it is missing or stale."""
+    mod, extra_flags = _variant(mod)
     out_dir = build_dir()
     lib = out_dir / f"libms_{mod.name}.so"
     stamp = out_dir / f"libms_{mod.name}.stamp"
@@ -159,7 +182,7 @@ def ensure_built(mod: Module, verbose_ptxas: bool = False) -> Path:
             if cxx is None:
                 raise RuntimeError("no C++ compiler (g++) found; the host core of miniserve_b200 cannot be built")
             tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
-            _run([cxx, *CXX_FLAGS, *defines, "-shared", "-o", str(tmp), *[str(CSRC / s) for s in mod.sources]],
+            _run([cxx, *CXX_FLAGS, *extra_flags, *defines, "-shared", "-o", str(tmp), *[str(CSRC / s) for s in mod.sources]],
                  f"{mod.name}")
         os.replace(tmp, lib)
         stamp.write_text(digest)

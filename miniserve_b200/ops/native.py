@@ -68,7 +68,7 @@ def host():
     _declare(lib, "ms_table_release_below", [_p, _ll, POINTER(c_int)])
     _declare(lib, "ms_table_copy_blocks", [_p, POINTER(c_int32), _i])
     _declare(lib, "ms_pack_step",
-             [_p, _ll, POINTER(_ll), _i, _i, _p, _p, _p, _p, _p, _i, _i, POINTER(c_void_p), _p, _ll, _i], _ll)
+             [_p, _ll, POINTER(_ll), _i, _i, _p, _p, _p, _p, _p, _i, _i, POINTER(c_void_p), _p, _ll, _i, _i], _ll)
     return lib
 
 
@@ -108,11 +108,11 @@ def kernels():
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
     _declare(lib, "ms_qk_norm_rope_kv",
-             [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p, _i, _p])
+             [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p])
     _declare(lib, "ms_rope_table", [_p, _p, _p, _i, _i, _p])
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_attention_rowwise",
-             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p])
+             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p, _i, _p])
     _declare(lib, "ms_nucleus_bytes", [])
     _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
     _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
@@ -139,7 +139,6 @@ def attn_tc():
     _declare(lib, "ms_attn_tc_set_pdl", [_i], None)
     _declare(lib, "ms_attn_tc_supports", [_i, _i, _i, _i])
     _declare(lib, "ms_attn_tc_plan", [_p, _p, _i, _i, _i, _i, _i, _p, _p], None)
-    _declare(lib, "ms_attn_tc_set_splits", [_i, _i], None)
     _declare(lib, "ms_attn_tc_scratch", [_i, _i, _i, _i, _i, _p, _p], None)
     _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _p, _i, _i, _p, _p, _p])
     lib.ms_attn_tc_set_pdl(int(pdl_enabled()))

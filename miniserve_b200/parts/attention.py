@@ -63,10 +63,13 @@ class GQAttention(Part):
                 w["k_norm.weight"] = WeightDecl((d,), init="ones_normal")
         return w
 
+    def stacks(self):
+        # one product makes q, k and v (miniserve/model/fused.py:41-95 joins the same rows)
+        return {"qkv_proj.weight": ("q_proj.weight", "k_proj.weight", "v_proj.weight")} if self.owns_cache else {}
+
     def bind(self, tensors):
         if self.owns_cache:
-            self.w_qkv = torch.cat((tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]),
-                                   dim=0).contiguous()
+            self.w_qkv = self.joined(tensors, "qkv_proj.weight", self.stacks()["qkv_proj.weight"])
         else:
             self.w_qkv = tensors["q_proj.weight"].contiguous()
         self.w_o = tensors["o_proj.weight"].contiguous()

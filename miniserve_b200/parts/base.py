@@ -105,9 +105,23 @@ class Part:
     def weights(self) -> dict[str, WeightDecl]:
         return {}
 
+    def stacks(self) -> dict[str, tuple[str, ...]]:
+        """Tensors this part wants joined along their first axis: ``{joined name: (declared names,
+        in order)}``. Whoever provides the weights (the loader, the random-weights mode) may then
+        hand ``bind`` the joined tensor under its name INSTEAD of the parts it is made of, built in
+        place in one buffer; a part that declares a stack accepts either."""
+        return {}
+
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for name in self.weights():
             setattr(self, "w_" + name.replace(".", "_"), tensors[name])
+
+    @staticmethod
+    def joined(tensors: Mapping[str, torch.Tensor], name: str, parts: tuple[str, ...]) -> torch.Tensor:
+        """The stack ``name`` from what ``bind`` was given: the joined tensor itself, or its parts."""
+        if name in tensors:
+            return tensors[name].contiguous()
+        return torch.cat([tensors[p] for p in parts], dim=0).contiguous()
 
     def sub_parts(self) -> dict[str, "Part"]:
         """Child parts by their tensor-name prefix."""
@@ -119,8 +133,15 @@ class Part:
             out.update(part.all_weights(prefix + sub_prefix))
         return out
 
+    def all_stacks(self, prefix: str = "") -> dict[str, tuple[str, ...]]:
+        out = {prefix + k: tuple(prefix + p for p in v) for k, v in self.stacks().items()}
+        for sub_prefix, part in self.sub_parts().items():
+            out.update(part.all_stacks(prefix + sub_prefix))
+        return out
+
     def bind_all(self, tensors: Mapping[str, torch.Tensor], prefix: str = "") -> None:
-        self.bind({k: tensors[prefix + k] for k in self.weights()})
+        names = list(self.weights()) + list(self.stacks())
+        self.bind({k: tensors[prefix + k] for k in names if prefix + k in tensors})
         for sub_prefix, part in self.sub_parts().items():
             part.bind_all(tensors, prefix + sub_prefix)
 

@@ -30,7 +30,7 @@ class DecoderModel:
         self.layers = [build_block(layer, self.env) for layer in spec.layers]
         self.prefixes = [layer.prefix for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, self.env)
-        self.final_norm_name = spec.final_norm.get("name", "model.norm.")
+        self.final_norm_name = spec.final_norm_prefix
         self.head = build_part("head", spec.head, self.env)
         self.entry_caches: list[EntryCache] = []
         for i, e in enumerate(spec.run_order):
@@ -64,6 +64,13 @@ class DecoderModel:
             out.update(layer.all_weights(prefix))
         out.update(self.final_norm.all_weights(self.final_norm_name))
         out.update(self.head.all_weights())
+        return out
+
+    def weight_stacks(self) -> dict[str, tuple[str, ...]]:
+        """Tensors that parts want joined (``Part.stacks``), by full name."""
+        out: dict[str, tuple[str, ...]] = {}
+        for prefix, layer in zip(self.prefixes, self.layers):
+            out.update(layer.all_stacks(prefix))
         return out
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:

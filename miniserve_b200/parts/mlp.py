@@ -26,8 +26,11 @@ class SwiGLU(Part):
             "down_proj.weight": WeightDecl((self.hidden, self.inter)),
         }
 
+    def stacks(self):
+        return {"gate_up_proj.weight": ("gate_proj.weight", "up_proj.weight")}
+
     def bind(self, tensors):
-        self.w_gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0).contiguous()
+        self.w_gate_up = self.joined(tensors, "gate_up_proj.weight", self.stacks()["gate_up_proj.weight"])
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x, ctx) -> torch.Tensor:

@@ -1,8 +1,9 @@
-"""Offline stress run: many requests of random length at once, run to completion.
+"""Offline stress run: many requests of random length, all submitted at once and run to the end.
 
-Checks that the engine neither stalls nor loses pages under cache pressure and reports how
-often requests were preempted; it measures no speed. Options as in
-miniserve/tools/stress.py:27-84.
+It answers whether the engine gets through cache pressure (no stall, no page lost, everything
+finished) and says how often it had to preempt; tokens per second are reported but it is no
+benchmark. The workload options and the keys of the report are those of
+miniserve/tools/stress.py:27-84, so that runs of the two engines can be laid side by side.
 
     python -m miniserve_b200.tools.stress --random tiny-b --num-requests 64 --kv-pool-tokens 2048
 """
@@ -13,8 +14,38 @@ import argparse
 import json
 import random
 import sys
+import time
 
 from ..engine.cli import add_engine_args, add_model_args, engine_kwargs
+
+
+class Watcher:
+    """What a stress run notes after every step (``Engine.generate(on_step=...)``)."""
+
+    def __init__(self):
+        self.steps = 0
+        self.by_phase = {"prefill": 0, "mixed": 0, "decode": 0}
+        self.widest_decode = 0
+        self.most_pages = 0
+
+    def __call__(self, engine, plan) -> None:
+        self.steps += 1
+        if plan is not None:
+            self.by_phase[plan.phase] += 1
+            self.widest_decode = max(self.widest_decode, plan.num_decode)
+        self.most_pages = max([self.most_pages] + [g.allocator.num_used for g in engine.cache.groups])
+        engine.cache.check_invariants()
+
+
+def workload(vocab: int, count: int, prompt_len, new_tokens, seed: int, temperature: float, top_p: float):
+    from ..engine import SamplingParams
+
+    rng = random.Random(seed)
+    prompts, params = [], []
+    for _ in range(count):
+        prompts.append([rng.randrange(vocab) for _ in range(rng.randint(*prompt_len))])
+        params.append(SamplingParams(rng.randint(*new_tokens), frozenset(), temperature, top_p))
+    return prompts, params
 
 
 def main(argv=None) -> int:
@@ -28,55 +59,44 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--capture-graphs-at-start", action="store_true",
-                    help="capture the decode graphs before the clock starts (else each at its first use, inside the timed run)")
-    ap.add_argument("--max-steps", type=int, default=1_000_000, help="fail if not done after this many steps")
+                    help="capture every decode graph before the clock starts instead of at its first use")
+    ap.add_argument("--max-steps", type=int, default=1_000_000, help="give up (exit code 1) after this many steps")
     args = ap.parse_args(argv)
-
-    from ..engine import LLM, RequestState, SamplingParams
-
-    llm = LLM(args.model, random=args.random, weights_seed=args.weights_seed, dtype=args.dtype, **engine_kwargs(args))
-    eng = llm.engine
-    if args.capture_graphs_at_start:
-        eng.capture_graphs(("greedy",) if args.temperature == 0 else ("temperature", "top_p") if args.top_p < 1 else ("temperature",))
-    vocab = llm.model.spec.vocab_size
-    rng = random.Random(args.workload_seed)
-    reqs = []
-    for _ in range(args.num_requests):
-        prompt = [rng.randrange(vocab) for _ in range(rng.randint(*args.prompt_len))]
-        params = SamplingParams(rng.randint(*args.max_new_tokens), frozenset(), args.temperature, args.top_p)
-        reqs.append(eng.add_request(prompt, params))
-    import time
 
     import torch
 
-    steps = max_decode_batch = max_used = 0
-    phases = {"prefill": 0, "mixed": 0, "decode": 0}
+    from ..engine import LLM
+
+    llm = LLM(args.model, random=args.random, weights_seed=args.weights_seed, dtype=args.dtype, **engine_kwargs(args))
+    engine = llm.engine
+    if args.capture_graphs_at_start:
+        modes = ("greedy",) if args.temperature == 0 else ("temperature", "top_p") if args.top_p < 1 else ("temperature",)
+        engine.capture_graphs(modes)
+    prompts, params = workload(llm.model.spec.vocab_size, args.num_requests, args.prompt_len, args.max_new_tokens,
+                               args.workload_seed, args.temperature, args.top_p)
+    watch = Watcher()
     torch.cuda.synchronize()
     began = time.perf_counter()
-    while eng.has_unfinished:
-        if steps >= args.max_steps:
-            print(f"not finished after {steps} steps", file=sys.stderr)
-            return 1
-        plan = eng.step()
-        steps += 1
-        if plan is not None:
-            phases[plan.phase] += 1
-            if plan.phase != "prefill":
-                max_decode_batch = max(max_decode_batch, plan.num_decode)
-        max_used = max(max_used, max(g.allocator.num_used for g in eng.cache.groups))
-        eng.cache.check_invariants()
+    try:
+        outputs = engine.generate(prompts, params, on_step=watch, max_steps=args.max_steps)
+    except RuntimeError as e:
+        print(e, file=sys.stderr)
+        return 1
     torch.cuda.synchronize()
     seconds = time.perf_counter() - began
+    finished = all(len(o) == p.max_new_tokens for o, p in zip(outputs, params))  # no stop tokens are set
+    prompt_tokens, output_tokens = sum(map(len, prompts)), sum(map(len, outputs))
     report = dict(
-        engine=engine_kwargs(args), num_requests=len(reqs), seconds=round(seconds, 3), steps_by_phase=phases,
-        tokens_per_second=round(sum(len(r.prompt_ids) + len(r.output_ids) for r in reqs) / seconds, 1),
-        prompt_tokens=sum(len(r.prompt_ids) for r in reqs), output_tokens=sum(len(r.output_ids) for r in reqs),
-        steps=steps, max_decode_batch=max_decode_batch, max_pages_used=max_used, pool_pages=eng.cache.num_pages,
-        preemptions=eng.scheduler.num_preemptions, preempted_requests=sum(r.num_preemptions > 0 for r in reqs),
-        all_finished=all(r.state is RequestState.FINISHED for r in reqs), pages_returned=eng.cache.is_idle(),
+        engine=engine_kwargs(args), num_requests=len(prompts), seconds=round(seconds, 3), steps_by_phase=watch.by_phase,
+        tokens_per_second=round((prompt_tokens + output_tokens) / seconds, 1),
+        prompt_tokens=prompt_tokens, output_tokens=output_tokens,
+        steps=watch.steps, max_decode_batch=watch.widest_decode, max_pages_used=watch.most_pages,
+        pool_pages=engine.cache.num_pages, preemptions=engine.scheduler.num_preemptions,
+        preempted_requests=engine.scheduler.num_preempted_requests,
+        all_finished=finished, pages_returned=engine.cache.is_idle(),
     )
     print(json.dumps(report, indent=2))
-    return 0 if report["all_finished"] and report["pages_returned"] else 1
+    return 0 if finished and report["pages_returned"] else 1
 
 
 if __name__ == "__main__":

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Any, Mapping
+from typing import Any, Mapping, Sequence
 
 import torch
 
@@ -19,21 +19,32 @@ from ..parts.base import WeightDecl
 
 
 def random_tensors(decls: Mapping[str, WeightDecl], seed: int, dtype: torch.dtype = torch.bfloat16,
-                   std: float = 0.02, device: torch.device | str = "cpu",
-                   draw_on_device: bool = False) -> dict[str, torch.Tensor]:
+                   std: float = 0.02, device: torch.device | str = "cpu", draw_on_device: bool = False,
+                   stacks: Mapping[str, Sequence[str]] | None = None) -> dict[str, torch.Tensor]:
     """``draw_on_device``: draw with the device's generator instead (fast for large models,
-    but the values then depend on the device type)."""
+    but the values then depend on the device type). ``stacks``: declared tensors that a part
+    wants joined (``Part.stacks``); each piece is drawn as it would be alone and written straight
+    into the joined tensor, which comes back under the stack's name instead of its pieces."""
+    from .loader import StackPlan
+
     gen_device = torch.device(device) if draw_on_device else torch.device("cpu")
     gen = torch.Generator(device=gen_device).manual_seed(seed)
+    plan = StackPlan(decls, stacks)
     out: dict[str, torch.Tensor] = {}
     for name, decl in decls.items():
         if decl.precision == "int32":
-            out[name] = torch.zeros(decl.shape, dtype=torch.int32, device=device)
-            continue
-        t = torch.randn(decl.shape, generator=gen, dtype=torch.float32, device=gen_device)
-        t = (1.0 + 0.1 * t) if decl.init == "ones_normal" else std * t
-        keep32 = decl.precision in ("float32", "stored")
-        out[name] = t.to(device=device, dtype=torch.float32 if keep32 else dtype).contiguous()
+            t, want = torch.zeros(decl.shape, dtype=torch.int32, device=device), torch.int32
+        else:
+            t = torch.randn(decl.shape, generator=gen, dtype=torch.float32, device=gen_device)
+            t = (1.0 + 0.1 * t) if decl.init == "ones_normal" else std * t
+            want = torch.float32 if decl.precision in ("float32", "stored") else dtype
+        if name in plan.place:
+            joined, row = plan.place[name]
+            if joined not in out:
+                out[joined] = torch.empty(plan.shape[joined], dtype=want, device=device)
+            out[joined][row:row + decl.shape[0]].copy_(t)
+        else:
+            out[name] = t.to(device=device, dtype=want).contiguous()
     return out
 
 

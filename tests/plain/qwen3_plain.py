@@ -136,7 +136,8 @@ def attention_block(cfg: dict, w: dict, i: int, x: torch.Tensor, positions: torc
     k = rms_norm(k, w[p + "k_norm.weight"], cfg["eps"])
     cos, sin = rope_cos_sin(positions, cfg["head_dim"], cfg["theta"], x.dtype)
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    o = causal_attention(q, k, v)
+    windows = cfg.get("windows")  # not a Qwen3 key: tests of windowed layers add a window (or None) per layer
+    o = causal_attention(q, k, v, window=windows[i] if windows else None)
     return o.reshape(t, cfg["heads"] * cfg["head_dim"]) @ w[p + "o_proj.weight"].T
 
 

@@ -248,7 +248,7 @@ def _pack(tables_by_group, q_start, q_len, ids, want, pad_rows=0, pad_page=(99,)
     qs, ql, tok, ss, wa, pp = arr(q_start), arr(q_len), arr(ids), arr([5] * rows), arr(want), arr(list(pad_page))
     total = lib.ms_pack_step(arena.ctypes.data, arena.size, offsets, rows, pad_rows, qs.ctypes.data, ql.ctypes.data,
                              tok.ctypes.data, ss.ctypes.data, wa.ctypes.data, len(want), groups, handles,
-                             pp.ctypes.data, indices_cap, int(want_pad))
+                             pp.ctypes.data, indices_cap, int(want_pad), 64)
     return total, arena, list(offsets)
 
 
@@ -268,7 +268,7 @@ def test_packer_against_a_naive_layout():
     assert arena[o[3]:o[3] + R + 1].tolist() == [0, 6, 8, 9]
     assert arena[o[4]:o[4] + R].tolist() == [0, 3, 0]
     assert arena[o[5]:o[5] + R].tolist() == [6, 5, 1]
-    assert arena[o[6]:o[6] + R].tolist() == [5, 5, -1]
+    assert arena[o[6]:o[6] + R].tolist() == [5, 5, 64]  # the padding row gets the spare state slot
     assert arena[o[7]:o[7] + 3].tolist() == [5, 7, 8]
     assert arena[o[8]:o[8] + R + 1].tolist() == [0, 2, 4, 5]
     assert arena[o[9]:o[9] + 5].tolist() == t0.blocks + t1.blocks + [99]
@@ -289,3 +289,80 @@ def test_packer_refuses_inconsistent_steps():
     assert total > 0 and o[10] - o[9] == 8  # fixed room, rounded up to 4 entries
     total, _, _ = _pack([[t]], [0], [5], [1, 2, 3, 4, 5], [4], indices_cap=1)
     assert total < 0
+
+
+def test_packer_packs_only_the_pages_a_windowed_table_still_holds():
+    """A table that has given pages back is packed from the entry below its first live page; the row's
+    base is where entry 0 would be, so kernels index by absolute page number all the same."""
+    a = BlockAllocator(32, 4)
+    t0, t1 = a.new_table(), a.new_table()
+    t0.append_tokens(22)          # pages 0..5
+    assert t0.release_below(17) == 4  # pages 0..3 lie wholly below 17
+    t1.append_tokens(5)
+    t0.append_tokens(1)
+    t1.append_tokens(2)
+    total, arena, o = _pack([[t0, t1]], [22, 5], [1, 2], [1, 2, 3], [0, 2])
+    assert total > 0
+    base0, base1, end = arena[o[8]:o[8] + 3].tolist()
+    packed = arena[o[9]:o[9] + end].tolist()
+    blocks0, blocks1 = t0.blocks, t1.blocks
+    assert end == (len(blocks0) - 3) + len(blocks1)  # three of the four freed entries are not packed at all
+    for page in range(3, len(blocks0)):               # the entry just below the live ones reads -1
+        assert packed[base0 + page] == blocks0[page]
+    assert packed[base0 + 3] == -1 and base0 == -3
+    for page in range(len(blocks1)):
+        assert packed[base1 + page] == blocks1[page]
+    # long decoding behind a window: the packed size stays bounded by what is held
+    for _ in range(200):
+        t0.append_tokens(1)
+        t0.release_below(t0.num_tokens - 10 + 1)
+    total, arena, o = _pack([[t0]], [t0.num_tokens - 1], [1], [7], [0], indices_cap=8)
+    assert total > 0 and t0.num_entries > 50 and t0.num_blocks <= 4
+
+
+def test_groups_may_have_pools_of_different_sizes_and_windows_bound_what_a_request_holds():
+    from miniserve_b200.cache.manager import group_needs, window_pages
+
+    entries = _entries(2, 1, 1)
+    needs, states = group_needs(entries)
+    assert [(n.window, c) for n, c in needs] == [(None, 2), (10, 1)] and len(states) == 1
+    cm = CacheManager(entries, num_pages=[24, 6], page_size=4, max_requests=3, step_tokens=8)
+    assert cm.group_pages() == (24, 6) and cm.num_pages == 24
+    # a long request may hold all its pages in the full group, but only window + step in the windowed one
+    assert cm.pages_for(80) == (20, window_pages(10, 4, 8)) == (20, 6)
+    assert cm.pages_for(7) == (2, 2)
+    with pytest.raises(ValueError, match="page counts"):
+        CacheManager(entries, num_pages=[24], page_size=4, max_requests=3)
+    r = cm.new_request()
+    for _ in range(10):  # 80 tokens in steps of 8: the windowed group never runs out of its 6 pages
+        cm.reserve([(r, 8)])
+        cm.trim(r)
+    assert cm.pages_held(r)[0] == 20 and cm.pages_held(r)[1] <= 6
+    cm.release(r)
+    assert cm.is_idle()
+
+
+def test_host_core_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The allocator, table and packer tests once more in a process whose host core is compiled with
+    -fsanitize=address,undefined (MINISERVE_HOST_SANITIZE=1): an out-of-bounds write, a use after
+    free or signed overflow in the C++ would end that process with a report."""
+    import os
+    import shutil
+    import subprocess
+    import sys
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc to ask for the sanitizer runtime")
+    runtime = subprocess.run([gcc, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    if not os.path.isfile(runtime):
+        pytest.skip("the AddressSanitizer runtime is not installed")
+    env = dict(os.environ, MINISERVE_HOST_SANITIZE="1", MINISERVE_BUILD_DIR=str(tmp_path), LD_PRELOAD=os.path.realpath(runtime),
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    proc = subprocess.run(
+        [sys.executable, "-m", "pytest", os.path.join(here, "test_cache.py"), "-q", "-x", "-p", "no:cacheprovider",
+         "-k", "not sanitizers"], capture_output=True, text=True, env=env, timeout=600, cwd=os.path.dirname(here))
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert (tmp_path / "libms_host_san.so").is_file(), "the sanitized host core was not the one that ran"
+    assert "AddressSanitizer" not in proc.stderr and "runtime error" not in proc.stderr, proc.stderr[-3000:]

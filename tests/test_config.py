@@ -84,7 +84,7 @@ def test_run_order_is_validated():
     cfg = Qwen3Config.from_dict(preset("tiny-a"))
     spec = qwen3_model_spec(cfg)
     kw = {f: getattr(spec, f) for f in ("architecture", "hidden_size", "vocab_size", "embedding", "layers",
-                                         "final_norm", "head")}
+                                         "final_norm", "head", "final_norm_prefix")}
     ModelSpec(run_order=(RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_of=1)), **kw)  # twice, shared: fine
     with pytest.raises(ValueError):
         ModelSpec(run_order=(RunEntry(5),), **kw)

@@ -413,16 +413,11 @@ def test_attention_bf16_decode_window_edge(window):
 
 
 @pytest.fixture(params=[None, (2, 1), (3, 2), (8, 1)], ids=lambda p: "auto" if p is None else f"splits{p[0]}x{p[1]}")
-def key_splits(request):
+def key_splits(request, monkeypatch):
     """Forces how the tcgen05 attention cuts a tile's keys between CTAs (None: its own choice, which
     is no cut for steps as small as a test's): (splits, least key tiles per split)."""
-    from miniserve_b200.ops import native
-
-    lib = native.attn_tc()
-    if request.param is not None:
-        lib.ms_attn_tc_set_splits(*request.param)
-    yield request.param
-    lib.ms_attn_tc_set_splits(0, 0)
+    monkeypatch.setattr(ops, "ATTN_TC_SPLITS", request.param)
+    return request.param
 
 
 TC_SHAPES = [(16, 8, 128, 16), (8, 8, 128, 8), (32, 8, 128, 32), (8, 1, 128, 16), (4, 2, 128, 128), (6, 2, 128, 64)]

@@ -132,6 +132,15 @@ class RunningMeanMixer(Part):
         return FixedState((self.hidden + 1,), torch.float32)
 
     def forward(self, x, ctx, cache):
+        if ctx.decode_only:
+            # one token per row: everything on the device, from the step's own tables, so that the pass can be
+            # captured in a CUDA graph (padding rows carry the spare slot and need no mask)
+            slots = ctx.state_slot.long()
+            state = cache.state[slots]
+            state = torch.where((ctx.q_start == 0)[:, None], torch.zeros_like(state), state)
+            sums, counts = state[:, :-1] + x.float(), state[:, -1:] + 1
+            cache.state[slots] = torch.cat((sums, counts), dim=1)
+            return ((sums / counts) @ self.w.T).to(x.dtype)
         out = torch.empty_like(x)
         at = 0
         for start, n, slot in zip(ctx.host_q_start, ctx.host_q_len, ctx.host_state_slot):
@@ -162,9 +171,9 @@ def _toy_spec(raw):
     return ModelSpec("ToyStateLM", hidden, raw["vocab"],
                      PartSpec("token_embedding", dict(vocab=raw["vocab"], hidden=hidden, name="embed.weight")),
                      layers, (RunEntry(0), RunEntry(1), RunEntry(0)),
-                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"], name="final.")),
+                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"])),
                      PartSpec("linear_head", dict(vocab=raw["vocab"], hidden=hidden, tied=True, name="head.weight",
-                                                  tied_to="embed.weight")))
+                                                  tied_to="embed.weight")), final_norm_prefix="final.")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -200,6 +209,32 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
         cache.release(b)
         cache.release(c)
         assert cache.is_idle()
+        # decode steps replayed from CUDA graphs over the mixer's state: three requests in a bucket of four
+        # (one padding row), token by token after a prompt portion, against the whole-sequence result
+        from miniserve_b200.engine.graphs import DecodeGraphs
+        from miniserve_b200.sampling import Sampler
+
+        cache3 = CacheManager(model.entry_caches, 24, 8, max_requests=4, dtype=dtype, device=DEV)
+        step3 = StepFunction(model, cache3)
+        graphs = DecodeGraphs(step3, Sampler(DEV, 61, 4), 4)
+        seqs = [ids, ids[::-1], ids[5:] + ids[:5]]
+        wholes = []
+        for seq in seqs:
+            rc = cache3.new_request()
+            wholes.append(step3.run([StepRow(rc, seq, range(30))]))
+            cache3.release(rc)
+        rcs = [cache3.new_request() for _ in seqs]
+        step3.run([StepRow(rc, seq[:9], []) for rc, seq in zip(rcs, seqs)])
+        for t in range(9, 30):
+            graphs.run([StepRow(rc, [seq[t]], (0,)) for rc, seq in zip(rcs, seqs)], None)
+            logits = graphs._graphs[(4, "greedy")].logits
+            for r in range(3):
+                assert torch.allclose(logits[r], wholes[r][t], **tol), f"request {r}, token {t}"
+        step3.check_status()
+        assert len(graphs._graphs) == 1 and graphs.replayed_launches > 0
+        for rc in rcs:
+            cache3.release(rc)
+        assert cache3.is_idle()
     finally:
         unregister_part("mixer", "running_mean")
         unregister_architecture("ToyStateLM")
@@ -231,7 +266,6 @@ class TopOneExperts(Part):
     def forward(self, x, ctx):
         from miniserve_b200 import ops
 
-        x = ops.materialize(x)
         logits = x.float() @ self.router.T
         prob, expert = torch.softmax(logits, -1).max(-1)
         self.chosen.append(expert.cpu())
@@ -281,8 +315,9 @@ def _toy_routed_spec(raw):
     return ModelSpec("ToyRoutedLM", hidden, raw["vocab"],
                      PartSpec("token_embedding", dict(vocab=raw["vocab"], hidden=hidden, name="embed.weight")),
                      layers, (RunEntry(0), RunEntry(1)),
-                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"], name="final.")),
-                     PartSpec("linear_head", dict(vocab=raw["vocab"], hidden=hidden, tied=False, name="head.weight")))
+                     PartSpec("rmsnorm", dict(size=hidden, eps=raw["eps"])),
+                     PartSpec("linear_head", dict(vocab=raw["vocab"], hidden=hidden, tied=False, name="head.weight")),
+                     final_norm_prefix="final.")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

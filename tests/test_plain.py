@@ -24,6 +24,20 @@ def test_plain_matches_reference_outputs(name, tmp_path):
     assert (ours - gold["logits"]).abs().max().item() < 2e-5
 
 
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_plain_sampler_matches_the_reference_samplers_noise_and_tokens(name, tmp_path):
+    """The hashed noise (bit for bit) and a continuation sampled at temperature 0.7, as the
+    reference's own sampler produced them (stored by tests/golden/make_golden.py)."""
+    raw, seed = CASES[name]
+    gold = load_file(str(GOLDEN / f"{name}.safetensors"))
+    for (sd, ct), row in zip(gold["noise_keys"].tolist(), gold["noise"]):
+        assert torch.equal(plain.uniform_noise(sd, ct, raw["vocab_size"]), row)
+    plain.write_random_model(tmp_path, raw, seed)
+    cfg, w = plain.read_config(tmp_path), plain.read_weights(tmp_path)
+    prompt = gold["ids"][:9].tolist()
+    assert plain.generate(cfg, w, prompt, 24, temperature=0.7, seed=11) == gold["sampled"].tolist()
+
+
 def test_tiny_configs_differ_in_every_size_and_option():
     a, b = plain.tiny_config_a(), plain.tiny_config_b()
     for key in ("hidden_size", "intermediate_size", "vocab_size", "num_hidden_layers", "num_attention_heads",

@@ -66,6 +66,11 @@ class ToyStep:
         return torch.stack(out) if out else torch.zeros((0, VOCAB))
 
 
+    def reset_after_fault(self):
+        self.status.zero_()
+        self.resets = getattr(self, "resets", 0) + 1
+
+
 class ToySampler:
     def sample(self, logits, temperatures=None, top_ps=None, seeds=None, counters=None, stream=None):
         n = logits.shape[0]
@@ -303,3 +308,72 @@ def test_random_load_equals_each_request_alone(pages, chunk, overlap):
         preemptions += eng.scheduler.num_preemptions
     if pages == 8:
         assert preemptions > 0, "the small pool must actually run out of pages"
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_raised_status_word_ends_the_step_once_and_the_engine_goes_on(overlap):
+    """A kernel that caught a fault raises the status word; the engine reports it once, frees nothing
+    twice, puts the word back and can be used again."""
+    from miniserve_b200.engine.step import StepError
+
+    eng = _engine(pages=32, overlap=overlap)
+    prompts = [[1, 2, 3, 4, 5], [6, 7, 8]]
+    reqs = [eng.add_request(p, SamplingParams(max_new_tokens=6)) for p in prompts]
+    eng.step()
+    eng.step_fn.status[0] = 31  # as a kernel would, from the device
+    with pytest.raises(StepError, match="31"):
+        while eng.has_unfinished:
+            eng.step()
+    assert eng.step_fn.resets == 1 and int(eng.step_fn.status[0]) == 0
+    for r in reqs:  # the caller gives up on what was running; nothing is released twice
+        if not r.is_done:
+            eng.abort(r.rid)
+    eng._inflight = None
+    eng.cache.check_invariants()
+    assert eng.cache.is_idle() and not eng.scheduler.has_unfinished
+    out = eng.generate(prompts, SamplingParams(max_new_tokens=4))
+    assert [len(o) for o in out] == [4, 4] and eng.cache.is_idle()
+
+
+def test_generate_leaves_nothing_behind_when_a_prompt_is_refused():
+    eng = _engine(pages=8, page=4)  # 32 tokens of cache
+    ok, too_long = [1, 2, 3], list(range(30))
+    with pytest.raises(ValueError, match="pool holds"):
+        eng.generate([ok, too_long], SamplingParams(max_new_tokens=8))
+    assert not eng.has_unfinished and not eng.requests and not eng.scheduler.waiting
+    with pytest.raises(ValueError, match="sampling parameters"):
+        eng.generate([ok, ok], [SamplingParams(max_new_tokens=1)])
+    assert eng.generate([ok], SamplingParams(max_new_tokens=3)) == [_alone(ok, SamplingParams(max_new_tokens=3), 0)]
+
+
+def test_engine_describes_itself():
+    eng = _engine(pages=16, chunk=8, max_running=4)
+    d = eng.describe() if eng.model is not None else None
+    assert d is None  # the stand-in engine has no model; the GPU tests check the description of a real one
+
+
+def test_overlap_with_every_running_request_preempted_is_no_stall():
+    """With overlap, a request preempted while its newest token is still on the device cannot be admitted
+    again before that token is read back. If nothing else can run, the step that reads it back launches
+    nothing; that is progress, not a stall (a model with a windowed cache group beside a full one, whose
+    full group is short, gets there)."""
+
+    class CountingStep(ToyStep):
+        def run(self, rows, prev_tokens=None):
+            rows = list(rows)
+            self.cache.reserve([(r.cache, len(r.tokens)) for r in rows])
+            out = [self.logits_of((id(r.cache) % 1000, r.cache.num_tokens, w)) for r in rows for w in r.want]
+            for r in rows:
+                self.cache.trim(r.cache)
+            return torch.stack(out) if out else torch.zeros((0, VOCAB))
+
+    entries = [EntryCache(0, PagedKV(1, 8, window=24)), EntryCache(1, PagedKV(1, 8)), EntryCache(2, PagedKV(1, 8, window=24))]
+    cm = CacheManager(entries, [24, 40], 8, 4, step_tokens=16)
+    eng = Engine(None, cache=cm, step_fn=CountingStep(cm), sampler=ToySampler(), max_running=4, chunked_prefill_size=16,
+                 cuda_graph=False, overlap=True)
+    rng = random.Random(9)
+    prompts = [[rng.randrange(VOCAB) for _ in range(n)] for n in (45, 3, 70, 17, 30)]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=80))
+    assert [len(o) for o in outs] == [80] * 5 and eng.scheduler.num_preemptions > 0
+    cm.check_invariants()
+    assert cm.is_idle()

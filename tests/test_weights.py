@@ -102,3 +102,59 @@ def test_stored_32bit_tensor_stays_when_declared_so(tmp_path):
     decls = {"a": WeightDecl((3,)), "b": WeightDecl((3,), precision="stored"), "t": WeightDecl((4,), precision="int32")}
     w = load_weights(tmp_path, decls, torch.bfloat16, "cpu")
     assert w["a"].dtype == torch.bfloat16 and w["b"].dtype == torch.float32 and w["t"].dtype == torch.int32
+
+
+def test_loader_joins_stacks_in_place_and_follows_rename_and_split_rules(tmp_path):
+    """A checkpoint that names a tensor differently and stores q, k and v as one matrix is read
+    through rules (data of the architecture); the parts' stacks come back joined, equal to the
+    concatenation of their pieces."""
+    from miniserve_b200.config import TensorRule
+
+    raw = preset("tiny-a")
+    write_model_folder(tmp_path, raw, seed=3)
+    model = _model(raw)
+    decls, stacks = model.weight_decls(), model.weight_stacks()
+    assert stacks["model.layers.0.self_attn.qkv_proj.weight"] == tuple(
+        f"model.layers.0.self_attn.{n}_proj.weight" for n in "qkv")
+    plain_load = load_weights(tmp_path, decls, torch.bfloat16, "cpu")
+    joined = load_weights(tmp_path, decls, torch.bfloat16, "cpu", stacks=stacks)
+    for name, pieces in stacks.items():
+        assert name in joined and not any(p in joined for p in pieces)
+        assert torch.equal(joined[name], torch.cat([plain_load[p] for p in pieces]))
+    model.bind(joined)  # the parts take the joined tensors as they are
+    assert model.layers[0].mixer.w_qkv.data_ptr() == joined["model.layers.0.self_attn.qkv_proj.weight"].data_ptr()
+    again = _model(raw)
+    again.bind(plain_load)
+    assert torch.equal(again.layers[1].feed_forward.w_gate_up, model.layers[1].feed_forward.w_gate_up)
+    # the same checkpoint stored the other way: the final norm under another name, q|k|v of layer 1 as one matrix
+    tensors = load_file(str(tmp_path / "model.safetensors"))
+    tensors["final_layernorm.scale"] = tensors.pop("model.norm.weight")
+    pre = "model.layers.1.self_attn."
+    fused = torch.cat([tensors.pop(pre + f"{n}_proj.weight") for n in "qkv"])
+    tensors[pre + "fused_qkv.weight"] = fused
+    other = tmp_path / "renamed"
+    other.mkdir()
+    save_file(tensors, str(other / "model.safetensors"))
+    rows = [decls[pre + f"{n}_proj.weight"].shape[0] for n in "qkv"]
+    rules = (TensorRule.rename("final_layernorm.scale", "model.norm.weight"),
+             TensorRule.split(pre + "fused_qkv.weight", *[(pre + f"{n}_proj.weight", r) for n, r in zip("qkv", rows)]))
+    mapped = load_weights(other, decls, torch.bfloat16, "cpu", rules=rules, stacks=stacks)
+    assert set(mapped) == set(joined) and all(torch.equal(mapped[k], joined[k]) for k in joined)
+    with pytest.raises(CheckpointMismatch) as ei:  # without the rules the same folder does not match, in one error
+        load_weights(other, decls, torch.bfloat16, "cpu", stacks=stacks)
+    assert "model.norm.weight" in ei.value.missing and pre + "fused_qkv.weight" in ei.value.unexpected
+    bad = (rules[0], TensorRule.split(pre + "fused_qkv.weight", (pre + "q_proj.weight", rows[0]), (pre + "k_proj.weight", 1)))
+    with pytest.raises(CheckpointMismatch) as ei:
+        load_weights(other, decls, torch.bfloat16, "cpu", rules=bad, stacks=stacks)
+    assert any("cannot be cut" in w for w in ei.value.wrong_shape) and pre + "v_proj.weight" in ei.value.missing
+
+
+def test_random_weights_fill_stacks_with_the_values_the_pieces_would_have():
+    raw = preset("tiny-b")
+    model = _model(raw)
+    decls, stacks = model.weight_decls(), model.weight_stacks()
+    alone = random_tensors(decls, 9)
+    joined = random_tensors(decls, 9, stacks=stacks)
+    for name, pieces in stacks.items():
+        assert torch.equal(joined[name], torch.cat([alone[p] for p in pieces]))
+    assert torch.equal(joined["lm_head.weight"], alone["lm_head.weight"])
