@@ -123,8 +123,12 @@ def test_generation_far_past_the_window_with_and_without_graphs(folder, dtype, c
         if dtype == "float32":
             assert o == plain.generate(cfg, w, p, 80)
         else:
-            seq = list(p)
-            for t in o[:40]:  # teacher-forced: every chosen token is (nearly) the plain implementation's best
-                logits = plain.all_logits(cfg, w, seq)[-1]
-                assert (logits.max() - logits[t]).item() <= 0.08, f"token {t} at {len(seq)}"
-                seq.append(t)
+            # teacher-forced: every chosen token is the plain implementation's best up to what rounding to
+            # bfloat16 moves logits by (measured on this very sequence: two logits that far apart may swap)
+            seq = list(p) + o[:40]
+            exact = plain.all_logits(cfg, w, seq)
+            rough = plain.all_logits(cfg, folder["w16"], seq).float()
+            slack = 2 * (rough - exact).abs().max().item()
+            for i, t in enumerate(o[:40]):
+                logits = exact[len(p) + i - 1]
+                assert (logits.max() - logits[t]).item() <= slack, f"token {t} at {len(p) + i}: beyond {slack:.3f}"
