@@ -9,8 +9,14 @@ It prints ONE JSON line: ``value`` is decoded tokens per second timed on the dev
 K steps; ``e2e`` is the same through the Python entry point with host tokens in and out;
 ``prefill`` is one 2,048-token prompt; ``roofline`` is the decode step's bytes (every weight it
 uses once, and the cache of the live requests) over its time against the measured copy
-bandwidth; ``points`` holds decode at batch 1 and 64. This engine runs on one GPU: for N > 1
-it prints a line that says so and exits with 2.
+bandwidth; ``points`` holds decode at batch 1 and 64 and at batch 8 behind 8,192 tokens. This
+engine runs on one GPU: for N > 1 it prints a line that says so and exits with 2.
+
+``--config 8b`` and ``--config 32b`` run the two larger workloads instead (Qwen3-8B shapes: 32
+requests with prompts of 128 to 4,096 tokens and 128 output tokens; Qwen3-32B shapes: 16 requests
+with 8,192-token prompts and 128 output tokens, in a pool too small for all of them) through
+``Engine.generate`` and print one line with tokens per second, the mean time of decode and of
+mixed steps, their fraction of the measured peaks, and the number of preemptions.
 """
 
 from __future__ import annotations
@@ -288,6 +294,8 @@ def run_ours(args) -> dict:
         pms, _, _ = time_decode(eng, b, CONTEXT, min(args.steps, 128), args.warmup)
         points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
     points[f"decode_b{args.batch}"] = round(value, 1)
+    long_ms, _, _ = time_decode(eng, 8, 4 * CONTEXT, min(args.steps, 64), args.warmup)
+    points[f"decode_b8_ctx{4 * CONTEXT}"] = round(8 * 1000.0 / long_ms, 1)
 
     pre_ms = time_prefill(eng, PREFILL_TOKENS)
     pre_flops = flops_of_prefill(raw, PREFILL_TOKENS)
@@ -312,13 +320,105 @@ def run_ours(args) -> dict:
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(round(launches * args.steps)),
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4),
-                    "frac": round(pre_flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(pre_flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peak": "burst"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"],
                      "step_bytes": int(step_bytes)},
         "points": points,
         "clocks": clocks,
     }
+
+
+WORKLOADS = {
+    # BASELINE config 4: continuous batching with a 2,048-token chunk budget, prompts uniform in [128, 4096]
+    "8b": dict(preset="8b", requests=32, prompt=(128, 4096), new_tokens=128, pool_pages=None),
+    # BASELINE config 5: 16 prompts of 8,192 tokens in a pool that admits nine of them (a prompt and one token
+    # each) and has 20 pages to spare: their 128 decoded tokens need 72, so admission stops AND requests are preempted
+    "32b": dict(preset="32b", requests=16, prompt=(8192, 8192), new_tokens=128, pool_pages=9 * 513 + 20),
+}
+
+
+def run_workload(args) -> dict:
+    import torch
+
+    from miniserve_b200.config import preset
+    from miniserve_b200.engine import LLM, SamplingParams
+
+    peaks = load_peaks()
+    wl = WORKLOADS[args.config]
+    raw = preset(wl["preset"])
+    full_layers = raw["num_hidden_layers"]
+    if args.layers is not None:
+        raw["num_hidden_layers"] = args.layers
+    rng = random.Random(0)
+    prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(rng.randint(*wl["prompt"]))] for _ in range(wl["requests"])]
+    need = sum(len(p) + wl["new_tokens"] for p in prompts)
+    pool_tokens = wl["pool_pages"] * 16 if wl["pool_pages"] else need + 4096
+    llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=pool_tokens, page_size=16, max_running=64,
+              chunked_prefill_size=2048)
+    eng = llm.engine
+    eng.capture_graphs(("greedy",))
+    weight_bytes, kv_per_token = llm.model.weight_bytes(), eng.cache.bytes_per_token()
+    h, inter = raw["hidden_size"], raw["intermediate_size"]
+    nq, nkv, d, layers = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["num_hidden_layers"]
+    per_token_flops = 2.0 * ((nq + 2 * nkv) * d * h + nq * d * h + 3 * h * inter) * layers
+    events, steps = [], []
+
+    def on_step(engine, plan):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        events.append(ev)
+        if plan is None:
+            steps.append(None)
+            return
+        ctx = sum(r.start + r.count for r in plan.rows)
+        # attention flops of the step: every new token against the keys before and with it
+        att = sum(4.0 * nq * d * (r.count * r.start + r.count * (r.count + 1) / 2) for r in plan.rows) * layers
+        steps.append((plan.phase, plan.num_tokens, len(plan.rows), ctx, att))
+
+    sampler = ClockSampler()
+    sampler.start()
+    torch.cuda.synchronize()
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    t0 = time.perf_counter()
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=wl["new_tokens"]), on_step=on_step)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    clocks = sampler.stop()
+    # device time of a step: from the end of the step before it to its own end
+    times, prev = [], first
+    for ev in events:
+        times.append(prev.elapsed_time(ev))
+        prev = ev
+    decode = [(ms, s) for ms, s in zip(times, steps) if s is not None and s[0] == "decode"]
+    mixed = [(ms, s) for ms, s in zip(times, steps) if s is not None and s[0] != "decode" and s[1] >= 2040]
+    out_tokens = sum(len(o) for o in outs)
+    result = {
+        "impl": "ours", "workload": f"Qwen3-{args.config.upper()} shapes, {wl['requests']} requests, prompts {wl['prompt'][0]}..{wl['prompt'][1]}, "
+                                    f"{wl['new_tokens']} output tokens each, chunk budget 2048",
+        "layers": layers, "layers_full_model": full_layers, "dtype": "bf16", "kv_pool_tokens": pool_tokens,
+        "tokens_needed_at_once": need, "seconds": round(seconds, 3),
+        "value": round((sum(map(len, prompts)) + out_tokens) / seconds, 1), "unit": "tokens/s (prompt + output)",
+        "output_tokens_per_s": round(out_tokens / seconds, 1), "steps": len(times),
+        "preemptions": eng.scheduler.num_preemptions, "preempted_requests": eng.scheduler.num_preempted_requests,
+        "all_finished": all(len(o) == wl["new_tokens"] for o in outs), "pages_returned": eng.cache.is_idle(),
+        "weight_bytes": weight_bytes, "clocks": clocks,
+    }
+    if decode:
+        ms = statistics.mean(t for t, _ in decode)
+        byts = statistics.mean(weight_bytes + s[3] * kv_per_token for _, s in decode)
+        result["decode_steps"] = {"count": len(decode), "mean_ms": round(ms, 3), "mean_batch": round(statistics.mean(s[2] for _, s in decode), 1),
+                                  "mean_bytes": int(byts), "achieved_gbs": round(byts / ms / 1e6, 1),
+                                  "frac_of_hbm_peak": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4), "peaks": peaks["source"]}
+    if mixed:
+        ms = statistics.mean(t for t, _ in mixed)
+        flops = statistics.mean(per_token_flops * s[1] + s[4] for _, s in mixed)
+        result["full_chunk_steps"] = {"count": len(mixed), "mean_ms": round(ms, 3), "mean_tokens": round(statistics.mean(s[1] for _, s in mixed), 1),
+                                      "achieved_tflops": round(flops / ms / 1e9, 1),
+                                      "frac_of_bf16_peak": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 4),
+                                      "peak": "sustained"}
+    return result
 
 
 def run_reference(args) -> dict:
@@ -345,8 +445,19 @@ def run_reference(args) -> dict:
         if raw.get("tie_word_embeddings"):
             weights["lm_head.weight"] = weights["model.embed_tokens.weight"]
         model = Qwen3ForCausalLM(Qwen3Config.from_dict(raw), weights)
-        eng = Engine(model, max_running=64, kv_pool_tokens=64 * (CONTEXT + DECODE_TOKENS) + 4096,
-                     radix=False, chunked_prefill_size=2048)
+        # the faster of the reference's two stock configurations: its fused FlashInfer operators (--fused-ops),
+        # where they build and run on this box; otherwise its default operators, with the reason
+        kw = dict(max_running=64, kv_pool_tokens=64 * (CONTEXT + DECODE_TOKENS) + 4096, radix=False, chunked_prefill_size=2048)
+        operators = "fused (fused_ops=True)"
+        try:
+            eng = Engine(model, fused_ops=True, **kw)
+            probe = eng.add_request([1, 2, 3], SamplingParams(max_new_tokens=2))
+            while eng.has_unfinished:
+                eng.step()
+            del probe
+        except Exception as e:  # noqa: BLE001
+            operators = f"default (fused_ops=True failed: {type(e).__name__}: {e})"[:160]
+            eng = Engine(model, **kw)
         rng = random.Random(1)
         prompts = [[rng.randrange(raw["vocab_size"]) for _ in range(CONTEXT)] for _ in range(args.batch)]
         reqs = [eng.add_request(p, SamplingParams(max_new_tokens=args.steps + args.warmup + 64)) for p in prompts]
@@ -372,7 +483,8 @@ def run_reference(args) -> dict:
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (token ids uniform over the vocabulary, random-init weights)",
         "config": {"model": "Qwen3-0.6B shapes", "layers": raw["num_hidden_layers"], "global_batch": args.batch,
-                   "seq_len": CONTEXT, "engine": "miniserve Engine.step (paged, CUDA graphs, overlap), wall clock"},
+                   "seq_len": CONTEXT, "engine": "miniserve Engine.step (paged, CUDA graphs, overlap), wall clock",
+                   "operators": operators},
         "e2e": {"value": round(args.batch * 1000.0 / ms, 1), "unit": "tokens/s"},
         "clocks": clocks,
     }
@@ -389,6 +501,8 @@ def main() -> int:
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--config", choices=["0.6b", "8b", "32b"], default="0.6b",
+                    help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -401,7 +515,10 @@ def main() -> int:
         args.warmup = 3
     global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.config != "0.6b" and args.impl == "ours":
+        result = run_workload(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
 

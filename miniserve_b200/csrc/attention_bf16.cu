@@ -256,31 +256,11 @@ constexpr int DC_WARPS = 4, DC_THREADS = DC_WARPS * 32, DC_STAGES = 3, DC_SLICE 
 
 struct DecodeSmem {
   static constexpr int q_elems = 16 * DPAD;
-  static constexpr int new_elems = 2 * D;  // this step's own key and value of the CTA's kv head (DecodeProj)
-  static constexpr int head_elems = q_elems + new_elems;
   static constexpr int stage_elems = 2 * DC_SLICE * DPAD;  // K slice then V slice
   static constexpr int pipe_elems = DC_WARPS * DC_STAGES * stage_elems;
-  static constexpr size_t bytes_pipe = (size_t)(head_elems + pipe_elems) * 2;
-  static constexpr size_t bytes_merge = (size_t)(DC_WARPS + 1) * 16 * (D + 2) * 4 + (size_t)head_elems * 2;
+  static constexpr size_t bytes_pipe = (size_t)(q_elems + pipe_elems) * 2;
+  static constexpr size_t bytes_merge = (size_t)(DC_WARPS + 1) * 16 * (D + 2) * 4 + (size_t)q_elems * 2;
   static constexpr size_t bytes = bytes_pipe > bytes_merge ? bytes_pipe : bytes_merge;
-};
-
-// When `qkv` is set, the kernel takes the q|k|v projection as it left the matrix product and does
-// itself what otherwise a kernel before it does (rope_kv.cu, same arithmetic): the per-head RMSNorm
-// of q and k, the rotation by position, and the write of the new key and value into their page
-// (miniserve/model/qwen3.py:118-123, miniserve/cache/kv_pool.py:46-50). Every CTA prepares the
-// queries of its own heads; the CTAs whose key range holds the newest position prepare the new key
-// and value, use them from shared memory, and one of them stores them for later steps.
-struct DecodeProj {
-  const __nv_bfloat16* qkv;        // [rows, (nq + 2 nkv) * D], or null: `q` holds finished queries and the cache is complete
-  const __nv_bfloat16* q_norm_w;   // [D] or null (no norm)
-  const __nv_bfloat16* k_norm_w;
-  const float* cos_sin;            // [rows, rot]: cos then sin of every rotation pair, or null (no rotation)
-  __nv_bfloat16* k_pool;           // the pools again, writable
-  __nv_bfloat16* v_pool;
-  int* status;                     // raised when the newest position has no page
-  int rot;                         // rotated width (0 without rotation)
-  float eps;
 };
 
 __global__ void __launch_bounds__(DC_THREADS)
@@ -289,7 +269,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
                    float scale_log2, int window, int page_shift, int num_splits, int* __restrict__ counters,
-                   int cluster_merge, const DecodeProj proj) {
+                   int cluster_merge) {
   // Until pdl_wait() below, only data written before this step is touched: the step's metadata and
   // the keys and values of older tokens. So the CTA may start streaming them while the kernels
   // before it (the q/k/v projection, the rotation and cache write) are still running.
@@ -308,8 +288,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* knew = qs + DecodeSmem::q_elems;  // [2][D]: the new key, then the new value
-  __nv_bfloat16* pipe = qs + DecodeSmem::head_elems + warp * DC_STAGES * DecodeSmem::stage_elems;
+  __nv_bfloat16* pipe = qs + DecodeSmem::q_elems + warp * DC_STAGES * DecodeSmem::stage_elems;
 
   PagedKV kv{k_pool, v_pool, page_indices + page_indptr[r], kvh, nkv, page_shift};
 
@@ -352,75 +331,14 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     issue(issued);
   }
   pdl_wait();
-  const bool projected = proj.qkv != nullptr;
-  const bool holds_newest = projected && s_begin <= newest_slice && newest_slice < s_end;
-  if (!projected) {
-    for (int idx = tid; idx < 16 * CHUNKS; idx += DC_THREADS) {
-      const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row < heads_here) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + head0 + row) * D + chunk * 8);
-      *reinterpret_cast<uint4*>(qs + row * DPAD + chunk * 8) = v;
-    }
-  } else {
-    // one warp per item: 0..15 the query rows of this CTA, 16 the new key, 17 the new value
-    const __nv_bfloat16* row_in = proj.qkv + (size_t)r * (nq + 2 * nkv) * D;
-    const int rot = proj.cos_sin ? proj.rot : 0, half = rot >> 1;
-    const float* cs = proj.cos_sin ? proj.cos_sin + (size_t)r * rot : nullptr;
-    for (int item = warp; item < 18; item += DC_WARPS) {
-      if (item >= 16 && !holds_newest) continue;
-      if (item < 16 && item >= heads_here) {
-        if (lane < CHUNKS) *reinterpret_cast<uint4*>(qs + item * DPAD + lane * 8) = make_uint4(0u, 0u, 0u, 0u);
-        continue;
-      }
-      const __nv_bfloat16* src = item < 16 ? row_in + (size_t)(head0 + item) * D
-                                           : row_in + (size_t)(nq + (item == 17 ? nkv : 0) + kvh) * D;
-      __nv_bfloat16* dst = item < 16 ? qs + item * DPAD : knew + (item - 16) * D;
-      if (item == 17) {
-        if (lane < CHUNKS) *reinterpret_cast<uint4*>(dst + lane * 8) = *reinterpret_cast<const uint4*>(src + lane * 8);
-        continue;
-      }
-      const __nv_bfloat16* nw = item < 16 ? proj.q_norm_w : proj.k_norm_w;
-      float inv = 1.f;
-      if (nw) {
-        float ss = 0.f;
-        for (int c = lane; c < D; c += 32) {
-          const float x = __bfloat162float(src[c]);
-          ss += x * x;
-        }
-        ss = warp_sum(ss);
-        inv = 1.0f / sqrtf(ss / (float)D + proj.eps);
-      }
-      for (int j = lane; j < half; j += 32) {
-        float lo = __bfloat162float(src[j]), hi = __bfloat162float(src[j + half]);
-        if (nw) {
-          lo = (lo * inv) * __bfloat162float(nw[j]);
-          hi = (hi * inv) * __bfloat162float(nw[j + half]);
-        }
-        const float c1 = cs[j], s1 = cs[half + j];
-        dst[j] = __float2bfloat16_rn(lo * c1 - hi * s1);
-        dst[j + half] = __float2bfloat16_rn(hi * c1 + lo * s1);
-      }
-      for (int c = rot + lane; c < D; c += 32) {  // beyond the rotated part: normalised only
-        float x = __bfloat162float(src[c]);
-        if (nw) x = (x * inv) * __bfloat162float(nw[c]);
-        dst[c] = __float2bfloat16_rn(x);
-      }
-    }
+  for (int idx = tid; idx < 16 * CHUNKS; idx += DC_THREADS) {
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < heads_here) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + head0 + row) * D + chunk * 8);
+    *reinterpret_cast<uint4*>(qs + row * DPAD + chunk * 8) = v;
   }
   for (; issued < DC_STAGES - 1; ++issued) issue(issued);
   __syncthreads();
-  if (holds_newest && blockIdx.z % chunks_per_group == 0 && tid < 2 * CHUNKS) {
-    // the new key and value go into their page for the steps to come (one CTA per request and kv head)
-    const int pos = kv_len - 1, page = kv.pages[pos >> page_shift];
-    if (page < 0) {  // a page the window has given back, or a table that is too short
-      if (tid == 0) atomicExch(proj.status, 2);
-    } else {
-      const int which = tid / CHUNKS, chunk = tid - which * CHUNKS;
-      __nv_bfloat16* pool = which ? proj.v_pool : proj.k_pool;
-      const size_t off = ((((size_t)page * nkv + kvh) << page_shift) + (pos & ((1 << page_shift) - 1))) * D;
-      *reinterpret_cast<uint4*>(pool + off + chunk * 8) = *reinterpret_cast<const uint4*>(knew + which * D + chunk * 8);
-    }
-  }
   uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
   if (Q_IN_REGS) {
 #pragma unroll
@@ -432,17 +350,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     issue(i + DC_STAGES - 1);
     cp_async_wait<DC_STAGES - 1>();
     __syncwarp();
-    __nv_bfloat16* kt = pipe + (i % DC_STAGES) * DecodeSmem::stage_elems;
-    __nv_bfloat16* vt = kt + DC_SLICE * DPAD;
-    if (holds_newest && my_first + i * DC_WARPS == newest_slice) {
-      // the copy brought what the page held before this step: put the new key and value in its place
-      const int row = kv_len - 1 - newest_slice * DC_SLICE;
-      if (lane < CHUNKS) {
-        *reinterpret_cast<uint4*>(kt + row * DPAD + lane * 8) = *reinterpret_cast<const uint4*>(knew + lane * 8);
-        *reinterpret_cast<uint4*>(vt + row * DPAD + lane * 8) = *reinterpret_cast<const uint4*>(knew + D + lane * 8);
-      }
-      __syncwarp();
-    }
+    const __nv_bfloat16* kt = pipe + (i % DC_STAGES) * DecodeSmem::stage_elems;
+    const __nv_bfloat16* vt = kt + DC_SLICE * DPAD;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
@@ -510,7 +419,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   for (int j = 0; j < 2; ++j) l_run[j] = quad_sum(l_run[j]);
   __syncthreads();  // the pipelines are drained: shared memory becomes the merge area
 
-  float* merge = reinterpret_cast<float*>(smem_raw + (size_t)DecodeSmem::head_elems * 2);  // [warps][16][D + 2]
+  float* merge = reinterpret_cast<float*>(smem_raw + (size_t)DecodeSmem::q_elems * 2);  // [warps][16][D + 2]
   float* cta_out = merge + (size_t)DC_WARPS * 16 * (D + 2);                              // [16][D + 2]
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -578,7 +487,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
         out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
       }
     }
-      cluster.sync();  // the others' shared memory lives until the first CTA has read it
+    cluster.sync();  // the others' shared memory lives until the first CTA has read it
     return;
   }
   if (num_splits == 1 || counters == nullptr) return;
@@ -696,28 +605,13 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
   return 0;
 }
 
-// One launcher for every decode entry point. `cluster`: the splits of a (request, head group) run as one
-// thread-block cluster (2 to 8 splits) and are merged through distributed shared memory, so that no
-// scratch, fence or ticket is needed. Otherwise, with `counters` (num_rows * kv_heads *
-// ceil(group / 16) ints, zero before the first launch, left zero by every launch) the split that
-// finishes last merges the partial results inside the same kernel; without, a second kernel does.
-static int launch_decode(void* out, void* part_o, void* part_ml, int* counters, const void* q, const DecodeProj& proj,
-                         const void* k_pool, const void* v_pool, const int* kv_len, const int* page_indptr,
-                         const int* page_indices, int num_rows, int nq, int nkv, float scale, int window, int page_size,
-                         int num_splits, bool cluster, cudaStream_t stream) {
-  if (num_rows == 0) return 0;
-  MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
-  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
-  MS_CHECK_ARG(num_splits >= 1 && num_splits <= 65535, "attention: bad split count %d", num_splits);
-  MS_CHECK_ARG(num_rows <= 65535, "attention: too many rows (%d) for one launch", num_rows);
-  if (cluster) {
-    MS_CHECK_ARG(num_splits >= 2 && num_splits <= 8, "attention: a cluster takes 2 to 8 splits, not %d", num_splits);
-  } else {
-    MS_CHECK_ARG(num_splits == 1 || (part_o != nullptr && part_ml != nullptr), "attention: splits need scratch memory");
-  }
-  MS_CHECK_ARG(q != nullptr || proj.qkv != nullptr, "attention: needs queries, finished or as the q|k|v projection");
-  const int group = nq / nkv;
-  // the attribute belongs to a device: set once for each
+MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
+                                       const void* k_pool, const void* v_pool, const int* kv_len,
+                                       const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
+                                       float scale, int window, int page_size, int num_splits, cudaStream_t stream);
+
+// The decode kernel's shared-memory attribute belongs to a device: set once for each.
+static int configure_decode() {
   static bool configured[64] = {};
   int dev = 0;
   MS_CHECK_CUDA(cudaGetDevice(&dev));
@@ -725,22 +619,6 @@ static int launch_decode(void* out, void* part_o, void* part_ml, int* counters, 
   if (!configured[dev]) {
     MS_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DecodeSmem::bytes));
     configured[dev] = true;
-  }
-  dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
-  if (cluster) {
-    MS_LAUNCH_CLUSTERED(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream, num_splits,
-        (__nv_bfloat16*)out, (float*)nullptr, (float*)nullptr, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-        (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
-        shift_of(page_size), num_splits, (int*)nullptr, 1, proj);
-    return 0;
-  }
-  MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
-      (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
-      shift_of(page_size), num_splits, counters, 0, proj);
-  if (num_splits > 1 && counters == nullptr) {
-    MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
-              (const float*)part_o, (const float*)part_ml, num_splits);
   }
   return 0;
 }
@@ -750,42 +628,56 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
                                  const void* v_pool, const int* kv_len, const int* page_indptr,
                                  const int* page_indices, int num_rows, int nq, int nkv, float scale, int window,
                                  int page_size, int num_splits, cudaStream_t stream) {
-  return launch_decode(out, part_o, part_ml, nullptr, q, DecodeProj{}, k_pool, v_pool, kv_len, page_indptr, page_indices, num_rows,
-                       nq, nkv, scale, window, page_size, num_splits, false, stream);
+  return MS_ATTN_FN(decode_fused)(out, part_o, part_ml, nullptr, q, k_pool, v_pool, kv_len, page_indptr, page_indices,
+                                  num_rows, nq, nkv, scale, window, page_size, num_splits, stream);
 }
 
-// As above, merged by the split that finishes last (see launch_decode).
+// As above; with `counters` (num_rows * kv_heads * ceil(group / 16) ints, zero before the first
+// launch, left zero by every launch) the split that finishes last merges the partial results
+// inside the same kernel and no second kernel is launched.
 MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
                                        float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
-  return launch_decode(out, part_o, part_ml, counters, q, DecodeProj{}, k_pool, v_pool, kv_len, page_indptr, page_indices,
-                       num_rows, nq, nkv, scale, window, page_size, num_splits, false, stream);
+  if (num_rows == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
+  MS_CHECK_ARG(num_splits >= 1 && num_splits <= 65535, "attention: bad split count %d", num_splits);
+  MS_CHECK_ARG(num_splits == 1 || (part_o != nullptr && part_ml != nullptr), "attention: splits need scratch memory");
+  MS_CHECK_ARG(num_rows <= 65535, "attention: too many rows (%d) for one launch", num_rows);
+  const int group = nq / nkv;
+  if (int rc = configure_decode()) return rc;
+  dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
+  MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
+      (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
+      shift_of(page_size), num_splits, counters, 0);
+  if (num_splits > 1 && counters == nullptr) {
+    MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
+              (const float*)part_o, (const float*)part_ml, num_splits);
+  }
+  return 0;
 }
 
-// The splits as one thread-block cluster.
+// The same with the splits of a (request, head group) as one thread-block cluster (2 to 8 splits):
+// partial results stay in shared memory and the cluster's first CTA adds them up through
+// distributed shared memory, so no scratch, no fence and no ticket are needed.
 MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* kv_len,
                                          const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
                                          float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
-  return launch_decode(out, nullptr, nullptr, nullptr, q, DecodeProj{}, k_pool, v_pool, kv_len, page_indptr, page_indices,
-                       num_rows, nq, nkv, scale, window, page_size, num_splits, true, stream);
-}
-
-// Decode attention straight from the q|k|v projection [rows, (nq + 2 nkv) * D] of a decode step (one
-// token per request, token i is row i): per-head norm, rotation and the cache write happen inside the
-// kernel (see DecodeProj). `cos_sin`: float32 [rows, rot] or null; `cluster` as in launch_decode.
-MS_EXPORT int MS_ATTN_FN(decode_qkv)(void* out, void* part_o, void* part_ml, int* counters, const void* qkv,
-                                     const void* q_norm_w, const void* k_norm_w, const float* cos_sin, int rot, float eps,
-                                     int* status, void* k_pool, void* v_pool, const int* kv_len, const int* page_indptr,
-                                     const int* page_indices, int num_rows, int nq, int nkv, float scale, int window,
-                                     int page_size, int num_splits, int cluster, cudaStream_t stream) {
-  MS_CHECK_ARG(qkv != nullptr && status != nullptr && (uintptr_t)qkv % 16 == 0, "attention: the q|k|v projection must be 16-byte aligned");
-  MS_CHECK_ARG((q_norm_w == nullptr) == (k_norm_w == nullptr), "attention: q and k are normalised together or not at all");
-  MS_CHECK_ARG(cos_sin == nullptr || (rot > 0 && rot % 2 == 0 && rot <= D), "attention: rotated width %d does not fit head size %d", rot, D);
-  DecodeProj proj{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, cos_sin,
-                  (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status, cos_sin ? rot : 0, eps};
-  return launch_decode(out, part_o, part_ml, counters, nullptr, proj, k_pool, v_pool, kv_len, page_indptr, page_indices, num_rows,
-                       nq, nkv, scale, window, page_size, num_splits, cluster != 0, stream);
+  if (num_rows == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
+  MS_CHECK_ARG(num_splits >= 2 && num_splits <= 8, "attention: a cluster takes 2 to 8 splits, not %d", num_splits);
+  MS_CHECK_ARG(num_rows <= 65535, "attention: too many rows (%d) for one launch", num_rows);
+  const int group = nq / nkv;
+  if (int rc = configure_decode()) return rc;
+  dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
+  MS_LAUNCH_CLUSTERED(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream, num_splits,
+      (__nv_bfloat16*)out, (float*)nullptr, (float*)nullptr, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
+      shift_of(page_size), num_splits, (int*)nullptr, 1);
+  return 0;
 }
 
 // ------------------------------------------------------------------ decode without allocation

@@ -39,7 +39,6 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     decode_only: bool = False
-    logit_rows_in_order: bool = False  # logits are wanted at every token of the step, in the tokens' order
     leading_single_rows: int = 0  # how many rows from the front bring exactly one token (decode rows come first in a mixed step)
     sm_count: int = 148
     scratch: dict = field(default_factory=dict)  # per-step or persistent scratch buffers of kernels

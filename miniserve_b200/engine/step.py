@@ -216,8 +216,6 @@ class StepFunction:
             host_state_slot=slots.tolist() + [self.cache.pad_state_slot] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
             decode_only=bool((q_len == 1).all()),
-            logit_rows_in_order=(len(want) == int(q_len.sum()) and want == list(range(len(want)))
-                                 and (pad_rows == 0 or want_pad_rows)),
             leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
 
     def reset_after_fault(self) -> None:

@@ -75,7 +75,6 @@ def _setting(name: str, default: str) -> str:
 TC_GEMM = _setting("MINISERVE_TC_GEMM", "auto")   # products with more than 16 rows on the tcgen05 kernels: auto, 1 or 0
 QKV_EPILOGUE = _flag("MINISERVE_QKV_EPILOGUE", "1")  # q/k norm, rotation and cache write in the q|k|v product's epilogue
 TC_ATTENTION = _flag("MINISERVE_TC_ATTENTION", "1")  # prompts on the tcgen05 attention kernel (head size 128)
-DECODE_CHAIN = _flag("MINISERVE_DECODE_CHAIN", "1")  # decode steps of up to 16 requests as chains of products in persistent kernels
 
 
 def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None,

@@ -44,7 +44,6 @@ def _lib(head_dim: int):
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
         ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
         ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
-        ("decode_qkv", [_p] * 8 + [_i, _f] + [_p] * 6 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
     ):
         fn = getattr(lib, pre + name)
         fn.argtypes, fn.restype = args, res
@@ -66,10 +65,13 @@ def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count:
     """How many ways the keys of each (request, kv head) are split across CTAs: as many as give
     one wave of two CTAs per SM, but at least 128 keys per split and at most 16 splits (measured on
     B200 at contexts of 512 to 8,192 and batches of 1 to 32: more splits only add partial results
-    to merge, fewer leave SMs idle). ``max_kv_len`` None (inside a CUDA graph, where the launch
-    cannot follow the context length): assume a few thousand keys."""
+    to merge, fewer leave SMs idle; one split too many and the CTAs no longer fit one wave: a
+    decode step of 8 requests at 2,048 tokens takes 1.28 ms with 4 splits, 1.34 with 3, 1.60 with 8).
+    ``max_kv_len`` None (inside a CUDA graph, where the launch cannot follow the context length):
+    assume a few thousand keys, and stay within the 8 splits that one thread-block cluster merges
+    (a single request: 0.98 ms per step with 8 splits, 0.99 with 16)."""
     want = (2 * sm_count) // max(rows * head_chunks, 1)
-    by_len = 16 if max_kv_len is None else max(1, -(-max_kv_len // 128))
+    by_len = 8 if max_kv_len is None else max(1, -(-max_kv_len // 128))
     return max(1, min(want, by_len, 16))
 
 
@@ -98,56 +100,37 @@ def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
 
 
-def run_decode(out: torch.Tensor, q: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-               scale: float, window: int | None, rows: int, projection: dict | None = None) -> None:
+def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
+               scale: float, window: int | None, rows: int) -> None:
     """Rows [0, rows) of the step, one new token each (so token i belongs to row i): keys split
-    across CTAs, partial results merged by the last CTA of each (row, head group) to finish, or,
-    for 2 to 8 splits, through the distributed shared memory of a thread-block cluster.
-
-    ``projection`` (instead of ``q``): the step's q|k|v projection as the matrix product left it,
-    ``dict(qkv=[rows, (nq + 2 nkv) * d], q_norm_w, k_norm_w, cos_sin=[rows, rot] | None, rot, eps)``;
-    the kernel then norms and rotates q and the new k itself and writes the new k, v into the cache
-    (what ``ops.qk_norm_rope_kv`` does as a kernel of its own)."""
-    if projection is None:
-        t, nq, d = q.shape
-    else:
-        t, nq, d = out.shape
+    across CTAs, partial results merged by the last CTA of each (row, head group) to finish."""
+    t, nq, d = q.shape
     nkv, page_size = k_pool.shape[1], k_pool.shape[2]
     fns = _lib(d)
     indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
     chunks = nkv * -(-(nq // nkv) // 16)
     splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
-    cluster = CLUSTER_MERGE and 2 <= splits <= 8
+    if CLUSTER_MERGE and 2 <= splits <= 8:
+        # the splits as one thread-block cluster: merged through distributed shared memory
+        _check(fns, fns["decode_cluster"](
+            out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream))
+        return
     part_o = part_ml = counters = None
-    if splits > 1 and not cluster:
-        part_o, part_ml = _scratch(ctx, rows, nq, splits, d, out.device)
+    if splits > 1:
+        part_o, part_ml = _scratch(ctx, rows, nq, splits, d, q.device)
         counters = ctx.scratch.get("attn_counters")
         if counters is None or counters.numel() < rows * chunks:
             # tickets of the fused merge: zero before the first launch, left zero by every launch
             if counters is not None:  # captured graphs may hold the smaller one's address: it stays alive
                 ctx.scratch.setdefault("retired", []).append(counters)
-            counters = torch.zeros(max(4096, rows * chunks), dtype=torch.int32, device=out.device)
+            counters = torch.zeros(max(4096, rows * chunks), dtype=torch.int32, device=q.device)
             ctx.scratch["attn_counters"] = counters
-
-    def ptr(x):
-        return None if x is None else x.data_ptr()
-
-    common = (ctx.kv_len.data_ptr(), indptr.data_ptr(), indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0),
-              page_size, splits)
-    if projection is not None:
-        p = projection
-        assert p["qkv"].shape == (t, (nq + 2 * nkv) * d) and p["qkv"].is_contiguous() and p["qkv"].dtype == torch.bfloat16
-        cos_sin = p.get("cos_sin")
-        assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (t, p["rot"]) and cos_sin.is_contiguous())
-        _check(fns, fns["decode_qkv"](
-            out.data_ptr(), ptr(part_o), ptr(part_ml), ptr(counters), p["qkv"].data_ptr(), ptr(p.get("q_norm_w")),
-            ptr(p.get("k_norm_w")), ptr(cos_sin), int(p.get("rot") or 0), float(p.get("eps") or 0.0), ctx.status.data_ptr(),
-            k_pool.data_ptr(), v_pool.data_ptr(), *common, int(cluster), ctx.stream))
-    elif cluster:
-        _check(fns, fns["decode_cluster"](out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), *common, ctx.stream))
-    else:
-        _check(fns, fns["decode_fused"](out.data_ptr(), ptr(part_o), ptr(part_ml), ptr(counters), q.data_ptr(), k_pool.data_ptr(),
-                                        v_pool.data_ptr(), *common, ctx.stream))
+    _check(fns, fns["decode_fused"](
+        out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
+        None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
+        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
+        launches=1)
 
 
 def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,

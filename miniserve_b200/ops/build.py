@@ -49,8 +49,8 @@ class Module:
 HOST = Module("host", ("host_core.cpp",), cuda=False, extra_deps=())
 KERNELS = Module(
     "kernels",
-    ("runtime.cu", "elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_skinny.cu", "decode_chain.cu",
-     "attention_rowwise.cu", "sampling.cu"),
+    ("runtime.cu", "elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_skinny.cu", "attention_rowwise.cu",
+     "sampling.cu"),
 )
 
 

@@ -99,12 +99,6 @@ def kernels():
     _declare(lib, "ms_gemm_skinny_gate_up_bf16", [_p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_set_stream", [_i], None)
-    _declare(lib, "ms_decode_chain", [_p, _p, _p, _i, _p])
-    _declare(lib, "ms_decode_chain_wrows", [_i, _i, _i])
-    _declare(lib, "ms_decode_chain_tiles", [_i, _i, _i])
-    _declare(lib, "ms_decode_chain_grid", [POINTER(c_int)])
-    _declare(lib, "ms_decode_chain_fits", [_i, _i])
-    _declare(lib, "ms_chain_embed", [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
     _declare(lib, "ms_qk_norm_rope_kv",

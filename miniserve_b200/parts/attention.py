@@ -101,25 +101,3 @@ class GQAttention(Part):
         ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
         return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream,
                           out=ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))
-
-    def chain_mixer(self, ctx, cache):
-        """This mixer for a decode chain (``parts/decode_chain.py``): the q|k|v product, then one
-        kernel that norms and rotates q and the new k, writes the new k, v into the cache and attends
-        over it, then the output product."""
-        from ..ops import attention_bf16
-        from .decode_chain import ChainMixer
-
-        if (self.env.dtype != torch.bfloat16 or not self.owns_cache or self.hidden % 8 or (self.heads * self.head_dim) % 8
-                or not attention_bf16.supports(self.head_dim, cache.page_size)):
-            return None
-        inv_freq, rotary_dim = self.position.kernel_table()
-
-        def run(projection: torch.Tensor, out: torch.Tensor) -> None:
-            rows = projection.shape[0]
-            table = self.position.step_table(ctx) if inv_freq is not None else None
-            attention_bf16.run_decode(
-                out.view(rows, self.heads, self.head_dim), None, cache.k, cache.v, ctx, cache.group, self.scale, self.window, rows,
-                projection=dict(qkv=projection, q_norm_w=self.w_q_norm, k_norm_w=self.w_k_norm, cos_sin=table,
-                                rot=rotary_dim if table is not None else 0, eps=self.qk_norm_eps))
-
-        return ChainMixer(self.w_qkv, self.w_o, run)

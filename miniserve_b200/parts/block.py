@@ -35,18 +35,6 @@ class PreNormBlock(Part):
         x = self.norm2.forward(total, a, ctx)
         return ResidualStream(total, self.feed_forward.forward(x, ctx))
 
-    def chain_layer(self, ctx, cache):
-        """This layer for a decode chain (``parts/decode_chain.py``), or None if one of its parts
-        does not take part in chains."""
-        from .decode_chain import ChainLayer
-
-        ask = lambda part, name, *args: getattr(part, name)(*args) if hasattr(part, name) else None  # noqa: E731
-        n1, n2 = ask(self.norm1, "chain_norm"), ask(self.norm2, "chain_norm")
-        mixer = ask(self.mixer, "chain_mixer", ctx, cache)
-        ff = ask(self.feed_forward, "chain_feed_forward")
-        if n1 is None or n2 is None or mixer is None or ff is None:
-            return None
-        return ChainLayer(n1, mixer, n2, ff)
 
 
 def build_block(layer: LayerSpec, env: BuildEnv) -> Part:

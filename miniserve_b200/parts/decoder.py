@@ -45,9 +45,6 @@ class DecoderModel:
                 owner = self.entry_caches[e.cache_of]
                 self.entry_caches.append(EntryCache(owner.owner, owner.need))
         self.bound = False
-        from .decode_chain import DecodeChain
-
-        self.decode_chain = DecodeChain(self)
 
     @property
     def dtype(self) -> torch.dtype:
@@ -122,11 +119,6 @@ class DecoderModel:
         # memory that goes back to the allocator while the graph still holds their addresses.
         ctx.step_cache.clear()
         ctx.buffers.clear()
-        if self.decode_chain.takes(ctx):
-            # small decode steps: the parts' products strung together in persistent kernels
-            logits = self.decode_chain.run(ctx, caches)
-            if logits is not None:
-                return logits
         stream = ResidualStream(self.embedding.forward(ctx))
         for i, entry in enumerate(self.spec.run_order):
             stream = self.layers[entry.layer].forward(stream, ctx, caches[i])

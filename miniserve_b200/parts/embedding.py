@@ -30,9 +30,6 @@ class TokenEmbedding(Part):
         ops.embed_gather(residual, self.table, ctx.token_ids, stream=ctx.stream)
         return residual
 
-    def chain_table(self):
-        """The table for a decode chain (``parts/decode_chain.py``), which gathers and prepares the first norm in one kernel."""
-        return self.table if self.table.dtype == torch.bfloat16 else None
 
 
 @register_part("head", "linear_head")
@@ -64,7 +61,3 @@ class LinearHead(Part):
         if x.shape[0]:
             ops.linear(x, self.weight, out=logits, stream=ctx.stream)
         return logits
-
-    def chain_weight(self):
-        """The head's matrix for a decode chain (``parts/decode_chain.py``): the last product of the last kernel."""
-        return self.weight if self.weight.dtype == torch.bfloat16 and self.hidden % 8 == 0 else None

@@ -45,11 +45,3 @@ class SwiGLU(Part):
             gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
             ops.silu_mul(act, gate_up, stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
-
-    def chain_feed_forward(self):
-        """The two products of this feed-forward for a decode chain (``parts/decode_chain.py``)."""
-        from .decode_chain import ChainFeedForward
-
-        if self.env.dtype != torch.bfloat16 or self.hidden % 8 or self.inter % 8:
-            return None
-        return ChainFeedForward(self.w_gate_up, self.w_down)

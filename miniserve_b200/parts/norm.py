@@ -30,8 +30,3 @@ class RMSNorm(Part):
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,
                         write_residual=write_residual, stream=ctx.stream)
         return out
-
-    def chain_norm(self):
-        """(weight, eps) for a decode chain (``parts/decode_chain.py``), which applies the norm inside
-        the products around it."""
-        return (self.w_weight, self.eps) if self.env.dtype == torch.bfloat16 else None

@@ -4,7 +4,6 @@ summaries under ``profiles/`` were measured and captured with.
     python -m miniserve_b200.tools.kernel_bench attn_decode --batch 64 --context 2048
     python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048
     python -m miniserve_b200.tools.kernel_bench skinny --m 8 --n 4096 --k 1024
-    python -m miniserve_b200.tools.kernel_bench chain --m 8 --hidden 1024 --mixed 2048 --inter 3072 --n 4096
 
 Each case rotates over enough copies of its inputs to exceed the L2 cache, captures one pass over
 all copies in a CUDA graph, and reports the time per launch with the bytes or flops it implies.
@@ -86,7 +85,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "chain"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -98,10 +97,6 @@ def main(argv=None) -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
-    ap.add_argument("--hidden", type=int, default=1024, help="chain: width of the residual stream")
-    ap.add_argument("--mixed", type=int, default=2048, help="chain: width of the mixer's output (heads x head size)")
-    ap.add_argument("--inter", type=int, default=3072, help="chain: width of the feed-forward")
-    ap.add_argument("--persistent", type=int, default=1, help="chain: 1 one persistent kernel, 0 one kernel per product")
     ap.add_argument("--gemm", choices=["auto", "tcgen05", "library"], default="auto",
                     help="gemm, gate_up: this package's tcgen05 kernels, the vendor library, or the engine's choice")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
@@ -147,35 +142,6 @@ def main(argv=None) -> int:
                 ops.linear(x, ws[i], out=o, stream=stream)
             else:
                 ops.linear_silu_mul(x, ws[i], o, scratch=scratch, stream=stream)
-    elif args.kernel == "chain":
-        # a layer's tail and the next projection as a chain (csrc/decode_chain.cu):
-        # o -> +residual, norm -> gate|up, SiLU * up -> down -> +residual, norm -> next q|k|v
-        from ..ops import decode_chain as chain
-
-        m, h, mw, inter, n = args.m, args.hidden, args.mixed, args.inter, args.n
-        byts = 2 * (h * mw + 2 * inter * h + h * inter + n * h)
-        work = dict(bytes=byts)
-        copies = max(2, int(L2_BYTES // byts) + 1)
-
-        def mk(rows, cols):
-            return [(torch.randn(rows, cols, device=dev) * cols ** -0.5).bfloat16() for _ in range(copies)]
-
-        w_o, w_gu, w_d, w_q = mk(h, mw), mk(2 * inter, h), mk(h, inter), mk(n, h)
-        nw = torch.ones(h, device=dev, dtype=torch.bfloat16)
-        res = torch.randn(m, h, device=dev)
-        mixed = torch.randn(m, mw, device=dev).bfloat16()
-        xa, xb = (torch.empty(m, h, device=dev, dtype=torch.bfloat16) for _ in range(2))
-        ssa, ssb = (torch.ones(m, chain.tiles(h), device=dev) for _ in range(2))
-        act = torch.empty(m, inter, device=dev, dtype=torch.bfloat16)
-        o = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-        sync, status = torch.zeros(4, dtype=torch.int32, device=dev), ops.device_status(dev)
-        progs = [[chain.Phase(w_o[i], mixed, chain.RESIDUAL, residual=res, norm_w=nw, xw_out=xb, sumsq_out=ssb),
-                  chain.Phase(w_gu[i], xb, chain.SILU_MUL, out=act, sumsq_in=ssb, eps=1e-6),
-                  chain.Phase(w_d[i], act, chain.RESIDUAL, residual=res, norm_w=nw, xw_out=xa, sumsq_out=ssa),
-                  chain.Phase(w_q[i], xa, chain.OUT_BF16, out=o, sumsq_in=ssa, eps=1e-6)] for i in range(copies)]
-
-        def calls(i, stream):
-            chain.run(progs[i], m, sync, status, stream, persistent=bool(args.persistent))
     elif args.kernel == "skinny":
         byts = args.n * args.k * 2
         work = dict(bytes=byts)

@@ -4,7 +4,7 @@ and Qwen3-8B layer sizes (fewer layers, random weights), default dispatch, no fo
 A 2,048-token prompt in one step and in portions of 1,024 behind the growing prefix; 32 decode steps
 at batch 8 replayed from CUDA graphs at a context beyond 2,048; one decode step at batch 40. At these
 sizes the steps run through the tcgen05 matrix product and attention (several key splits), the
-decode chains or weight-streaming products, the cluster-merged decode attention and, at batch 40,
+weight-streaming products, the cluster-merged decode attention and, at batch 40,
 the vendor library's products: the test asserts that they did. float32 results must agree bit for
 bit between the cuts; bfloat16 results are held to the plain implementation's own bfloat16 noise."""
 
@@ -146,7 +146,7 @@ def test_prompt_whole_and_in_portions_then_graph_decode_at_batch_8_and_a_step_at
         assert seen.decode_splits and all(2 <= n <= 8 for n in seen.decode_splits), \
             f"decode attention at batch 8 was not merged inside a cluster: splits {set(seen.decode_splits)}"
 
-    # ---- one decode step at batch 40 (beyond the weight-streaming products and the chains): eagerly
+    # ---- one decode step at batch 40 (beyond the weight-streaming products): eagerly
     more = [cache.new_request() for _ in range(rows_max - 8)]
     for i in range(0, len(more), 2):
         step.run([StepRow(more[i], prompt, []), StepRow(more[i + 1], prompt, [])])
