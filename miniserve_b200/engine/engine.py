@@ -114,6 +114,14 @@ class Engine:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.step_fn, self.sampler, cuda_graph_max_bs or max_running)
+            if model.shape_static:
+                from .graphs import StepGraphs
+
+                # the arena holds the largest step at the fixed layout now, so that it does not move under captured graphs
+                budget = (chunked_prefill_size if chunked_prefill_size else max_prefill_tokens) + max_running
+                self.step_fn.reserve_arena(3 * (budget + 4) + 6 * (max_running + 8)
+                                           + self.cache.num_groups * (self.graphs.indices_cap + max_running + 16) + 256)
+                self.step_fn.graphs = StepGraphs(self.step_fn, self.graphs.indices_cap)
         self.overlap = overlap
         self.num_steps = 0
         self.stalled = False  # the last step() neither launched a step nor read one back
@@ -161,7 +169,7 @@ class Engine:
                                pages=g.allocator.num_blocks, page_size=g.page_size) for g in c.groups],
             cache_bytes=c.pool_bytes(), cache_bytes_per_token=c.bytes_per_token(), state_bytes=c.state_bytes(),
             request_slots=c.max_requests, graph_buckets=list(self.graphs.buckets) if self.graphs is not None else [],
-            **self.settings)
+            step_graphs=getattr(self.step_fn, "graphs", None) is not None, **self.settings)
 
     # ------------------------------------------------------------------ requests
     def capture_graphs(self, modes=("greedy",)) -> int:

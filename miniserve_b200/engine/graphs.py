@@ -1,4 +1,5 @@
-"""CUDA graphs for decode-only steps.
+"""CUDA graphs: for decode-only steps (``DecodeGraphs``) and for other steps whose shape comes again
+(``StepGraphs``, at the end of this file).
 
 A decode step of a small model is launch-bound: a few hundred short kernels. The reference
 captures one graph per batch-size bucket and pads a step up to its bucket with rows that write
@@ -55,6 +56,13 @@ class DecodeGraphs:
     def takes(self, num_rows: int) -> bool:
         return num_rows <= self.max_batch
 
+    def _drop_all(self) -> None:
+        """The arena moved: every captured address is stale. The graphs' memory pool goes with its last
+        graph, so the next capture starts a new one."""
+        self._graphs.clear()
+        self._pool = None
+        self._generation = self.step_fn.arena_generation
+
     def _bucket(self, n: int) -> int:
         return next(b for b in self.buckets if b >= n)
 
@@ -63,8 +71,7 @@ class DecodeGraphs:
         sampled tokens of the real rows, int32 on the device."""
         sf = self.step_fn
         if sf.arena_generation != self._generation:
-            self._graphs.clear()
-            self._generation = sf.arena_generation
+            self._drop_all()
         n = len(rows)
         bucket = self._bucket(n)
         pad = bucket - n
@@ -73,8 +80,7 @@ class DecodeGraphs:
             mode = "top_p" if any(p < 1 for p in sampling["top_ps"]) else "temperature"
         ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # the arena moved while preparing
-            self._graphs.clear()
-            self._generation = sf.arena_generation
+            self._drop_all()
         cap = self._graphs.get((bucket, mode))
         if cap is not None and cap.sampler_scratch is not None and cap.sampler_scratch is not self.sampler._scratch:
             cap = None  # the sampler has moved to a larger scratch since: the graph's address is stale
@@ -170,3 +176,146 @@ class DecodeGraphs:
         if self._pool is None:
             self._pool = graph.pool()
         return _Captured(graph, tokens, logits, f32, i64, launches, self.sampler._scratch if mode == "top_p" else None)
+
+
+class _Recorder:
+    """Captures one pass of the model as a chain of pieces: CUDA graphs, and between them the calls
+    that operations kept out of the graphs (``defer``)."""
+
+    def __init__(self, pool, stream: torch.cuda.Stream):
+        self.pool, self.stream = pool, stream
+        self.pieces: list = []  # torch.cuda.CUDAGraph | callable(ctx)
+        self._open: torch.cuda.CUDAGraph | None = None
+
+    def begin(self) -> None:
+        self._open = torch.cuda.CUDAGraph()
+        self._open.capture_begin(pool=self.pool)
+
+    def end(self) -> None:
+        if self._open is not None:
+            self._open.capture_end()
+            self.pieces.append(self._open)
+            self._open = None
+
+    def defer(self, call) -> None:
+        self.end()
+        self.pieces.append(call)
+        self.begin()
+
+
+class _Pieces:
+    __slots__ = ("pieces", "logits", "layout", "launches", "uses")
+
+    def __init__(self, pieces, logits, layout, launches):
+        self.pieces, self.logits, self.layout, self.launches, self.uses = pieces, logits, layout, launches, 0
+
+
+class StepGraphs:
+    """Prompt and mixed steps of a shape that comes again, replayed from CUDA graphs.
+
+    A step that is not decode-only launches a couple of hundred kernels from Python; for a small model
+    the stream launches cost more than the host takes to issue them (Qwen3-0.6B sizes, 2,048 tokens:
+    3.86 ms launched eagerly with the host ahead, 3.59 ms replayed). What the kernels of such a step
+    get from the host is the number of tokens, of rows and of wanted logits; everything else they read
+    from the step's arrays, which the packer lays out at fixed places for a given (tokens, rows,
+    wanted) when it is given a fixed number of page entries. The exception is attention, whose
+    kernels, grids and key splits follow the rows' lengths and starts: ``ops.attention`` keeps itself
+    out of the capture and is called again for every step, between the graphs.
+
+    The second step with the same (tokens, rows, wanted) is captured while it runs, later ones replay.
+    Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
+    dropped beyond ``max_shapes``. The logits of a replayed step live in the graphs' memory and are
+    overwritten by the next replayed step.
+    """
+
+    def __init__(self, step_fn: StepFunction, indices_cap: int, max_shapes: int = 8, min_tokens: int = 16):
+        self.step_fn = step_fn
+        self.indices_cap = indices_cap
+        self.max_shapes, self.min_tokens = max_shapes, min_tokens
+        self.enabled = bool(step_fn.model.shape_static)
+        self._seen: dict[tuple, int] = {}
+        self._shapes: dict[tuple, _Pieces] = {}  # insertion order = least recently used first
+        self._pool = None
+        self._generation = step_fn.arena_generation
+        self.capture_stream = torch.cuda.Stream(device=step_fn.device)
+        self.replayed_launches = 0  # kernels of this package launched from inside replayed graphs
+        self.captures = 0
+
+    def _drop_all(self) -> None:
+        """The arena moved: every captured address is stale. The graphs' memory pool goes with its last
+        graph, so the next capture starts a new one."""
+        self._shapes.clear()
+        self._pool = None
+        self._generation = self.step_fn.arena_generation
+
+    def _key(self, rows: Sequence[StepRow]) -> tuple | None:
+        tokens = sum(len(r.tokens) for r in rows)
+        if not self.enabled or tokens < self.min_tokens or tokens == len(rows):  # decode-only steps have graphs of their own
+            return None
+        return tokens, len(rows), sum(len(r.want) for r in rows)
+
+    def run(self, rows: Sequence[StepRow], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
+        """The step's logits, or None if this step is left to the eager path (nothing was touched then)."""
+        key = self._key(rows)
+        if key is None:
+            return None
+        sf = self.step_fn
+        if sf.arena_generation != self._generation:
+            self._drop_all()
+        held = self._shapes.get(key)
+        if held is None:
+            n = self._seen.get(key, 0) + 1
+            if len(self._seen) > 4096:
+                self._seen.clear()
+            self._seen[key] = n
+            if n < 2:
+                return None
+        ctx = sf.prepare(rows, indices_cap=self.indices_cap, prev_tokens=prev_tokens)
+        if sf.arena_generation != self._generation:  # it moved while preparing this step
+            self._drop_all()
+            held = None
+        if held is not None and held.layout != ctx.layout:
+            held = None  # cannot happen for one key; checked because a graph that reads the wrong place reads garbage silently
+        if held is None:
+            held = self._capture(ctx)
+            self._shapes.pop(key, None)
+            self._shapes[key] = held
+            while len(self._shapes) > self.max_shapes:
+                self._shapes.pop(next(iter(self._shapes)))
+        else:
+            self._shapes[key] = self._shapes.pop(key)  # now the most recently used
+        ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream
+        for piece in held.pieces:
+            if isinstance(piece, torch.cuda.CUDAGraph):
+                piece.replay()
+            else:
+                piece(ctx)
+        held.uses += 1
+        self.replayed_launches += held.launches
+        return held.logits
+
+    def _capture(self, ctx) -> _Pieces:
+        from ..ops import native
+
+        sf = self.step_fn
+        torch.cuda.current_stream(sf.device).synchronize()
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        s = self.capture_stream
+        rec = _Recorder(self._pool, s)
+        before = native.LAUNCHES[0]
+        ctx.recorder = rec
+        try:
+            with torch.cuda.stream(s):
+                ctx.stream = s.cuda_stream
+                rec.begin()
+                try:
+                    logits = sf.model.forward(ctx, sf.cache.entry_views)
+                finally:
+                    rec.end()
+        finally:
+            ctx.recorder = None
+        launches = native.LAUNCHES[0] - before
+        native.LAUNCHES[0] = before  # a capture launches nothing
+        self.captures += 1
+        return _Pieces(rec.pieces, logits, ctx.layout, launches)

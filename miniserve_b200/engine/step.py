@@ -74,6 +74,9 @@ class StepFunction:
         self.sm_count = props.multi_processor_count
         self.persistent_scratch: dict = {}
         self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
+        # StepGraphs (engine/graphs.py) when the engine replays recurring step shapes from CUDA graphs; its
+        # run() returns None for a step it does not take, which then runs eagerly
+        self.graphs = None
 
     # ------------------------------------------------------------------ arena
     def _grow(self, ints: int) -> None:
@@ -104,8 +107,10 @@ class StepFunction:
         """Run one step. Returns float32 logits ``[wanted, vocab]`` on the device, in the order
         of the rows and of each row's ``want``. Raises ``OutOfBlocks`` (nothing changed) if
         the pool cannot hold the step's new tokens."""
-        ctx = self.prepare(rows, pad_rows, prev_tokens=prev_tokens)
-        logits = self.model.forward(ctx, self.cache.entry_views)
+        logits = self.graphs.run(rows, prev_tokens) if self.graphs is not None and pad_rows == 0 else None
+        if logits is None:
+            ctx = self.prepare(rows, pad_rows, prev_tokens=prev_tokens)
+            logits = self.model.forward(ctx, self.cache.entry_views)
         for r in rows:
             self.cache.trim(r.cache)
         return logits
@@ -216,7 +221,8 @@ class StepFunction:
             host_state_slot=slots.tolist() + [self.cache.pad_state_slot] * pad_rows,
             max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
             decode_only=bool((q_len == 1).all()),
-            leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch)
+            leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch,
+            layout=tuple(o))
 
     def reset_after_fault(self) -> None:
         """After a kernel raised the status word: wait for what is in flight, then zero the word and

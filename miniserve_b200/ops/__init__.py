@@ -399,6 +399,13 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
+    if ctx.recorder is not None:
+        # The pass is being captured as a chain of CUDA graphs. Which kernels run here, their grids and
+        # their key splits depend on each row's length and start, which a graph cannot hold: the call
+        # is left out of the graphs and made again for every step that replays them, with that
+        # step's context (the operand tensors are the captured pass's own and do not move).
+        ctx.recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window))
+        return
     if q.dtype == torch.bfloat16:
         # rows at the front that bring one token each (a decode step, or the decoding requests
         # of a mixed step) go to the split-key kernel, the rest to a tiled kernel

@@ -20,6 +20,7 @@ class GQAttention(Part):
     (a query sees only the last ``window`` keys), optional ``scale``, and ``kv_source``:
     ``own`` (default) or ``shared`` (the layer has no k/v projections and attends over the
     cache of the run entry named by ``RunEntry.cache_of``)."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -98,6 +98,14 @@ CacheNeed = PagedKV | FixedState
 class Part:
     """Common behaviour: keep the spec and environment, declare and receive weights."""
 
+    # True if the kernels this part launches, their grids and their arguments follow from the step's
+    # number of tokens (and of wanted rows) alone, not from how the tokens are shared among rows:
+    # everything row-dependent is read on the device from the step's arrays, or goes through
+    # ``ops.attention``, which keeps itself out of captured graphs. A model whose parts all say so can
+    # have recurring step shapes replayed from CUDA graphs (``DecoderModel.shape_static``). A part that
+    # reads ``ctx.host_*`` to decide what to launch leaves it False.
+    shape_static = False
+
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec
         self.env = env

@@ -12,6 +12,7 @@ class PreNormBlock(Part):
     The adds are fused into the norm that follows them, so the block hands its last addend
     on as ``pending``. Parameters: ``names`` maps mixer / feed_forward / norm1 / norm2 to their
     tensor-name prefixes inside the layer."""
+    shape_static = True
 
     def __init__(self, spec, env: BuildEnv, layer: LayerSpec | None = None):
         super().__init__(spec, env)

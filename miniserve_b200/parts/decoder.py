@@ -47,6 +47,21 @@ class DecoderModel:
         self.bound = False
 
     @property
+    def shape_static(self) -> bool:
+        """Whether every part says that its launches follow from the step's token count alone
+        (``Part.shape_static``): then a pass can be captured into CUDA graphs and replayed for
+        later steps of the same shape."""
+
+        def ok(part) -> bool:
+            subs = list(part.sub_parts().values())
+            pos = getattr(part, "position", None)
+            if pos is not None:
+                subs.append(pos)
+            return bool(getattr(part, "shape_static", False)) and all(ok(p) for p in subs)
+
+        return all(ok(p) for p in [self.embedding, self.final_norm, self.head, *self.layers])
+
+    @property
     def dtype(self) -> torch.dtype:
         return self.env.dtype
 

@@ -12,6 +12,7 @@ from .base import Part, WeightDecl, param, register_part
 class TokenEmbedding(Part):
     """h = table[ids] (miniserve/model/qwen3.py:211), widened to the float32 residual stream.
     Parameters: ``vocab``, ``hidden``, ``name`` (the tensor's full name)."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -38,6 +39,7 @@ class LinearHead(Part):
     embedding table itself and no tensor of its own is read (miniserve/model/weights.py:116-119,
     135-136). Logits are returned in float32. Parameters: ``vocab``, ``hidden``, ``tied``,
     ``name``, ``tied_to``."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -13,6 +13,7 @@ class SwiGLU(Part):
     """down(silu(gate(x)) * up(x)), no biases (miniserve/model/qwen3.py:128-131). The gate and
     up matrices are stacked at load so that one product makes both
     (miniserve/model/fused.py:41-95 does the same). Parameters: ``hidden``, ``intermediate``."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

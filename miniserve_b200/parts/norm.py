@@ -12,6 +12,7 @@ from .base import Part, WeightDecl, param, register_part
 class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * weight, statistics in float32, no bias and no ``1 +``
     offset (miniserve/model/qwen3.py:78-82). Parameters: ``size``, ``eps``."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -13,6 +13,7 @@ class RotaryNeox(Part):
     CPU in float32 from an int64 arange exactly as the reference does
     (miniserve/model/qwen3.py:98-101); the kernel multiplies by the position and takes
     cos/sin in float32. Parameters: ``head_dim``, ``theta``, optional ``rotary_dim``."""
+    shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -44,6 +45,7 @@ class RotaryNeox(Part):
 @register_part("position", "none")
 class NoPosition(Part):
     """No position encoding: q and k pass through unrotated."""
+    shape_static = True
 
     def kernel_table(self):
         return None, 0
