@@ -27,7 +27,6 @@
 namespace ms {
 
 constexpr int AT_D = 128, AT_ROWS = 128, AT_KEYS = 128;
-constexpr uint32_t AT_WAIT_LIMIT = 1u << 24;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 constexpr int AT_BLOCK = 128 * 64 * 2;  // one [128 rows][64 bf16] swizzled block: 16 KB
 
@@ -41,19 +40,7 @@ __device__ __forceinline__ void at_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void at_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(at_smem(bar)) : "memory");
 }
-__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = at_smem(bar);
-  for (uint32_t i = 0; i < AT_WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_bounded(at_smem(bar), parity); }
 __device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -195,6 +182,79 @@ __device__ __forceinline__ bool at_group_any(int id, bool flag) {
       "bar.red.or.pred q, %1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
       : "=r"(res) : "r"(id), "r"((uint32_t)flag) : "memory");
   return res != 0;
+}
+
+// A new running maximum for a row: the stale one is kept while the new one exceeds it by at most
+// 2^8 after scaling (the same maximum scales the sum, so the result stays exact); returns the factor
+// that what was accumulated so far has to be scaled by (1: nothing to do).
+__device__ __forceinline__ float at_new_maximum(float m_tile, float& m_used, float scale_log2) {
+  const float m_new = fmaxf(m_used, m_tile);
+  if (m_used == -INFINITY) {
+    m_used = m_new;
+  } else if ((m_new - m_used) * scale_log2 > 8.f) {
+    const float alpha = at_ex2((m_used - m_new) * scale_log2);
+    m_used = m_new;
+    return alpha;
+  }
+  return 1.f;
+}
+// O *= alpha for this thread's row. Called when S(j) is complete, so the product P(j-1) V(j-1) issued
+// before it is complete too: O is quiet.
+__device__ __forceinline__ void at_rescale(uint32_t t_o, float alpha) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float ov[32];
+    at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+    at_tmem_st32(t_o + (uint32_t)(c * 32), ov);
+  }
+}
+// The softmax step of one row for a tile in which the row sees only the keys at offsets
+// [seen_lo, seen_hi]. The scores are read twice, 32 columns at a time: once for the maximum, once for
+// the exponentials (chunk c of P, 16 columns, lies below chunk c + 1 of S, so chunks are read and
+// written in turn). A function of its own: inlined beside the all-in-registers form of interior tiles
+// it cost that form its registers. Returns the sum of the row's exponentials.
+__device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int seen_lo, int seen_hi, float scale_log2,
+                                                float& m_used, float& l_sum) {
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    at_tmem_ld32(t_s + (uint32_t)(c * 32), v);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int off = c * 32 + i;
+      mx[i & 3] = fmaxf(mx[i & 3], off <= seen_hi && off >= seen_lo ? v[i] : -INFINITY);
+    }
+  }
+  const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
+  if (__any_sync(0xffffffffu, alpha != 1.f)) {
+    at_rescale(t_o, alpha);
+    l_sum *= alpha;
+  }
+  const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    at_tmem_ld32(t_s + (uint32_t)(c * 32), v);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const int off = c * 32 + i;
+      const float e0 = off <= seen_hi && off >= seen_lo ? at_ex2(fmaf(v[i], scale_log2, -m_sub)) : 0.f;
+      const float e1 = off + 1 <= seen_hi && off + 1 >= seen_lo ? at_ex2(fmaf(v[i + 1], scale_log2, -m_sub)) : 0.f;
+      part[(i >> 1) & 3] += e0 + e1;
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+      pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
+    }
+    at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
+  }
+  return (part[0] + part[1]) + (part[2] + part[3]);
 }
 
 // What one work item (a tile of 2 x 128 query rows, one group of heads, one split of the keys)
@@ -477,69 +537,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         AT_FENCE_AFTER();
         const int key0 = (tile_begin + j) * AT_KEYS;
         const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
-        // the whole row of scores in registers: four loads in flight, one wait
-        float sv[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
         if (interior) {
+          // every key of the tile is seen by every row of the group: the whole row of scores in
+          // registers, four loads in flight, one wait
+          float sv[4][32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
-        } else {
+          const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            at_rescale(t_o, alpha);
+            l_sum *= alpha;
+          }
+          // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
+          const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + c * 32 + i;
-              const bool valid = key <= qpos && key >= lo_mine && (window <= 0 || key > qpos - window);
-              sv[c][i] = valid ? sv[c][i] : -INFINITY;
-              mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
-            }
-        }
-        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        const float m_new = fmaxf(m_used, m_tile);
-        float alpha = 1.f;
-        bool rescale = false;
-        if (m_used == -INFINITY) {
-          m_used = m_new;
-        } else if ((m_new - m_used) * scale_log2 > 8.f) {
-          alpha = at_ex2((m_used - m_new) * scale_log2);
-          m_used = m_new;
-          rescale = true;
-        }
-        if (__any_sync(0xffffffffu, rescale)) {
-          // S(j) is complete, so the product P(j-1) V(j-1) issued before it is complete too: O is quiet
-#pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            float ov[32];
-            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-            at_tmem_st32(t_o + (uint32_t)(c * 32), ov);
+            for (int i = 0; i < 32; i += 2) {
+              const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
+              const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
+              const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
+              part[(i >> 1) & 3] += e0 + e1;
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+              pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
+            }
+            at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
           }
-          l_sum *= alpha;
-        }
-        // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
-        // (masked scores are -inf and give 0)
-        const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
-            const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
-            const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
-            part[(i >> 1) & 3] += e0 + e1;
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
-          }
-          at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
+        } else {
+          // a tile on the diagonal, at a window's edge or at the request's end: the keys of the tile
+          // that this row sees are those at offsets [seen_lo, seen_hi]
+          const int seen_hi = qpos - key0;
+          const int seen_lo = max(lo_mine, window > 0 ? qpos - window + 1 : 0) - key0;
+          part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum);
         }
         l_sum += (part[0] + part[1]) + (part[2] + part[3]);
         const int valid_keys = kv_len - key0;

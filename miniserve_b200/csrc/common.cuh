@@ -106,6 +106,32 @@ __device__ __forceinline__ void pdl_prologue() {
   pdl_wait();
 }
 
+// ---- bounded wait on an mbarrier
+// Waits for the phase of the given parity of the mbarrier at shared-memory address `bar`, for at
+// most MS_WAIT_NS of the global timer (looked at every 64 failed polls; a poll itself may block
+// for a while inside the hardware). A wait that ends this way returns false: the caller raises the
+// device status word and winds its pipeline down, so a protocol error or a lost arrival costs a
+// couple of seconds and an error on the host, not a GPU that no longer answers.
+constexpr unsigned long long MS_WAIT_NS = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  unsigned long long began = 0;
+  for (uint32_t polls = 1;; ++polls) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((polls & 63u) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (began == 0) began = now;
+      else if (now - began > MS_WAIT_NS) return false;
+    }
+  }
+}
+
 inline int& pdl_switch() {
   static int on = 1;
   return on;

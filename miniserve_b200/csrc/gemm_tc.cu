@@ -26,7 +26,6 @@ namespace ms {
 
 constexpr int TC_BM = 128, TC_BK = 64;
 constexpr int TC_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;  // polls of an mbarrier before giving up (far beyond any real wait)
 
 enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_SILU_MUL = 2, TC_QKV_ROPE = 3 };
 
@@ -58,20 +57,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity. Returns false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
+// Bounded wait for the phase with the given parity. Returns false if the time limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_bounded(smem_u32(bar), parity); }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -290,6 +277,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // One 32-column chunk of a row of the accumulator (and of the up half for SiLU * up), to global memory.
+// SiLU with the fast exponential and division: both are good to about two float32 ulps, far inside
+// the bfloat16 rounding that follows. For x below -88 the exponential overflows to infinity and the
+// quotient is -0, the limit of SiLU there.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 template <int EPI>
 __device__ __forceinline__ void store_chunk(void* __restrict__ out, const uint32_t (&acc)[32], const uint32_t (&up)[32], int row,
                                             int col0, int N_out) {
@@ -822,7 +814,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
               for (int q = 0; q < 32; ++q) {
                 const float x = __uint_as_float(acc[q]);
-                v[q] = x / (1.0f + expf(-x)) * __uint_as_float(up[q]);
+                v[q] = silu_fast(x) * __uint_as_float(up[q]);
               }
             } else {
               asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");

@@ -399,7 +399,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
-    if ctx.recorder is not None:
+    if getattr(ctx, "recorder", None) is not None:
         # The pass is being captured as a chain of CUDA graphs. Which kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold: the call
         # is left out of the graphs and made again for every step that replays them, with that
