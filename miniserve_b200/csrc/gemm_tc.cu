@@ -37,7 +37,7 @@ struct QkvEpilogue {
   __nv_bfloat16* v_pool;
   const __nv_bfloat16* q_norm_w;    // [128] or null (no norm)
   const __nv_bfloat16* k_norm_w;
-  const float* cos_sin;             // [T, 128]: cos then sin of every rotation pair of a token, or null (no rotation)
+  const float* cos_sin;             // the rotation table by tiles of 128 tokens (rope_kv.cu, ms_rope_table_tile), or null (no rotation)
   const int* positions;
   const int* row_of_token;
   const int* page_indptr;
@@ -515,6 +515,18 @@ __device__ __forceinline__ bool epilogue_all(int id, bool flag) {
 }
 __device__ __forceinline__ void epilogue_sync(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id) : "memory"); }
 
+// The q|k|v epilogue's ring for the rotation table: four slots of [128 tokens][8 cosines] then
+// [128 tokens][8 sines] (float32), one quarter of a half head each, read by both groups of epilogue warps
+// (a tile's two heads are of one kind and of the same tokens).
+constexpr int CS_SLOTS = 4;
+constexpr int CS_SLOT_BYTES = 2 * TC_BM * 8 * 4;
+constexpr int CS_RING_BYTES = CS_SLOTS * CS_SLOT_BYTES;  // 32 KB
+// `bytes` contiguous bytes (a multiple of 16, both addresses 16-byte aligned) from global to this CTA's shared memory
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 constexpr int PAIR_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int PAIR_BN = 256;                    // the wide tile; outputs too narrow for it take 128 columns
 constexpr int PAIR_OUT_BYTES = TC_BM * 64 * 2;  // one [128][64] bfloat16 tile of the epilogue's four
@@ -531,11 +543,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int row_dst[2][TC_BM];  // TC_QKV_ROPE: the pool row (page, kv head, slot) each row of a k or v head goes to (-1: none)
+  __shared__ uint64_t cs_full[CS_SLOTS], cs_empty[CS_SLOTS];  // TC_QKV_ROPE: a slot of the cos/sin ring has landed / has been read by all eight warps
   constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;  // output columns per tile
   constexpr int STAGE_BYTES = pair_stage_bytes(BN);
   constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators (512 or 256 columns)
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
 
+  unsigned char* smem_cs = smem + (size_t)STAGES * STAGE_BYTES + 4 * PAIR_OUT_BYTES;  // TC_QKV_ROPE only
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0: the CTA that issues the products
   const int k_iters = (K + TC_BK - 1) / TC_BK;
@@ -558,6 +572,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 16);  // one arrival per epilogue warp of both CTAs
+    }
+    for (int i = 0; i < CS_SLOTS; ++i) {
+      mbar_init(&cs_full[i], 1);
+      mbar_init(&cs_empty[i], 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -634,24 +652,53 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quad = warp & 3, eg = (warp - 2) >> 2;
     const bool issuer = (int)threadIdx.x == 64 + 128 * eg;
     int tc = 0, out_buf = 0;
+    uint32_t cs_count = 0;  // TC_QKV_ROPE: quarters of the cos/sin table that have been through the ring before this tile
     const bool tma_out = EPI != TC_OUT_F32 && EPI != TC_QKV_ROPE && N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tc) {
       const int buf = tc & 1;
       const int n0 = tile_n(tile) * COLS, m0 = tile_m(tile) * 2 * TC_BM + (int)rank * TC_BM;
       const int row = m0 + quad * 32 + lane;
+      // TC_QKV_ROPE: the rotation's cosines and sines of the tile's 128 tokens come through a ring of four
+      // slots filled by bulk copies, a quarter of a half head (8 pairs) per slot, asked for four quarters
+      // ahead by the first thread of the first group. Every thread reads its token's 32 + 32 bytes of a
+      // slot. Read from a [T, 128] table in global memory instead (512 bytes apart from thread to thread)
+      // the same values took 3 to 7 us of a tile's epilogue, more than the tile's products; fetched from
+      // that table by TMA in boxes of 128 x 32 bytes still 2 to 5 us (a request per token and box).
+      bool qkv_rotated = false;
+      const bool cs_producer = issuer && eg == 0;
+      auto cs_issue = [&](uint32_t fill, int quarter) {  // the producer thread only
+        const uint32_t slot = fill % CS_SLOTS;
+        if (fill >= CS_SLOTS && !mbar_wait(&cs_empty[slot], ((fill / CS_SLOTS) - 1) & 1u)) atomicExch(status, 15);
+        mbar_expect_tx(&cs_full[slot], CS_SLOT_BYTES);
+        // the table is laid out by tiles of 128 tokens and quarters, so a slot's worth is one contiguous block
+        bulk_load(smem_cs + (size_t)slot * CS_SLOT_BYTES, qe.cos_sin + ((size_t)(m0 / TC_BM) * 8 + quarter) * (CS_SLOT_BYTES / 4),
+                  CS_SLOT_BYTES, &cs_full[slot]);
+      };
+      if constexpr (EPI == TC_QKV_ROPE) {
+        qkv_rotated = qe.cos_sin != nullptr && n0 / 128 < qe.nq + qe.nkv;  // q and k heads; the same for both groups
+        if (qkv_rotated && cs_producer) {
+          for (int ahead = 0; ahead < CS_SLOTS; ++ahead) cs_issue(cs_count + ahead, ahead);  // before the accumulator is waited for
+        }
+      }
       // the four epilogue warps go on together or stop together (they meet at barriers below)
       if (!epilogue_all(1 + eg, mbar_wait(&acc_full[buf], (tc >> 1) & 1))) {
         atomicExch(status, 13);
+        if (qkv_rotated && cs_producer) {
+          // what was asked for above must have landed before this CTA's shared memory may go away
+          for (int ahead = 0; ahead < CS_SLOTS; ++ahead) mbar_wait(&cs_full[(cs_count + ahead) % CS_SLOTS], ((cs_count + ahead) / CS_SLOTS) & 1u);
+        }
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quad * 32) << 16);
       if constexpr (EPI == TC_QKV_ROPE) {
         // A tile's 256 columns are two whole heads; each group of warps takes one. A thread owns a
-        // token's row of its head: it reads the 128 values twice from tensor memory (once for the
-        // sum of squares, once to normalise and rotate), puts the result into the group's two
-        // swizzled [128][64] tiles, and the tiles leave by TMA (q) or by row copies into the
-        // token's cache page (k, v).
+        // token's row of its head: it reads the 128 values from tensor memory once, keeps them as 64
+        // pairs of bfloat16 (the product is rounded to bfloat16 first, as when it is stored) and
+        // gives the accumulator back at once; then it normalises and rotates from registers, puts
+        // the result into the group's two swizzled [128][64] tiles, and the tiles leave by TMA (q) or
+        // by row copies into the token's cache page (k, v). Reads of tensor memory are slow while
+        // the next tile's products run (0.6 us for the 128 columns with the tensor cores idle, 1.7 busy).
         const int r = quad * 32 + lane, tok = m0 + r;
         const int head = n0 / 128 + eg;
         const bool is_q = head < qe.nq, is_v = head >= qe.nq + qe.nkv;
@@ -659,77 +706,76 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t head_addr = lane_addr + (uint32_t)(128 * eg);
         unsigned char* stage_lo = smem + (size_t)STAGES * STAGE_BYTES + (size_t)(2 * eg) * PAIR_OUT_BYTES;
         unsigned char* stage_hi = stage_lo + PAIR_OUT_BYTES;
-        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // the stores of the tile before have read both
-        epilogue_sync(1 + eg);
-        float inv = 1.f;
-        if (nw) {
-          float ss = 0.f;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t acc[32];
-            tmem_ld32(head_addr + (uint32_t)(32 * c), acc);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        uint32_t packed[64];  // elements 2 i and 2 i + 1 of the head
+        float ss = 0.f;
 #pragma unroll
-            for (int q = 0; q < 32; ++q) {
-              const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[q])));  // the product is rounded to bfloat16 first, as when it is stored
-              ss += x * x;
-            }
-          }
-          inv = 1.0f / sqrtf(ss / 128.f + qe.eps);
-        }
-        const float* table = (qe.cos_sin && !is_v && tok < M) ? qe.cos_sin + (size_t)tok * 128 : nullptr;
-#pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh) {
-          // the half's cos and sin first: their way from memory overlaps the reads of tensor memory
-          float4 cs4[8], sn4[8];
-          if (table) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              cs4[q] = *reinterpret_cast<const float4*>(table + 32 * hh + 4 * q);
-              sn4[q] = *reinterpret_cast<const float4*>(table + 64 + 32 * hh + 4 * q);
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              cs4[q] = make_float4(1.f, 1.f, 1.f, 1.f);
-              sn4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          }
-          uint32_t lo[32], hi[32];
-          tmem_ld32(head_addr + (uint32_t)(32 * hh), lo);
-          tmem_ld32(head_addr + (uint32_t)(64 + 32 * hh), hi);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(head_addr + (uint32_t)(32 * c), acc);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {  // eight rotation pairs at a time
-            float l[8], h[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              l[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[8 * q + e])));
-              h[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[8 * q + e])));
-            }
-            if (nw) {
-              float wl[8], wh[8];
-              bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 32 * hh + 8 * q), wl);
-              bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 64 + 32 * hh + 8 * q), wh);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                l[e] = (l[e] * inv) * wl[e];
-                h[e] = (h[e] * inv) * wh[e];
-              }
-            }
-            const float cs[8] = {cs4[2 * q].x, cs4[2 * q].y, cs4[2 * q].z, cs4[2 * q].w, cs4[2 * q + 1].x, cs4[2 * q + 1].y, cs4[2 * q + 1].z, cs4[2 * q + 1].w};
-            const float sn[8] = {sn4[2 * q].x, sn4[2 * q].y, sn4[2 * q].z, sn4[2 * q].w, sn4[2 * q + 1].x, sn4[2 * q + 1].y, sn4[2 * q + 1].z, sn4[2 * q + 1].w};
-            float ol[8], oh[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              ol[e] = l[e] * cs[e] - h[e] * sn[e];
-              oh[e] = h[e] * cs[e] + l[e] * sn[e];
-            }
-            const int chunk = 4 * hh + q;  // elements 32 hh + 8 q .. + 7 of the head's first half, and of its second
-            *reinterpret_cast<uint4*>(stage_lo + r * 128 + ((chunk ^ (r & 7)) << 4)) = float_to_bf16x8(ol);
-            *reinterpret_cast<uint4*>(stage_hi + r * 128 + ((chunk ^ (r & 7)) << 4)) = float_to_bf16x8(oh);
+          for (int i = 0; i < 32; i += 2) {
+            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]));
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(&p);
+            const float x0 = __uint_as_float(u << 16), x1 = __uint_as_float(u & 0xFFFF0000u);
+            ss += x0 * x0;
+            ss += x1 * x1;
+            packed[16 * c + (i >> 1)] = u;
           }
         }
+        // the accumulator is free for the tile after the next one
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_first_cta(&acc_empty[buf]);
+        const float inv = nw ? 1.0f / sqrtf(ss / 128.f + qe.eps) : 1.f;
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // the stores of the tile before have read both tiles
+        epilogue_sync(1 + eg);
+        bool cs_ok = true;
+#pragma unroll
+        for (int qi = 0; qi < 8; ++qi) {  // eight rotation pairs at a time: elements 8 qi .. + 7 of the head's first half, and of its second
+          float l[8], h[8];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const uint32_t ul = packed[(8 * qi + e) >> 1], uh = packed[(64 + 8 * qi + e) >> 1];
+            l[e] = __uint_as_float(ul << 16);
+            l[e + 1] = __uint_as_float(ul & 0xFFFF0000u);
+            h[e] = __uint_as_float(uh << 16);
+            h[e + 1] = __uint_as_float(uh & 0xFFFF0000u);
+          }
+          if (nw) {
+            float wl[8], wh[8];
+            bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 8 * qi), wl);
+            bf16x8_to_float(*reinterpret_cast<const uint4*>(nw + 64 + 8 * qi), wh);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              l[e] = (l[e] * inv) * wl[e];
+              h[e] = (h[e] * inv) * wh[e];
+            }
+          }
+          float cs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, sn[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (qkv_rotated) {
+            const uint32_t fill = cs_count + (uint32_t)qi, slot = fill % CS_SLOTS;
+            cs_ok = cs_ok && mbar_wait(&cs_full[slot], (fill / CS_SLOTS) & 1u);
+            const float4* mine = reinterpret_cast<const float4*>(smem_cs + (size_t)slot * CS_SLOT_BYTES + r * 32);
+            const float4 c0 = mine[0], c1 = mine[1], s0 = mine[CS_SLOT_BYTES / 32], s1 = mine[CS_SLOT_BYTES / 32 + 1];
+            cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+            sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+            // this warp has its values; when all eight warps have, the slot takes the quarter four further on
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&cs_empty[slot]);
+            if (cs_producer && qi + CS_SLOTS < 8) cs_issue(fill + CS_SLOTS, qi + CS_SLOTS);
+          }
+          float ol[8], oh[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            ol[e] = l[e] * cs[e] - h[e] * sn[e];
+            oh[e] = h[e] * cs[e] + l[e] * sn[e];
+          }
+          *reinterpret_cast<uint4*>(stage_lo + r * 128 + ((qi ^ (r & 7)) << 4)) = float_to_bf16x8(ol);
+          *reinterpret_cast<uint4*>(stage_hi + r * 128 + ((qi ^ (r & 7)) << 4)) = float_to_bf16x8(oh);
+        }
+        if (qkv_rotated) cs_count += 8;
+        if (!cs_ok) atomicExch(status, 15);
         if (!is_q) {
           // where this token's row of the head goes in the pool
           int dst = -1;
@@ -844,9 +890,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           out_buf ^= 1;
         }
       }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive_first_cta(&acc_empty[buf]);
+      if constexpr (EPI != TC_QKV_ROPE) {  // (that epilogue has given the accumulator back already)
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_first_cta(&acc_empty[buf]);
+      }
     }
     if (issuer) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // every store has landed
   }
@@ -948,7 +996,7 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   } else if (EPI != TC_OUT_F32 && N_out % 8 == 0 && (uintptr_t)out % 16 == 0) {
     if (int rc = make_map(&map_out, out, M, N_out, TC_BM)) return rc;
   }
-  constexpr size_t smem = (size_t)STAGES * pair_stage_bytes(BN) + 4 * PAIR_OUT_BYTES + 1024;
+  constexpr size_t smem = (size_t)STAGES * pair_stage_bytes(BN) + 4 * PAIR_OUT_BYTES + (EPI == TC_QKV_ROPE ? CS_RING_BYTES : 0) + 1024;
   static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
   auto kernel = gemm_tc_pair_kernel<BN, STAGES, EPI>;
   static bool configured = false;
@@ -964,8 +1012,8 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   const long long tiles = (long long)ceil_div(N_out, COLS) * ceil_div(M, 2 * TC_BM);
   MS_CHECK_ARG(tiles < (1LL << 30), "gemm_tc: too many tiles (%lld)", tiles);
   const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), PAIR_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K, up_row_offset,
-                      status, qe);
+  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(2 * pairs), PAIR_THREADS, smem, stream, 2, map_a, map_w, map_out, out, M, N_out, K,
+                      up_row_offset, status, qe);
   return 0;
 }
 
@@ -1030,7 +1078,7 @@ MS_EXPORT int ms_gemm_tc_qkv_bf16(void* q_out, const void* x, const void* w_qkv,
   const QkvEpilogue qe = {(__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w,
                           cos_sin, positions, row_of_token, page_indptr, page_indices, nq, nkv, shift, eps};
   const int n_total = (nq + 2 * nkv) * 128;
-  return launch_tc_pair<256, 5, TC_QKV_ROPE>(q_out, x, w_qkv, M, n_total, n_total, K, 0, status, stream, qe);
+  return launch_tc_pair<256, 4, TC_QKV_ROPE>(q_out, x, w_qkv, M, n_total, n_total, K, 0, status, stream, qe);
 }
 
 MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, int N, int K, int epilogue, int* status,

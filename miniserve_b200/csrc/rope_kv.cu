@@ -252,9 +252,30 @@ __global__ void rope_table_kernel(float* __restrict__ table, const int* __restri
   table[(size_t)t * rot + half + j] = sn;
 }
 
+// The same table laid out for a reader that walks 128 tokens at a time, eight rotation pairs at a time (the
+// q|k|v product's epilogue in gemm_tc.cu fetches such a piece with one bulk copy):
+// tiled[tile of 128 tokens][eighth of the 64 pairs][cos, sin][token within the tile][pair within the eighth].
+// Tokens beyond the last one (the last tile's unused rows) are left as they are.
+__global__ void rope_table_tile_kernel(float* __restrict__ tiled, const float* __restrict__ table, int num_tokens) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)num_tokens * 128) return;
+  const int t = (int)(idx >> 7), col = (int)(idx & 127);
+  const int is_sin = col >> 6, pair = col & 63;
+  tiled[((((size_t)(t >> 7) * 8 + (pair >> 3)) * 2 + is_sin) * 128 + (t & 127)) * 8 + (pair & 7)] = table[idx];
+}
+
 }  // namespace ms
 
 using namespace ms;
+
+// table: float32 [T, 128] (64 cosines then 64 sines per token); tiled: float32 [ceil(T / 128), 8, 2, 128, 8]
+MS_EXPORT int ms_rope_table_tile(float* tiled, const float* table, int num_tokens, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const long long items = (long long)num_tokens * 128;
+  MS_LAUNCH(rope_table_tile_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, tiled, table, num_tokens);
+  return 0;
+}
 
 MS_EXPORT int ms_rope_table(float* table, const int* positions, const float* inv_freq, int num_tokens, int rotary_dim,
                             cudaStream_t stream) {

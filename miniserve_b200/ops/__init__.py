@@ -16,7 +16,7 @@ from .native import NativeError, OutOfBlocks
 
 __all__ = [
     "NativeError", "OutOfBlocks", "dtype_code", "embed_gather", "add_rmsnorm", "silu_mul", "linear", "linear_silu_mul",
-    "silu_mul_is_fused", "qkv_fused_ok", "qkv_norm_rope_kv", "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table",
+    "silu_mul_is_fused", "qkv_fused_ok", "qkv_norm_rope_kv", "linear_tc", "device_status", "qk_norm_rope_kv", "rope_table", "rope_table_tiled",
     "attention", "attention_rowwise", "sample", "to_float", "require_cuda_kernels",
 ]
 
@@ -309,10 +309,10 @@ def qkv_fused_ok(x: torch.Tensor, w_qkv: torch.Tensor, nq: int, nkv: int, d: int
         return False
     if d != 128 or rotary_dim not in (0, 128) or nq % 2 or nkv % 2 or (q_norm_w is None) != (k_norm_w is None):
         return False
-    # the epilogue's work per tile does not depend on k: it hides behind the products of the next tile
-    # when k is long (measured at 2,048 rows: 76 against 83 us for 4096 -> 6144 columns, 148 against
-    # 164 us for 5120 -> 10240) and does not when k is short (30 against 25 us for 1024 -> 4096)
-    if x.shape[0] <= SKINNY_MAX_M or x.shape[1] < 2048:
+    # the epilogue's work per tile does not depend on k and hides behind the products of the next tile
+    # (measured at 2,048 rows: 23.0 against 25.4 us for 1024 -> 4096 columns, 79 against 85 us for
+    # 4096 -> 6144, 160 against 170 us for 5120 -> 10240; at 4,096 rows 34 against 46 us for 1024 -> 4096)
+    if x.shape[0] <= SKINNY_MAX_M or x.shape[1] < 1024:
         return False
     return TC_GEMM == "1" or tc_gemm_ok(x, w_qkv)
 
@@ -322,7 +322,7 @@ def qkv_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                      positions: torch.Tensor, row_of_token: torch.Tensor, page_indptr: torch.Tensor,
                      page_indices: torch.Tensor, page_size: int, stream=None) -> None:
     """The q|k|v projection of x [T, K] with what follows it in its epilogue: per-head norm of q and
-    k, rotation by position (``cos_sin``: the step's float32 table [T, 128], None for no rotation),
+    k, rotation by position (``cos_sin``: the step's float32 table as ``rope_table_tiled`` lays it out, None for no rotation),
     q to ``q_out`` [T, nq, 128] and the new k, v into their pages. The same arithmetic as
     ``linear`` followed by ``qk_norm_rope_kv``, without the [T, (nq + 2 nkv) * 128] tensor in between."""
     _check_dev(q_out, k_pool, v_pool, x, w_qkv, q_norm_w, k_norm_w, cos_sin, positions, row_of_token, page_indptr, page_indices)
@@ -330,7 +330,7 @@ def qkv_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     nkv = k_pool.shape[1]
     assert d == 128 and k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
     assert x.dtype == torch.bfloat16 and w_qkv.shape == ((nq + 2 * nkv) * d, x.shape[1]) and x.shape[0] == t
-    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (t, d))
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (-(-t // 128), 8, 2, 128, 8))
     lib = native.gemm_tc()
     native.kernel_check(lib.ms_gemm_tc_qkv_bf16(
         _ptr(q_out), _ptr(x), _ptr(w_qkv), t, x.shape[1], nq, nkv, _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w), _ptr(k_norm_w),
@@ -345,6 +345,19 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, num_tokens: int,
     native.kernel_check(k.ms_rope_table(_ptr(table), _ptr(positions), _ptr(inv_freq), num_tokens, rotary_dim,
                                         _stream(stream)))
     return table
+
+
+def rope_table_tiled(table: torch.Tensor, stream=None) -> torch.Tensor:
+    """The cos/sin table [T, 128] of a step laid out by tiles of 128 tokens and eighths of the 64 rotation
+    pairs, float32 [ceil(T / 128), 8, 2, 128, 8]: what ``qkv_norm_rope_kv`` reads (a piece per bulk copy).
+    Rows of the last tile beyond T are not written."""
+    _check_dev(table)
+    assert table.dtype == torch.float32 and table.dim() == 2 and table.shape[1] == 128
+    t = table.shape[0]
+    tiled = torch.empty((-(-t // 128), 8, 2, 128, 8), dtype=torch.float32, device=table.device)
+    k = native.kernels()
+    native.kernel_check(k.ms_rope_table_tile(_ptr(tiled), _ptr(table), t, _stream(stream)))
+    return tiled
 
 
 def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -104,6 +104,7 @@ def kernels():
     _declare(lib, "ms_qk_norm_rope_kv",
              [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p, _i, _p])
     _declare(lib, "ms_rope_table", [_p, _p, _p, _i, _i, _p])
+    _declare(lib, "ms_rope_table_tile", [_p, _p, _i, _p])
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_attention_rowwise",
              [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p, _i, _p])

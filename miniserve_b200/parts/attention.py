@@ -88,8 +88,14 @@ class GQAttention(Part):
                 and ops.qkv_fused_ok(x, self.w_qkv, self.heads, self.kv_heads, self.head_dim, rotary_dim if inv_freq is not None else 0,
                                      cache.k, self.w_q_norm, self.w_k_norm)):
             # prompt steps: norm, rotation and cache write in the product's epilogue
-            ops.qkv_norm_rope_kv(q, cache.k, cache.v, x, self.w_qkv, self.w_q_norm, self.w_k_norm,
-                                 self.position.step_table(ctx) if inv_freq is not None else None, self.qk_norm_eps,
+            tiled = None
+            if inv_freq is not None:
+                table = self.position.step_table(ctx)
+                key = ("rope_table_tiled", table.data_ptr())
+                tiled = ctx.step_cache.get(key)
+                if tiled is None:  # once per step; every layer with the same table shares it
+                    tiled = ctx.step_cache[key] = ops.rope_table_tiled(table, stream=ctx.stream)
+            ops.qkv_norm_rope_kv(q, cache.k, cache.v, x, self.w_qkv, self.w_q_norm, self.w_k_norm, tiled, self.qk_norm_eps,
                                  ctx.positions, ctx.row_of_token, indptr, indices, cache.page_size, stream=ctx.stream)
         else:
             qkv = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))

@@ -243,7 +243,16 @@ def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nq, nkv,
     q2 = torch.full_like(q1, float("nan"))
     ops.qk_norm_rope_kv(q1, a.k_pool, a.v_pool, ops.linear(x, w), qw, kw, inv_freq, d if rotate else 0, eps, a.positions, a.row_of_token,
                         a.page_indptr, a.page_indices, page, a.status, cos_sin=table)
-    ops.qkv_norm_rope_kv(q2, b.k_pool, b.v_pool, x, w, qw, kw, table, eps, b.positions, b.row_of_token, b.page_indptr, b.page_indices, page)
+    tiled = None
+    if rotate:
+        # the epilogue reads the table by tiles of 128 tokens and eighths of the 64 pairs
+        tiled = ops.rope_table_tiled(table)
+        padded = torch.zeros((tiled.shape[0] * 128, 128), device=DEV)
+        padded[:t] = table
+        want = padded.view(-1, 128, 2, 8, 8).permute(0, 3, 2, 1, 4)  # [tile, eighth, cos|sin, token, pair]
+        live = torch.arange(tiled.shape[0] * 128, device=DEV).view(-1, 1, 1, 128, 1).expand_as(want) < t
+        assert torch.equal(torch.where(live, tiled, 0), torch.where(live, want, 0))
+    ops.qkv_norm_rope_kv(q2, b.k_pool, b.v_pool, x, w, qw, kw, tiled, eps, b.positions, b.row_of_token, b.page_indptr, b.page_indices, page)
     torch.cuda.synchronize()
     assert a.status.item() == 0 and ops.device_status(DEV).item() == 0
     tol = dict(atol=3e-2, rtol=2e-2)
