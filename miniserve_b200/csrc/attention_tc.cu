@@ -357,9 +357,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int page_shift,
-                        const AtGrid gr, int* __restrict__ status,
+                        const AtGrid gr_given, int* __restrict__ status,
                         float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
-                        int* __restrict__ tickets) {
+                        int* __restrict__ tickets, const int* __restrict__ plan) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_final[2];
@@ -367,11 +367,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ int ticket_of[2];
   __shared__ int item_slot;       // the item the CTA works on (-1: none left)
   __shared__ int failed;          // a bounded wait gave up somewhere: the CTA winds down
-  const int G = gr.G, window = gr.window;
-  const int tpc = AT_ROWS / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   pdl_prologue();
+  // A launch that was captured into a CUDA graph takes what follows from the rows' lengths (tiles per
+  // row, rows, key splits) from device memory, where the host puts it before every replay: the
+  // launch itself (a CTA per SM, these arguments) is then the same for every step of its size.
+  AtGrid gr = gr_given;
+  if (plan != nullptr) {
+    gr.q_tiles = plan[0];
+    gr.rows = plan[1];
+    gr.splits = plan[2];
+    gr.max_tiles_per_item = plan[3];
+    part_ml = reinterpret_cast<float2*>(part_o + (size_t)gr.q_tiles * gr.rows * gr.head_groups * 2 * gr.splits * (AT_ROWS * AT_D));
+  }
+  const int G = gr.G, window = gr.window;
+  const int tpc = AT_ROWS / G;
   int next_item = -1;  // held by the scheduler warp
   if (warp == 8) {
     next_item = at_claim(queue, gr, cu_q, q_start, lane, true);
@@ -786,8 +797,16 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
                                  int window, int page_size, int* status, int splits, int min_tiles, float* partials,
-                                 int* queue, cudaStream_t stream) {
-  if (num_rows == 0) return 0;
+                                 int* queue, const int* plan, cudaStream_t stream) {
+  // plan: null, or four device ints (tiles of queries per row, rows, key splits, least key tiles per split) that
+  // ms_attn_tc_write_plan fills before the launch runs; num_rows, max_q_len, splits and min_tiles are then unused
+  if (num_rows == 0 && plan == nullptr) return 0;
+  if (plan != nullptr) {
+    num_rows = 1;
+    max_q_len = num_tokens;
+    splits = 2;  // (only says that there is scratch for partial results)
+    min_tiles = 1;
+  }
   MS_CHECK_ARG(splits >= 1 && splits <= 64 && min_tiles >= 1, "attention_tc: %d key splits of at least %d tiles", splits, min_tiles);
   // partials and queue: sized by ms_attn_tc_scratch (the work queue's two counters, then the tickets
   // of the groups whose keys are split)
@@ -841,10 +860,40 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   const long long total = (long long)gr.q_tiles * gr.rows * gr.head_groups * gr.splits;
   MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
-  const unsigned grid = (unsigned)(total < sm_count ? total : sm_count);
+  const unsigned grid = (unsigned)(plan == nullptr && total < sm_count ? total : sm_count);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
             q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status,
             partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
-            queue + 2);
+            queue + 2, plan);
+  return 0;
+}
+
+namespace ms {
+__global__ void attn_tc_plan_kernel(int* __restrict__ plan, int q_tiles, int rows, int splits, int min_tiles) {
+  pdl_prologue();
+  plan[0] = q_tiles;
+  plan[1] = rows;
+  plan[2] = splits;
+  plan[3] = min_tiles;
+}
+}  // namespace ms
+
+// Plans a step's attention as ms_attn_tc_plan does and puts the plan where a captured launch reads it
+// (a one-thread kernel in stream order: its arguments travel with the launch, so no host buffer has to
+// outlive the call). The key splits are cut down until their partial results fit partial_floats; the
+// work queue must hold queue_ints.
+MS_EXPORT int ms_attn_tc_write_plan(int* plan, const int* q_start, const int* q_len, int num_rows, int max_q_len, int nq, int nkv,
+                                    int window, int sm_count, long long partial_floats, long long queue_ints, cudaStream_t stream) {
+  MS_CHECK_ARG(plan != nullptr && num_rows > 0 && max_q_len > 0, "attention_tc: a plan needs rows");
+  int splits = 1, min_tiles = AT_MIN_TILES;
+  ms_attn_tc_plan(q_start, q_len, num_rows, nq, nkv, window, sm_count, &splits, &min_tiles);
+  long long need_f = 0, need_i = 0;
+  for (;; --splits) {
+    ms_attn_tc_scratch(max_q_len, num_rows, nq, nkv, splits, &need_f, &need_i);
+    if (splits == 1 || need_f <= partial_floats) break;
+  }
+  MS_CHECK_ARG(need_i <= queue_ints, "attention_tc: the work queue holds %lld entries, the step needs %lld", queue_ints, need_i);
+  const int G = at_heads_per_cta(nq, nkv);
+  MS_LAUNCH(attn_tc_plan_kernel, 1, 1, 0, stream, plan, ceil_div(max_q_len, 2 * (AT_ROWS / G)), num_rows, splits, min_tiles);
   return 0;
 }

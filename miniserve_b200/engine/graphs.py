@@ -182,9 +182,14 @@ class _Recorder:
     """Captures one pass of the model as a chain of pieces: CUDA graphs, and between them the calls
     that operations kept out of the graphs (``defer``)."""
 
-    def __init__(self, pool, stream: torch.cuda.Stream):
+    def __init__(self, pool, stream: torch.cuda.Stream, rows_all_prompts: bool):
         self.pool, self.stream = pool, stream
         self.pieces: list = []  # torch.cuda.CUDAGraph | callable(ctx)
+        self.hooks: list = []  # callable(ctx), run before the pieces of every replay
+        self.shared: dict = {}  # what operations of one captured pass share (a plan written once per step, say)
+        # whether no step of the captured shape has a row that brings a single token (decoding rows, which
+        # attention sends to another kernel): then attention can stay inside the graph
+        self.rows_all_prompts = rows_all_prompts
         self._open: torch.cuda.CUDAGraph | None = None
 
     def begin(self) -> None:
@@ -198,16 +203,21 @@ class _Recorder:
             self._open = None
 
     def defer(self, call) -> None:
+        """Keep ``call(ctx)`` out of the graphs: it is made between them, with every step's own context."""
         self.end()
         self.pieces.append(call)
         self.begin()
 
+    def before(self, call) -> None:
+        """Have ``call(ctx)`` made before the graphs of every step that replays them (and of this one)."""
+        self.hooks.append(call)
+
 
 class _Pieces:
-    __slots__ = ("pieces", "logits", "layout", "launches", "uses")
+    __slots__ = ("pieces", "hooks", "logits", "layout", "launches", "uses")
 
-    def __init__(self, pieces, logits, layout, launches):
-        self.pieces, self.logits, self.layout, self.launches, self.uses = pieces, logits, layout, launches, 0
+    def __init__(self, pieces, hooks, logits, layout, launches):
+        self.pieces, self.hooks, self.logits, self.layout, self.launches, self.uses = pieces, hooks, logits, layout, launches, 0
 
 
 class StepGraphs:
@@ -219,10 +229,12 @@ class StepGraphs:
     get from the host is the number of tokens, of rows and of wanted logits; everything else they read
     from the step's arrays, which the packer lays out at fixed places for a given (tokens, rows,
     wanted) when it is given a fixed number of page entries. The exception is attention, whose
-    kernels, grids and key splits follow the rows' lengths and starts: ``ops.attention`` keeps itself
-    out of the capture and is called again for every step, between the graphs.
+    kernels, grids and key splits follow the rows' lengths and starts. In steps without decoding rows
+    the tcgen05 attention kernel is launched with a CTA per SM and reads its plan from device memory,
+    where a hook writes it before every replay: such a step is one graph. Else ``ops.attention`` keeps
+    itself out of the capture and is called again for every step, between the graphs.
 
-    The second step with the same (tokens, rows, wanted) is captured while it runs, later ones replay.
+    The second step with the same (tokens, rows, wanted, decoding rows or not) is captured while it runs, later ones replay.
     Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
     dropped beyond ``max_shapes``. The logits of a replayed step live in the graphs' memory and are
     overwritten by the next replayed step.
@@ -252,7 +264,8 @@ class StepGraphs:
         tokens = sum(len(r.tokens) for r in rows)
         if not self.enabled or tokens < self.min_tokens or tokens == len(rows):  # decode-only steps have graphs of their own
             return None
-        return tokens, len(rows), sum(len(r.want) for r in rows)
+        # decoding rows come first in a mixed step; whether there are any decides which attention kernels run
+        return tokens, len(rows), sum(len(r.want) for r in rows), len(rows[0].tokens) == 1
 
     def run(self, rows: Sequence[StepRow], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """The step's logits, or None if this step is left to the eager path (nothing was touched then)."""
@@ -277,7 +290,7 @@ class StepGraphs:
         if held is not None and held.layout != ctx.layout:
             held = None  # cannot happen for one key; checked because a graph that reads the wrong place reads garbage silently
         if held is None:
-            held = self._capture(ctx)
+            held = self._capture(ctx, rows_all_prompts=not key[3])
             self._shapes.pop(key, None)
             self._shapes[key] = held
             while len(self._shapes) > self.max_shapes:
@@ -285,6 +298,8 @@ class StepGraphs:
         else:
             self._shapes[key] = self._shapes.pop(key)  # now the most recently used
         ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream
+        for hook in held.hooks:
+            hook(ctx)
         for piece in held.pieces:
             if isinstance(piece, torch.cuda.CUDAGraph):
                 piece.replay()
@@ -294,7 +309,7 @@ class StepGraphs:
         self.replayed_launches += held.launches
         return held.logits
 
-    def _capture(self, ctx) -> _Pieces:
+    def _capture(self, ctx, rows_all_prompts: bool) -> _Pieces:
         from ..ops import native
 
         sf = self.step_fn
@@ -302,7 +317,7 @@ class StepGraphs:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         s = self.capture_stream
-        rec = _Recorder(self._pool, s)
+        rec = _Recorder(self._pool, s, rows_all_prompts)
         before = native.LAUNCHES[0]
         ctx.recorder = rec
         try:
@@ -318,4 +333,4 @@ class StepGraphs:
         launches = native.LAUNCHES[0] - before
         native.LAUNCHES[0] = before  # a capture launches nothing
         self.captures += 1
-        return _Pieces(rec.pieces, logits, ctx.layout, launches)
+        return _Pieces(rec.pieces, rec.hooks, logits, ctx.layout, launches)

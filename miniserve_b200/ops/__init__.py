@@ -412,12 +412,19 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
-    if getattr(ctx, "recorder", None) is not None:
-        # The pass is being captured as a chain of CUDA graphs. Which kernels run here, their grids and
-        # their key splits depend on each row's length and start, which a graph cannot hold: the call
-        # is left out of the graphs and made again for every step that replays them, with that
-        # step's context (the operand tensors are the captured pass's own and do not move).
-        ctx.recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window))
+    recorder = getattr(ctx, "recorder", None)
+    if recorder is not None and q.dtype == torch.bfloat16 and (attention_tc_ok(q, k_pool) or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
+        # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
+        # their key splits depend on each row's length and start, which a graph cannot hold.
+        if attention_tc_ok(q, k_pool) and ctx.leading_single_rows == 0 and recorder.rows_all_prompts:
+            # No decoding rows in steps of this shape: the tcgen05 kernel alone, launched with a CTA per
+            # SM and taking the plan of the step's rows from device memory, where it is written before
+            # every replay. The launch stays inside the graph.
+            _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder)
+            return
+        # Else the call is left out of the graphs and made again for every step that replays them, with
+        # that step's context (the operand tensors are the captured pass's own and do not move).
+        recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window))
         return
     if q.dtype == torch.bfloat16:
         # rows at the front that bring one token each (a decode step, or the decoding requests
@@ -447,6 +454,47 @@ def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
     if not TC_ATTENTION or q.shape[2] != 128:
         return False
     return bool(native.attn_tc().ms_attn_tc_supports(q.shape[2], k_pool.shape[2], q.shape[1], k_pool.shape[1]))
+
+
+_ATTN_TC_PLANNED_SCRATCH = 1 << 25  # floats of partial results that a captured launch may use (128 MB)
+
+
+def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder) -> None:
+    """The tcgen05 attention of a step without decoding rows, launched so that a CUDA graph can hold it:
+    one CTA per SM, the step's plan (query tiles, rows, key splits) read from device memory. Launches
+    with the same heads and window in one pass share the plan, which ``recorder`` has written before
+    every replay."""
+    _check_dev(out, q, k_pool, v_pool)
+    t, nq, d = q.shape
+    nkv = k_pool.shape[1]
+    lib = native.attn_tc()
+    key = ("attn_tc_planned", nq, nkv, int(window or 0))
+    held = recorder.shared.get(key)
+    if held is None:
+        # (not zeros: made during a capture, the fill would be part of the graph and wipe the plan at every replay)
+        plan = torch.empty(8, dtype=torch.int32, device=q.device)
+        part = torch.empty(_ATTN_TC_PLANNED_SCRATCH, dtype=torch.float32, device=q.device)
+        queue = ctx.scratch.get("attn_tc_queue")
+        if queue is None:
+            queue = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)  # zero before the first launch, left zero by every launch
+            ctx.scratch["attn_tc_queue"] = queue
+        held = recorder.shared[key] = (plan, part, queue)
+
+        def write_plan(step, plan=plan, part=part, queue=queue):
+            rows = step.num_rows
+            starts = (ctypes.c_int * rows)(*step.host_q_start[:rows])
+            lens = (ctypes.c_int * rows)(*step.host_q_len[:rows])
+            native.kernel_check(lib.ms_attn_tc_write_plan(_ptr(plan), starts, lens, rows, step.max_q_len, nq, nkv, int(window or 0),
+                                                          step.sm_count, part.numel(), queue.numel(), step.stream),
+                                lib=lib, errfn="ms_attn_tc_last_error")
+
+        recorder.before(write_plan)
+    plan, part, queue = held
+    native.kernel_check(lib.ms_attn_tc_prefill(
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.page_indptr[group]),
+        _ptr(ctx.page_indices[group]), 0, t, 0, nq, nkv, k_pool.shape[0], float(scale), int(window or 0), k_pool.shape[2],
+        _ptr(device_status(q.device)), 0, 0, _ptr(part), _ptr(queue), _ptr(plan), ctx.stream),
+        lib=lib, errfn="ms_attn_tc_last_error")
 
 
 def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
@@ -493,5 +541,5 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), ctx.stream),
+        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), None, ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")

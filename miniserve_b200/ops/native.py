@@ -135,7 +135,8 @@ def attn_tc():
     _declare(lib, "ms_attn_tc_supports", [_i, _i, _i, _i])
     _declare(lib, "ms_attn_tc_plan", [_p, _p, _i, _i, _i, _i, _i, _p, _p], None)
     _declare(lib, "ms_attn_tc_scratch", [_i, _i, _i, _i, _i, _p, _p], None)
-    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _p, _i, _i, _p, _p, _p])
+    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _p, _i, _i, _p, _p, _p, _p])
+    _declare(lib, "ms_attn_tc_write_plan", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _p])
     lib.ms_attn_tc_set_pdl(int(pdl_enabled()))
     return lib
 

@@ -95,15 +95,24 @@ def test_recurring_shapes_replay_with_the_same_bits_however_the_rows_share_the_t
     p.step([("a0", 1, (0,)), ("a2", 1, (0,)), ("c", 38, ())])
     p.step([("a0", 1, (0,)), ("a2", 9, (8,)), ("c", 30, ())])
     p.step([("a0", 1, ()), ("b", 2, (0, 1)), ("c", 37, ())])
-    p.step([("a0", 20, (19,)), ("a2", 10, (3,)), ("b", 10, ())])
     assert g.captures == 2
+    # the same numbers without a decoding row at the front: a shape of its own, whose attention stays inside the graph
+    p.step([("a0", 20, (19,)), ("a2", 10, (3,)), ("b", 10, ())])
+    p.step([("a0", 5, (4,)), ("a2", 30, (3,)), ("b", 5, ())])
+    p.step([("b", 2, ()), ("c", 2, (0, 1)), ("a0", 36, ())])
+    assert g.captures == 3
+    whole = [h for k, h in g._shapes.items() if not k[3]]
+    mixed = [h for k, h in g._shapes.items() if k[3]]
+    assert all(len(h.pieces) == 1 for h in whole), "a step without decoding rows is one graph"
+    if dtype == "bfloat16":
+        assert all(len(h.pieces) == 2 * RAW["num_hidden_layers"] + 1 for h in mixed), "attention between the graphs"
     # decode-only steps and tiny steps are not taken
     before = sum(h.uses for h in g._shapes.values())
     p.step([("a0", 1, (0,)), ("b", 1, (0,))])
     p.step([("a0", 1, (0,)), ("b", 1, (0,))])
     p.step([("c", 3, (2,))])
     p.step([("c", 3, (2,))])
-    assert sum(h.uses for h in g._shapes.values()) == before and g.captures == 2
+    assert sum(h.uses for h in g._shapes.values()) == before and g.captures == 3
     p.finish()
 
 
