@@ -215,7 +215,10 @@ __device__ __forceinline__ void at_rescale(uint32_t t_o, float alpha) {
 // [seen_lo, seen_hi]. The scores are read twice, 32 columns at a time: once for the maximum, once for
 // the exponentials (chunk c of P, 16 columns, lies below chunk c + 1 of S, so chunks are read and
 // written in turn). A function of its own: inlined beside the all-in-registers form of interior tiles
-// it cost that form its registers. Returns the sum of the row's exponentials.
+// it cost that form its registers. The one-pass form (the whole row in registers here too) was tried in
+// this function and measured slower inside a prompt step (3.60 against 3.53 ms for 2,048 tokens): its
+// 128 live values cost the kernel around the call more than the second read costs here.
+// Returns the sum of the row's exponentials.
 __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int seen_lo, int seen_hi, float scale_log2,
                                                 float& m_used, float& l_sum) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -627,57 +630,90 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       } else if (n_mine > 0) {
-        // One of several splits of this group's keys: leave the partial result, take a ticket.
-        // Partial results are laid out [group of rows][split][4 columns][row], so that the 128
+        // One of several splits of this group's keys. Each takes a ticket when it is done. All but the
+        // last leave their partial result (unnormalised O, the maximum it is scaled by, the sum) and
+        // count themselves done; the last waits until the others are (they took their tickets before
+        // it and depend on nothing of it, so this is a wait for writes in flight), then adds the
+        // partial results up in the order of the splits, its own from tensor memory, and writes the
+        // rows. Partial results are laid out [group of rows][split][4 columns][row], so that the 128
         // threads of a group (one row each) write and read whole 512-byte lines together.
         const size_t unit = ((size_t)(it.rank * gr.rows + r) * gr.head_groups + head0 / G) * 2 + g;
         float4* po = reinterpret_cast<float4*>(part_o) + (unit * gr.splits + split) * (32 * 128) + row;
         float2* pml = part_ml + unit * gr.splits * 128 + row;
+        int* ticket = tickets + unit;
+        int* done = tickets + (size_t)gr.q_tiles * gr.rows * gr.head_groups * 2 + unit;
+        // all 128 threads of the group meet here, also after a wait that gave up: then nobody takes a ticket
+        const bool bad = at_group_any(1 + g, !ok);
+        if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
+        at_group_sync(1 + g);
+        const bool last = !bad && ticket_of[g] == it.shares[g] - 1;
+        if (!bad && !last) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float ov[32];
-          at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          if (ok) {
+          for (int c = 0; c < 4; ++c) {
+            float ov[32];
+            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
             for (int i = 0; i < 8; ++i) po[(c * 8 + i) * 128] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
           }
-        }
-        if (ok) pml[split * 128] = make_float2(m_used, l_sum);
-        __threadfence();
-        // all 128 threads of the group meet here, also after a wait that gave up: then nobody merges
-        const bool bad = at_group_any(1 + g, !ok);
-        int* ticket = tickets + unit;
-        if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
-        at_group_sync(1 + g);
-        if (!bad && ticket_of[g] == it.shares[g] - 1) {
-          if (row == 0) *ticket = 0;  // left as it was found, for the next launch
+          pml[split * 128] = make_float2(m_used, l_sum);
           __threadfence();
+          at_group_sync(1 + g);
+          if (row == 0) atomicAdd(done, 1);
+        } else if (last) {
+          if (row == 0) {
+            // bounded like every wait: a split that took its ticket and never finishes is an error, not a hang
+            unsigned long long began = 0;
+            bool there = false;
+            for (uint32_t polls = 1; !there; ++polls) {
+              there = *reinterpret_cast<volatile int*>(done) >= it.shares[g] - 1;
+              if (!there && (polls & 63u) == 0) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+                if (began == 0) began = now;
+                else if (now - began > MS_WAIT_NS) break;
+              }
+            }
+            if (!there) atomicExch(status, 35);
+            *ticket = 0;  // both left as they were found, for the next launch
+            *done = 0;
+            __threadfence();
+          }
+          at_group_sync(1 + g);
           const float4* pall = reinterpret_cast<const float4*>(part_o) + unit * gr.splits * (32 * 128) + row;
-          float m_all = -INFINITY;
-          for (int sp = 0; sp < it.shares[g]; ++sp) m_all = fmaxf(m_all, __ldcg(&pml[sp * 128]).x);
+          float m_all = m_used;
+          for (int sp = 0; sp < it.shares[g]; ++sp)
+            if (sp != split) m_all = fmaxf(m_all, __ldcg(&pml[sp * 128]).x);
           float l_all = 0.f;
           for (int sp = 0; sp < it.shares[g]; ++sp) {
-            const float2 ml = __ldcg(&pml[sp * 128]);
+            const float2 ml = sp == split ? make_float2(m_used, l_sum) : __ldcg(&pml[sp * 128]);
             l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
           }
           const float inv = 1.0f / l_all;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            float acc[32];
+            float own[32], acc[32];
+            at_tmem_ld32(t_o + (uint32_t)(c * 32), own);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0.f;
             for (int sp = 0; sp < it.shares[g]; ++sp) {
-              const float2 ml = __ldcg(&pml[sp * 128]);
-              const float w = ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2);
-              const float4* src = pall + (size_t)sp * (32 * 128) + (c * 8) * 128;
+              if (sp == split) {
+                const float w = l_sum == 0.f ? 0.f : at_ex2((m_used - m_all) * scale_log2);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 v = __ldcg(src + i * 128);
-                acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
-                acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
-                acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
-                acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, own[i], acc[i]);
+              } else {
+                const float2 ml = __ldcg(&pml[sp * 128]);
+                const float w = ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2);
+                const float4* src = pall + (size_t)sp * (32 * 128) + (c * 8) * 128;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 v = __ldcg(src + i * 128);
+                  acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
+                  acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
+                  acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
+                  acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+                }
               }
             }
             if (store) {
@@ -790,7 +826,7 @@ MS_EXPORT void ms_attn_tc_scratch(int max_q_len, int num_rows, int nq, int nkv, 
   const int G = at_heads_per_cta(nq, nkv);
   const long long units = (long long)ceil_div(max_q_len, 2 * (AT_ROWS / G)) * num_rows * (nq / G) * 2;  // groups of 128 rows
   *partial_floats = splits > 1 ? units * splits * (AT_ROWS * AT_D + AT_ROWS * 2) : 0;
-  *queue_ints = 2 + units;
+  *queue_ints = 2 + 2 * units;  // the queue's two counters, a ticket and a count of finished splits per group of rows
 }
 
 MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
