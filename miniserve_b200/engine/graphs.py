@@ -182,8 +182,9 @@ class _Recorder:
     """Captures one pass of the model as a chain of pieces: CUDA graphs, and between them the calls
     that operations kept out of the graphs (``defer``)."""
 
-    def __init__(self, pool, stream: torch.cuda.Stream, rows_all_prompts: bool):
+    def __init__(self, pool, stream: torch.cuda.Stream, rows_all_prompts: bool, lasting: dict):
         self.pool, self.stream = pool, stream
+        self.lasting = lasting  # what captures of different shapes share (scratch that only one step at a time uses)
         self.pieces: list = []  # torch.cuda.CUDAGraph | callable(ctx)
         self.hooks: list = []  # callable(ctx), run before the pieces of every replay
         self.shared: dict = {}  # what operations of one captured pass share (a plan written once per step, say)
@@ -240,11 +241,28 @@ class StepGraphs:
     overwritten by the next replayed step.
     """
 
-    def __init__(self, step_fn: StepFunction, indices_cap: int, max_shapes: int = 8, min_tokens: int = 16):
+    def __init__(self, step_fn: StepFunction, indices_cap: int, max_shapes: int = 32, min_tokens: int = 16,
+                 max_step_flops: float = 8e12, capture_every: int = 32):
         self.step_fn = step_fn
         self.indices_cap = indices_cap
         self.max_shapes, self.min_tokens = max_shapes, min_tokens
         self.enabled = bool(step_fn.model.shape_static)
+        # Only steps that the launches weigh on are taken: a step of more than max_step_flops (about 6 ms of
+        # products at the tensor cores' rate) gains nothing measurable from a replay, and a capture costs
+        # tens of milliseconds (Qwen3-8B sizes, 32 requests with prompts of 128 to 4,096 tokens: the
+        # 2,048-token steps took 36 ms on average with their shapes captured, 31 ms without).
+        model = step_fn.model
+        per_weight = 2 if model.dtype == torch.bfloat16 else 4
+        self.flops_per_token = 2.0 * model.weight_bytes() / per_weight if model.bound else 0.0
+        self.max_step_flops = max_step_flops
+        # A capture costs about two eager steps on top of its own (Qwen3-0.6B sizes: 10 ms against 3.5 to
+        # 4 ms) and a replay saves 0.5 ms of a 2,048-token step, 1.8 ms of a 256-token one: a shape has to
+        # come back a dozen times to pay for its capture. Shapes are captured at their second sighting,
+        # at most one in `capture_every` steps that the graphs are asked about, so that a load whose
+        # shapes keep changing loses a few per cent at worst.
+        self.capture_every = capture_every
+        self._since_capture = capture_every
+        self._lasting: dict = {}
         self._seen: dict[tuple, int] = {}
         self._shapes: dict[tuple, _Pieces] = {}  # insertion order = least recently used first
         self._pool = None
@@ -257,12 +275,15 @@ class StepGraphs:
         """The arena moved: every captured address is stale. The graphs' memory pool goes with its last
         graph, so the next capture starts a new one."""
         self._shapes.clear()
+        self._lasting.clear()
         self._pool = None
         self._generation = self.step_fn.arena_generation
 
     def _key(self, rows: Sequence[StepRow]) -> tuple | None:
         tokens = sum(len(r.tokens) for r in rows)
         if not self.enabled or tokens < self.min_tokens or tokens == len(rows):  # decode-only steps have graphs of their own
+            return None
+        if tokens * self.flops_per_token > self.max_step_flops:
             return None
         # decoding rows come first in a mixed step; whether there are any decides which attention kernels run
         return tokens, len(rows), sum(len(r.want) for r in rows), len(rows[0].tokens) == 1
@@ -276,12 +297,13 @@ class StepGraphs:
         if sf.arena_generation != self._generation:
             self._drop_all()
         held = self._shapes.get(key)
+        self._since_capture += 1
         if held is None:
             n = self._seen.get(key, 0) + 1
             if len(self._seen) > 4096:
                 self._seen.clear()
             self._seen[key] = n
-            if n < 2:
+            if n < 2 or self._since_capture <= self.capture_every:
                 return None
         ctx = sf.prepare(rows, indices_cap=self.indices_cap, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # it moved while preparing this step
@@ -293,8 +315,11 @@ class StepGraphs:
             held = self._capture(ctx, rows_all_prompts=not key[3])
             self._shapes.pop(key, None)
             self._shapes[key] = held
+            self._since_capture = 0
             while len(self._shapes) > self.max_shapes:
-                self._shapes.pop(next(iter(self._shapes)))
+                dropped = next(iter(self._shapes))
+                self._shapes.pop(dropped)
+                self._seen.pop(dropped, None)  # it has to come twice again
         else:
             self._shapes[key] = self._shapes.pop(key)  # now the most recently used
         ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream
@@ -317,7 +342,7 @@ class StepGraphs:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         s = self.capture_stream
-        rec = _Recorder(self._pool, s, rows_all_prompts)
+        rec = _Recorder(self._pool, s, rows_all_prompts, self._lasting)
         before = native.LAUNCHES[0]
         ctx.recorder = rec
         try:

@@ -473,7 +473,9 @@ def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float,
     if held is None:
         # (not zeros: made during a capture, the fill would be part of the graph and wipe the plan at every replay)
         plan = torch.empty(8, dtype=torch.int32, device=q.device)
-        part = torch.empty(_ATTN_TC_PLANNED_SCRATCH, dtype=torch.float32, device=q.device)
+        part = recorder.lasting.get("attn_tc_partials")  # one for all captured shapes: steps run one after the other
+        if part is None:
+            part = recorder.lasting["attn_tc_partials"] = torch.empty(_ATTN_TC_PLANNED_SCRATCH, dtype=torch.float32, device=q.device)
         queue = ctx.scratch.get("attn_tc_queue")
         if queue is None:
             queue = torch.zeros(1 << 16, dtype=torch.int32, device=q.device)  # zero before the first launch, left zero by every launch

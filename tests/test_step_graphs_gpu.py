@@ -44,6 +44,7 @@ class Pair:
                                     device=self.model.device, poison=True) for _ in range(2)]
         self.eager = StepFunction(self.model, self.caches[0])
         self.graphed = StepFunction(self.model, self.caches[1], arena_ints=arena_ints)
+        graph_args.setdefault("capture_every", 0)  # the tests want every capture at once
         self.graphs = StepGraphs(self.graphed, indices_cap=pages + 2 * slots + 4, **graph_args)
         self.graphed.graphs = self.graphs
         self.requests: dict[str, tuple] = {}
@@ -131,6 +132,23 @@ def test_shapes_beyond_the_limit_are_dropped_and_captured_again(folder):
     p.finish()
 
 
+def test_captures_are_spaced_out(folder):
+    p = Pair(folder, "bfloat16", capture_every=5)
+    g = p.graphs
+    def once(n, i):
+        p.step([(f"t{n}_{i}", n, (n - 1,))])
+        p.end(f"t{n}_{i}")
+    once(48, 0)
+    once(48, 1)
+    assert g.captures == 1  # the second sighting, and nothing was captured lately
+    for i in range(5):
+        once(64, i)
+    assert g.captures == 1  # seen five times, but the last capture is less than six steps back
+    once(64, 5)
+    assert g.captures == 2
+    p.finish()
+
+
 def test_an_arena_that_has_to_grow_drops_the_graphs(folder):
     p = Pair(folder, "bfloat16", pages=160, arena_ints=1024)
     g = p.graphs
@@ -161,6 +179,11 @@ def test_a_model_with_a_part_that_reads_the_rows_on_the_host_is_left_alone(folde
         p.caches[1].release(rc)
     finally:
         SwiGLU.shape_static = True
+    # nor is a step taken whose products outweigh its launches by far
+    heavy = StepGraphs(p.graphed, indices_cap=100, max_step_flops=1e6)
+    rc = p.caches[1].new_request()
+    assert heavy.enabled and heavy.run([StepRow(rc, [1] * 64, (63,))]) is None and heavy.run([StepRow(rc, [1] * 64, (63,))]) is None
+    p.caches[1].release(rc)
     p.finish()
 
 
