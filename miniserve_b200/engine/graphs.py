@@ -182,15 +182,15 @@ class _Recorder:
     """Captures one pass of the model as a chain of pieces: CUDA graphs, and between them the calls
     that operations kept out of the graphs (``defer``)."""
 
-    def __init__(self, pool, stream: torch.cuda.Stream, rows_all_prompts: bool, lasting: dict):
+    def __init__(self, pool, stream: torch.cuda.Stream, single_rows: int, lasting: dict):
         self.pool, self.stream = pool, stream
         self.lasting = lasting  # what captures of different shapes share (scratch that only one step at a time uses)
         self.pieces: list = []  # torch.cuda.CUDAGraph | callable(ctx)
         self.hooks: list = []  # callable(ctx), run before the pieces of every replay
         self.shared: dict = {}  # what operations of one captured pass share (a plan written once per step, say)
-        # whether no step of the captured shape has a row that brings a single token (decoding rows, which
-        # attention sends to another kernel): then attention can stay inside the graph
-        self.rows_all_prompts = rows_all_prompts
+        # how many rows at the front of every step of the captured shape bring a single token (decoding
+        # rows, which attention sends to another kernel than the rest)
+        self.single_rows = single_rows
         self._open: torch.cuda.CUDAGraph | None = None
 
     def begin(self) -> None:
@@ -230,12 +230,14 @@ class StepGraphs:
     get from the host is the number of tokens, of rows and of wanted logits; everything else they read
     from the step's arrays, which the packer lays out at fixed places for a given (tokens, rows,
     wanted) when it is given a fixed number of page entries. The exception is attention, whose
-    kernels, grids and key splits follow the rows' lengths and starts. In steps without decoding rows
-    the tcgen05 attention kernel is launched with a CTA per SM and reads its plan from device memory,
-    where a hook writes it before every replay: such a step is one graph. Else ``ops.attention`` keeps
-    itself out of the capture and is called again for every step, between the graphs.
+    kernels, grids and key splits follow the rows' lengths and starts. With head size 128 the decoding
+    rows at the front of a step (their number is part of the shape) go to the split-key kernel as
+    inside a decode graph, and the tcgen05 kernel for the rest is launched with a CTA per SM and reads
+    its plan from device memory, where a hook writes it before every replay: the step is one graph.
+    Else ``ops.attention`` keeps itself out of the capture and is called again for every step, between
+    the graphs.
 
-    The second step with the same (tokens, rows, wanted, decoding rows or not) is captured while it runs, later ones replay.
+    The second step with the same (tokens, rows, wanted, decoding rows) is captured while it runs, later ones replay.
     Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
     dropped beyond ``max_shapes``. The logits of a replayed step live in the graphs' memory and are
     overwritten by the next replayed step.
@@ -285,8 +287,9 @@ class StepGraphs:
             return None
         if tokens * self.flops_per_token > self.max_step_flops:
             return None
-        # decoding rows come first in a mixed step; whether there are any decides which attention kernels run
-        return tokens, len(rows), sum(len(r.want) for r in rows), len(rows[0].tokens) == 1
+        # decoding rows come first in a mixed step; how many there are decides which attention kernels run on what
+        single = next((i for i, r in enumerate(rows) if len(r.tokens) != 1), len(rows))
+        return tokens, len(rows), sum(len(r.want) for r in rows), single
 
     def run(self, rows: Sequence[StepRow], prev_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """The step's logits, or None if this step is left to the eager path (nothing was touched then)."""
@@ -312,7 +315,7 @@ class StepGraphs:
         if held is not None and held.layout != ctx.layout:
             held = None  # cannot happen for one key; checked because a graph that reads the wrong place reads garbage silently
         if held is None:
-            held = self._capture(ctx, rows_all_prompts=not key[3])
+            held = self._capture(ctx, single_rows=key[3])
             self._shapes.pop(key, None)
             self._shapes[key] = held
             self._since_capture = 0
@@ -334,17 +337,25 @@ class StepGraphs:
         self.replayed_launches += held.launches
         return held.logits
 
-    def _capture(self, ctx, rows_all_prompts: bool) -> _Pieces:
+    def _capture(self, ctx, single_rows: int) -> _Pieces:
         from ..ops import native
+
+        import gc
 
         sf = self.step_fn
         torch.cuda.current_stream(sf.device).synchronize()
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         s = self.capture_stream
-        rec = _Recorder(self._pool, s, rows_all_prompts, self._lasting)
+        rec = _Recorder(self._pool, s, single_rows, self._lasting)
         before = native.LAUNCHES[0]
         ctx.recorder = rec
+        # No garbage collection while a capture is open: a graph of an earlier, dropped set that the
+        # collector frees in the middle of it destroys its CUDA objects, which is not allowed then and
+        # voids the capture. What is garbage already goes now.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
         try:
             with torch.cuda.stream(s):
                 ctx.stream = s.cuda_stream
@@ -355,6 +366,8 @@ class StepGraphs:
                     rec.end()
         finally:
             ctx.recorder = None
+            if collecting:
+                gc.enable()
         launches = native.LAUNCHES[0] - before
         native.LAUNCHES[0] = before  # a capture launches nothing
         self.captures += 1

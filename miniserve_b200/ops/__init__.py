@@ -416,11 +416,22 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     if recorder is not None and q.dtype == torch.bfloat16 and (attention_tc_ok(q, k_pool) or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold.
-        if attention_tc_ok(q, k_pool) and ctx.leading_single_rows == 0 and recorder.rows_all_prompts:
-            # No decoding rows in steps of this shape: the tcgen05 kernel alone, launched with a CTA per
-            # SM and taking the plan of the step's rows from device memory, where it is written before
-            # every replay. The launch stays inside the graph.
-            _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder)
+        single = ctx.leading_single_rows
+        if attention_tc_ok(q, k_pool) and single == recorder.single_rows and (single == 0 or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
+            # Steps of this shape have `single` decoding rows at the front and prompt rows behind them. The
+            # decoding rows go to the split-key kernel as inside a decode graph (its launch follows their
+            # number alone). The prompt rows go to the tcgen05 kernel, launched with a CTA per SM and
+            # taking the plan of its rows from device memory, where it is written before every replay.
+            # Both launches stay inside the graph.
+            if single:
+                inside = ctx.graph_bucket
+                ctx.graph_bucket = ctx.graph_bucket or single
+                try:
+                    attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+                finally:
+                    ctx.graph_bucket = inside
+            if single < ctx.num_rows:
+                _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder, single)
             return
         # Else the call is left out of the graphs and made again for every step that replays them, with
         # that step's context (the operand tensors are the captured pass's own and do not move).
@@ -459,16 +470,17 @@ def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
 _ATTN_TC_PLANNED_SCRATCH = 1 << 25  # floats of partial results that a captured launch may use (128 MB)
 
 
-def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder) -> None:
-    """The tcgen05 attention of a step without decoding rows, launched so that a CUDA graph can hold it:
-    one CTA per SM, the step's plan (query tiles, rows, key splits) read from device memory. Launches
-    with the same heads and window in one pass share the plan, which ``recorder`` has written before
-    every replay."""
+def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder,
+                          first_row: int = 0) -> None:
+    """The tcgen05 attention of the rows from ``first_row`` on, launched so that a CUDA graph can hold it:
+    one CTA per SM, the plan of those rows (query tiles, rows, key splits) read from device memory.
+    Launches with the same heads and window in one pass share the plan, which ``recorder`` has
+    written before every replay."""
     _check_dev(out, q, k_pool, v_pool)
     t, nq, d = q.shape
     nkv = k_pool.shape[1]
     lib = native.attn_tc()
-    key = ("attn_tc_planned", nq, nkv, int(window or 0))
+    key = ("attn_tc_planned", nq, nkv, int(window or 0), first_row)
     held = recorder.shared.get(key)
     if held is None:
         # (not zeros: made during a capture, the fill would be part of the graph and wipe the plan at every replay)
@@ -483,17 +495,18 @@ def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float,
         held = recorder.shared[key] = (plan, part, queue)
 
         def write_plan(step, plan=plan, part=part, queue=queue):
-            rows = step.num_rows
-            starts = (ctypes.c_int * rows)(*step.host_q_start[:rows])
-            lens = (ctypes.c_int * rows)(*step.host_q_len[:rows])
+            rows = step.num_rows - first_row
+            starts = (ctypes.c_int * rows)(*step.host_q_start[first_row:first_row + rows])
+            lens = (ctypes.c_int * rows)(*step.host_q_len[first_row:first_row + rows])
             native.kernel_check(lib.ms_attn_tc_write_plan(_ptr(plan), starts, lens, rows, step.max_q_len, nq, nkv, int(window or 0),
                                                           step.sm_count, part.numel(), queue.numel(), step.stream),
                                 lib=lib, errfn="ms_attn_tc_last_error")
 
         recorder.before(write_plan)
     plan, part, queue = held
+    skip = 4 * first_row  # the per-row tables are int32
     native.kernel_check(lib.ms_attn_tc_prefill(
-        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.page_indptr[group]),
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), 0, t, 0, nq, nkv, k_pool.shape[0], float(scale), int(window or 0), k_pool.shape[2],
         _ptr(device_status(q.device)), 0, 0, _ptr(part), _ptr(queue), _ptr(plan), ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")

@@ -1,7 +1,10 @@
 """Prompt and mixed steps replayed from CUDA graphs (``engine/graphs.py``, ``StepGraphs``) against the
 same steps launched eagerly: the same bits, whichever way a step of a recurring shape (tokens, rows,
-wanted logits) shares its tokens among its rows. Two step functions over the same model and caches of
-their own run the same steps; one has the graphs.
+wanted logits, decoding rows) shares its tokens among its rows. Two step functions over the same model
+and caches of their own run the same steps; one has the graphs. One exception to "the same bits": in
+bfloat16 the decoding rows of a captured step have their keys split as inside a decode graph (by the
+number of rows, not by their lengths), so their sums are taken in another order; from the first such
+step on the two sides are compared within bfloat16's resolution instead. float32 stays exact throughout.
 
 The model has head size 128, so the steps run through the tcgen05 attention (kept out of the graphs
 and called between them with each step's own geometry), the decode attention for the single-token
@@ -49,6 +52,7 @@ class Pair:
         self.graphed.graphs = self.graphs
         self.requests: dict[str, tuple] = {}
         self.rng = random.Random(9)
+        self.exact = True  # until a bfloat16 step with decoding rows has been captured
 
     def step(self, rows):
         """rows: (request name, number of new tokens, wanted places). The same bits from both, or it fails."""
@@ -60,9 +64,16 @@ class Pair:
             for side in range(2):
                 built[side].append(StepRow(self.requests[name][side], tokens, want))
         want = self.eager.run(built[0]).clone()
+        captures = self.graphs.captures
         got = self.graphed.run(built[1]).clone()
+        if self.model.dtype == torch.bfloat16 and self.graphs.captures > captures and len(built[1][0].tokens) == 1:
+            self.exact = False
         assert got.shape == want.shape
-        assert torch.equal(got, want), f"step {rows}: off by {(got - want).abs().max().item():.3e}"
+        off = (got - want).abs().max().item() if got.numel() else 0.0
+        if self.exact:
+            assert torch.equal(got, want), f"step {rows}: off by {off:.3e}"
+        else:
+            assert off <= 2.0 ** -6 * max(1.0, want.abs().max().item()), f"step {rows}: off by {off:.3e}"
         return got
 
     def end(self, name):
@@ -102,11 +113,7 @@ def test_recurring_shapes_replay_with_the_same_bits_however_the_rows_share_the_t
     p.step([("a0", 5, (4,)), ("a2", 30, (3,)), ("b", 5, ())])
     p.step([("b", 2, ()), ("c", 2, (0, 1)), ("a0", 36, ())])
     assert g.captures == 3
-    whole = [h for k, h in g._shapes.items() if not k[3]]
-    mixed = [h for k, h in g._shapes.items() if k[3]]
-    assert all(len(h.pieces) == 1 for h in whole), "a step without decoding rows is one graph"
-    if dtype == "bfloat16":
-        assert all(len(h.pieces) == 2 * RAW["num_hidden_layers"] + 1 for h in mixed), "attention between the graphs"
+    assert all(len(h.pieces) == 1 for h in g._shapes.values()), "with head size 128 every step is one graph"
     # decode-only steps and tiny steps are not taken
     before = sum(h.uses for h in g._shapes.values())
     p.step([("a0", 1, (0,)), ("b", 1, (0,))])
@@ -114,6 +121,24 @@ def test_recurring_shapes_replay_with_the_same_bits_however_the_rows_share_the_t
     p.step([("c", 3, (2,))])
     p.step([("c", 3, (2,))])
     assert sum(h.uses for h in g._shapes.values()) == before and g.captures == 3
+    p.finish()
+
+
+def test_attention_kept_out_of_the_graphs_when_its_launch_follows_the_rows(folder, monkeypatch):
+    """Without the tcgen05 attention kernel (whose plan can live on the device) attention is called between
+    the graphs, with every step's own rows."""
+    from miniserve_b200 import ops
+
+    monkeypatch.setattr(ops, "TC_ATTENTION", False)
+    p = Pair(folder, "bfloat16")
+    g = p.graphs
+    for i in range(3):
+        p.step([(f"a{i}", 96, (95,))])
+    p.step([("a0", 1, (0,)), ("a2", 9, (8,)), ("c", 30, ())])
+    p.step([("a0", 1, ()), ("b", 2, (0, 1)), ("c", 37, ())])
+    p.step([("a0", 1, (0,)), ("b", 20, (0,)), ("c", 19, ())])
+    assert g.captures == 2 and sum(h.uses for h in g._shapes.values()) == 4
+    assert all(len(h.pieces) == 2 * RAW["num_hidden_layers"] + 1 for h in g._shapes.values())
     p.finish()
 
 
