@@ -23,7 +23,9 @@ def add_engine_args(parser: argparse.ArgumentParser) -> None:
     g.add_argument("--chunked-prefill-size", type=int, default=None,
                    help="token budget of a step: decoding requests first, the rest filled with portions of prompts; "
                         "0 runs every prompt whole, in steps without decoding (default: 2048)")
-    g.add_argument("--disable-cuda-graph", action="store_true", help="launch the kernels of decode steps one by one")
+    g.add_argument("--disable-cuda-graph", action="store_true", help="launch the kernels of every step one by one")
+    g.add_argument("--disable-step-graphs", action="store_true",
+                   help="keep the graphs of decode steps, launch prompt and mixed steps one kernel at a time")
     g.add_argument("--cuda-graph-max-bs", type=int, default=None,
                    help="decode steps up to this many requests replay a captured graph, padded to the next power of two "
                         "or to this number (default: --max-running)")
@@ -51,6 +53,7 @@ def engine_kwargs(args: argparse.Namespace) -> dict:
         seed=args.seed,
         chunked_prefill_size=args.chunked_prefill_size,
         cuda_graph=not args.disable_cuda_graph,
+        step_graphs=not args.disable_step_graphs,
         cuda_graph_max_bs=args.cuda_graph_max_bs,
         overlap=not args.disable_overlap,
         poison_on_free=args.poison_on_free,

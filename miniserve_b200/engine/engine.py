@@ -77,7 +77,7 @@ class Engine:
                  max_running: int = 64, max_prefill_tokens: int = 8192, chunked_prefill_size: int | None = None,
                  seed: int = 0, cuda_graph: bool = True, cuda_graph_max_bs: int | None = None,
                  kv_mem_fraction: float = 0.9, overlap: bool = True, cache: CacheManager | None = None, step_fn=None,
-                 sampler=None, poison_on_free: bool = False):
+                 sampler=None, poison_on_free: bool = False, step_graphs: bool = True):
         """``kv_pool_tokens``: exact size of the cache pool in tokens, rounded down to whole pages
         (default: ``kv_mem_fraction`` of the memory the device has free after the weights, less a
         reserve for activations). ``chunked_prefill_size``: tokens per step, decode tokens included,
@@ -85,6 +85,7 @@ class Engine:
         prefill-only steps; default 2048. ``seed`` seeds the sampling of requests that bring no
         seed of their own, in submission order. ``cuda_graph``: replay captured CUDA graphs for
         decode-only steps of up to ``cuda_graph_max_bs`` requests (default ``max_running``).
+        ``step_graphs``: with ``cuda_graph``, also capture prompt and mixed steps whose shape comes again.
         ``overlap``: launch each step before reading back the previous one.
         Names and meanings follow miniserve/engine/engine.py:42-77. ``cache``, ``step_fn`` and
         ``sampler`` replace the ones the engine would build (a test can run the whole loop on the
@@ -114,7 +115,7 @@ class Engine:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self.step_fn, self.sampler, cuda_graph_max_bs or max_running)
-            if model.shape_static:
+            if step_graphs and model.shape_static:
                 from .graphs import StepGraphs
 
                 # the arena holds the largest step at the fixed layout now, so that it does not move under captured graphs

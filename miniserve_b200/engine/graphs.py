@@ -167,10 +167,18 @@ class DecodeGraphs:
         torch.cuda.current_stream(sf.device).synchronize()
         from ..ops import native
 
+        import gc
+
         graph = torch.cuda.CUDAGraph()
         before = native.LAUNCHES[0]
-        with torch.cuda.graph(graph, pool=self._pool, stream=s):
-            logits, tokens = self._forward(ctx, bucket, mode, f32, i64)
+        collecting = gc.isenabled()  # no collection while the capture is open (see StepGraphs._capture)
+        try:
+            with torch.cuda.graph(graph, pool=self._pool, stream=s):
+                gc.disable()
+                logits, tokens = self._forward(ctx, bucket, mode, f32, i64)
+        finally:
+            if collecting:
+                gc.enable()
         launches = native.LAUNCHES[0] - before
         native.LAUNCHES[0] = before  # a capture launches nothing
         if self._pool is None:
@@ -244,7 +252,7 @@ class StepGraphs:
     """
 
     def __init__(self, step_fn: StepFunction, indices_cap: int, max_shapes: int = 32, min_tokens: int = 16,
-                 max_step_flops: float = 8e12, capture_every: int = 32):
+                 max_step_flops: float = 8e12, capture_every: int = 64, sightings: int = 4):
         self.step_fn = step_fn
         self.indices_cap = indices_cap
         self.max_shapes, self.min_tokens = max_shapes, min_tokens
@@ -257,12 +265,15 @@ class StepGraphs:
         per_weight = 2 if model.dtype == torch.bfloat16 else 4
         self.flops_per_token = 2.0 * model.weight_bytes() / per_weight if model.bound else 0.0
         self.max_step_flops = max_step_flops
-        # A capture costs about two eager steps on top of its own (Qwen3-0.6B sizes: 10 ms against 3.5 to
-        # 4 ms) and a replay saves 0.5 ms of a 2,048-token step, 1.8 ms of a 256-token one: a shape has to
-        # come back a dozen times to pay for its capture. Shapes are captured at their second sighting,
-        # at most one in `capture_every` steps that the graphs are asked about, so that a load whose
-        # shapes keep changing loses a few per cent at worst.
-        self.capture_every = capture_every
+        # A capture costs the host about 6 ms (Qwen3-0.6B sizes), during which steps already launched go
+        # on; a replay saves the device 0.3 ms of a 2,048-token step and the host most of its 2.6 ms of
+        # launching, which counts where steps are short (a 256-token step: 3.8 -> 2.0 ms). Loads whose
+        # shapes keep changing gain nothing from captures, so they are kept rare: a shape is captured at
+        # its fourth sighting, at most one in `capture_every` steps that the graphs are asked about.
+        # Measured with 128 to 256 requests of random lengths (tools/stress): within 1 % either way of
+        # the same run without these graphs; the same step again and again (bench.py's prefill) 4.14 -> 3.46 ms
+        # together with the kernels' gains.
+        self.capture_every, self.sightings = capture_every, sightings
         self._since_capture = capture_every
         self._lasting: dict = {}
         self._seen: dict[tuple, int] = {}
@@ -306,7 +317,7 @@ class StepGraphs:
             if len(self._seen) > 4096:
                 self._seen.clear()
             self._seen[key] = n
-            if n < 2 or self._since_capture <= self.capture_every:
+            if n < self.sightings or self._since_capture <= self.capture_every:
                 return None
         ctx = sf.prepare(rows, indices_cap=self.indices_cap, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # it moved while preparing this step
@@ -343,7 +354,7 @@ class StepGraphs:
         import gc
 
         sf = self.step_fn
-        torch.cuda.current_stream(sf.device).synchronize()
+        # (no wait for the device: a capture launches nothing, and steps still running go on meanwhile)
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         s = self.capture_stream

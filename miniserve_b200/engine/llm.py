@@ -26,7 +26,7 @@ class LLM:
         config.json dict, filled with random weights from ``weights_seed``. The remaining
         keywords are the engine's (``kv_pool_tokens``, ``page_size``, ``max_running``,
         ``max_prefill_tokens``, ``chunked_prefill_size``, ``seed``, ``cuda_graph``,
-        ``cuda_graph_max_bs``, ``overlap``)."""
+        ``cuda_graph_max_bs``, ``step_graphs``, ``overlap``)."""
         if (model is None) == (random is None):
             raise ValueError("give either a model folder or random=PRESET")
         if model is not None:

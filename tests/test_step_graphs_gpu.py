@@ -47,7 +47,8 @@ class Pair:
                                     device=self.model.device, poison=True) for _ in range(2)]
         self.eager = StepFunction(self.model, self.caches[0])
         self.graphed = StepFunction(self.model, self.caches[1], arena_ints=arena_ints)
-        graph_args.setdefault("capture_every", 0)  # the tests want every capture at once
+        graph_args.setdefault("capture_every", 0)  # the tests want every capture at once,
+        graph_args.setdefault("sightings", 2)      # at a shape's second sighting
         self.graphs = StepGraphs(self.graphed, indices_cap=pages + 2 * slots + 4, **graph_args)
         self.graphed.graphs = self.graphs
         self.requests: dict[str, tuple] = {}
