@@ -136,8 +136,8 @@ __host__ __device__ constexpr uint32_t at_idesc(bool b_mn) {
 // goes through shared memory: the softmax threads store it (bfloat16, two per 32-bit column) into
 // the tensor-memory columns its S tile occupied, and the second product takes its A operand from
 // there. Tensor memory: S/P of A [0,128), S/P of B [128,256), O of A [256,384), O of B [384,512).
-// Warps 0-3: softmax A, 4-7: softmax B, 8: TMA, 9: MMA.
-constexpr int AT_THREADS = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
+// Warps 0-3: softmax A, 4-7: softmax B, 8: TMA, 9: MMA, 10-11: idle (registers are handed over by groups of four warps).
+constexpr int AT_THREADS = 384;  // 8 softmax warps, 1 TMA warp, 1 MMA warp, 2 warps that only make up the third group of four
 
 struct AtSmem {
   static constexpr int q = 0;                     // group A: 2 blocks, group B: 2 blocks
@@ -415,327 +415,353 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   AT_FENCE_AFTER();
   const uint32_t tmem = tmem_slot;
 
-  for (;;) {
-    const int cur = item_slot;
-    if (cur < 0) break;
-    AtItem it;
-    at_item(it, cur, gr, cu_q, q_start);
-    const int r = it.r, tok0 = it.tok0, q_len = it.q_len, m0 = it.m0, start = it.start, kv_len = it.kv_len;
-    const int head0 = it.head0, kvh = head0 / (nq / nkv), split = it.split, tile_begin = it.tile_begin, n_all = it.n_all;
-    const bool has_b = it.has_b;
-    // timing experiments only: the first CTA stamps clock64() at the hand-off points of its first item
-
-    if (warp == 8) {
-      // ---------------------------------------------------------- TMA producer (and scheduler)
-      if (lane == 0) {
-        at_expect_tx(&q_full, (has_b ? 4 : 2) * AT_BLOCK);
-        at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
-        at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
-        if (has_b) {
-          at_tma_3d(smem + AtSmem::q + 2 * AT_BLOCK, &map_q, &q_full, 0, head0, tok0 + m0 + tpc);
-          at_tma_3d(smem + AtSmem::q + 3 * AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0 + tpc);
-        }
-      }
-      const int* pages = page_indices + page_indptr[r];
-      const int page_size = 1 << page_shift;
-      const int box_rows = min(page_size, AT_KEYS);
-      bool ok = true;
-      for (int j = 0; j < n_all; ++j) {
-        const int s = j & 1;
-        const int key0 = (tile_begin + j) * AT_KEYS;
-        const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
-        int my_row = 0;
-        if (lane < boxes) {
-          const int key = key0 + lane * box_rows;
-          const int page = pages[key >> page_shift];
-          my_row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
-        }
-        if (j >= 2) {
-          if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) {
-            if (lane == 0) {
-              atomicExch(status, 31);
-              failed = 1;
-            }
-            break;
+  // The roles part for good here, each with its own loop over the items, because they part in registers
+  // too: 12 warps of 168 registers fill the register file, the softmax warps (a whole row of scores each,
+  // 128 values) want more and the two warps that issue copies and products, and their two idle
+  // companions, need few. Warps 8 to 11 give theirs up, warps 0 to 7 take them.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n");
+    for (;;) {
+      const int cur = item_slot;
+      if (cur < 0) break;
+      AtItem it;
+      at_item(it, cur, gr, cu_q, q_start);
+      const int r = it.r, tok0 = it.tok0, m0 = it.m0, kv_len = it.kv_len;
+      const int head0 = it.head0, kvh = head0 / (nq / nkv), tile_begin = it.tile_begin, n_all = it.n_all;
+      const bool has_b = it.has_b;
+      if (warp == 8) {
+        // ---------------------------------------------------------- TMA producer (and scheduler)
+        if (lane == 0) {
+          at_expect_tx(&q_full, (has_b ? 4 : 2) * AT_BLOCK);
+          at_tma_3d(smem + AtSmem::q, &map_q, &q_full, 0, head0, tok0 + m0);
+          at_tma_3d(smem + AtSmem::q + AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0);
+          if (has_b) {
+            at_tma_3d(smem + AtSmem::q + 2 * AT_BLOCK, &map_q, &q_full, 0, head0, tok0 + m0 + tpc);
+            at_tma_3d(smem + AtSmem::q + 3 * AT_BLOCK, &map_q, &q_full, 64, head0, tok0 + m0 + tpc);
           }
         }
-        unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
-        unsigned char* vt = kt + 2 * AT_BLOCK;
-        if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
+        const int* pages = page_indices + page_indptr[r];
+        const int page_size = 1 << page_shift;
+        const int box_rows = min(page_size, AT_KEYS);
+        bool ok = true;
+        for (int j = 0; j < n_all; ++j) {
+          const int s = j & 1;
+          const int key0 = (tile_begin + j) * AT_KEYS;
+          const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
+          int my_row = 0;
+          if (lane < boxes) {
+            const int key = key0 + lane * box_rows;
+            const int page = pages[key >> page_shift];
+            my_row = (max(page, 0) * nkv + kvh) * page_size + (key & (page_size - 1));
+          }
+          if (j >= 2) {
+            if (lane == 0) ok = at_wait(&kv_empty[s], ((j >> 1) - 1) & 1);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+              if (lane == 0) {
+                atomicExch(status, 31);
+                failed = 1;
+              }
+              break;
+            }
+          }
+          unsigned char* kt = smem + AtSmem::kv + s * AtSmem::stage;
+          unsigned char* vt = kt + 2 * AT_BLOCK;
+          if (lane == 0) at_expect_tx(&kv_full[s], (uint32_t)boxes * box_rows * 128 * 4);
+          __syncwarp();
+          if (lane < boxes) {
+            const int off = lane * box_rows * 128;
+            at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
+            at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
+            at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
+            at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
+          }
+        }
+        // all loads of this item are on their way: find the next one while the others compute
         __syncwarp();
-        if (lane < boxes) {
-          const int off = lane * box_rows * 128;
-          at_tma_2d(kt + off, &map_k, &kv_full[s], 0, my_row);
-          at_tma_2d(kt + AT_BLOCK + off, &map_k, &kv_full[s], 64, my_row);
-          at_tma_2d(vt + off, &map_v, &kv_full[s], 0, my_row);
-          at_tma_2d(vt + AT_BLOCK + off, &map_v, &kv_full[s], 64, my_row);
+        next_item = at_claim(queue, gr, cu_q, q_start, lane, false);
+      } else if (warp == 9) {
+        // ---------------------------------------------------------- MMA issuer
+        if (at_elect()) {
+          constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
+          bool ok = at_wait(&q_full, 0);
+          int kv_ready = -1;  // the last tile whose kv_full this thread has waited for
+          auto need_kv = [&](int j) -> bool {
+            if (j <= kv_ready) return true;
+            if (!at_wait(&kv_full[j & 1], (j >> 1) & 1)) return false;
+            kv_ready = j;
+            AT_FENCE_AFTER();
+            return true;
+          };
+          auto issue_s = [&](int g, int j) -> bool {
+            if (!need_kv(j)) return false;
+            const unsigned char* kt = smem + AtSmem::kv + (j & 1) * AtSmem::stage;
+            const unsigned char* qt = smem + AtSmem::q + g * 2 * AT_BLOCK;
+  #pragma unroll
+            for (int kk = 0; kk < AT_D / 16; ++kk) {
+              const uint64_t da = at_desc(qt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+              const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
+              at_mma(tmem + (uint32_t)(g * 128), da, db, idesc_s, kk != 0);
+            }
+            at_commit(&s_full[g]);
+            return true;
+          };
+          if (ok && it.n_tiles[0] > 0) ok = issue_s(0, 0);
+          if (ok && it.n_tiles[1] > 0) ok = issue_s(1, 0);
+          for (int j = 0; j < n_all && ok; ++j) {
+            const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
+  #pragma unroll 1
+            for (int g = 0; g < 2 && ok; ++g) {
+              if (j >= it.n_tiles[g]) continue;
+              if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
+              AT_FENCE_AFTER();
+  #pragma unroll
+              for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
+                // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
+                // B = V [keys][d], MN-major
+                const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
+                at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
+              }
+              if (j + 1 < it.n_tiles[g]) {
+                ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
+              } else {
+                at_commit(&o_final[g]);
+              }
+            }
+            // the producer waits for this only before tile j + 2: an arrival that nobody waits for
+            // must not be in flight when the barriers are set up again for the next item
+            if (ok && j + 2 < n_all) at_commit(&kv_empty[j & 1]);
+          }
+          if (!ok) {
+            atomicExch(status, 33);
+            failed = 1;
+          }
         }
       }
-      // all loads of this item are on their way: find the next one while the others compute
-      __syncwarp();
-      next_item = at_claim(queue, gr, cu_q, q_start, lane, false);
-    } else if (warp == 9) {
-      // ---------------------------------------------------------- MMA issuer
-      if (at_elect()) {
-        constexpr uint32_t idesc_s = at_idesc(false), idesc_o = at_idesc(true);
-        bool ok = at_wait(&q_full, 0);
-        int kv_ready = -1;  // the last tile whose kv_full this thread has waited for
-        auto need_kv = [&](int j) -> bool {
-          if (j <= kv_ready) return true;
-          if (!at_wait(&kv_full[j & 1], (j >> 1) & 1)) return false;
-          kv_ready = j;
+      // ------------------------------------------------------------ between items
+      // Everything of this item is over: every product has completed (the softmax groups waited for
+      // the last ones), every arrival that was asked for has been waited for. The barriers start
+      // again from phase 0 and the scheduler publishes the next item.
+      AT_FENCE_BEFORE();
+      __syncthreads();
+      if (failed) break;
+      if (threadIdx.x == 0) init_barriers();
+      if (warp == 8 && lane == 0) item_slot = next_item;
+      __syncthreads();
+      AT_FENCE_AFTER();
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n");
+    for (;;) {
+      const int cur = item_slot;
+      if (cur < 0) break;
+      AtItem it;
+      at_item(it, cur, gr, cu_q, q_start);
+      const int r = it.r, tok0 = it.tok0, q_len = it.q_len, m0 = it.m0, start = it.start, kv_len = it.kv_len;
+      const int head0 = it.head0, split = it.split, tile_begin = it.tile_begin;
+      {
+        // ---------------------------------------------------------- softmax, thread = row of its group
+        const int g = warp >> 2;
+        const int row = threadIdx.x & 127;                // row within the group = tensor-memory lane
+        const int tok = row / G, hd = row - tok * G;
+        const int tok_in_req = m0 + g * tpc + tok;
+        const int qpos = start + tok_in_req;
+        const int lo_mine = it.lo_g[g], lo_max_mine = it.lo_max[g], q_first_mine = it.q_first[g];
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
+        const int n_mine = it.n_tiles[g];
+        float m_used = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_mine && ok; ++j) {
+          if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
           AT_FENCE_AFTER();
-          return true;
-        };
-        auto issue_s = [&](int g, int j) -> bool {
-          if (!need_kv(j)) return false;
-          const unsigned char* kt = smem + AtSmem::kv + (j & 1) * AtSmem::stage;
-          const unsigned char* qt = smem + AtSmem::q + g * 2 * AT_BLOCK;
-#pragma unroll
-          for (int kk = 0; kk < AT_D / 16; ++kk) {
-            const uint64_t da = at_desc(qt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-            const uint64_t db = at_desc(kt + (kk >> 2) * AT_BLOCK, 16, 1024) + (uint64_t)(2 * (kk & 3));
-            at_mma(tmem + (uint32_t)(g * 128), da, db, idesc_s, kk != 0);
-          }
-          at_commit(&s_full[g]);
-          return true;
-        };
-        if (ok && it.n_tiles[0] > 0) ok = issue_s(0, 0);
-        if (ok && it.n_tiles[1] > 0) ok = issue_s(1, 0);
-        for (int j = 0; j < n_all && ok; ++j) {
-          const unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
-#pragma unroll 1
-          for (int g = 0; g < 2 && ok; ++g) {
-            if (j >= it.n_tiles[g]) continue;
-            if (!at_wait(&p_full[g], j & 1)) { ok = false; break; }
-            AT_FENCE_AFTER();
-#pragma unroll
-            for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
-              // A = P of this group in tensor memory: 16 keys = 8 columns of packed bf16 pairs;
-              // B = V [keys][d], MN-major
-              const uint64_t db = at_desc(vt + kk * 2048, AT_BLOCK, 1024);
-              at_mma_ts(tmem + (uint32_t)(256 + g * 128), tmem + (uint32_t)(g * 128 + kk * 8), db, idesc_o, (j | kk) != 0);
+          const int key0 = (tile_begin + j) * AT_KEYS;
+          const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+          if (interior) {
+            // every key of the tile is seen by every row of the group: the whole row of scores in
+            // registers, four loads in flight, one wait
+            float sv[4][32];
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  #pragma unroll
+            for (int c = 0; c < 4; ++c)
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
+            const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+              at_rescale(t_o, alpha);
+              l_sum *= alpha;
             }
-            if (j + 1 < it.n_tiles[g]) {
-              ok = issue_s(g, j + 1);  // overwrites this group's S/P columns: ordered after the product above
-            } else {
-              at_commit(&o_final[g]);
+            // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
+            const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+  #pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
+                const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
+                const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
+                part[(i >> 1) & 3] += e0 + e1;
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
+                pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
+              }
+              at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
             }
+          } else {
+            // a tile on the diagonal, at a window's edge or at the request's end: the keys of the tile
+            // that this row sees are those at offsets [seen_lo, seen_hi]
+            const int seen_hi = qpos - key0;
+            const int seen_lo = max(lo_mine, window > 0 ? qpos - window + 1 : 0) - key0;
+            part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum);
           }
-          // the producer waits for this only before tile j + 2: an arrival that nobody waits for
-          // must not be in flight when the barriers are set up again for the next item
-          if (ok && j + 2 < n_all) at_commit(&kv_empty[j & 1]);
+          l_sum += (part[0] + part[1]) + (part[2] + part[3]);
+          const int valid_keys = kv_len - key0;
+          if (valid_keys < AT_KEYS && row >= valid_keys) {
+            unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
+  #pragma unroll
+            for (int h = 0; h < 2; ++h)
+  #pragma unroll
+              for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(vt + h * AT_BLOCK + row * 128 + cc * 16) = make_uint4(0u, 0u, 0u, 0u);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+          AT_FENCE_BEFORE();
+          at_arrive(&p_full[g]);
         }
+        if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
         if (!ok) {
-          atomicExch(status, 33);
+          atomicExch(status, 34);
           failed = 1;
         }
-      }
-    } else {
-      // ---------------------------------------------------------- softmax, thread = row of its group
-      const int g = warp >> 2;
-      const int row = threadIdx.x & 127;                // row within the group = tensor-memory lane
-      const int tok = row / G, hd = row - tok * G;
-      const int tok_in_req = m0 + g * tpc + tok;
-      const int qpos = start + tok_in_req;
-      const int lo_mine = it.lo_g[g], lo_max_mine = it.lo_max[g], q_first_mine = it.q_first[g];
-      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-      const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
-      const int n_mine = it.n_tiles[g];
-      float m_used = -INFINITY, l_sum = 0.f;
-      bool ok = true;
-      for (int j = 0; j < n_mine && ok; ++j) {
-        if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
         AT_FENCE_AFTER();
-        const int key0 = (tile_begin + j) * AT_KEYS;
-        const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-        if (interior) {
-          // every key of the tile is seen by every row of the group: the whole row of scores in
-          // registers, four loads in flight, one wait
-          float sv[4][32];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[c][i]);
-          const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
-            at_rescale(t_o, alpha);
-            l_sum *= alpha;
-          }
-          // P = 2^(s * scale - max), packed two bf16 per column into the columns S came from
-          const float m_sub = (m_used == -INFINITY ? 0.f : m_used) * scale_log2;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float x0 = fmaf(sv[c][i], scale_log2, -m_sub), x1 = fmaf(sv[c][i + 1], scale_log2, -m_sub);
-              const float e0 = (i & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x0) : at_ex2(x0);
-              const float e1 = ((i + 1) & 7) < AT_EMULATED_OF_8 ? at_ex2_poly(x1) : at_ex2(x1);
-              part[(i >> 1) & 3] += e0 + e1;
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
-              pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
-            }
-            at_tmem_st16(t_s + (uint32_t)(c * 16), pk);
-          }
-        } else {
-          // a tile on the diagonal, at a window's edge or at the request's end: the keys of the tile
-          // that this row sees are those at offsets [seen_lo, seen_hi]
-          const int seen_hi = qpos - key0;
-          const int seen_lo = max(lo_mine, window > 0 ? qpos - window + 1 : 0) - key0;
-          part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum);
-        }
-        l_sum += (part[0] + part[1]) + (part[2] + part[3]);
-        const int valid_keys = kv_len - key0;
-        if (valid_keys < AT_KEYS && row >= valid_keys) {
-          unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(vt + h * AT_BLOCK + row * 128 + cc * 16) = make_uint4(0u, 0u, 0u, 0u);
-          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        }
-        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-        AT_FENCE_BEFORE();
-        at_arrive(&p_full[g]);
-      }
-      if (ok && n_mine > 0) ok = at_wait(&o_final[g], 0);
-      if (!ok) {
-        atomicExch(status, 34);
-        failed = 1;
-      }
-      AT_FENCE_AFTER();
-      const bool store = tok_in_req < q_len;
-      const size_t item = (size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd;  // (token, head) of this row
-      __nv_bfloat16* dst = out + item * AT_D;
-      if (it.shares[g] <= 1) {
-        if (ok && n_mine > 0) {
-          const float inv = 1.0f / l_sum;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            float ov[32];
-            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (store) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(ov + i, inv);
-            }
-          }
-        }
-      } else if (n_mine > 0) {
-        // One of several splits of this group's keys. Each takes a ticket when it is done. All but the
-        // last leave their partial result (unnormalised O, the maximum it is scaled by, the sum) and
-        // count themselves done; the last waits until the others are (they took their tickets before
-        // it and depend on nothing of it, so this is a wait for writes in flight), then adds the
-        // partial results up in the order of the splits, its own from tensor memory, and writes the
-        // rows. Partial results are laid out [group of rows][split][4 columns][row], so that the 128
-        // threads of a group (one row each) write and read whole 512-byte lines together.
-        const size_t unit = ((size_t)(it.rank * gr.rows + r) * gr.head_groups + head0 / G) * 2 + g;
-        float4* po = reinterpret_cast<float4*>(part_o) + (unit * gr.splits + split) * (32 * 128) + row;
-        float2* pml = part_ml + unit * gr.splits * 128 + row;
-        int* ticket = tickets + unit;
-        int* done = tickets + (size_t)gr.q_tiles * gr.rows * gr.head_groups * 2 + unit;
-        // all 128 threads of the group meet here, also after a wait that gave up: then nobody takes a ticket
-        const bool bad = at_group_any(1 + g, !ok);
-        if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
-        at_group_sync(1 + g);
-        const bool last = !bad && ticket_of[g] == it.shares[g] - 1;
-        if (!bad && !last) {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            float ov[32];
-            at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 8; ++i) po[(c * 8 + i) * 128] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
-          }
-          pml[split * 128] = make_float2(m_used, l_sum);
-          __threadfence();
-          at_group_sync(1 + g);
-          if (row == 0) atomicAdd(done, 1);
-        } else if (last) {
-          if (row == 0) {
-            // bounded like every wait: a split that took its ticket and never finishes is an error, not a hang
-            unsigned long long began = 0;
-            bool there = false;
-            for (uint32_t polls = 1; !there; ++polls) {
-              there = *reinterpret_cast<volatile int*>(done) >= it.shares[g] - 1;
-              if (!there && (polls & 63u) == 0) {
-                unsigned long long now;
-                asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-                if (began == 0) began = now;
-                else if (now - began > MS_WAIT_NS) break;
+        const bool store = tok_in_req < q_len;
+        const size_t item = (size_t)(tok0 + (store ? tok_in_req : 0)) * nq + head0 + hd;  // (token, head) of this row
+        __nv_bfloat16* dst = out + item * AT_D;
+        if (it.shares[g] <= 1) {
+          if (ok && n_mine > 0) {
+            const float inv = 1.0f / l_sum;
+  #pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float ov[32];
+              at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+              asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+              if (store) {
+  #pragma unroll
+                for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(ov + i, inv);
               }
             }
-            if (!there) atomicExch(status, 35);
-            *ticket = 0;  // both left as they were found, for the next launch
-            *done = 0;
-            __threadfence();
           }
+        } else if (n_mine > 0) {
+          // One of several splits of this group's keys. Each takes a ticket when it is done. All but the
+          // last leave their partial result (unnormalised O, the maximum it is scaled by, the sum) and
+          // count themselves done; the last waits until the others are (they took their tickets before
+          // it and depend on nothing of it, so this is a wait for writes in flight), then adds the
+          // partial results up in the order of the splits, its own from tensor memory, and writes the
+          // rows. Partial results are laid out [group of rows][split][4 columns][row], so that the 128
+          // threads of a group (one row each) write and read whole 512-byte lines together.
+          const size_t unit = ((size_t)(it.rank * gr.rows + r) * gr.head_groups + head0 / G) * 2 + g;
+          float4* po = reinterpret_cast<float4*>(part_o) + (unit * gr.splits + split) * (32 * 128) + row;
+          float2* pml = part_ml + unit * gr.splits * 128 + row;
+          int* ticket = tickets + unit;
+          int* done = tickets + (size_t)gr.q_tiles * gr.rows * gr.head_groups * 2 + unit;
+          // all 128 threads of the group meet here, also after a wait that gave up: then nobody takes a ticket
+          const bool bad = at_group_any(1 + g, !ok);
+          if (row == 0 && !bad) ticket_of[g] = atomicAdd(ticket, 1);
           at_group_sync(1 + g);
-          const float4* pall = reinterpret_cast<const float4*>(part_o) + unit * gr.splits * (32 * 128) + row;
-          float m_all = m_used;
-          for (int sp = 0; sp < it.shares[g]; ++sp)
-            if (sp != split) m_all = fmaxf(m_all, __ldcg(&pml[sp * 128]).x);
-          float l_all = 0.f;
-          for (int sp = 0; sp < it.shares[g]; ++sp) {
-            const float2 ml = sp == split ? make_float2(m_used, l_sum) : __ldcg(&pml[sp * 128]);
-            l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
-          }
-          const float inv = 1.0f / l_all;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            float own[32], acc[32];
-            at_tmem_ld32(t_o + (uint32_t)(c * 32), own);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-            for (int sp = 0; sp < it.shares[g]; ++sp) {
-              if (sp == split) {
-                const float w = l_sum == 0.f ? 0.f : at_ex2((m_used - m_all) * scale_log2);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, own[i], acc[i]);
-              } else {
-                const float2 ml = __ldcg(&pml[sp * 128]);
-                const float w = ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2);
-                const float4* src = pall + (size_t)sp * (32 * 128) + (c * 8) * 128;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float4 v = __ldcg(src + i * 128);
-                  acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
-                  acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
-                  acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
-                  acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+          const bool last = !bad && ticket_of[g] == it.shares[g] - 1;
+          if (!bad && !last) {
+  #pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float ov[32];
+              at_tmem_ld32(t_o + (uint32_t)(c * 32), ov);
+              asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+  #pragma unroll
+              for (int i = 0; i < 8; ++i) po[(c * 8 + i) * 128] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
+            }
+            pml[split * 128] = make_float2(m_used, l_sum);
+            __threadfence();
+            at_group_sync(1 + g);
+            if (row == 0) atomicAdd(done, 1);
+          } else if (last) {
+            if (row == 0) {
+              // bounded like every wait: a split that took its ticket and never finishes is an error, not a hang
+              unsigned long long began = 0;
+              bool there = false;
+              for (uint32_t polls = 1; !there; ++polls) {
+                there = *reinterpret_cast<volatile int*>(done) >= it.shares[g] - 1;
+                if (!there && (polls & 63u) == 0) {
+                  unsigned long long now;
+                  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+                  if (began == 0) began = now;
+                  else if (now - began > MS_WAIT_NS) break;
                 }
               }
+              if (!there) atomicExch(status, 35);
+              *ticket = 0;  // both left as they were found, for the next launch
+              *done = 0;
+              __threadfence();
             }
-            if (store) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
+            at_group_sync(1 + g);
+            const float4* pall = reinterpret_cast<const float4*>(part_o) + unit * gr.splits * (32 * 128) + row;
+            float m_all = m_used;
+            for (int sp = 0; sp < it.shares[g]; ++sp)
+              if (sp != split) m_all = fmaxf(m_all, __ldcg(&pml[sp * 128]).x);
+            float l_all = 0.f;
+            for (int sp = 0; sp < it.shares[g]; ++sp) {
+              const float2 ml = sp == split ? make_float2(m_used, l_sum) : __ldcg(&pml[sp * 128]);
+              l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
+            }
+            const float inv = 1.0f / l_all;
+  #pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float own[32], acc[32];
+              at_tmem_ld32(t_o + (uint32_t)(c * 32), own);
+              asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+              for (int sp = 0; sp < it.shares[g]; ++sp) {
+                if (sp == split) {
+                  const float w = l_sum == 0.f ? 0.f : at_ex2((m_used - m_all) * scale_log2);
+  #pragma unroll
+                  for (int i = 0; i < 32; ++i) acc[i] = fmaf(w, own[i], acc[i]);
+                } else {
+                  const float2 ml = __ldcg(&pml[sp * 128]);
+                  const float w = ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2);
+                  const float4* src = pall + (size_t)sp * (32 * 128) + (c * 8) * 128;
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 v = __ldcg(src + i * 128);
+                    acc[4 * i] = fmaf(w, v.x, acc[4 * i]);
+                    acc[4 * i + 1] = fmaf(w, v.y, acc[4 * i + 1]);
+                    acc[4 * i + 2] = fmaf(w, v.z, acc[4 * i + 2]);
+                    acc[4 * i + 3] = fmaf(w, v.w, acc[4 * i + 3]);
+                  }
+                }
+              }
+              if (store) {
+  #pragma unroll
+                for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c * 32 + i) = at_pack8(acc + i, inv);
+              }
             }
           }
+          at_group_sync(1 + g);  // ticket_of[g] is free for the next item
         }
-        at_group_sync(1 + g);  // ticket_of[g] is free for the next item
       }
+      // ------------------------------------------------------------ between items
+      // Everything of this item is over: every product has completed (the softmax groups waited for
+      // the last ones), every arrival that was asked for has been waited for. The barriers start
+      // again from phase 0 and the scheduler publishes the next item.
+      AT_FENCE_BEFORE();
+      __syncthreads();
+      if (failed) break;
+      if (threadIdx.x == 0) init_barriers();
+      __syncthreads();
+      AT_FENCE_AFTER();
     }
-    // ------------------------------------------------------------ between items
-    // Everything of this item is over: every product has completed (the softmax groups waited for
-    // the last ones), every arrival that was asked for has been waited for. The barriers start
-    // again from phase 0 and the scheduler publishes the next item.
-    AT_FENCE_BEFORE();
-    __syncthreads();
-    if (failed) break;
-    if (threadIdx.x == 0) init_barriers();
-    if (warp == 8 && lane == 0) item_slot = next_item;
-    __syncthreads();
-    AT_FENCE_AFTER();
   }
   AT_FENCE_BEFORE();
   __syncthreads();
