@@ -245,8 +245,8 @@ class StepGraphs:
     Else ``ops.attention`` keeps itself out of the capture and is called again for every step, between
     the graphs.
 
-    The second step with the same (tokens, rows, wanted, decoding rows) is captured while it runs, later ones replay.
-    Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
+    A step whose (tokens, rows, wanted, decoding rows) have been seen ``sightings`` times is captured while
+    it runs, later ones replay. Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
     dropped beyond ``max_shapes``. The logits of a replayed step live in the graphs' memory and are
     overwritten by the next replayed step.
     """
@@ -258,9 +258,10 @@ class StepGraphs:
         self.max_shapes, self.min_tokens = max_shapes, min_tokens
         self.enabled = bool(step_fn.model.shape_static)
         # Only steps that the launches weigh on are taken: a step of more than max_step_flops (about 6 ms of
-        # products at the tensor cores' rate) gains nothing measurable from a replay, and a capture costs
-        # tens of milliseconds (Qwen3-8B sizes, 32 requests with prompts of 128 to 4,096 tokens: the
-        # 2,048-token steps took 36 ms on average with their shapes captured, 31 ms without).
+        # products at the tensor cores' rate) gains nothing measurable from a replay, and its capture is
+        # a whole pass of the host over a large model (Qwen3-8B sizes, 32 requests with prompts of 128 to
+        # 4,096 tokens: the 2,048-token steps took 36 ms on average with their shapes captured at the
+        # second sighting, 31 ms without).
         model = step_fn.model
         per_weight = 2 if model.dtype == torch.bfloat16 else 4
         self.flops_per_token = 2.0 * model.weight_bytes() / per_weight if model.bound else 0.0
