@@ -22,6 +22,22 @@ __global__ void embed_gather_kernel(float* __restrict__ residual, const T* __res
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Elem<T>::load(src + i);
 }
 
+// bfloat16 rows that are a multiple of 8 wide: eight elements per thread (a 16-byte load, two 16-byte stores)
+__global__ void embed_gather_bf16x8_kernel(float* __restrict__ residual, const __nv_bfloat16* __restrict__ table,
+                                           const int* __restrict__ ids, int hidden8, int vocab, int tokens) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)tokens * hidden8) return;
+  const int t = (int)(idx / hidden8), c = (int)(idx - (long long)t * hidden8);
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  float v[8];
+  bf16x8_to_float(reinterpret_cast<const uint4*>(table + (size_t)id * hidden8 * 8)[c], v);
+  float4* dst = reinterpret_cast<float4*>(residual + (size_t)t * hidden8 * 8) + 2 * c;
+  dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+  dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
 // ---------------------------------------------------------------- (add +) RMSNorm (+ gather)
 // For output row i: r = rows ? rows[i] : i.
 //   h = residual[r] (+ delta[r] if delta)            float32
@@ -185,10 +201,15 @@ MS_EXPORT int ms_embed_gather(void* residual_f32, const void* table, const int* 
   if (tokens == 0) return 0;
   MS_CHECK_ARG(tokens > 0 && hidden > 0 && vocab > 0, "embed_gather: bad sizes T=%d H=%d V=%d", tokens, hidden, vocab);
   const int threads = hidden >= 256 ? 256 : 64;
-  if (dtype == MS_F32)
+  if (dtype == MS_F32) {
     MS_LAUNCH(embed_gather_kernel<float>, tokens, threads, 0, stream, (float*)residual_f32, (const float*)table, ids, hidden, vocab);
-  else
+  } else if (hidden % 8 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)residual_f32 % 16 == 0) {
+    const long long items = (long long)tokens * (hidden / 8);
+    MS_LAUNCH(embed_gather_bf16x8_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, (float*)residual_f32, (const __nv_bfloat16*)table, ids,
+              hidden / 8, vocab, tokens);
+  } else {
     MS_LAUNCH(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (float*)residual_f32, (const __nv_bfloat16*)table, ids, hidden, vocab);
+  }
   return 0;
 }
 

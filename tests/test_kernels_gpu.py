@@ -28,7 +28,7 @@ def _tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden, vocab, tokens", [(24, 77, 5), (1000, 333, 130)])
+@pytest.mark.parametrize("hidden, vocab, tokens", [(24, 77, 5), (27, 50, 9), (1000, 333, 130)])
 def test_embed_gather(dtype, hidden, vocab, tokens):
     table = torch.randn(vocab, hidden, device=DEV).to(dtype)
     ids = torch.randint(0, vocab, (tokens,), device=DEV, dtype=torch.int32)
