@@ -113,7 +113,7 @@ __device__ __forceinline__ void pdl_prologue() {
 // device status word and winds its pipeline down, so a protocol error or a lost arrival costs a
 // couple of seconds and an error on the host, not a GPU that no longer answers.
 constexpr unsigned long long MS_WAIT_NS = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned long long limit_ns = MS_WAIT_NS) {
   unsigned long long began = 0;
   for (uint32_t polls = 1;; ++polls) {
     uint32_t done;
@@ -127,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
       if (began == 0) began = now;
-      else if (now - began > MS_WAIT_NS) return false;
+      else if (now - began > limit_ns) return false;
     }
   }
 }

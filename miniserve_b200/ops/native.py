@@ -93,6 +93,7 @@ def kernels():
     lib.ms_kernels_set_pdl(int(pdl_enabled()))
     _declare(lib, "ms_device_sm_count", [_i, POINTER(c_int)])
     _declare(lib, "ms_device_arch", [_i, POINTER(c_int), POINTER(c_int)])
+    _declare(lib, "ms_wait_selftest", [_p, _ll, _i, _p])
     _declare(lib, "ms_fill_tokens", [_p, _p, _p, _p, _i, _p])
     _declare(lib, "ms_embed_gather", [_p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])

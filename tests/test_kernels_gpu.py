@@ -584,3 +584,27 @@ def test_top_p_distribution():
     freq = torch.bincount(got, minlength=vocab).float() / rows
     expect = torch.tensor([0.4, 0.25, 0.15, 0, 0, 0, 0, 0]) / 0.8
     assert (freq - expect).abs().max().item() < 0.015
+
+
+def test_a_wait_that_nothing_answers_gives_up_raises_the_status_word_and_leaves_the_device_usable():
+    """The tensor-core pipelines wait on mbarriers with a time limit and raise the device status word when
+    it runs out. Here a kernel waits on a barrier that nobody arrives on, with a limit of 50 ms: it ends
+    by itself, the word says so, and the next kernel runs."""
+    import time
+
+    from miniserve_b200.ops import native
+
+    k = native.kernels()
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    native.kernel_check(k.ms_wait_selftest(word.data_ptr(), 50_000_000, 77, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert word.item() == 77
+    assert 0.04 <= took < 1.0, f"the wait of 50 ms took {took:.3f} s"
+    out = torch.empty(5, 24, device=DEV)
+    table = torch.randn(7, 24, device=DEV)
+    ids = torch.arange(5, device=DEV, dtype=torch.int32)
+    ops.embed_gather(out, table, ids)
+    assert torch.equal(out, table[:5])
