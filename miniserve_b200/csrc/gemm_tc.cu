@@ -504,6 +504,149 @@ __device__ __forceinline__ void mbar_arrive_first_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(remote) : "memory");
 }
 
+// ---------------------------------------------------------------- decode products with a long k
+// out[M, N] = X[M, K] W[N, K]^T for a handful of tokens (M <= 64), with the operands swapped: 128 rows
+// of W are the instruction's M, the tokens its N (16, 32 or 64 columns of tensor memory). Such a
+// product is a stream of weights; here TMA keeps it coming, eight to eleven stages of 16 KB per CTA in
+// flight (some 180 KB a CTA against the 32 KB of registers a CTA of gemm_skinny.cu has in flight), and
+// one thread issues the products. K is cut into slices, the CTAs of a thread-block cluster (along x),
+// so that a narrow output still gives every SM a CTA; their partial sums meet in shared memory,
+// every CTA of the cluster adding up the tokens that fall to it, in the order of the slices.
+// The weights of the first stages are asked for before the wait on the kernels launched earlier
+// (they do not depend on them), the activations after it.
+template <int BT, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      __nv_bfloat16* __restrict__ out, int M, int N, int K, int slices, int iters_per_slice,
+                      int* __restrict__ status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  constexpr int W_BYTES = TC_BM * TC_BK * 2, X_BYTES = BT * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+  constexpr uint32_t TMEM_COLS = BT <= 32 ? 32 : 64;
+  float* part = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE_BYTES);  // [BT tokens][128 rows of W]: this slice's sums
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_ctarank();
+  const int n0 = ((int)blockIdx.x / slices) * TC_BM;
+  const int k_iters = (K + TC_BK - 1) / TC_BK;
+  const int it0 = min(k_iters, rank * iters_per_slice), n_it = min(k_iters, it0 + iters_per_slice) - it0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const int ahead = min(n_it, STAGES);
+      for (int i = 0; i < ahead; ++i) {  // weights only: nothing of this step is read yet
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES, &map_w, &full_bar[i], (it0 + i) * TC_BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < ahead; ++i) tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_BYTES, &map_x, &full_bar[i], (it0 + i) * TC_BK, 0);
+      for (int i = ahead; i < n_it; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+          atomicExch(status, 16);
+          break;
+        }
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)s * STAGE_BYTES, &map_w, &full_bar[s], (it0 + i) * TC_BK, n0);
+        tma_load_2d(smem + (size_t)s * STAGE_BYTES + W_BYTES, &map_x, &full_bar[s], (it0 + i) * TC_BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc(TC_BM, BT);
+      for (int i = 0; i < n_it; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
+          atomicExch(status, 17);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned char* w_tile = smem + (size_t)s * STAGE_BYTES;
+        const uint64_t da = make_smem_desc(w_tile), db = make_smem_desc(w_tile + W_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i | k) != 0);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(&accum_bar);
+    }
+  } else {
+    // warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31, i.e. rows of W
+    pdl_wait();
+    const int quad = warp & 3, l = quad * 32 + lane;
+    bool ok = true;
+    if (n_it > 0) {
+      ok = mbar_wait(&accum_bar, 0);
+      if (!ok) atomicExch(status, 18);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < BT; c += 32) {
+      uint32_t acc[32];
+      if (n_it > 0 && ok) {
+        tmem_ld32(lane_addr + (uint32_t)c, acc);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (c + j < BT) part[(c + j) * TC_BM + l] = __uint_as_float(acc[j]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // every slice's sums are in its shared memory
+  if (warp >= 2) {
+    const int l = (warp & 3) * 32 + lane;
+    if (n0 + l < N) {
+      // the tokens rank, rank + slices, ...: all slices' sums of a token are asked for together (eight
+      // loads from the cluster's shared memory in flight), then added in the order of the slices
+      uint32_t peer[8];
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+        asm("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(peer[sl]) : "r"(smem_u32(part + l)), "r"((uint32_t)(sl < slices ? sl : 0)));
+      for (int tok = rank; tok < M; tok += slices) {
+        float v[8];
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) {
+          v[sl] = 0.f;
+          if (sl < slices) asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v[sl]) : "r"(peer[sl] + (uint32_t)(tok * TC_BM * 4)));
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) sum += v[sl];
+        out[(size_t)tok * N + n0 + l] = __float2bfloat16_rn(sum);
+      }
+    }
+  }
+  cluster_sync_all();  // nobody's shared memory goes away while another CTA may still read it
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // AND of a flag over the 128 threads of a group of epilogue warps (hardware barrier `id`), and their plain barrier
 __device__ __forceinline__ bool epilogue_all(int id, bool flag) {
   uint32_t res;
@@ -1017,6 +1160,53 @@ static int launch_tc_pair(void* out, const void* A, const void* W, int M, int N_
   return 0;
 }
 
+template <int BT, int STAGES>
+static int launch_tc_decode(void* out, const void* X, const void* W, int M, int N, int K, int* status, cudaStream_t stream) {
+  CUtensorMap map_w, map_x;
+  if (int rc = make_map(&map_w, W, N, K, TC_BM)) return rc;
+  if (int rc = make_map(&map_x, X, M, K, BT)) return rc;
+  constexpr size_t smem = (size_t)STAGES * (TC_BM + BT) * TC_BK * 2 + (size_t)BT * TC_BM * 4 + 1024;
+  static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
+  auto kernel = gemm_tc_decode_kernel<BT, STAGES>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int dev = 0;
+    MS_CHECK_CUDA(cudaGetDevice(&dev));
+    MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    configured = true;
+  }
+  // Slices of k: as many as still let every cluster be resident at once (clusters are placed within a
+  // group of SMs, so fewer fit than SMs / size), each of at least four k-blocks, at most eight.
+  static int fit[9] = {0};  // how many clusters of each size the device holds at once
+  if (fit[1] == 0) {
+    for (int size = 1; size <= 8; ++size) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(size * sm_count));
+      cfg.blockDim = dim3(TC_THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = (unsigned)size;
+      attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = sm_count / size / 2;
+      fit[size] = n;
+    }
+  }
+  const int tiles = ceil_div(N, TC_BM), k_iters = ceil_div(K, TC_BK);
+  int slices = 1;
+  for (int size = 2; size <= 8 && size <= k_iters / 4; ++size)
+    if (fit[size] >= tiles) slices = size;
+  const int iters_per_slice = ceil_div(k_iters, slices);
+  MS_LAUNCH_CLUSTERED(kernel, (unsigned)(tiles * slices), TC_THREADS, smem, stream, slices, map_w, map_x, (__nv_bfloat16*)out, M, N, K, slices,
+                      iters_per_slice, status);
+  return 0;
+}
+
 }  // namespace ms
 
 using namespace ms;
@@ -1121,4 +1311,16 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
       return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }
+}
+
+// out [M, N] bfloat16 = X [M, K] W [N, K]^T for M <= 64 tokens (decode steps), see gemm_tc_decode_kernel.
+MS_EXPORT int ms_gemm_tc_decode_bf16(void* out, const void* X, const void* W, int M, int N, int K, int* status, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  MS_CHECK_ARG(M > 0 && M <= 64 && N > 0 && K > 0, "gemm_tc: a decode product takes 1..64 rows, not M=%d (N=%d K=%d)", M, N, K);
+  MS_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+  MS_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  MS_CHECK_ARG(status != nullptr, "gemm_tc: needs a status word");
+  if (M <= 16) return launch_tc_decode<16, 11>(out, X, W, M, N, K, status, stream);
+  if (M <= 32) return launch_tc_decode<32, 10>(out, X, W, M, N, K, status, stream);
+  return launch_tc_decode<64, 8>(out, X, W, M, N, K, status, stream);
 }

@@ -152,6 +152,21 @@ def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
+def linear_tc_decode(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """x [M, K] (M <= 64) times weight [N, K]^T on the tcgen05 tensor cores with the operands swapped (the
+    weight's rows are the instruction's M, the tokens its N), the weights streamed by TMA and k cut
+    into the CTAs of a thread-block cluster: the decode product for a long k."""
+    _check_dev(x, weight, out)
+    m, kdim = x.shape
+    n = weight.shape[0]
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert weight.shape[1] == kdim and out.shape == (m, n) and m <= 64
+    lib = native.gemm_tc()
+    native.kernel_check(lib.ms_gemm_tc_decode_bf16(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, _ptr(device_status(x.device)),
+                                                   _stream(stream)), lib=lib, errfn="ms_gemm_tc_last_error")
+    return out
+
+
 _TC_PREFERS: dict[tuple, bool] = {}
 
 
@@ -205,11 +220,33 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return k <= 4096 and m <= 8 and (n <= 4096 or n >= 8 * 16 * _sm_count(x.device))
 
 
+TC_DECODE_MAX_M = 32
+
+
+def _tc_decode_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None) -> bool:
+    """Whether a decode product goes to the tcgen05 kernel with swapped operands (``linear_tc_decode``):
+    up to 32 rows, a long k onto a narrow output (the down projections, and o of a small model), where
+    its TMA-fed weight stream was measured faster than both the register-fed kernel of
+    ``gemm_skinny.cu`` and the vendor library. Measured on B200 (us, this kernel against what ran before):
+    4096 x 12288 at 1 / 8 / 16 / 28 rows 18.6 / 19.4 / 20.0 / 20.9 against 30.7 / 29.2 / 22.4 / 22.6;
+    5120 x 25600: 41.0 / 42.1 / 42.8 / 44.5 against 47.2 / 45.9 / 46.3 / 49.9; 1024 x 3072 at 16 / 28 rows
+    4.5 / 5.1 against 6.6 / 7.0; 1024 x 2048: 4.1 / 4.6 against 4.5 / 5.7. Wide outputs (6144 x 4096,
+    24576 x 4096) and square ones stay where they were: there it ties or loses."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if TC_GEMM == "0" or not 0 < m <= TC_DECODE_MAX_M or k < 2048 or k < 2 * n or k % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return False
+    if out is not None and (out.dtype != torch.bfloat16 or out.data_ptr() % 16):
+        return False
+    return m > 8 or not _skinny_ok(x, weight)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """x [M, K] times weight[N, K]^T -> [M, N].
 
     float32: this package's FFMA kernel (true 32-bit, fixed summation order per element).
-    bfloat16 with at most 16 rows (decode steps): this package's weight-streaming kernel.
+    bfloat16 with at most 16 rows (decode steps): this package's weight-streaming kernel; with up to 32
+    rows and a long k onto a narrow output: the tcgen05 kernel with swapped operands (``_tc_decode_ok``).
     bfloat16 otherwise: this package's tcgen05 kernel where it is the faster choice
     (``tc_gemm_ok``), else the vendor library's matrix product with float32 accumulation.
     ``out`` may be float32 (logits) or bfloat16.
@@ -227,6 +264,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
         native.kernel_check(k.ms_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), m, n, kdim, kdim, kdim, n, _stream(stream)))
         return out
     assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    if _tc_decode_ok(x, weight, out):
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        return linear_tc_decode(x, weight, out, stream=stream)
     if _skinny_ok(x, weight):
         k = native.kernels()
         if out is None:

@@ -121,6 +121,7 @@ def gemm_tc():
     _declare(lib, "ms_gemm_tc_last_error", [], c_char_p)
     _declare(lib, "ms_gemm_tc_set_pdl", [_i], None)
     _declare(lib, "ms_gemm_tc_bf16", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
+    _declare(lib, "ms_gemm_tc_decode_bf16", [_p, _p, _p, _i, _i, _i, _p, _p])
     _declare(lib, "ms_gemm_tc_set_config", [_i], None)
     _declare(lib, "ms_gemm_tc_prefers", [_i, _i, _i, _i])
     _declare(lib, "ms_gemm_tc_qkv_bf16", [_p, _p, _p, _i, _i, _i, _i] + [_p] * 9 + [_i, _f, _p, _p])

@@ -165,6 +165,29 @@ def test_skinny_gemm_bf16(m, n, k):
     assert torch.equal(one_tile, out32)
 
 
+@pytest.mark.parametrize("m", [1, 7, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n, k", [(1024, 3072), (4096, 12288), (1000, 2056), (130, 264), (77, 25600), (6144, 4096)])
+def test_tcgen05_decode_product_with_swapped_operands(m, n, k):
+    """The decode product on the tensor cores (the weight's rows as the instruction's M, k cut into the CTAs
+    of a cluster) against float32 matmul, at widths and k that are no multiples of its tiles; a row's
+    result does not depend on the rows beside it."""
+    torch.manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * k ** -0.5).bfloat16()
+    out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.linear_tc_decode(x, w, out)
+    torch.cuda.synchronize()
+    assert ops.device_status(DEV).item() == 0
+    expect = x.float() @ w.float().T
+    assert torch.allclose(out.float(), expect, atol=2e-2, rtol=2e-2)
+    alone = torch.empty(1, n, device=DEV, dtype=torch.bfloat16)
+    ops.linear_tc_decode(x[m - 1:m].contiguous(), w, alone)
+    assert torch.equal(alone[0], out[m - 1])
+    # and linear() sends the long and narrow ones of up to 32 rows here
+    if m <= 32 and k >= 2 * n and k >= 2048 and (m > 8 or k > 3072):
+        assert ops._tc_decode_ok(x, w, None) and torch.equal(ops.linear(x, w), out)
+
+
 @pytest.mark.parametrize("m, inter, k", [(1, 3072, 1024), (8, 3072, 1024), (13, 224, 96), (16, 136, 64), (5, 2048, 4096)])
 def test_skinny_gate_up_with_the_activation_in_its_epilogue(m, inter, k):
     """One kernel for silu(x Wg^T) * (x Wu^T) at decode sizes: the same numbers as the product into a
