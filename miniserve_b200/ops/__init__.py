@@ -230,24 +230,24 @@ def _tc_decode_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | Non
     a weight of a few MB is on the chip when the activations arrive. Measured on B200:
 
     * a long k onto a narrow output (k at least 2,048 and twice the output's width: the down
-      projections, o of a small model), 2 to 32 rows. Alone, in us against what ran before: 4096 x 12288
+      projections, o of a small model), up to 32 rows. Alone, in us against what ran before: 4096 x 12288
       at 1 / 8 / 16 / 28 rows 18.6 / 19.4 / 20.0 / 20.9 against 30.7 / 29.2 / 22.4 / 22.6; 5120 x 25600:
       41.0 / 42.1 / 42.8 / 44.5 against 47.2 / 45.9 / 46.3 / 49.9; 1024 x 3072 at 16 / 28 rows 4.5 / 5.1
       against 6.6 / 7.0. Inside a decode step of Qwen3-0.6B sizes: 1.282 -> 1.199 ms at batch 8,
-      1.198 -> 1.096 at batch 4, 1.010 -> 0.994 at batch 2 (and 0.965 -> 1.009 at batch 1, which
-      therefore stays where it was);
+      1.198 -> 1.096 at batch 4, 1.010 -> 0.994 at batch 2 (and 0.965 -> 1.009 at batch 1: a single
+      row stays on the register-fed kernel where that takes the shape, k up to 3,072);
     * any other product whose weight is at most 16 MB (it is then in flight whole), 9 to 32 rows:
       batch 16 1.640 -> 1.604 ms on top of the first rule (with 4 rows the same change loses: 1.096 -> 1.254).
 
     Large wide outputs (6144 x 4096, 24576 x 4096) tie or lose against the library and stay there."""
     m, k = x.shape
     n = weight.shape[0]
-    if TC_GEMM == "0" or not 2 <= m <= TC_DECODE_MAX_M or k % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
+    if TC_GEMM == "0" or not 1 <= m <= TC_DECODE_MAX_M or k % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
         return False
     if out is not None and (out.dtype != torch.bfloat16 or out.data_ptr() % 16):
         return False
     if k >= 2048 and k >= 2 * n:
-        return True
+        return m >= 2 or not _skinny_ok(x, weight)  # a single row stays on the register-fed kernel where that takes the shape
     return m >= 9 and n * k * 2 <= (16 << 20)
 
 
