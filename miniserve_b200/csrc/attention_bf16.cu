@@ -475,14 +475,29 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     if (cluster.block_rank() == 0) {
       for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
         const int row = idx / D, c = idx - row * D;
+        // every split's three values are asked for together (one trip to the other CTAs' shared
+        // memory instead of two), then combined in the order of the splits
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          ms[sp] = -INFINITY;
+          ls[sp] = os[sp] = 0.f;
+          if (sp < num_splits) {
+            const float* src = cluster.map_shared_rank(cta_out, sp) + row * (D + 2);
+            ms[sp] = src[D];
+            ls[sp] = src[D + 1];
+            os[sp] = src[c];
+          }
+        }
         float m = -INFINITY;
-        for (int sp = 0; sp < num_splits; ++sp) m = fmaxf(m, cluster.map_shared_rank(cta_out, sp)[row * (D + 2) + D]);
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) m = fmaxf(m, ms[sp]);
         float acc = 0.f, l = 0.f;
-        for (int sp = 0; sp < num_splits; ++sp) {
-          const float* src = cluster.map_shared_rank(cta_out, sp) + row * (D + 2);
-          const float wgt = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
-          acc += wgt * src[c];
-          l += wgt * src[D + 1];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          const float wgt = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - m);
+          acc += wgt * os[sp];
+          l += wgt * ls[sp];
         }
         out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
       }
