@@ -533,6 +533,10 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int k_iters = (K + TC_BK - 1) / TC_BK;
   const int it0 = min(k_iters, rank * iters_per_slice), n_it = min(k_iters, it0 + iters_per_slice) - it0;
 
+  // Thread 0 is the producer. It sets the barriers up and asks for the weights of the first stages at
+  // once, before tensor memory is allocated and before the wait on the kernels launched earlier: the
+  // weights depend on neither.
+  const int ahead = min(n_it, STAGES);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -540,6 +544,10 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
     mbar_init(&accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    for (int i = 0; i < ahead; ++i) {
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      tma_load_2d(smem + (size_t)i * STAGE_BYTES, &map_w, &full_bar[i], (it0 + i) * TC_BK, n0);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
@@ -552,12 +560,7 @@ gemm_tc_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   pdl_launch_dependents();
 
   if (warp == 0) {
-    if (elect_one()) {
-      const int ahead = min(n_it, STAGES);
-      for (int i = 0; i < ahead; ++i) {  // weights only: nothing of this step is read yet
-        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-        tma_load_2d(smem + (size_t)i * STAGE_BYTES, &map_w, &full_bar[i], (it0 + i) * TC_BK, n0);
-      }
+    if (threadIdx.x == 0) {
       pdl_wait();
       for (int i = 0; i < ahead; ++i) tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_BYTES, &map_x, &full_bar[i], (it0 + i) * TC_BK, 0);
       for (int i = ahead; i < n_it; ++i) {
