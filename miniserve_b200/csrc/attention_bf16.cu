@@ -250,8 +250,9 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
 // One CTA per (split, request, kv head x 16 query heads of its group). The four warps take
 // 16-key slices of the CTA's key range in turn; each warp runs its own cp.async pipeline into
 // its own shared memory, so no block-wide barrier sits in the loop. At the end the warps' partial
-// (max, sum, output) are merged in shared memory and written as one partial per split, or as
-// the final output when there is a single split.
+// (max, sum, output) lie in shared memory. Splits that run as one thread-block cluster add up all
+// warps' partials of all splits from there, each CTA its share of the output; otherwise the CTA
+// merges its warps and writes one partial per split, or the final output when there is a single split.
 constexpr int DC_WARPS = 4, DC_THREADS = DC_WARPS * 32, DC_STAGES = 3, DC_SLICE = 16;
 
 struct DecodeSmem {
@@ -259,7 +260,7 @@ struct DecodeSmem {
   static constexpr int stage_elems = 2 * DC_SLICE * DPAD;  // K slice then V slice
   static constexpr int pipe_elems = DC_WARPS * DC_STAGES * stage_elems;
   static constexpr size_t bytes_pipe = (size_t)(q_elems + pipe_elems) * 2;
-  static constexpr size_t bytes_merge = (size_t)(DC_WARPS + 1) * 16 * (D + 2) * 4 + (size_t)q_elems * 2;
+  static constexpr size_t bytes_merge = (size_t)DC_WARPS * 16 * (D + 2) * 4 + (size_t)q_elems * 2;
   static constexpr size_t bytes = bytes_pipe > bytes_merge ? bytes_pipe : bytes_merge;
 };
 
@@ -420,9 +421,9 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   __syncthreads();  // the pipelines are drained: shared memory becomes the merge area
 
   float* merge = reinterpret_cast<float*>(smem_raw + (size_t)DecodeSmem::q_elems * 2);  // [warps][16][D + 2]
-  float* cta_out = merge + (size_t)DC_WARPS * 16 * (D + 2);                              // [16][D + 2]
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
+    if (g + 8 * j >= heads_here) continue;  // rows of the tile that stand for no query head
     float* row = merge + ((size_t)warp * 16 + g + 8 * j) * (D + 2);
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) {
@@ -433,6 +434,54 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       row[D] = m_run[j];
       row[D + 1] = l_run[j];
     }
+  }
+  if (num_splits > 1 && cluster_merge) {
+    // The splits of a (request, head group) are one thread-block cluster. Every warp's partial result
+    // stays in its CTA's shared memory; after one cluster barrier each CTA adds up its share of the
+    // output's elements over all warps of all splits through distributed shared memory:
+    // out = sum_p w_p O_p / sum_p w_p l_p with w_p = 2^(m_p - max m). All of a batch's values are asked
+    // for together (one trip to the other CTAs' shared memory), four splits to a batch.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int total = heads_here * D, share = (total + num_splits - 1) / num_splits;
+    const int first = (int)cluster.block_rank() * share, last = min(total, first + share);
+    for (int idx = first + tid; idx < last; idx += DC_THREADS) {
+      const int row = idx / D, c = idx - row * D;
+      float acc = 0.f, l = 0.f, m = -INFINITY;
+      for (int s0 = 0; s0 < num_splits; s0 += 4) {
+        float ms[4 * DC_WARPS], ls[4 * DC_WARPS], os[4 * DC_WARPS];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bool in = s0 + i < num_splits;
+          const float* base = cluster.map_shared_rank(merge, in ? s0 + i : 0) + (size_t)row * (D + 2);
+#pragma unroll
+          for (int w = 0; w < DC_WARPS; ++w) {
+            const float* src = base + (size_t)w * 16 * (D + 2);
+            ms[i * DC_WARPS + w] = in ? src[D] : -INFINITY;
+            ls[i * DC_WARPS + w] = in ? src[D + 1] : 0.f;
+            os[i * DC_WARPS + w] = in ? src[c] : 0.f;
+          }
+        }
+        float m_new = m;
+#pragma unroll
+        for (int i = 0; i < 4 * DC_WARPS; ++i) m_new = fmaxf(m_new, ms[i]);
+        if (m_new == -INFINITY) continue;
+        const float keep = m == -INFINITY ? 0.f : exp2f(m - m_new);
+        acc *= keep;
+        l *= keep;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 4 * DC_WARPS; ++i) {
+          const float wgt = ms[i] == -INFINITY ? 0.f : exp2f(ms[i] - m);
+          acc += wgt * os[i];
+          l += wgt * ls[i];
+        }
+      }
+      out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
+    }
+    cluster.sync();  // shared memory lives until every CTA of the cluster has read it
+    return;
   }
   __syncthreads();
   for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
@@ -451,14 +500,6 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     const int head = head0 + row;
     if (num_splits == 1) {
       out[((size_t)r * nq + head) * D + c] = __float2bfloat16_rn(acc / l);
-    } else if (cluster_merge) {
-      // the splits of a (request, head group) are one thread-block cluster: the partial result
-      // stays in this CTA's shared memory, where the cluster's first CTA reads it
-      cta_out[row * (D + 2) + c] = acc;
-      if (c == 0) {
-        cta_out[row * (D + 2) + D] = m;
-        cta_out[row * (D + 2) + D + 1] = l;
-      }
     } else {
       const size_t p = ((size_t)r * nq + head) * num_splits + split;
       part_o[p * D + c] = acc;
@@ -467,43 +508,6 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
         part_ml[2 * p + 1] = l;
       }
     }
-  }
-  if (num_splits > 1 && cluster_merge) {
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();  // every split's partial result is in its shared memory
-    if (cluster.block_rank() == 0) {
-      for (int idx = tid; idx < heads_here * D; idx += DC_THREADS) {
-        const int row = idx / D, c = idx - row * D;
-        // every split's three values are asked for together (one trip to the other CTAs' shared
-        // memory instead of two), then combined in the order of the splits
-        float ms[8], ls[8], os[8];
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) {
-          ms[sp] = -INFINITY;
-          ls[sp] = os[sp] = 0.f;
-          if (sp < num_splits) {
-            const float* src = cluster.map_shared_rank(cta_out, sp) + row * (D + 2);
-            ms[sp] = src[D];
-            ls[sp] = src[D + 1];
-            os[sp] = src[c];
-          }
-        }
-        float m = -INFINITY;
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) m = fmaxf(m, ms[sp]);
-        float acc = 0.f, l = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) {
-          const float wgt = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - m);
-          acc += wgt * os[sp];
-          l += wgt * ls[sp];
-        }
-        out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
-      }
-    }
-    cluster.sync();  // the others' shared memory lives until the first CTA has read it
-    return;
   }
   if (num_splits == 1 || counters == nullptr) return;
   // The split that finishes last merges them all (a ticket per (request, head chunk); no waiting):
