@@ -699,6 +699,36 @@ MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k
   return 0;
 }
 
+// How many clusters of `num_splits` CTAs of the decode kernel this device holds at a time (a cluster
+// lies within one GPC, so this is not SM count x 2 / num_splits). A launch with more (request, head
+// group) items than that runs in two rounds.
+MS_EXPORT int MS_ATTN_FN(decode_clusters_resident)(int num_splits, int* out) {
+  MS_CHECK_ARG(num_splits >= 1 && num_splits <= 8, "attention: a cluster takes up to 8 splits, not %d", num_splits);
+  static int cached[64][9] = {};
+  int dev = 0;
+  MS_CHECK_CUDA(cudaGetDevice(&dev));
+  MS_CHECK_ARG(dev >= 0 && dev < 64, "attention: device index %d is not supported", dev);
+  if (cached[dev][num_splits] == 0) {
+    if (int rc = configure_decode()) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_splits, 1024, 1);
+    cfg.blockDim = dim3(DC_THREADS);
+    cfg.dynamicSmemBytes = DecodeSmem::bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = num_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    MS_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel, &cfg));
+    cached[dev][num_splits] = n > 0 ? n : -1;
+  }
+  *out = cached[dev][num_splits] > 0 ? cached[dev][num_splits] : 0;
+  return 0;
+}
+
 // ------------------------------------------------------------------ decode without allocation
 // See attention_noalloc.h: the same computation as the decode entry point above, with the
 // split-K scratch in a file-scope device array instead of caller-provided memory.

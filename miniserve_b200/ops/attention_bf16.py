@@ -44,6 +44,7 @@ def _lib(head_dim: int):
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
         ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
         ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("decode_clusters_resident", [_i, ctypes.POINTER(c_int)], c_int),
     ):
         fn = getattr(lib, pre + name)
         fn.argtypes, fn.restype = args, res
@@ -61,7 +62,20 @@ def _check(fns, rc: int, launches: int = 1) -> None:
         raise native.NativeError(fns["last_error"]().decode())
 
 
-def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count: int) -> int:
+@lru_cache(maxsize=None)
+def clusters_resident(head_dim: int, splits: int, device_index: int = 0) -> int:
+    """How many thread-block clusters of ``splits`` decode CTAs the device holds at a time (a cluster
+    lies within one GPC: on a B200 with head size 128, 71 clusters of 4 and 33 of 8, not 74 and 37)."""
+    fns = _lib(head_dim)
+    out = c_int(0)
+    with torch.cuda.device(device_index):
+        rc = fns["decode_clusters_resident"](splits, ctypes.byref(out))
+    if rc != 0:
+        raise native.NativeError(fns["last_error"]().decode())
+    return out.value
+
+
+def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count: int, resident=None) -> int:
     """How many ways the keys of each (request, kv head) are split across CTAs: as many as give
     one wave of two CTAs per SM, but at least 128 keys per split and at most 16 splits (measured on
     B200 at contexts of 512 to 8,192 and batches of 1 to 32: more splits only add partial results
@@ -69,10 +83,19 @@ def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count:
     decode step of 8 requests at 2,048 tokens takes 1.28 ms with 4 splits, 1.34 with 3, 1.60 with 8).
     ``max_kv_len`` None (inside a CUDA graph, where the launch cannot follow the context length):
     assume a few thousand keys, and stay within the 8 splits that one thread-block cluster merges
-    (a single request: 0.98 ms per step with 8 splits, 0.99 with 16)."""
-    want = (2 * sm_count) // max(rows * head_chunks, 1)
+    (a single request: 0.98 ms per step with 8 splits, 0.99 with 16).
+    ``resident(splits)``: how many clusters of that size the device holds at a time; splits that run
+    as a cluster (2 to 8) are reduced until every (request, head group) has its cluster in the first
+    wave (6 requests x 8 head groups in clusters of 6: 48 clusters where 45 fit, and the step took 1.33 ms
+    against 1.17 for 8 requests in clusters of 4)."""
+    items = max(rows * head_chunks, 1)
+    want = (2 * sm_count) // items
     by_len = 8 if max_kv_len is None else max(1, -(-max_kv_len // 128))
-    return max(1, min(want, by_len, 16))
+    splits = max(1, min(want, by_len, 16))
+    if resident is not None:
+        while 2 <= splits <= 8 and resident(splits) < items:
+            splits -= 1
+    return splits
 
 
 def _scratch(ctx, rows: int, nq: int, splits: int, d: int, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -109,7 +132,8 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     fns = _lib(d)
     indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
     chunks = nkv * -(-(nq // nkv) // 16)
-    splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count)
+    fit = (lambda n: clusters_resident(d, n, q.device.index or 0)) if CLUSTER_MERGE else None
+    splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count, fit)
     if CLUSTER_MERGE and 2 <= splits <= 8:
         # the splits as one thread-block cluster: merged through distributed shared memory
         _check(fns, fns["decode_cluster"](

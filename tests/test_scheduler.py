@@ -377,3 +377,22 @@ def test_overlap_with_every_running_request_preempted_is_no_stall():
     assert [len(o) for o in outs] == [80] * 5 and eng.scheduler.num_preemptions > 0
     cm.check_invariants()
     assert cm.is_idle()
+
+
+def test_graph_batch_sizes_and_key_splits_of_a_decode_step():
+    """The padded batch sizes that decode graphs are captured for, and how many CTAs share a request's keys
+    (host decisions: ``engine/graphs.py`` graph_buckets, ``ops/attention_bf16.py`` choose_splits)."""
+    from miniserve_b200.engine.graphs import graph_buckets
+    from miniserve_b200.ops.attention_bf16 import choose_splits
+
+    assert graph_buckets(1) == [1] and graph_buckets(8) == [1, 2, 4, 8] and graph_buckets(9) == [1, 2, 4, 8, 9]
+    assert graph_buckets(24) == [1, 2, 4, 8, 16, 24] and graph_buckets(40) == [1, 2, 4, 8, 16, 24, 32, 40]
+    assert graph_buckets(64) == [1, 2, 4, 8, 16, 24, 32, 48, 64]
+    # clusters of n CTAs that a B200 holds at a time with head size 128 (a cluster stays inside one GPC)
+    resident = {2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33}.__getitem__
+    assert choose_splits(8, 8, None, 148, resident) == 4
+    assert choose_splits(6, 8, None, 148) == 6 and choose_splits(6, 8, None, 148, resident) == 5  # 48 clusters of 6 where 45 fit
+    assert choose_splits(12, 8, None, 148, resident) == 2  # 96 clusters of 3 where 93 fit
+    assert choose_splits(1, 8, None, 148, resident) == 8 and choose_splits(4, 8, None, 148, resident) == 8
+    assert choose_splits(1, 8, 200, 148, resident) == 2  # never fewer than 128 keys to a split
+    assert choose_splits(64, 8, None, 148, resident) == 1 and choose_splits(1, 8, 8192, 148) == 16
