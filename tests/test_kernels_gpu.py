@@ -598,6 +598,41 @@ def test_top_p_matches_the_plain_sampler():
     assert got[5] < max(1, int(0.55 * vocab) + 2)
 
 
+@pytest.mark.parametrize("vocab", [20011, 151936, 420000])
+def test_top_p_over_a_large_vocabulary_matches_the_plain_sampler(vocab):
+    """From 16,384 tokens on a row's nucleus is found by a thread-block cluster of 8 CTAs that keep the row's
+    probabilities in shared memory; beyond what that holds (420,000 here) by one CTA that walks the row."""
+    torch.manual_seed(vocab)
+    rows = 9
+    logits = torch.randn(rows, vocab, device=DEV) * 4
+    logits[1, :] = 0.5                      # all ties: the first tokens in index order are kept
+    logits[2, 1000:1040] = 9.0              # a tied group at the cut, across a warp's and (at 151,936) no CTA's edge
+    logits[2, vocab - 3:] = 9.0             # ... and in the last CTA's stretch
+    logits[3, 7] = 30.0                     # one token holds nearly all the mass
+    temps = [0.9, 1.0, 1.0, 1.0, 0.0, 0.8, 1.3, 0.6, 1.0]
+    tops = [0.9, 0.3, 0.35, 0.5, 0.9, 1.0, 0.99, 0.05, 0.7]
+    seeds = list(range(50, 50 + rows))
+    counters = list(range(3, 3 + rows))
+    got = _sample(logits, temps, tops, seeds, counters)
+    expect = [plain.sample_token(logits[r].cpu(), temps[r], seeds[r], counters[r], tops[r]) for r in range(rows)]
+    same = sum(g == e for g, e in zip(got, expect))
+    assert same >= rows - 1, (got, expect)  # a cut that falls within rounding of top_p may go either way
+    for r in range(rows):
+        if temps[r] == 0 or tops[r] >= 1:
+            assert got[r] == expect[r]
+            continue
+        p = torch.softmax(logits[r].cpu().float() / temps[r], -1)
+        sp, order = torch.sort(p, descending=True, stable=True)
+        keep = (torch.cumsum(sp, 0) - sp) < tops[r] + 1e-5
+        assert got[r] in set(order[keep].tolist()), r
+    assert got[1] < int(0.3 * vocab) + 2 and got[3] == 7
+    # the same rows alone and in another order give the same tokens
+    perm = [4, 8, 0, 2]
+    again = _sample(logits[perm].contiguous(), [temps[i] for i in perm], [tops[i] for i in perm], [seeds[i] for i in perm],
+                    [counters[i] for i in perm])
+    assert again == [got[i] for i in perm]
+
+
 def test_top_p_distribution():
     vocab = 8
     probs = torch.tensor([0.4, 0.25, 0.15, 0.1, 0.05, 0.03, 0.01, 0.01])
