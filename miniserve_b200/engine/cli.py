@@ -38,7 +38,10 @@ def add_engine_args(parser: argparse.ArgumentParser) -> None:
     # options of miniserve/engine/cli.py that choose between implementations of which this engine has one:
     # taken, with their single value, so that a command line written for that engine still parses
     g.add_argument("--attention", choices=["paged"], default="paged", help="the cache is always paged here")
-    g.add_argument("--schedule-policy", choices=["fcfs"], default="fcfs", help="requests are always admitted in arrival order here")
+    g.add_argument("--schedule-policy", choices=["fcfs", "sjf"], default="fcfs",
+                   help="fcfs: waiting requests are tried in arrival order and the newest admitted one is preempted; sjf: least "
+                        "remaining work first, most remaining work preempted (the reference's third policy, cache, orders by a "
+                        "prefix cache, which is not here)")
     g.add_argument("--block-backend", choices=["cpp"], default="cpp", help="page bookkeeping is always the C++ one here")
     g.add_argument("--disable-radix", action="store_true", help="accepted and ignored: there is no prefix cache here")
     g.add_argument("--fused-ops", action="store_true", help="accepted and ignored: the fused kernels are the only ones here")
@@ -57,6 +60,7 @@ def engine_kwargs(args: argparse.Namespace) -> dict:
         cuda_graph_max_bs=args.cuda_graph_max_bs,
         overlap=not args.disable_overlap,
         poison_on_free=args.poison_on_free,
+        schedule_policy=args.schedule_policy,
     )
 
 

@@ -77,7 +77,7 @@ class Engine:
                  max_running: int = 64, max_prefill_tokens: int = 8192, chunked_prefill_size: int | None = None,
                  seed: int = 0, cuda_graph: bool = True, cuda_graph_max_bs: int | None = None,
                  kv_mem_fraction: float = 0.9, overlap: bool = True, cache: CacheManager | None = None, step_fn=None,
-                 sampler=None, poison_on_free: bool = False, step_graphs: bool = True):
+                 sampler=None, poison_on_free: bool = False, step_graphs: bool = True, schedule_policy: str = "fcfs"):
         """``kv_pool_tokens``: exact size of the cache pool in tokens, rounded down to whole pages
         (default: ``kv_mem_fraction`` of the memory the device has free after the weights, less a
         reserve for activations). ``chunked_prefill_size``: tokens per step, decode tokens included,
@@ -87,6 +87,7 @@ class Engine:
         decode-only steps of up to ``cuda_graph_max_bs`` requests (default ``max_running``).
         ``step_graphs``: with ``cuda_graph``, also capture prompt and mixed steps whose shape comes again.
         ``overlap``: launch each step before reading back the previous one.
+        ``schedule_policy``: "fcfs" or "sjf" (``Scheduler``).
         Names and meanings follow miniserve/engine/engine.py:42-77. ``cache``, ``step_fn`` and
         ``sampler`` replace the ones the engine would build (a test can run the whole loop on the
         host against a stand-in step function this way). ``poison_on_free``: a debugging aid, see
@@ -102,9 +103,10 @@ class Engine:
         self.cache = cache
         self.settings = dict(kv_pool_tokens=kv_pool_tokens, page_size=page_size, max_running=max_running,
                              max_prefill_tokens=max_prefill_tokens, chunked_prefill_size=chunked_prefill_size, seed=seed,
-                             cuda_graph=cuda_graph, cuda_graph_max_bs=cuda_graph_max_bs or max_running, overlap=overlap)
+                             cuda_graph=cuda_graph, cuda_graph_max_bs=cuda_graph_max_bs or max_running, overlap=overlap,
+                             schedule_policy=schedule_policy)
         self.step_fn = step_fn if step_fn is not None else StepFunction(model, self.cache)
-        self.scheduler = Scheduler(self.cache, max_running, max_prefill_tokens, chunked_prefill_size)
+        self.scheduler = Scheduler(self.cache, max_running, max_prefill_tokens, chunked_prefill_size, schedule_policy)
         self.sampler = sampler if sampler is not None else Sampler(model.device, model.spec.vocab_size, max_running)
         self.requests: dict[int, Request] = {}
         self._rids = itertools.count()

@@ -18,6 +18,14 @@ Decisions, following miniserve/engine/scheduler.py:
   holds, keeps its output, and goes to the front of the waiting queue to be run again from its
   first token (:281-323). So the oldest request always progresses and nothing deadlocks.
 
+* Two policies decide the order in which waiting requests are tried and who is preempted
+  (miniserve/engine/policy.py:44-69): ``fcfs``, arrival order and the newest admitted request as
+  above; ``sjf``, least remaining work first (the prompt tokens still to compute plus the tokens the
+  request may still generate) and the request with the most remaining work preempted. Under both,
+  admission stops at the first request in its order that does not fit, and the oldest running
+  request is never preempted. The reference's third policy orders by what a prefix cache holds;
+  there is none here.
+
 Budgets are per cache group (a tuple of page counts) and include the slot for per-request state.
 """
 
@@ -28,6 +36,15 @@ from dataclasses import dataclass, field
 
 from ..cache.manager import CacheManager
 from .request import Request, RequestState
+
+
+def remaining_work(r: Request) -> int:
+    """Prompt (and, after a preemption, output) tokens still to compute, plus the tokens the request may
+    still generate: what the shortest-job-first policy orders by (miniserve/engine/policy.py:53-56)."""
+    return r.seq_len - r.num_cached + r.params.max_new_tokens - len(r.output_ids)
+
+
+POLICIES = ("fcfs", "sjf")
 
 
 @dataclass
@@ -65,7 +82,10 @@ def _add(a: tuple[int, ...], b: tuple[int, ...]) -> tuple[int, ...]:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_running: int = 64, max_prefill_tokens: int = 8192,
-                 chunked_prefill_size: int = 2048):
+                 chunked_prefill_size: int = 2048, policy: str = "fcfs"):
+        if policy not in POLICIES:
+            raise ValueError(f"unknown schedule policy {policy!r}; choose from {list(POLICIES)}")
+        self.policy = policy
         if max_running < 1 or max_prefill_tokens < 1:
             raise ValueError("max_running and max_prefill_tokens must be positive")
         if chunked_prefill_size < 0:
@@ -127,6 +147,19 @@ class Scheduler:
     def _admission_need(self, req: Request) -> tuple[int, ...]:
         return self.cache.pages_for(req.seq_len + 1)
 
+    # ------------------------------------------------------------------ policy
+    def _in_order(self) -> list[Request]:
+        """The waiting requests in the order admission tries them."""
+        if self.policy == "sjf":
+            return sorted(self.waiting, key=remaining_work)  # stable: equals keep their arrival order
+        return list(self.waiting)
+
+    def _victim(self, candidates: list[Request]) -> Request:
+        """Whom to preempt among ``candidates`` (running requests in admission order, the oldest left out)."""
+        if self.policy == "sjf":
+            return max(reversed(candidates), key=remaining_work)  # among equals the newest admitted
+        return candidates[-1]
+
     # ------------------------------------------------------------------ preemption
     def _preempt(self, req: Request) -> None:
         req.transition(RequestState.WAITING)
@@ -151,7 +184,7 @@ class Scheduler:
                 candidates = [r for r in pool if r is not self.running[0]]
                 if not candidates:
                     raise RuntimeError("a lone request does not fit in the pool")  # add() rejects those
-                victim = candidates[-1]
+                victim = self._victim(candidates)
             if pool is not self.running and victim in pool:
                 pool.remove(victim)
             self._preempt(victim)
@@ -185,7 +218,7 @@ class Scheduler:
                 n = min(r.seq_len - start, budget)
                 rows.append(PlanRow(r, start, n))
                 budget -= n
-        for req in list(self.waiting):
+        for req in self._in_order():
             if budget <= 0 or len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
                 break
             if req.num_pending:  # its last token is not read back yet; its prefill needs it
@@ -203,7 +236,7 @@ class Scheduler:
     def _schedule_whole(self) -> Plan | None:
         admitted: list[Request] = []
         budget = self.max_prefill_tokens
-        for req in list(self.waiting):
+        for req in self._in_order():
             if len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
                 break
             if req.num_pending:

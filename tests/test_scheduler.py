@@ -207,6 +207,46 @@ def test_pages_run_out_newest_is_preempted_oldest_never_and_output_is_unchanged(
     assert eng.cache.is_idle()
 
 
+def test_shortest_job_first_orders_admission_and_picks_the_longest_to_preempt():
+    """``schedule_policy="sjf"``: least remaining work first (prompt tokens still to compute plus tokens that
+    may still be generated), equals in arrival order, and still no skipping past one that does not fit."""
+    eng = _engine(pages=64, chunk=64, max_running=2, schedule_policy="sjf")
+    a = eng.add_request([1] * 9, SamplingParams(4))    # 13 to go
+    b = eng.add_request([1] * 3, SamplingParams(30))   # 33
+    c = eng.add_request([1] * 5, SamplingParams(2))    # 7
+    d = eng.add_request([1] * 4, SamplingParams(3))    # 7, after c
+    plan = eng.step()
+    assert [r.request.rid for r in plan.rows] == [c.rid, d.rid]  # two may run
+    while not (c.is_done and d.is_done):
+        eng.step()
+    assert [r.request.rid for r in eng.step().rows][-1] in (a.rid, b.rid) and a.state is not RequestState.WAITING
+    while eng.has_unfinished:
+        eng.step()
+    assert eng.cache.is_idle()
+    # the one with least work does not fit: nothing behind it is tried
+    eng = _engine(pages=6, page=4, chunk=64, schedule_policy="sjf")
+    eng.add_request([1] * 13, SamplingParams(8))   # runs first (alone in the queue), holds 4 of 6 pages
+    eng.step()
+    eng.add_request([1] * 9, SamplingParams(1))    # 10 to go, needs 3 pages: does not fit
+    eng.add_request([1] * 2, SamplingParams(20))   # 22 to go, would fit
+    assert [r.request.rid for r in eng.step().rows] == [0]
+    assert sorted(r.rid for r in eng.scheduler.waiting) == [1, 2]
+    # when pages run out the request with most left to do goes, never the oldest
+    eng = _engine(pages=10, page=4, chunk=32, schedule_policy="sjf")
+    reqs = [eng.add_request([3 + i] * 6, SamplingParams(n)) for i, n in enumerate((10, 4, 10, 6))]
+    victims = []
+    while eng.has_unfinished:
+        plan = eng.step()
+        victims += [v.rid for v in plan.preempted]
+        assert reqs[0] not in plan.preempted
+        eng.cache.check_invariants()
+    assert victims and victims[0] == 2  # most remaining work among all but the oldest (ties: the newest)
+    for r in reqs:
+        assert r.output_ids == _alone(r.prompt_ids, r.params, r.seed)
+    with pytest.raises(ValueError, match="unknown schedule policy"):
+        _engine(pages=8, schedule_policy="cache")
+
+
 def test_preempted_request_reruns_prompt_plus_output():
     eng = _engine(pages=5, page=4, chunk=32)
     a = eng.add_request([1] * 7, SamplingParams(8))
@@ -272,13 +312,15 @@ def test_stop_token_is_kept_and_ends_the_request():
 
 
 # ------------------------------------------------------------------ randomised load
+@pytest.mark.parametrize("policy", ["fcfs", "sjf"])
 @pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("pages, chunk", [(8, 3), (16, 3), (64, 3), (8, 2048), (16, 2048), (64, 2048), (8, 0), (64, 0)])
-def test_random_load_equals_each_request_alone(pages, chunk, overlap):
+def test_random_load_equals_each_request_alone(pages, chunk, overlap, policy):
     preemptions = 0
     for seed in range(6):
         rng = random.Random(1000 * pages + seed)
-        eng = _engine(pages=pages, page=4, chunk=chunk, max_running=6, seed=seed, max_prefill_tokens=24, overlap=overlap)
+        eng = _engine(pages=pages, page=4, chunk=chunk, max_running=6, seed=seed, max_prefill_tokens=24, overlap=overlap,
+                      schedule_policy=policy)
         specs = []
         for i in range(12):
             prompt = [rng.randrange(VOCAB) for _ in range(rng.randint(1, 14))]
