@@ -45,6 +45,8 @@ def add_engine_args(parser: argparse.ArgumentParser) -> None:
     g.add_argument("--block-backend", choices=["cpp"], default="cpp", help="page bookkeeping is always the C++ one here")
     g.add_argument("--disable-radix", action="store_true", help="accepted and ignored: there is no prefix cache here")
     g.add_argument("--fused-ops", action="store_true", help="accepted and ignored: the fused kernels are the only ones here")
+    g.add_argument("--attn-workspace-mb", type=int, default=None,
+                   help="accepted and ignored: the attention kernels' scratch memory is sized by the engine")
 
 
 def engine_kwargs(args: argparse.Namespace) -> dict:
