@@ -45,6 +45,7 @@ class StepContext:
     step_cache: dict = field(default_factory=dict)  # what parts compute once per step and share (e.g. the rotation table)
     buffers: dict = field(default_factory=dict)  # activation buffers of this step, by (role, shape, dtype): see buffer()
     graph_bucket: int = 0  # > 0 while a CUDA graph for this padded batch size is captured or replayed
+    graph_kv_len: int = 0  # inside a decode graph: the context length its launches are laid out for (0: a few thousand keys)
     # Set while a pass is captured as a chain of CUDA graphs (engine/graphs.py, StepGraphs): an operation whose
     # launches depend on how the step's tokens are shared among rows hands itself to ``recorder.defer``
     # instead of launching; it is then called with each later step's context, between the graphs.

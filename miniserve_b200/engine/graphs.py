@@ -11,7 +11,12 @@ take 2.07 ms per step padded to 24 rows against 2.28 padded to 32, 40 requests 3
 power of two); a graph holds the
 whole forward pass and the sampling kernel; the step's metadata is packed on the host and
 copied into a fixed device arena before the replay, so nothing inside the graph moves.
-Graphs are captured on first use of their bucket.
+Graphs are captured on first use of their bucket. A bucket has a graph for each class of context
+length (the longest row's: below 8,192 keys, from 8,192, from 32,768, from 131,072), because the
+attention kernel's launch inside a graph cannot follow the lengths: a graph for short contexts cuts a
+request's keys 8 ways at most, which leaves most SMs idle when one request holds 100,000 keys; the
+graphs for long contexts cut them as many ways as the CTAs that fit the GPU at once (measured at batch 1
+and 32,768 keys: 2.83 ms per step with the 8-way graph, see the design notes for the figures after).
 """
 
 from __future__ import annotations
@@ -21,6 +26,13 @@ from typing import Sequence
 import torch
 
 from .step import StepFunction, StepRow
+
+
+LENGTH_CLASSES = (0, 8192, 32768, 131072)
+
+
+def length_class(max_kv_len: int) -> int:
+    return max(c for c in LENGTH_CLASSES if c <= max_kv_len)
 
 
 def graph_buckets(max_bs: int) -> list[int]:
@@ -54,7 +66,7 @@ class DecodeGraphs:
         self.indices_cap = max(g.allocator.num_blocks for g in cache.groups) + 2 * self.max_batch + 4 if cache.groups else 4
         step_fn.reserve_arena(16 * (self.max_batch + 8) + cache.num_groups * (self.indices_cap + self.max_batch + 16) + 256)
         self._generation = step_fn.arena_generation
-        self._graphs: dict[tuple[int, str], _Captured] = {}
+        self._graphs: dict[tuple[int, str, int], _Captured] = {}  # (bucket, sampling mode, length class)
         self._pool = None
         self.capture_stream = torch.cuda.Stream(device=step_fn.device)
         self.replayed_launches = 0  # kernels of this package launched through graph replays so far
@@ -87,12 +99,13 @@ class DecodeGraphs:
         ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # the arena moved while preparing
             self._drop_all()
-        cap = self._graphs.get((bucket, mode))
+        klass = length_class(ctx.max_kv_len)
+        cap = self._graphs.get((bucket, mode, klass))
         if cap is not None and cap.sampler_scratch is not None and cap.sampler_scratch is not self.sampler._scratch:
             cap = None  # the sampler has moved to a larger scratch since: the graph's address is stale
         if cap is None:
-            cap = self._capture(ctx, bucket, mode)
-            self._graphs[(bucket, mode)] = cap
+            cap = self._capture(ctx, bucket, mode, klass)
+            self._graphs[(bucket, mode, klass)] = cap
         if sampling is not None:
             f32 = torch.ones((2, bucket), dtype=torch.float32)
             i64 = torch.zeros((2, bucket), dtype=torch.int64)
@@ -131,10 +144,11 @@ class DecodeGraphs:
         torch.cuda.current_stream(sf.device).synchronize()
         return len(self._graphs) - before
 
-    def _forward(self, ctx, bucket: int, mode: str, f32, i64):
+    def _forward(self, ctx, bucket: int, mode: str, klass: int, f32, i64):
         sf = self.step_fn
         ctx.stream = torch.cuda.current_stream(sf.device).cuda_stream
         ctx.graph_bucket = bucket
+        ctx.graph_kv_len = klass
         logits = sf.model.forward(ctx, sf.cache.entry_views)
         tokens = torch.empty(bucket, dtype=torch.int32, device=sf.device)
         from .. import ops
@@ -147,7 +161,7 @@ class DecodeGraphs:
                        stream=ctx.stream)
         return logits, tokens
 
-    def _capture(self, ctx, bucket: int, mode: str) -> _Captured:
+    def _capture(self, ctx, bucket: int, mode: str, klass: int) -> _Captured:
         sf = self.step_fn
         f32 = torch.zeros((2, bucket), dtype=torch.float32, device=sf.device)
         f32[1] = 1.0
@@ -166,7 +180,7 @@ class DecodeGraphs:
         kept = [(st, st[slots].clone()) for st in states.values()]
         with torch.cuda.stream(s):
             s.wait_stream(torch.cuda.current_stream(sf.device))
-            self._forward(ctx, bucket, mode, f32, i64)
+            self._forward(ctx, bucket, mode, klass, f32, i64)
         s.synchronize()
         for st, value in kept:
             st[slots] = value
@@ -181,7 +195,7 @@ class DecodeGraphs:
         try:
             with torch.cuda.graph(graph, pool=self._pool, stream=s):
                 gc.disable()
-                logits, tokens = self._forward(ctx, bucket, mode, f32, i64)
+                logits, tokens = self._forward(ctx, bucket, mode, klass, f32, i64)
         finally:
             if collecting:
                 gc.enable()

@@ -77,21 +77,28 @@ def clusters_resident(head_dim: int, splits: int, device_index: int = 0) -> int:
 
 def choose_splits(rows: int, head_chunks: int, max_kv_len: int | None, sm_count: int, resident=None) -> int:
     """How many ways the keys of each (request, kv head) are split across CTAs: as many as give
-    one wave of two CTAs per SM, but at least 128 keys per split and at most 16 splits (measured on
-    B200 at contexts of 512 to 8,192 and batches of 1 to 32: more splits only add partial results
-    to merge, fewer leave SMs idle; one split too many and the CTAs no longer fit one wave: a
+    one wave of two CTAs per SM, but at least 128 keys per split and at most 16 splits up to 4,096 keys
+    (measured on B200 at contexts of 512 to 4,096 and batches of 1 to 32: more splits only add partial
+    results to merge, fewer leave SMs idle; one split too many and the CTAs no longer fit one wave: a
     decode step of 8 requests at 2,048 tokens takes 1.28 ms with 4 splits, 1.34 with 3, 1.60 with 8).
-    ``max_kv_len`` None (inside a CUDA graph, where the launch cannot follow the context length):
-    assume a few thousand keys, and stay within the 8 splits that one thread-block cluster merges
-    (a single request: 0.98 ms per step with 8 splits, 0.99 with 16).
+    Beyond that a split is not asked to walk more than 256 keys while CTAs would be idle: a single
+    request of 8,192 keys is cut 32 ways, of 32,768 keys 37 ways (every CTA that fits): 1.33 -> 1.15 ms
+    per step at 8,192 keys, 2.83 -> 1.60 at 32,768, 9.01 -> 3.43 at 131,072 (4.7 TB/s).
+    ``max_kv_len`` None (inside a CUDA graph for short contexts, where the launch cannot follow the
+    context length): assume a few thousand keys, and stay within the 8 splits that one thread-block
+    cluster merges (a single request: 0.98 ms per step with 8 splits, 0.99 with 16).
     ``resident(splits)``: how many clusters of that size the device holds at a time; splits that run
     as a cluster (2 to 8) are reduced until every (request, head group) has its cluster in the first
     wave (6 requests x 8 head groups in clusters of 6: 48 clusters where 45 fit, and the step took 1.33 ms
-    against 1.17 for 8 requests in clusters of 4)."""
+    against 1.17 for 8 requests in clusters of 4). A few more than 8 splits are not worth leaving the
+    cluster for: 9 to 11 become 8."""
     items = max(rows * head_chunks, 1)
     want = (2 * sm_count) // items
     by_len = 8 if max_kv_len is None else max(1, -(-max_kv_len // 128))
-    splits = max(1, min(want, by_len, 16))
+    most = 16 if max_kv_len is None else max(16, max_kv_len // 256)
+    splits = max(1, min(want, by_len, most))
+    if 8 < splits < 12:
+        splits = 8
     if resident is not None:
         while 2 <= splits <= 8 and resident(splits) < items:
             splits -= 1
@@ -133,7 +140,8 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     indptr, indices = ctx.page_indptr[group], ctx.page_indices[group]
     chunks = nkv * -(-(nq // nkv) // 16)
     fit = (lambda n: clusters_resident(d, n, q.device.index or 0)) if CLUSTER_MERGE else None
-    splits = choose_splits(rows, chunks, None if ctx.graph_bucket else ctx.max_kv_len, ctx.sm_count, fit)
+    known = ctx.max_kv_len if not ctx.graph_bucket else (getattr(ctx, "graph_kv_len", 0) or None)
+    splits = choose_splits(rows, chunks, known, ctx.sm_count, fit)
     if CLUSTER_MERGE and 2 <= splits <= 8:
         # the splits as one thread-block cluster: merged through distributed shared memory
         _check(fns, fns["decode_cluster"](

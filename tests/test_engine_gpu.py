@@ -174,3 +174,25 @@ def test_graphs_captured_at_the_start_in_every_mode(folder):
                 chunked_prefill_size=24, cuda_graph=False)
     assert nucleus == eager.generate(prompts[:1], SamplingParams(9, temperature=0.8, top_p=0.8, seed=3))[0]
     assert len(llm.engine.graphs._graphs) == captured  # nothing was captured again
+
+
+def test_a_long_request_decodes_through_the_graph_for_its_class_of_context_length(tmp_path):
+    """A request past 8,192 tokens replays the decode graph captured for long contexts (its keys shared
+    out among as many CTAs as fit the GPU, merged through scratch memory), a short one beside it the graph
+    for short contexts afterwards; the tokens are those of the same engine without graphs."""
+    raw = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 2,
+           "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 256, "vocab_size": 701, "rms_norm_eps": 1e-6,
+           "rope_theta": 1000000.0, "tie_word_embeddings": True, "hidden_act": "silu", "max_position_embeddings": 16384}
+    plain.write_random_model(tmp_path, raw, seed=5, dtype=torch.bfloat16)
+    rng = random.Random(3)
+    prompts = [[rng.randrange(701) for _ in range(n)] for n in (8200, 60)]
+    params = [SamplingParams(max_new_tokens=5), SamplingParams(max_new_tokens=12)]
+    outs = {}
+    for graphs in (True, False):
+        llm = LLM(tmp_path, dtype="bfloat16", kv_pool_tokens=16384, page_size=16, max_running=4, cuda_graph=graphs)
+        outs[graphs] = llm.generate(prompts, params)
+        assert llm.engine.cache.is_idle()
+        if graphs:
+            classes = {key[2] for key in llm.engine.graphs._graphs}
+            assert classes == {0, 8192}, classes
+    assert outs[True] == outs[False]

@@ -435,6 +435,34 @@ def test_attention_bf16_decode(nq, nkv, d, page, splits, monkeypatch):
     assert torch.allclose(out.float()[1:3], ref[1:3], **BF16_TOL)
 
 
+@pytest.mark.parametrize("graph_kv_len", [0, 8192, 32768])
+def test_attention_bf16_decode_of_long_contexts_as_laid_out_inside_a_graph(graph_kv_len):
+    """Inside a CUDA graph the launch follows the batch size and the graph's class of context length, not
+    the rows' lengths: a short class cuts the keys 8 ways as one cluster, the long classes as many ways as
+    CTAs fit the GPU (merged through scratch memory by the last CTA to finish). Rows far shorter than the
+    class leave most of their splits without keys. One key far back carries row 0's result."""
+    seen = []
+    choose = attention_bf16.choose_splits
+
+    def spy(*a, **k):
+        seen.append(choose(*a, **k))
+        return seen[-1]
+
+    import unittest.mock as mock
+
+    rows = [(9000, 1), (40, 1), (8191, 1)]
+    pb, q, ref, scale = _attention_case(torch.bfloat16, rows, 4, 2, 128, 16, needle=3)
+    ctx = make_context(pb)
+    ctx.graph_bucket, ctx.graph_kv_len = 4, graph_kv_len
+    out = torch.full_like(q, float("nan"))
+    with mock.patch.object(attention_bf16, "choose_splits", spy):
+        attention_bf16.run(out, q, pb.k_pool, pb.v_pool, ctx, 0, scale, None)
+    assert seen == [{0: 8, 8192: 32, 32768: 49}[graph_kv_len]]  # 3 rows x 2 head groups share 296 CTAs
+    assert ref[0, 0].mean().item() > 40  # the far key dominates row 0
+    assert torch.allclose(out.float(), ref, atol=0.3, rtol=2e-2)
+    assert torch.allclose(out.float()[1:2], ref[1:2], **BF16_TOL)
+
+
 @pytest.mark.parametrize("window", [1, 16, 17, 100])
 def test_attention_bf16_decode_window_edge(window):
     rows = [(200, 1), (5, 1), (99, 1), (100, 1)]

@@ -437,4 +437,9 @@ def test_graph_batch_sizes_and_key_splits_of_a_decode_step():
     assert choose_splits(12, 8, None, 148, resident) == 2  # 96 clusters of 3 where 93 fit
     assert choose_splits(1, 8, None, 148, resident) == 8 and choose_splits(4, 8, None, 148, resident) == 8
     assert choose_splits(1, 8, 200, 148, resident) == 2  # never fewer than 128 keys to a split
-    assert choose_splits(64, 8, None, 148, resident) == 1 and choose_splits(1, 8, 8192, 148) == 16
+    assert choose_splits(64, 8, None, 148, resident) == 1 and choose_splits(1, 8, 4000, 148) == 16
+    # long contexts: as many CTAs as fit the GPU at once; a few more than a cluster's 8 splits stay a cluster
+    assert choose_splits(1, 8, 8192, 148, resident) == 32 and choose_splits(1, 8, 131072, 148, resident) == 37
+    assert choose_splits(2, 8, 32768, 148, resident) == 18 and choose_splits(4, 8, 32768, 148, resident) == 8
+    from miniserve_b200.engine.graphs import length_class
+    assert [length_class(n) for n in (1, 8191, 8192, 40000, 131072, 10 ** 6)] == [0, 0, 8192, 32768, 131072, 131072]
