@@ -9,7 +9,7 @@ It prints ONE JSON line: ``value`` is decoded tokens per second timed on the dev
 K steps; ``e2e`` is the same through the Python entry point with host tokens in and out;
 ``prefill`` is one 2,048-token prompt; ``roofline`` is the decode step's bytes (every weight it
 uses once, and the cache of the live requests) over its time against the measured copy
-bandwidth; ``points`` holds decode at batch 1 and 64 and at batch 8 behind 8,192 tokens. This
+bandwidth; ``points`` holds decode at batch 1 and 64, at batch 8 behind 8,192 tokens and at batch 1 behind 32,768. This
 engine runs on one GPU: for N > 1 it prints a line that says so and exits with 2.
 
 ``--config 8b`` and ``--config 32b`` run the two larger workloads instead (Qwen3-8B shapes: 32
@@ -296,6 +296,8 @@ def run_ours(args) -> dict:
     points[f"decode_b{args.batch}"] = round(value, 1)
     long_ms, _, _ = time_decode(eng, 8, 4 * CONTEXT, min(args.steps, 64), args.warmup)
     points[f"decode_b8_ctx{4 * CONTEXT}"] = round(8 * 1000.0 / long_ms, 1)
+    far_ms, _, _ = time_decode(eng, 1, 16 * CONTEXT, min(args.steps, 32), args.warmup)  # one request far into its context
+    points[f"decode_b1_ctx{16 * CONTEXT}"] = round(1000.0 / far_ms, 1)
 
     pre_ms = time_prefill(eng, PREFILL_TOKENS)
     pre_flops = flops_of_prefill(raw, PREFILL_TOKENS)
