@@ -218,14 +218,18 @@ class Scheduler:
                 n = min(r.seq_len - start, budget)
                 rows.append(PlanRow(r, start, n))
                 budget -= n
+        margin = None  # what the running requests may still allocate: counted once, then kept up to date
         for req in self._in_order():
             if budget <= 0 or len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
                 break
             if req.num_pending:  # its last token is not read back yet; its prefill needs it
                 break
-            if not self.cache.fits(self._admission_need(req), margin=self._outstanding(self.running)):
+            if margin is None:
+                margin = self._outstanding(self.running)
+            if not self.cache.fits(self._admission_need(req), margin=margin):
                 break
             self._admit(req)
+            margin = _add(margin, self._outstanding((req,)))
             n = min(req.seq_len, budget)
             rows.append(PlanRow(req, 0, n))
             budget -= n
@@ -236,6 +240,7 @@ class Scheduler:
     def _schedule_whole(self) -> Plan | None:
         admitted: list[Request] = []
         budget = self.max_prefill_tokens
+        margin = None
         for req in self._in_order():
             if len(self.running) >= self.max_running or self.cache.num_free_slots == 0:
                 break
@@ -243,9 +248,12 @@ class Scheduler:
                 break
             if admitted and req.seq_len > budget:  # the first is admitted even over the budget
                 break
-            if not self.cache.fits(self._admission_need(req), margin=self._outstanding(self.running)):
+            if margin is None:
+                margin = self._outstanding(self.running)
+            if not self.cache.fits(self._admission_need(req), margin=margin):
                 break
             self._admit(req)
+            margin = _add(margin, self._outstanding((req,)))
             admitted.append(req)
             budget -= req.seq_len
         if admitted:
