@@ -225,15 +225,16 @@ MS_EXPORT int ms_table_copy_blocks(void* h, int* out, int cap) {
 // Arena layout (int32 entries; every field starts on a multiple of 4 entries):
 //   token_ids[T'] positions[T'] row_of_token[T'] cu_q[R'+1] q_start[R'] kv_len[R'] state_slot[R']
 //   logit_rows[W] then for each cache group g: page_indptr_g[R'+1] page_indices_g[P_g]
-// with R' = rows + pad_rows and T' = tokens + pad_rows. Of a table only the pages it still holds
+// with R' = rows + pad_rows and T' = tokens + pad_rows * pad_len. Of a table only the pages it still holds
 // are packed (and the entry just below them, which reads -1): page_indptr_g[r] is the index that
 // the table's entry 0 WOULD have, so that page_indices_g[page_indptr_g[r] + (position / page_size)]
 // is right for every position a kernel may ask for (those the window still reaches), whatever a
 // windowed group has given back; it can be negative. So a step never packs more entries than
-// the pool has pages, plus one per row. A padding row is one token 0 at
-// position 0 whose single page is `pad_page` (a page outside the allocator) and whose state slot is
-// `pad_state_slot` (a slot no request gets, so that a mixer with state needs no mask); with want_pad_rows its
-// logits are wanted too, so that the layout depends on R' alone. indices_cap > 0 gives every
+// the pool has pages, plus one per row. A padding row is pad_len tokens 0 at
+// positions 0 .. pad_len - 1 whose every page is `pad_page` (a page outside the allocator, of
+// pad_page_size tokens; what the row's tokens write there overlaps and is never read for a result) and
+// whose state slot is `pad_state_slot` (a slot no request gets, so that a mixer with state needs no
+// mask); with want_pad_rows the logits of its last token are wanted too, so that the layout depends on R' alone. indices_cap > 0 gives every
 // group's page_indices exactly that many entries (a layout that does not move with the number of
 // pages, as a captured CUDA graph needs); 0 packs them tightly.
 // offsets_out receives the start of each field: 8 + 2*groups entries, then the total.
@@ -243,14 +244,17 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
                                  const int* q_start, const int* q_len, const int* token_ids,
                                  const int* state_slot, const int* logit_rows, int num_logit_rows, int groups,
                                  void* const* tables /* [groups][rows] */, const int* pad_page /* [groups] */,
-                                 long long indices_cap, int want_pad_rows, int pad_state_slot) {
+                                 long long indices_cap, int want_pad_rows, int pad_state_slot, int pad_len,
+                                 int pad_page_size) {
   if (rows < 0 || pad_rows < 0 || groups < 0) return -err(VALUE_ERROR, "pack_step: negative count");
+  if (pad_len < 1 || pad_page_size < 1) return -err(VALUE_ERROR, "pack_step: a padding row of %d tokens on pages of %d", pad_len, pad_page_size);
+  const long long pad_pages = (pad_len + pad_page_size - 1) / pad_page_size;
   long long T = 0;
   for (int r = 0; r < rows; ++r) {
     if (q_len[r] < 1) return -err(VALUE_ERROR, "pack_step: row %d brings %d tokens", r, q_len[r]);
     T += q_len[r];
   }
-  const long long Tp = T + pad_rows, Rp = rows + pad_rows;
+  const long long Tp = T + (long long)pad_rows * pad_len, Rp = rows + pad_rows;
   long long off = 0;
   int f = 0;
   auto field = [&](long long n) {
@@ -263,7 +267,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
                   o_kv = field(Rp), o_ss = field(Rp), o_lr = field(num_logit_rows + (want_pad_rows ? pad_rows : 0));
   std::vector<long long> o_indptr(groups), o_indices(groups);
   for (int g = 0; g < groups; ++g) {
-    long long pages = pad_rows;
+    long long pages = pad_rows * pad_pages;
     for (int r = 0; r < rows; ++r) {
       auto* t = static_cast<Table*>(tables[(size_t)g * rows + r]);
       if (t->num_tokens != (long long)q_start[r] + q_len[r])
@@ -283,7 +287,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
   arena[o_cu] = 0;
   for (int r = 0; r < Rp; ++r) {
     const bool pad = r >= rows;
-    const int n = pad ? 1 : q_len[r], s = pad ? 0 : q_start[r];
+    const int n = pad ? pad_len : q_len[r], s = pad ? 0 : q_start[r];
     for (int i = 0; i < n; ++i, ++t) {
       arena[o_ids + t] = pad ? 0 : token_ids[t];
       arena[o_pos + t] = s + i;
@@ -299,7 +303,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
     arena[o_lr + i] = logit_rows[i];
   }
   if (want_pad_rows)
-    for (int i = 0; i < pad_rows; ++i) arena[o_lr + num_logit_rows + i] = (int32_t)(T + i);
+    for (int i = 0; i < pad_rows; ++i) arena[o_lr + num_logit_rows + i] = (int32_t)(T + (long long)(i + 1) * pad_len - 1);
   for (int g = 0; g < groups; ++g) {
     long long p = 0;
     for (int r = 0; r < Rp; ++r) {
@@ -311,7 +315,7 @@ MS_EXPORT long long ms_pack_step(int32_t* arena, long long arena_cap, long long*
         p += (long long)tb->blocks.size() - from;
       } else {
         arena[o_indptr[g] + r] = (int32_t)p;
-        arena[o_indices[g] + p++] = pad_page[g];
+        for (long long k = 0; k < pad_pages; ++k) arena[o_indices[g] + p++] = pad_page[g];
       }
     }
     arena[o_indptr[g] + Rp] = (int32_t)p;

@@ -122,9 +122,11 @@ class Engine:
 
                 # the arena holds the largest step at the fixed layout now, so that it does not move under captured graphs
                 budget = (chunked_prefill_size if chunked_prefill_size else max_prefill_tokens) + max_running
-                self.step_fn.reserve_arena(3 * (budget + 4) + 6 * (max_running + 8)
-                                           + self.cache.num_groups * (self.graphs.indices_cap + max_running + 16) + 256)
-                self.step_fn.graphs = StepGraphs(self.step_fn, self.graphs.indices_cap)
+                # (a padded step's extra row brings up to 128 tokens and their page entries)
+                cap = self.graphs.indices_cap + -(-128 // self.cache.page_size)
+                self.step_fn.reserve_arena(3 * (budget + 132) + 6 * (max_running + 8)
+                                           + self.cache.num_groups * (cap + max_running + 16) + 256)
+                self.step_fn.graphs = StepGraphs(self.step_fn, cap)
         self.overlap = overlap
         self.num_steps = 0
         self.stalled = False  # the last step() neither launched a step nor read one back

@@ -35,11 +35,10 @@ class StepRow:
     fill_from: int | None = None
 
 
-def _leading_ones(q_len: np.ndarray, pad_rows: int) -> int:
-    """How many rows from the front bring exactly one token (padding rows, which follow the real
-    ones, bring one token each)."""
+def _leading_ones(q_len: np.ndarray, pad_rows: int, pad_len: int = 1) -> int:
+    """How many rows from the front bring exactly one token (padding rows follow the real ones)."""
     other = np.flatnonzero(q_len != 1)
-    return int(other[0]) if other.size else len(q_len) + pad_rows
+    return int(other[0]) if other.size else len(q_len) + (pad_rows if pad_len == 1 else 0)
 
 
 class StepError(RuntimeError):
@@ -93,13 +92,14 @@ class StepFunction:
             torch.cuda.current_stream(self.device).synchronize()
             self._grow(ints)
 
-    def _arena_need(self, rows: Sequence[StepRow], pad_rows: int, indices_cap: int = 0) -> int:
-        t = sum(len(r.tokens) for r in rows) + pad_rows
+    def _arena_need(self, rows: Sequence[StepRow], pad_rows: int, indices_cap: int = 0, pad_len: int = 1) -> int:
+        t = sum(len(r.tokens) for r in rows) + pad_rows * pad_len
         r = len(rows) + pad_rows
         w = sum(len(x.want) for x in rows)
         pages = sum(sum(tb.num_entries + tb.blocks_needed(len(x.tokens)) for tb in x.cache.tables) for x in rows)
         groups = self.cache.num_groups
-        return (3 * (t + 4) + 4 * (r + 5) + (w + pad_rows + 4) + groups * (r + 5 + pad_rows + 4 + indices_cap)
+        pad_pages = pad_rows * -(-pad_len // self.cache.page_size)
+        return (3 * (t + 4) + 4 * (r + 5) + (w + pad_rows + 4) + groups * (r + 5 + pad_pages + 4 + indices_cap)
                 + pages + 64)
 
     # ------------------------------------------------------------------ the step
@@ -116,9 +116,9 @@ class StepFunction:
         return logits
 
     def prepare(self, rows: Sequence[StepRow], pad_rows: int = 0, indices_cap: int = 0,
-                want_pad_rows: bool = False, prev_tokens: torch.Tensor | None = None) -> StepContext:
+                want_pad_rows: bool = False, prev_tokens: torch.Tensor | None = None, pad_len: int = 1) -> StepContext:
         """Reserve pages, pack the step and start its copy to the device. ``pad_rows`` adds
-        padding rows (one token at position 0 on a page outside the allocator);
+        padding rows (``pad_len`` tokens from position 0 on, on a page outside the allocator);
         ``indices_cap`` / ``want_pad_rows`` ask for the layout that depends on the padded row
         count alone (see ``csrc/host_core.cpp``), which captured graphs need."""
         if not rows:
@@ -146,7 +146,7 @@ class StepFunction:
         if fills:
             if prev_tokens is None or any(len(rows[i].tokens) != 1 for i, _ in fills):
                 raise ValueError("a row filled from the previous step brings exactly one token and needs that step's tokens")
-        need = self._arena_need(rows, pad_rows, indices_cap) + 2 * len(fills) + 8
+        need = self._arena_need(rows, pad_rows, indices_cap, pad_len) + 2 * len(fills) + 8
         if need > self._arena_ints:
             torch.cuda.current_stream(self.device).synchronize()
             self._grow(2 * need)
@@ -169,7 +169,7 @@ class StepFunction:
         total = self._host_lib.ms_pack_step(
             pinned.data_ptr(), self._arena_ints, offsets, len(rows), pad_rows, q_start.ctypes.data,
             q_len.ctypes.data, ids.ctypes.data, slots.ctypes.data, want_arr.ctypes.data, len(want), groups, tables,
-            pad_page.ctypes.data, indices_cap, int(want_pad_rows), self.cache.pad_state_slot)
+            pad_page.ctypes.data, indices_cap, int(want_pad_rows), self.cache.pad_state_slot, pad_len, self.cache.page_size)
         if total < 0:
             # undo the reservation so that a failed step leaves the tables as they were
             for r, n in zip(rows, q_len):
@@ -196,7 +196,7 @@ class StepFunction:
         ev.record(stream)
         self._events[turn] = ev
 
-        t_all = int(q_len.sum()) + pad_rows
+        t_all = int(q_len.sum()) + pad_rows * pad_len
         r_all = len(rows) + pad_rows
         o = list(offsets)
 
@@ -217,11 +217,11 @@ class StepFunction:
             state_slot=view(o[6], r_all),
             logit_rows=view(o[7], max(len(want) + (pad_rows if want_pad_rows else 0), 1)),
             page_indptr=page_indptr, page_indices=page_indices, status=self.status,
-            host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [1] * pad_rows,
+            host_q_start=q_start.tolist() + [0] * pad_rows, host_q_len=q_len.tolist() + [pad_len] * pad_rows,
             host_state_slot=slots.tolist() + [self.cache.pad_state_slot] * pad_rows,
-            max_q_len=int(q_len.max()), max_kv_len=int(kv_end.max()),
+            max_q_len=max(int(q_len.max()), pad_len if pad_rows else 1), max_kv_len=max(int(kv_end.max()), pad_len if pad_rows else 1),
             decode_only=bool((q_len == 1).all()),
-            leading_single_rows=_leading_ones(q_len, pad_rows), sm_count=self.sm_count, scratch=self.persistent_scratch,
+            leading_single_rows=_leading_ones(q_len, pad_rows, pad_len), sm_count=self.sm_count, scratch=self.persistent_scratch,
             layout=tuple(o))
 
     def reset_after_fault(self) -> None:

@@ -68,7 +68,7 @@ def host():
     _declare(lib, "ms_table_release_below", [_p, _ll, POINTER(c_int)])
     _declare(lib, "ms_table_copy_blocks", [_p, POINTER(c_int32), _i])
     _declare(lib, "ms_pack_step",
-             [_p, _ll, POINTER(_ll), _i, _i, _p, _p, _p, _p, _p, _i, _i, POINTER(c_void_p), _p, _ll, _i, _i], _ll)
+             [_p, _ll, POINTER(_ll), _i, _i, _p, _p, _p, _p, _p, _i, _i, POINTER(c_void_p), _p, _ll, _i, _i, _i, _i], _ll)
     return lib
 
 

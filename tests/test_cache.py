@@ -235,7 +235,8 @@ def test_no_page_is_lost_held_twice_or_freed_twice_under_random_orders():
 
 
 # ------------------------------------------------------------------ the step packer
-def _pack(tables_by_group, q_start, q_len, ids, want, pad_rows=0, pad_page=(99,), indices_cap=0, want_pad=False):
+def _pack(tables_by_group, q_start, q_len, ids, want, pad_rows=0, pad_page=(99,), indices_cap=0, want_pad=False, pad_len=1,
+          page_size=4):
     lib = native.host()
     rows, groups = len(q_len), len(tables_by_group)
     arena = np.full(4096, -7, dtype=np.int32)
@@ -248,7 +249,7 @@ def _pack(tables_by_group, q_start, q_len, ids, want, pad_rows=0, pad_page=(99,)
     qs, ql, tok, ss, wa, pp = arr(q_start), arr(q_len), arr(ids), arr([5] * rows), arr(want), arr(list(pad_page))
     total = lib.ms_pack_step(arena.ctypes.data, arena.size, offsets, rows, pad_rows, qs.ctypes.data, ql.ctypes.data,
                              tok.ctypes.data, ss.ctypes.data, wa.ctypes.data, len(want), groups, handles,
-                             pp.ctypes.data, indices_cap, int(want_pad), 64)
+                             pp.ctypes.data, indices_cap, int(want_pad), 64, pad_len, page_size)
     return total, arena, list(offsets)
 
 
@@ -273,6 +274,29 @@ def test_packer_against_a_naive_layout():
     assert arena[o[8]:o[8] + R + 1].tolist() == [0, 2, 4, 5]
     assert arena[o[9]:o[9] + 5].tolist() == t0.blocks + t1.blocks + [99]
     assert all(x % 4 == 0 for x in o)
+
+
+def test_packer_pads_with_a_row_of_several_tokens():
+    """A padding row of 6 tokens on pages of 4: positions 0..5, two page entries that both name the page
+    outside the allocator, the spare state slot; the real rows are packed as without it."""
+    a = BlockAllocator(16, 4)
+    t0 = a.new_table()
+    t0.append_tokens(5)
+    total, arena, o = _pack([[t0]], [2], [3], [7, 8, 9], [2], pad_rows=1, pad_len=6)
+    assert total > 0
+    T, R = 9, 2
+    assert arena[o[0]:o[0] + T].tolist() == [7, 8, 9, 0, 0, 0, 0, 0, 0]
+    assert arena[o[1]:o[1] + T].tolist() == [2, 3, 4, 0, 1, 2, 3, 4, 5]
+    assert arena[o[2]:o[2] + T].tolist() == [0, 0, 0] + [1] * 6
+    assert arena[o[3]:o[3] + R + 1].tolist() == [0, 3, 9]
+    assert arena[o[4]:o[4] + R].tolist() == [2, 0] and arena[o[5]:o[5] + R].tolist() == [5, 6]
+    assert arena[o[6]:o[6] + R].tolist() == [5, 64]
+    assert arena[o[7]:o[7] + 1].tolist() == [2]
+    assert arena[o[8]:o[8] + R + 1].tolist() == [0, 2, 4]
+    assert arena[o[9]:o[9] + 4].tolist() == t0.blocks + [99, 99]
+    total, arena, o = _pack([[t0]], [2], [3], [7, 8, 9], [2], pad_rows=2, pad_len=3, want_pad=True)
+    assert arena[o[7]:o[7] + 3].tolist() == [2, 5, 8]  # with their logits wanted: each padding row's last token
+    assert _pack([[t0]], [2], [3], [7, 8, 9], [2], pad_rows=1, pad_len=0)[0] < 0
 
 
 def test_packer_refuses_inconsistent_steps():

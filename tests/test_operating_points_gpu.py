@@ -136,7 +136,7 @@ def test_prompt_whole_and_in_portions_then_graph_decode_at_batch_8_and_a_step_at
     for t in range(DECODE):
         tokens = [seq_a[PROMPT + t]] + [seq_b[PROMPT + t]] * 7
         got = graphs.run([StepRow(rc, [tok], (0,)) for rc, tok in zip(batch, tokens)], None)
-        logits = graphs._graphs[(8, "greedy")].logits
+        logits = graphs._graphs[(8, "greedy", 0)].logits
         assert got.tolist() == torch.argmax(logits[:8], -1).tolist()
         for r in decoded:
             decoded[r].append(logits[r].clone())

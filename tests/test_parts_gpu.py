@@ -227,7 +227,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
         step3.run([StepRow(rc, seq[:9], []) for rc, seq in zip(rcs, seqs)])
         for t in range(9, 30):
             graphs.run([StepRow(rc, [seq[t]], (0,)) for rc, seq in zip(rcs, seqs)], None)
-            logits = graphs._graphs[(4, "greedy")].logits
+            logits = graphs._graphs[(4, "greedy", 0)].logits
             for r in range(3):
                 assert torch.allclose(logits[r], wholes[r][t], **tol), f"request {r}, token {t}"
         step3.check_status()
