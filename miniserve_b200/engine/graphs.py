@@ -273,8 +273,9 @@ class StepGraphs:
     depend on the padding; in bfloat16 the products of the padded step may round differently, within
     what another cut of the same tokens would change.
 
-    A step whose (tokens, rows, wanted, decoding rows) have been seen ``sightings`` times (twice, if it
-    has no decoding rows: prompts alone) is captured while it runs, later ones replay. Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
+    A step whose (tokens, rows, wanted, decoding rows) have been seen ``sightings`` times is captured while
+    it runs, later ones replay; a step without decoding rows (prompts alone) at its second sighting, and
+    with an eighth of the distance that is otherwise kept between two captures. Only models whose parts all declare ``shape_static`` are taken. The least recently used shapes are
     dropped beyond ``max_shapes``. The logits of a replayed step live in the graphs' memory and are
     overwritten by the next replayed step.
     """
@@ -355,7 +356,9 @@ class StepGraphs:
             if len(self._seen) > 4096:
                 self._seen.clear()
             self._seen[key] = n
-            if n < (self.sightings if key[3] else min(self.sightings, 2)) or self._since_capture <= self.capture_every:
+            # prompts alone come in few shapes once padded, and come again: they are captured sooner
+            sightings, gap = (self.sightings, self.capture_every) if key[3] else (min(self.sightings, 2), self.capture_every // 8)
+            if n < sightings or self._since_capture <= gap:
                 return None
         pad = key[0] - sum(len(r.tokens) for r in rows)
         ctx = sf.prepare(rows, pad_rows=1 if pad else 0, pad_len=max(pad, 1), indices_cap=self.indices_cap, prev_tokens=prev_tokens)

@@ -94,6 +94,8 @@ def main(argv=None) -> int:
         pool_pages=engine.cache.num_pages, preemptions=engine.scheduler.num_preemptions,
         preempted_requests=engine.scheduler.num_preempted_requests,
         all_finished=finished, pages_returned=engine.cache.is_idle(),
+        graphs_captured=dict(decode=len(engine.graphs._graphs) if engine.graphs is not None else 0,
+                             steps=engine.step_fn.graphs.captures if getattr(engine.step_fn, "graphs", None) is not None else 0),
     )
     print(json.dumps(report, indent=2))
     return 0 if finished and report["pages_returned"] else 1
