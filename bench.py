@@ -332,9 +332,9 @@ def run_ours(args) -> dict:
 
 
 WORKLOADS = {
-    # BASELINE config 4: continuous batching with a 2,048-token chunk budget, prompts uniform in [128, 4096]
+    # the reference's serving workload at Qwen3-8B sizes: continuous batching with a 2,048-token chunk budget, prompts uniform in [128, 4096]
     "8b": dict(preset="8b", requests=32, prompt=(128, 4096), new_tokens=128, pool_pages=None),
-    # BASELINE config 5: 16 prompts of 8,192 tokens in a pool that admits nine of them (a prompt and one token
+    # its workload at Qwen3-32B sizes: 16 prompts of 8,192 tokens in a pool that admits nine of them (a prompt and one token
     # each) and has 20 pages to spare: their 128 decoded tokens need 72, so admission stops AND requests are preempted
     "32b": dict(preset="32b", requests=16, prompt=(8192, 8192), new_tokens=128, pool_pages=9 * 513 + 20),
 }
