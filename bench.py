@@ -359,7 +359,7 @@ def run_workload(args) -> dict:
     llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=pool_tokens, page_size=16, max_running=64,
               chunked_prefill_size=2048)
     eng = llm.engine
-    eng.capture_graphs(("greedy",))
+    eng.capture_graphs(("greedy",), context_lengths=(wl["prompt"][0], wl["prompt"][1] + wl["new_tokens"]))
     weight_bytes, kv_per_token = llm.model.weight_bytes(), eng.cache.bytes_per_token()
     h, inter = raw["hidden_size"], raw["intermediate_size"]
     nq, nkv, d, layers = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["num_hidden_layers"]

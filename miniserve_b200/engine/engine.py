@@ -177,15 +177,18 @@ class Engine:
             step_graphs=getattr(self.step_fn, "graphs", None) is not None, **self.settings)
 
     # ------------------------------------------------------------------ requests
-    def capture_graphs(self, modes=("greedy",)) -> int:
+    def capture_graphs(self, modes=("greedy",), context_lengths=(0,)) -> int:
         """Capture the decode graphs of every batch bucket now (while the engine is idle) instead
         of at their first use; returns how many were captured. ``modes``: of "greedy",
-        "temperature", "top_p"."""
+        "temperature", "top_p". ``context_lengths``: lengths that requests will reach; the graphs of
+        their classes of context length are captured (those for short contexts by default)."""
         if self.graphs is None:
             return 0
         if self.has_unfinished:
             raise RuntimeError("graphs are captured at the start, before any request is submitted")
-        return self.graphs.capture_all(modes)
+        from .graphs import length_class
+
+        return self.graphs.capture_all(modes, sorted({length_class(max(int(n), 1)) for n in context_lengths}))
 
     def add_request(self, prompt_ids: Sequence[int], params: SamplingParams) -> Request:
         req = Request(next(self._rids), list(prompt_ids), params)

@@ -84,9 +84,12 @@ class DecodeGraphs:
     def _bucket(self, n: int) -> int:
         return next(b for b in self.buckets if b >= n)
 
-    def run(self, rows: Sequence[StepRow], sampling: dict | None, prev_tokens: torch.Tensor | None = None) -> torch.Tensor:
+    def run(self, rows: Sequence[StepRow], sampling: dict | None, prev_tokens: torch.Tensor | None = None,
+            klass: int | None = None) -> torch.Tensor:
         """One decode step (every row brings one token and wants its logits). Returns the
-        sampled tokens of the real rows, int32 on the device."""
+        sampled tokens of the real rows, int32 on the device. ``klass``: the class of context length whose
+        graph to use (default: the class of the longest row; any class gives the same tokens, a graph's
+        class only decides how its attention launch shares out the keys)."""
         sf = self.step_fn
         if sf.arena_generation != self._generation:
             self._drop_all()
@@ -99,7 +102,8 @@ class DecodeGraphs:
         ctx = sf.prepare(rows, pad_rows=pad, indices_cap=self.indices_cap, want_pad_rows=True, prev_tokens=prev_tokens)
         if sf.arena_generation != self._generation:  # the arena moved while preparing
             self._drop_all()
-        klass = length_class(ctx.max_kv_len)
+        if klass is None:
+            klass = length_class(ctx.max_kv_len)
         cap = self._graphs.get((bucket, mode, klass))
         if cap is not None and cap.sampler_scratch is not None and cap.sampler_scratch is not self.sampler._scratch:
             cap = None  # the sampler has moved to a larger scratch since: the graph's address is stale
@@ -122,10 +126,11 @@ class DecodeGraphs:
             sf.cache.trim(r.cache)
         return cap.tokens[:n]
 
-    def capture_all(self, modes: Sequence[str] = ("greedy",)) -> int:
+    def capture_all(self, modes: Sequence[str] = ("greedy",), classes: Sequence[int] = (0,)) -> int:
         """Capture the graphs of every batch bucket now instead of at their first use (the reference
-        captures at start-up, miniserve/engine/cuda_graph.py). Needs an idle cache: it steps
-        ``max_batch`` one-token requests that it creates and releases. Returns how many it captured."""
+        captures at start-up, miniserve/engine/cuda_graph.py), for the given classes of context length.
+        Needs an idle cache: it steps ``max_batch`` one-token requests that it creates and releases.
+        Returns how many it captured."""
         sf = self.step_fn
         sampling_for = {
             "greedy": lambda n: None,
@@ -133,11 +138,11 @@ class DecodeGraphs:
             "top_p": lambda n: dict(temperatures=[1.0] * n, top_ps=[0.5] * n, seeds=[0] * n, counters=[0] * n),
         }
         before = len(self._graphs)
-        for mode in modes:
+        for mode, klass in ((m, k) for m in modes for k in classes):
             for bucket in self.buckets:
                 caches = [sf.cache.new_request() for _ in range(bucket)]
                 try:
-                    self.run([StepRow(c, [0], (0,)) for c in caches], sampling_for[mode](bucket))
+                    self.run([StepRow(c, [0], (0,)) for c in caches], sampling_for[mode](bucket), klass=klass)
                 finally:
                     for c in caches:
                         sf.cache.release(c)
