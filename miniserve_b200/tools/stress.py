@@ -71,7 +71,7 @@ def main(argv=None) -> int:
     engine = llm.engine
     if args.capture_graphs_at_start:
         modes = ("greedy",) if args.temperature == 0 else ("temperature", "top_p") if args.top_p < 1 else ("temperature",)
-        engine.capture_graphs(modes)
+        engine.capture_graphs(modes, context_lengths=(args.prompt_len[0], args.prompt_len[1] + args.max_new_tokens[1]))
     prompts, params = workload(llm.model.spec.vocab_size, args.num_requests, args.prompt_len, args.max_new_tokens,
                                args.workload_seed, args.temperature, args.top_p)
     watch = Watcher()
