@@ -181,14 +181,16 @@ class Engine:
         """Capture the decode graphs of every batch bucket now (while the engine is idle) instead
         of at their first use; returns how many were captured. ``modes``: of "greedy",
         "temperature", "top_p". ``context_lengths``: lengths that requests will reach; the graphs of
-        their classes of context length are captured (those for short contexts by default)."""
+        every class of context length from the shortest's to the longest's are captured (those for short
+        contexts by default)."""
         if self.graphs is None:
             return 0
         if self.has_unfinished:
             raise RuntimeError("graphs are captured at the start, before any request is submitted")
-        from .graphs import length_class
+        from .graphs import LENGTH_CLASSES, length_class
 
-        return self.graphs.capture_all(modes, sorted({length_class(max(int(n), 1)) for n in context_lengths}))
+        lo, hi = (length_class(max(int(f(context_lengths)), 1)) for f in (min, max))
+        return self.graphs.capture_all(modes, [c for c in LENGTH_CLASSES if lo <= c <= hi])
 
     def add_request(self, prompt_ids: Sequence[int], params: SamplingParams) -> Request:
         req = Request(next(self._rids), list(prompt_ids), params)
