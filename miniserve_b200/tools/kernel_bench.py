@@ -4,6 +4,7 @@ summaries under ``profiles/`` were measured and captured with.
     python -m miniserve_b200.tools.kernel_bench attn_decode --batch 64 --context 2048
     python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048
     python -m miniserve_b200.tools.kernel_bench skinny --m 8 --n 4096 --k 1024
+    python -m miniserve_b200.tools.kernel_bench sample --batch 8 --top-p 0.9
 
 Each case rotates over enough copies of its inputs to exceed the L2 cache, captures one pass over
 all copies in a CUDA graph, and reports the time per launch with the bytes or flops it implies.
@@ -85,7 +86,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -99,6 +100,9 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--gemm", choices=["auto", "tcgen05", "library"], default="auto",
                     help="gemm, gate_up: this package's tcgen05 kernels, the vendor library, or the engine's choice")
+    ap.add_argument("--vocab", type=int, default=151936, help="sample: tokens in a row of logits")
+    ap.add_argument("--temperature", type=float, default=0.8, help="sample: 0 is greedy")
+    ap.add_argument("--top-p", type=float, default=1.0, help="sample: below 1, the nucleus is found first")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -142,6 +146,25 @@ def main(argv=None) -> int:
                 ops.linear(x, ws[i], out=o, stream=stream)
             else:
                 ops.linear_silu_mul(x, ws[i], o, scratch=scratch, stream=stream)
+    elif args.kernel == "sample":
+        # --batch rows of float32 logits, each row with its own seed
+        byts = args.batch * args.vocab * 4
+        work = dict(bytes=byts)
+        copies = max(2, min(16, int(L2_BYTES // byts) + 1))
+        logits = [torch.randn(args.batch, args.vocab, device=dev) * 3 for _ in range(copies)]
+        tokens = torch.empty(args.batch, dtype=torch.int32, device=dev)
+        temp = torch.full((args.batch,), args.temperature, device=dev)
+        top_p = torch.full((args.batch,), args.top_p, device=dev) if args.top_p < 1 else None
+        seed = torch.arange(args.batch, dtype=torch.int64, device=dev)
+        counter = torch.full((args.batch,), 5, dtype=torch.int64, device=dev)
+        nucleus = torch.empty(args.batch * ops.nucleus_bytes(), dtype=torch.uint8, device=dev)
+
+        def calls(i, stream):
+            if args.temperature == 0:
+                ops.sample(tokens, logits[i], stream=stream)
+            else:
+                ops.sample(tokens, logits[i], temperature=temp, top_p=top_p, seed=seed, counter=counter,
+                           scratch=nucleus if top_p is not None else None, stream=stream)
     elif args.kernel == "skinny":
         byts = args.n * args.k * 2
         work = dict(bytes=byts)
