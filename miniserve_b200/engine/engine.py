@@ -177,12 +177,13 @@ class Engine:
             step_graphs=getattr(self.step_fn, "graphs", None) is not None, **self.settings)
 
     # ------------------------------------------------------------------ requests
-    def capture_graphs(self, modes=("greedy",), context_lengths=(0,)) -> int:
+    def capture_graphs(self, modes=("greedy",), context_lengths=(0,), prompt_tokens: int = 0) -> int:
         """Capture the decode graphs of every batch bucket now (while the engine is idle) instead
         of at their first use; returns how many were captured. ``modes``: of "greedy",
         "temperature", "top_p". ``context_lengths``: lengths that requests will reach; the graphs of
         every class of context length from the shortest's to the longest's are captured (those for short
-        contexts by default)."""
+        contexts by default). ``prompt_tokens``: also capture the step graphs that lone prompts of up to so
+        many tokens meet (no more than a step's token budget), so that the first requests replay them."""
         if self.graphs is None:
             return 0
         if self.has_unfinished:
@@ -190,7 +191,11 @@ class Engine:
         from .graphs import LENGTH_CLASSES, length_class
 
         lo, hi = (length_class(max(int(f(context_lengths)), 1)) for f in (min, max))
-        return self.graphs.capture_all(modes, [c for c in LENGTH_CLASSES if lo <= c <= hi])
+        count = self.graphs.capture_all(modes, [c for c in LENGTH_CLASSES if lo <= c <= hi])
+        step_graphs = getattr(self.step_fn, "graphs", None)
+        if prompt_tokens and step_graphs is not None:
+            count += step_graphs.capture_prompt_shapes(min(prompt_tokens, self.scheduler.chunked_prefill_size or prompt_tokens))
+        return count
 
     def add_request(self, prompt_ids: Sequence[int], params: SamplingParams) -> Request:
         req = Request(next(self._rids), list(prompt_ids), params)

@@ -395,6 +395,34 @@ class StepGraphs:
         self.replayed_launches += held.launches
         return held.logits
 
+    def capture_prompt_shapes(self, max_tokens: int) -> int:
+        """Capture now, on an idle cache, the shapes that lone prompts of up to ``max_tokens`` tokens meet
+        (every padded size up to there), instead of at their second sighting: each size is first run
+        once as it is (what a kernel or the library sets up at its first use must not happen inside a
+        capture), then captured from a prompt one token shorter. Returns how many were captured."""
+        if not self.enabled or not self.pad:
+            return 0
+        sf = self.step_fn
+        sizes = sorted({self.padded(n) for n in range(max(self.min_tokens, 2), max_tokens + 1)})
+        sizes = [n for n in sizes if n <= max_tokens and n * self.flops_per_token <= self.max_step_flops]
+        before = self.captures
+        kept = self.sightings, self.capture_every, self.max_shapes
+        self.max_shapes = max(self.max_shapes, len(self._shapes) + len(sizes))
+        try:
+            for n in sizes:
+                for tokens, sightings in ((n, 1 << 30), (n - 1, 1)):
+                    rows = [StepRow(sf.cache.new_request(), [0] * tokens, (tokens - 1,))]
+                    self.sightings, self.capture_every, self._since_capture = sightings, 0, 1
+                    try:
+                        if self._key(rows) not in self._shapes:
+                            sf.run(rows)
+                    finally:
+                        sf.cache.release(rows[0].cache)
+        finally:
+            self.sightings, self.capture_every = kept[0], kept[1]
+        torch.cuda.current_stream(sf.device).synchronize()
+        return self.captures - before
+
     def _capture(self, ctx, single_rows: int) -> _Pieces:
         from ..ops import native
 

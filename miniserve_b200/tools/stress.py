@@ -59,7 +59,7 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--capture-graphs-at-start", action="store_true",
-                    help="capture every decode graph before the clock starts instead of at its first use")
+                    help="capture every decode graph, and the step graphs of lone prompts, before the clock starts instead of at their first use")
     ap.add_argument("--max-steps", type=int, default=1_000_000, help="give up (exit code 1) after this many steps")
     args = ap.parse_args(argv)
 
@@ -71,7 +71,8 @@ def main(argv=None) -> int:
     engine = llm.engine
     if args.capture_graphs_at_start:
         modes = ("greedy",) if args.temperature == 0 else ("temperature", "top_p") if args.top_p < 1 else ("temperature",)
-        engine.capture_graphs(modes, context_lengths=(args.prompt_len[0], args.prompt_len[1] + args.max_new_tokens[1]))
+        engine.capture_graphs(modes, context_lengths=(args.prompt_len[0], args.prompt_len[1] + args.max_new_tokens[1]),
+                              prompt_tokens=args.prompt_len[1])
     prompts, params = workload(llm.model.spec.vocab_size, args.num_requests, args.prompt_len, args.max_new_tokens,
                                args.workload_seed, args.temperature, args.top_p)
     watch = Watcher()

@@ -277,3 +277,20 @@ def test_generation_with_prompts_in_equal_portions_replays_graphs_and_gives_the_
         else:
             assert llm.engine.step_fn.graphs is None
     assert outs[True] == outs[False]
+
+
+def test_prompt_shapes_captured_ahead_are_replayed_by_the_first_requests(folder):
+    from miniserve_b200.engine import LLM, SamplingParams
+
+    rng = random.Random(4)
+    prompts = [[rng.randrange(RAW["vocab_size"]) for _ in range(n)] for n in (17, 90, 131, 250, 300)]
+    params = SamplingParams(max_new_tokens=4)
+    eager = LLM(folder, dtype="float32", kv_pool_tokens=2048, page_size=PAGE, max_running=4, cuda_graph=False)
+    llm = LLM(folder, dtype="float32", kv_pool_tokens=2048, page_size=PAGE, max_running=4)
+    g = llm.engine.step_fn.graphs
+    captured = llm.engine.capture_graphs(prompt_tokens=320)
+    assert g.captures == 9 and set(g._shapes) == {(n, 2, 1, 0) for n in (32, 64, 96, 128, 160, 192, 224, 256, 320)}
+    assert captured == g.captures + len(llm.engine.graphs._graphs) and llm.engine.cache.is_idle()
+    outs = [llm.generate([p], params)[0] for p in prompts]
+    assert g.captures == 9 and sum(h.uses for h in g._shapes.values()) == 9 + len(prompts)
+    assert outs == [eager.generate([p], params)[0] for p in prompts]
