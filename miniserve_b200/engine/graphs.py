@@ -404,7 +404,8 @@ class StepGraphs:
             return 0
         sf = self.step_fn
         sizes = sorted({self.padded(n) for n in range(max(self.min_tokens, 2), max_tokens + 1)})
-        sizes = [n for n in sizes if n <= max_tokens and n * self.flops_per_token <= self.max_step_flops]
+        room = min((g.allocator.num_blocks for g in sf.cache.groups), default=0) * sf.cache.page_size if sf.cache.groups else max_tokens
+        sizes = [n for n in sizes if n <= min(max_tokens, room) and n * self.flops_per_token <= self.max_step_flops]
         before = self.captures
         kept = self.sightings, self.capture_every, self.max_shapes
         self.max_shapes = max(self.max_shapes, len(self._shapes) + len(sizes))
