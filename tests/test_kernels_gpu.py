@@ -463,6 +463,17 @@ def test_attention_bf16_decode_of_long_contexts_as_laid_out_inside_a_graph(graph
     assert torch.allclose(out.float()[1:2], ref[1:2], **BF16_TOL)
 
 
+def test_the_device_says_how_many_clusters_of_decode_ctas_it_holds():
+    """Key splits that run as a cluster are chosen so that every cluster is resident at once; the number
+    comes from the device (a cluster lies within one GPC, so it is less than SMs x CTAs per SM / size)."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    counts = [attention_bf16.clusters_resident(128, n) for n in range(1, 9)]
+    assert all(c >= 1 for c in counts) and counts == sorted(counts, reverse=True)
+    assert counts[0] <= 4 * sms and all(n * c <= counts[0] for n, c in zip(range(1, 9), counts))
+    splits = attention_bf16.choose_splits(8, 8, None, sms, lambda n: attention_bf16.clusters_resident(128, n))
+    assert 1 <= splits <= 8 and (splits == 1 or attention_bf16.clusters_resident(128, splits) >= 64)
+
+
 @pytest.mark.parametrize("window", [1, 16, 17, 100])
 def test_attention_bf16_decode_window_edge(window):
     rows = [(200, 1), (5, 1), (99, 1), (100, 1)]
