@@ -28,7 +28,7 @@ def add_engine_args(parser: argparse.ArgumentParser) -> None:
                    help="keep the graphs of decode steps, launch prompt and mixed steps one kernel at a time")
     g.add_argument("--cuda-graph-max-bs", type=int, default=None,
                    help="decode steps up to this many requests replay a captured graph, padded to the next power of two "
-                        "or to this number (default: --max-running)")
+                        "(from 16 on also the size halfway to it) or to this number (default: --max-running)")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                    help="bfloat16: the serving kernels; float32: the whole model in true 32-bit")
     g.add_argument("--disable-overlap", action="store_true",

@@ -31,6 +31,8 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--stop-token-ids", default="", metavar="ID,ID,...")
+    ap.add_argument("--capture-graphs-at-start", action="store_true",
+                    help="capture the CUDA graphs that these requests will replay before the clock starts instead of at their first use")
     args = ap.parse_args(argv)
 
     from ..engine import LLM, SamplingParams
@@ -46,6 +48,10 @@ def main(argv=None) -> int:
         ap.error("give --prompt-ids or --prompt-len")
     stop = frozenset(int(x) for x in args.stop_token_ids.split(",") if x.strip())
     params = SamplingParams(args.max_new_tokens, stop, args.temperature, args.top_p)
+    if args.capture_graphs_at_start:
+        modes = ("greedy",) if args.temperature == 0 else ("top_p",) if args.top_p < 1 else ("temperature",)
+        longest = max(map(len, prompts))
+        llm.engine.capture_graphs(modes, context_lengths=(min(map(len, prompts)), longest + args.max_new_tokens), prompt_tokens=longest)
     t0 = time.perf_counter()
     outputs = llm.generate(prompts, params)
     dt = time.perf_counter() - t0
